@@ -1,0 +1,226 @@
+// Client side of the capture protocol: thread -> client mapping, the gate every
+// interposed call passes through, and the two control calls client scripts make
+// (`block`, `stop`).
+//
+// Reference behaviour being replaced: get_idx / block in
+// src/cuda_capture/utils_interc.cpp:3-64 and the exported block(int)/stop() in
+// src/cuda_capture/intercept_temp.cpp:124-142.
+#include "capture_core.h"
+
+#include <dlfcn.h>
+#include <sched.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <sys/syscall.h>
+#include <unistd.h>
+
+#if defined(__x86_64__)
+#include <immintrin.h>
+#define ORION_PAUSE() _mm_pause()
+#else
+#define ORION_PAUSE() ((void)0)
+#endif
+
+static orion_shared g_shared;
+
+extern "C" orion_shared* orion_capture_shared(void) {
+    g_shared.abi_version = ORION_CAPTURE_ABI_VERSION;
+    return &g_shared;
+}
+
+// ORION_CAPTURE_STATS=1: print the per-type call counts when the process exits.
+__attribute__((constructor)) static void orion_capture_ctor() {
+    const char* e = getenv("ORION_CAPTURE_STATS");
+    if (e && atoi(e)) {
+        atexit([] {
+            fprintf(stderr, "orion capture: seen/scheduled per record type:");
+            for (int t = 0; t < ORION_REC_TYPE_COUNT; t++)
+                if (g_shared.seen[t].load()) fprintf(stderr, " %d:%llu/%llu", t, (unsigned long long)g_shared.seen[t].load(),
+                                                     (unsigned long long)g_shared.captured[t].load());
+            fprintf(stderr, " passthrough:%llu\n", (unsigned long long)g_shared.passthrough.load());
+        });
+    }
+}
+
+namespace orion_capture {
+
+static thread_local int tls_idx = -1;
+static thread_local int tls_epoch = -1;
+static thread_local int tls_tid = 0;
+
+static inline int my_tid() {
+    if (!tls_tid) tls_tid = (int)syscall(SYS_gettid);
+    return tls_tid;
+}
+
+// Pin a client thread the first time it is seen, like the reference
+// (utils_interc.cpp:36-49), but only when the scheduler asked for it and with an
+// offset it chose (several replicas on one host must not share cores).
+static void maybe_pin(int slot, int idx) {
+    orion_shared& sh = g_shared;
+    if (!sh.pin_threads || sh.affinity_set[slot].load(std::memory_order_relaxed)) return;
+    cpu_set_t mask;
+    CPU_ZERO(&mask);
+    CPU_SET(sh.core_offset + idx, &mask);
+    if (sched_setaffinity(0, sizeof(mask), &mask) != 0) perror("orion: sched_setaffinity");
+    sh.affinity_set[slot].store(1, std::memory_order_relaxed);
+}
+
+int client_index_of_thread() {
+    orion_shared& sh = g_shared;
+    if (!sh.active.load(std::memory_order_acquire)) return -1;
+    int ep = sh.epoch.load(std::memory_order_acquire);
+    if (ep == tls_epoch) return tls_idx;
+    int tid = my_tid();
+    int idx = -1;
+    for (int i = 0; i < ORION_MAX_THREADS; i++) {
+        if (sh.thread_ids[i].load(std::memory_order_relaxed) == tid) {
+            idx = sh.thread_client[i].load(std::memory_order_relaxed);
+            if (idx >= 0 && idx < sh.num_clients) maybe_pin(i, idx);
+            break;
+        }
+    }
+    if (idx >= sh.num_clients) idx = -1;   // the scheduler's own thread passes through
+    tls_idx = idx;
+    tls_epoch = ep;
+    return idx;
+}
+
+int client_index_of_stream(void* stream) {
+    orion_shared& sh = g_shared;
+    if (!stream || !sh.active.load(std::memory_order_acquire)) return -1;
+    for (int i = 0; i < sh.num_clients; i++)
+        if (sh.client_stream[i] == stream) return i;
+    return -1;
+}
+
+static inline bool is_default_stream(void* s) {
+    uintptr_t v = (uintptr_t)s;
+    return v == 0 || v == 1 || v == 2;   // NULL, cudaStreamLegacy, cudaStreamPerThread
+}
+
+bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
+    orion_shared& sh = g_shared;
+    sh.seen[type & 31].fetch_add(1, std::memory_order_relaxed);
+    int idx = client_index_of_thread();
+    if (idx < 0) idx = client_index_of_stream(user_stream);   // e.g. the autograd thread replaying a client's stream
+    if (idx < 0) {
+        if (sh.active.load(std::memory_order_relaxed)) sh.passthrough.fetch_add(1, std::memory_order_relaxed);
+        return false;
+    }
+    orion_ring& r = sh.rings[idx];
+    uint64_t seq = r.tail.load(std::memory_order_relaxed);
+    orion_record& rec = r.recs[seq % ORION_RING_CAP];
+    rec.type = type;
+    rec.flags = 0;
+    rec.tag = tag;
+    r.tail.store(seq + 1, std::memory_order_release);
+    sh.captured[type & 31].fetch_add(1, std::memory_order_relaxed);
+
+    // Wait for the grant.  The high-priority client (last index) spins; best-effort
+    // clients yield the core now and then so that they do not starve it.
+    const bool hp = idx == sh.num_clients - 1;
+    uint32_t spins = 0;
+    while (r.granted.load(std::memory_order_acquire) <= seq) {
+        if (!sh.active.load(std::memory_order_acquire)) {
+            // Scheduler detached while we were queued: run the call unscheduled.
+            r.granted.store(seq + 1, std::memory_order_release);
+            r.grant.stream = sh.client_stream[idx];
+            r.grant.event = nullptr;
+            break;
+        }
+        ORION_PAUSE();
+        if (!hp && (++spins & 0x3ff) == 0) sched_yield();
+    }
+    g->idx = idx;
+    g->seq = seq;
+    g->event = r.grant.event;
+    g->stream = is_default_stream(user_stream) ? r.grant.stream : user_stream;
+    return true;
+}
+
+void gate_end(Gate* g) {
+    orion_ring& r = g_shared.rings[g->idx];
+    if (g->event) real_event_record(g->event, g->stream);
+    r.submitted.store(g->seq + 1, std::memory_order_release);
+}
+
+}  // namespace orion_capture
+
+using namespace orion_capture;
+
+extern "C" {
+
+// Client waits until request `it` has completed on the GPU (intercept_temp.cpp:125-130).
+void block(int it) {
+    orion_shared& sh = g_shared;
+    int idx = client_index_of_thread();
+    if (idx < 0) return;
+    if (it < 0 || it >= sh.request_status_len[idx]) {
+        fprintf(stderr, "orion: block(%d) outside the %d requests announced for client %d\n", it, sh.request_status_len[idx], idx);
+        return;
+    }
+    std::atomic<uint8_t>* st = sh.request_status[idx];
+    const bool hp = idx == sh.num_clients - 1;
+    uint32_t spins = 0;
+    while (!st[it].load(std::memory_order_acquire)) {
+        if (!sh.active.load(std::memory_order_acquire)) return;
+        ORION_PAUSE();
+        if (!hp && (++spins & 0x3ff) == 0) sched_yield();
+    }
+}
+
+// Cooperative stop: true once the scheduler asked this client to finish; the
+// acknowledgement lets the scheduler count the client as done (intercept_temp.cpp:132-141).
+bool stop() {
+    orion_shared& sh = g_shared;
+    int idx = client_index_of_thread();
+    if (idx < 0) return false;
+    bool res = sh.client_stop[idx].load(std::memory_order_acquire) != 0;
+    if (res) sh.client_stop_ack[idx].store(1, std::memory_order_release);
+    return res;
+}
+
+// Queue one op of the given record type without any CUDA call behind it: the hook
+// for first-class ops and for host-only tests.  Returns the client index, -1 when
+// the calling thread is not a registered client.
+int orion_capture_op(int type) {
+    Gate g;
+    if (!gate_begin(&g, type, nullptr, 0)) return -1;
+    gate_end(&g);
+    return g.idx;
+}
+
+int orion_capture_client_index(void) { return client_index_of_thread(); }
+
+void* orion_capture_client_stream(int idx) {
+    if (idx < 0 || idx >= g_shared.num_clients) return nullptr;
+    return g_shared.client_stream[idx];
+}
+
+// Register the calling thread as (a helper thread of) client `idx`; used for
+// threads the scheduler could not know at setup time.
+int orion_capture_register_thread(int idx) {
+    orion_shared& sh = g_shared;
+    if (idx < 0 || idx >= sh.num_clients) return -1;
+    int tid = my_tid();
+    for (int i = sh.num_clients + 1; i < ORION_MAX_THREADS; i++) {
+        int32_t expect = 0;
+        if (sh.thread_ids[i].load() == tid || sh.thread_ids[i].compare_exchange_strong(expect, tid)) {
+            sh.thread_client[i].store(idx);
+            sh.epoch.fetch_add(1);
+            return 0;
+        }
+    }
+    return -1;
+}
+
+unsigned long long orion_capture_count(int type) {
+    if (type < 0) return g_shared.passthrough.load();
+    return g_shared.captured[type & 31].load();
+}
+
+// Every intercepted call of a record type, whether it was scheduled or passed through.
+unsigned long long orion_capture_seen(int type) { return g_shared.seen[type & 31].load(); }
+
+}  // extern "C"

@@ -1,0 +1,174 @@
+// C-ABI front of the tensor-core kernels: argument checks, tile / split-K choice,
+// per-stream scratch, and the device status word.  Declarations and the reference
+// call each entry point replaces are in include/orion_kernels.h.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "igemm_params.h"
+
+namespace {
+
+struct Scratch {
+    float* partial = nullptr;
+    int* counters = nullptr;
+    size_t partial_bytes = 0;
+};
+constexpr int kMaxTilesSplit = 4096;                    // counters per stream
+constexpr size_t kScratchBytes = 32u << 20;             // split-K partial sums per stream
+
+std::mutex g_mu;
+std::unordered_map<uint64_t, Scratch> g_scratch;        // key: device << 48 ^ stream
+std::unordered_map<int, int*> g_status;                 // per device
+
+int* status_word(int dev) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_status.find(dev);
+    if (it != g_status.end()) return it->second;
+    int* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+    g_status[dev] = p;
+    return p;
+}
+
+// Split-K scratch is private to a stream: two clients that run split-K convolutions
+// at the same time on different streams must not share partial sums.
+Scratch* scratch_for(int dev, cudaStream_t s) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    uint64_t key = ((uint64_t)dev << 56) ^ (uint64_t)(uintptr_t)s;
+    auto it = g_scratch.find(key);
+    if (it != g_scratch.end()) return &it->second;
+    Scratch sc;
+    if (cudaMalloc(&sc.partial, kScratchBytes) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&sc.counters, kMaxTilesSplit * sizeof(int)) != cudaSuccess) return nullptr;
+    sc.partial_bytes = kScratchBytes;
+    cudaMemsetAsync(sc.partial, 0, kScratchBytes, s);
+    cudaMemsetAsync(sc.counters, 0, kMaxTilesSplit * sizeof(int), s);
+    g_scratch[key] = sc;
+    return &g_scratch[key];
+}
+
+}  // namespace
+
+extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out) {
+    const int bk = dtype == 0 ? 32 : 64;
+    const int kblocks = R * ((S * C + bk - 1) / bk);
+    const int tiles_m = (int)((M + 127) / 128);
+    int bn = 128;
+    const int rem = Kout % 128;
+    if (Kout <= 64 || (rem > 0 && rem <= 64 && Kout < 256)) bn = 64;
+    if ((long long)tiles_m * ((Kout + 127) / 128) < num_ctas && Kout >= 128) bn = 64;   // more tiles for small problems
+    const int tiles = tiles_m * ((Kout + bn - 1) / bn);
+    int splits = 1;
+    if (tiles * 2 <= num_ctas && kblocks >= 8) {
+        splits = num_ctas / tiles;
+        if (splits > kblocks / 4) splits = kblocks / 4;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    *bn_out = bn;
+    *splits_out = splits;
+    return 0;
+}
+
+extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, const float* scale, const float* shift,
+                                     const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R,
+                                     int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn,
+                                     int splits, float* scratch, int* counters, int num_ctas, void* stream) {
+    if (dtype != 0 && dtype != 1) return -1;
+    if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || Kout <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
+        dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0)
+        return -1;
+    if (Nb == 0) return 0;
+    const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / stride_h + 1;
+    const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / stride_w + 1;
+    if (P <= 0 || Q <= 0) return -1;
+    const int elem = dtype == 0 ? 4 : 2;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)residual) % 16) return -2;   // 128-bit accesses
+    int dev = 0;
+    cudaGetDevice(&dev);
+    IgemmParams p;
+    memset(&p, 0, sizeof p);
+    p.x = x; p.w = w; p.y = y; p.scale = scale; p.shift = shift; p.residual = residual;
+    p.relu = relu; p.dtype = dtype;
+    p.Nb = Nb; p.H = H; p.W = W; p.C = C; p.Kout = Kout; p.R = R; p.S = S; p.P = P; p.Q = Q;
+    p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
+    const long long M = (long long)Nb * P * Q;
+    if (M > 0x7fffffffLL) return -1;
+    p.M = (int)M;
+    const int bk = 128 / elem;
+    p.kblocks_per_r = (S * C + bk - 1) / bk;
+    p.num_kblocks = R * p.kblocks_per_r;
+    if (bn != 64 && bn != 128) return -1;
+    p.tiles_m = (int)((M + 127) / 128);
+    p.tiles_n = (Kout + bn - 1) / bn;
+    if (splits < 1 || splits > p.num_kblocks) return -1;
+    p.splits = splits;
+    p.status = status_word(dev);
+    if (splits > 1) {
+        if (!scratch || !counters) return -1;
+        p.scratch = scratch;
+        p.counters = counters;
+    }
+    const int units = p.tiles_m * p.tiles_n * splits;
+    const int grid = units < num_ctas ? units : num_ctas;
+    return ob200_igemm_launch(&p, bn, grid, stream);
+}
+
+extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const float* scale, const float* shift,
+                                  const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
+                                  int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas,
+                                  void* stream) {
+    if (Nb <= 0 || H <= 0 || W <= 0) return Nb == 0 ? 0 : -1;
+    const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / (stride_h > 0 ? stride_h : 1) + 1;
+    const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / (stride_w > 0 ? stride_w : 1) + 1;
+    int bn = 128, splits = 1;
+    ob200_plan_conv(dtype, (long long)Nb * P * Q, Kout, R, S, C, num_ctas, &bn, &splits);
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    if (splits > 1) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const long long tiles = (long long)(((long long)Nb * P * Q + 127) / 128) * ((Kout + bn - 1) / bn);
+        Scratch* sc = scratch_for(dev, (cudaStream_t)stream);
+        if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
+            splits = 1;
+        } else {
+            scratch = sc->partial;
+            counters = sc->counters;
+        }
+    }
+    return ob200_conv2d_fprop_ex(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h,
+                                 pad_w, dil_h, dil_w, bn, splits, scratch, counters, num_ctas, stream);
+}
+
+// y[M, N] = x[M, K] . w[N, K]^T (+ bias) (+ ReLU): a 1x1 convolution over M "pixels".
+extern "C" int ob200_linear(const void* x, const void* w, void* y, const float* bias, int relu, int dtype, int M, int N, int K,
+                            int num_ctas, void* stream) {
+    if (M == 0) return 0;
+    return ob200_conv2d_fprop(x, w, y, nullptr, bias, nullptr, relu, dtype, M, 1, 1, K, N, 1, 1, 1, 1, 0, 0, 1, 1, num_ctas, stream);
+}
+
+// Reads and clears the device status word of the current device (synchronises the
+// device).  0 = no kernel reported a timed-out wait since the last call.
+extern "C" int ob200_read_status(void) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int* p = status_word(dev);
+    if (!p) return -1;
+    int v = 0;
+    if (cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemset(p, 0, sizeof v);
+    return v;
+}
+
+extern "C" int ob200_sm_count(void) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    return n;
+}

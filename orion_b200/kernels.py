@@ -1,0 +1,144 @@
+"""ctypes binding of liborion_kernels.so (the sm_100a workload kernels).
+
+Tensors are passed as raw device pointers; torch is used only to own memory and
+streams.  There is no fallback: if the library is missing or a launch fails the
+call raises.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "lib", "liborion_kernels.so")
+_lib = None
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError("liborion_kernels.so is not built; run `python -m orion_b200.build`")
+        L = ctypes.CDLL(_LIB_PATH)
+        L.ob200_conv2d_fprop.argtypes = [c_void_p] * 6 + [c_int] * 15 + [c_int, c_void_p]
+        L.ob200_conv2d_fprop_ex.argtypes = [c_void_p] * 6 + [c_int] * 15 + [c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
+        L.ob200_linear.argtypes = [c_void_p] * 4 + [c_int] * 5 + [c_int, c_void_p]
+        L.ob200_plan_conv.argtypes = [c_int, c_ll, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
+        L.ob200_bn_inference_f32.argtypes = [c_void_p] * 6 + [c_float, c_ll, c_int, c_int, c_int, c_void_p]
+        L.ob200_binary_f32.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_int, c_void_p]
+        L.ob200_maxpool_nhwc_f32.argtypes = [c_void_p] * 2 + [c_int] * 7 + [c_int, c_void_p]
+        L.ob200_avgpool_nhwc_f32.argtypes = [c_void_p] * 2 + [c_int] * 3 + [c_int, c_void_p]
+        for name in ("ob200_conv2d_fprop", "ob200_conv2d_fprop_ex", "ob200_linear", "ob200_plan_conv", "ob200_bn_inference_f32",
+                     "ob200_binary_f32", "ob200_maxpool_nhwc_f32", "ob200_avgpool_nhwc_f32", "ob200_read_status",
+                     "ob200_sm_count"):
+            getattr(L, name).restype = c_int
+        _lib = L
+    return _lib
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise RuntimeError("%s failed with code %d" % (what, rc))
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise TypeError("orion_b200 kernels take float32 or bfloat16, got %s" % t.dtype)
+
+
+def sm_count():
+    return lib().ob200_sm_count()
+
+
+def read_status():
+    """Device status word (synchronises): 0 unless a kernel gave up on a bounded wait."""
+    return lib().ob200_read_status()
+
+
+def conv2d_nhwc(x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, shift=None, residual=None, relu=False,
+                num_ctas=None, bn=None, splits=None, out=None):
+    """x: [N, H, W, C] contiguous, w: [K, R, S, C] contiguous -> [N, P, Q, K]."""
+    assert x.is_cuda and x.is_contiguous() and w.is_contiguous() and x.dtype == w.dtype
+    Nb, H, W, C = x.shape
+    K, R, S, C2 = w.shape
+    assert C == C2
+    P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) // stride[0] + 1
+    Q = (W + 2 * padding[1] - dilation[1] * (S - 1) - 1) // stride[1] + 1
+    y = out if out is not None else torch.empty((Nb, P, Q, K), device=x.device, dtype=x.dtype)
+    n = num_ctas or sm_count()
+    args = [_ptr(x), _ptr(w), _ptr(y), _ptr(scale), _ptr(shift), _ptr(residual), int(relu), _dtype_code(x), Nb, H, W, C, K, R, S,
+            stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1]]
+    if bn is None and splits is None:
+        _check(lib().ob200_conv2d_fprop(*args, n, _stream()), "ob200_conv2d_fprop")
+    else:
+        bn = bn or 128
+        splits = splits or 1
+        scratch = counters = None
+        if splits > 1:
+            tiles = ((Nb * P * Q + 127) // 128) * ((K + bn - 1) // bn)
+            scratch = torch.zeros(tiles * 128 * bn, device=x.device, dtype=torch.float32)
+            counters = torch.zeros(tiles, device=x.device, dtype=torch.int32)
+        _check(lib().ob200_conv2d_fprop_ex(*args, bn, splits, _ptr(scratch), _ptr(counters), n, _stream()),
+               "ob200_conv2d_fprop_ex")
+    return y
+
+
+def linear(x, w, bias=None, relu=False, num_ctas=None):
+    """x: [M, K], w: [N, K] -> [M, N]."""
+    assert x.is_cuda and x.is_contiguous() and w.is_contiguous() and x.dtype == w.dtype
+    M, K = x.shape
+    N = w.shape[0]
+    y = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    _check(lib().ob200_linear(_ptr(x), _ptr(w), _ptr(y), _ptr(bias), int(relu), _dtype_code(x), M, N, K,
+                              num_ctas or sm_count(), _stream()), "ob200_linear")
+    return y
+
+
+def bn_inference(x, gamma, beta, mean, var, eps, relu=False, num_ctas=None, out=None):
+    """Channel-last batch-norm inference: x [..., C] float32."""
+    assert x.is_contiguous() and x.dtype == torch.float32
+    C = x.shape[-1]
+    y = out if out is not None else torch.empty_like(x)
+    _check(lib().ob200_bn_inference_f32(_ptr(x), _ptr(y), _ptr(gamma), _ptr(beta), _ptr(mean), _ptr(var), float(eps), x.numel(), C,
+                                        int(relu), num_ctas or sm_count(), _stream()), "ob200_bn_inference_f32")
+    return y
+
+
+def binary(a, b=None, mode=0, num_ctas=None, out=None):
+    """mode 0: relu(a); 1: a + b; 2: relu(a + b)."""
+    assert a.is_contiguous() and a.dtype == torch.float32
+    y = out if out is not None else torch.empty_like(a)
+    _check(lib().ob200_binary_f32(_ptr(a), _ptr(b), _ptr(y), a.numel(), mode, num_ctas or sm_count(), _stream()),
+           "ob200_binary_f32")
+    return y
+
+
+def maxpool_nhwc(x, k, stride, pad, num_ctas=None):
+    Nb, H, W, C = x.shape
+    P = (H + 2 * pad - k) // stride + 1
+    Q = (W + 2 * pad - k) // stride + 1
+    y = torch.empty((Nb, P, Q, C), device=x.device, dtype=x.dtype)
+    _check(lib().ob200_maxpool_nhwc_f32(_ptr(x), _ptr(y), Nb, H, W, C, k, stride, pad, num_ctas or sm_count(), _stream()),
+           "ob200_maxpool_nhwc_f32")
+    return y
+
+
+def avgpool_nhwc(x, num_ctas=None):
+    Nb, H, W, C = x.shape
+    y = torch.empty((Nb, C), device=x.device, dtype=x.dtype)
+    _check(lib().ob200_avgpool_nhwc_f32(_ptr(x), _ptr(y), Nb, H * W, C, num_ctas or sm_count(), _stream()),
+           "ob200_avgpool_nhwc_f32")
+    return y
