@@ -92,8 +92,26 @@ def build_host(force=False):
     return outs
 
 
+def build_glue(force=False):
+    """The PyTorch adapter (dispatcher overrides + orion:: ops); links liborion_kernels.so."""
+    import torch
+    from torch.utils import cpp_extension
+    src = os.path.join(CSRC, "torch_glue", "glue.cpp")
+    out = os.path.join(LIB, "liborion_torch.so")
+    if force or _stale(out, [src]):
+        os.makedirs(LIB, exist_ok=True)
+        tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-w", src, "-o", out,
+               "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI), "-I/usr/local/cuda/include"]
+        cmd += ["-I" + p for p in cpp_extension.include_paths()]
+        cmd += ["-L" + tlib, "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+                "-L" + LIB, "-lorion_kernels", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib]
+        _run(cmd)
+    return out
+
+
 def build_all(force=False):
-    return [build_kernels(force)] + build_host(force)
+    return [build_kernels(force)] + build_host(force) + [build_glue(force)]
 
 
 if __name__ == "__main__":

@@ -47,6 +47,7 @@ namespace orion_capture {
 static thread_local int tls_idx = -1;
 static thread_local int tls_epoch = -1;
 static thread_local int tls_tid = 0;
+static thread_local bool tls_in_gate = false;   // a call made while this thread is already inside a gate passes through
 
 static inline int my_tid() {
     if (!tls_tid) tls_tid = (int)syscall(SYS_gettid);
@@ -101,11 +102,24 @@ static inline bool is_default_stream(void* s) {
 
 bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
     orion_shared& sh = g_shared;
+    if (tls_in_gate) return false;
     sh.seen[type & 31].fetch_add(1, std::memory_order_relaxed);
+    g->launch = nullptr;
     int idx = client_index_of_thread();
     if (idx < 0) idx = client_index_of_stream(user_stream);   // e.g. the autograd thread replaying a client's stream
     if (idx < 0) {
         if (sh.active.load(std::memory_order_relaxed)) sh.passthrough.fetch_add(1, std::memory_order_relaxed);
+        if (profile_enabled()) {   // unscheduled profiling run: time the call on the caller's stream
+            g->idx = -2;
+            g->seq = 0;
+            g->stream = user_stream;
+            g->event = nullptr;
+            g->type = type;
+            g->tag = tag;
+            tls_in_gate = true;
+            profile_begin(g);
+            return true;
+        }
         return false;
     }
     orion_ring& r = sh.rings[idx];
@@ -132,14 +146,22 @@ bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
         ORION_PAUSE();
         if (!hp && (++spins & 0x3ff) == 0) sched_yield();
     }
+    tls_in_gate = true;
     g->idx = idx;
     g->seq = seq;
+    g->type = type;
+    g->tag = tag;
     g->event = r.grant.event;
     g->stream = is_default_stream(user_stream) ? r.grant.stream : user_stream;
     return true;
 }
 
 void gate_end(Gate* g) {
+    tls_in_gate = false;
+    if (g->idx == -2) {
+        profile_end(g);
+        return;
+    }
     orion_ring& r = g_shared.rings[g->idx];
     if (g->event) real_event_record(g->event, g->stream);
     r.submitted.store(g->seq + 1, std::memory_order_release);
@@ -154,6 +176,7 @@ extern "C" {
 // Client waits until request `it` has completed on the GPU (intercept_temp.cpp:125-130).
 void block(int it) {
     orion_shared& sh = g_shared;
+    profile_mark_iteration(it);
     int idx = client_index_of_thread();
     if (idx < 0) return;
     if (it < 0 || it >= sh.request_status_len[idx]) {
@@ -163,11 +186,13 @@ void block(int it) {
     std::atomic<uint8_t>* st = sh.request_status[idx];
     const bool hp = idx == sh.num_clients - 1;
     uint32_t spins = 0;
+    sh.rings[idx].blocked_on.store((int64_t)it + 1, std::memory_order_release);
     while (!st[it].load(std::memory_order_acquire)) {
-        if (!sh.active.load(std::memory_order_acquire)) return;
+        if (!sh.active.load(std::memory_order_acquire)) break;
         ORION_PAUSE();
         if (!hp && (++spins & 0x3ff) == 0) sched_yield();
     }
+    sh.rings[idx].blocked_on.store(0, std::memory_order_release);
 }
 
 // Cooperative stop: true once the scheduler asked this client to finish; the

@@ -1,5 +1,6 @@
 // Internal interface between the capture core and the interposers.
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 #include "../policy/op_types.h"
@@ -7,11 +8,21 @@
 
 namespace orion_capture {
 
+struct LaunchInfo {       // filled by the kernel-launch interposers for the profile recorder
+    const void* func;
+    unsigned grid[3], block[3];
+    size_t shared_mem;
+};
+
 struct Gate {
-    int idx;
+    int idx;        // client index; -2 = unscheduled call that is being profiled
     uint64_t seq;
     void* stream;   // stream to launch on (the caller's, or the client's scheduler stream)
     void* event;    // event to record behind the op
+    int type;
+    uint64_t tag;
+    const LaunchInfo* launch;
+    void* prof_start;
 };
 
 // Returns false when the calling thread is not a scheduled client (pass through).
@@ -26,5 +37,11 @@ int client_index_of_stream(void* stream);
 // cudaEventRecord of the real runtime (resolved lazily; a no-op when no CUDA
 // runtime is loaded, which is the case in host-only tests).
 void real_event_record(void* event, void* stream);
+
+// Profile recorder (profile_recorder.cpp): active when ORION_PROFILE_OUT is set.
+bool profile_enabled();
+void profile_begin(Gate* g);
+void profile_end(Gate* g);
+void profile_mark_iteration(int it);
 
 }  // namespace orion_capture

@@ -48,6 +48,7 @@ struct alignas(64) orion_ring {
     // written by the client
     alignas(64) std::atomic<uint64_t> tail;
     alignas(64) std::atomic<uint64_t> submitted;
+    std::atomic<int64_t> blocked_on;         // request index + 1 while the client sits in block(it), else 0
     // written by the scheduler
     alignas(64) std::atomic<uint64_t> granted;
     orion_grant grant;

@@ -24,10 +24,26 @@
 
 using namespace orion_capture;
 
+// The real symbol: next in the global lookup order when the library was loaded at
+// start-up, else (torch dlopen()s cuDNN and cuBLAS privately) from the library's own handle.
+static void* find_real(const char* name) {
+    void* p = dlsym(RTLD_NEXT, name);
+    if (p) return p;
+    static const char* sonames[] = {"libcudart.so.12", "libcublas.so.12", "libcublasLt.so.12", "libcudnn.so.9",
+                                    "libcudnn_graph.so.9", "libcudnn_cnn.so.9", "libcudnn_ops.so.9", "libcudnn_adv.so.9"};
+    for (const char* so : sonames) {
+        void* h = dlopen(so, RTLD_NOW | RTLD_NOLOAD);
+        if (!h) continue;
+        p = dlsym(h, name);
+        if (p) return p;
+    }
+    return nullptr;
+}
+
 template <typename F>
 static inline F resolve(F& slot, const char* name) {
     if (!slot) {
-        slot = (F)dlsym(RTLD_NEXT, name);
+        slot = (F)find_real(name);
         if (!slot) {
             fprintf(stderr, "orion: real symbol %s not found behind the capture library\n", name);
             abort();
@@ -41,7 +57,7 @@ static cudaError_t (*real_cudaEventRecord)(cudaEvent_t, cudaStream_t);
 namespace orion_capture {
 void real_event_record(void* event, void* stream) {
     if (!real_cudaEventRecord) {
-        real_cudaEventRecord = (decltype(real_cudaEventRecord))dlsym(RTLD_NEXT, "cudaEventRecord");
+        real_cudaEventRecord = (decltype(real_cudaEventRecord))find_real("cudaEventRecord");
         if (!real_cudaEventRecord) return;   // host-only process: nothing to record
     }
     real_cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream);
@@ -57,6 +73,8 @@ cudaError_t cudaLaunchKernel(const void* func, dim3 gridDim, dim3 blockDim, void
     Gate g;
     if (!gate_begin(&g, ORION_KERNEL_RECORD, stream, (uint64_t)(uintptr_t)func))
         return real_cudaLaunchKernel(func, gridDim, blockDim, args, sharedMem, stream);
+    LaunchInfo li{func, {gridDim.x, gridDim.y, gridDim.z}, {blockDim.x, blockDim.y, blockDim.z}, sharedMem};
+    g.launch = &li;
     cudaError_t e = real_cudaLaunchKernel(func, gridDim, blockDim, args, sharedMem, (cudaStream_t)g.stream);
     gate_end(&g);
     return e;
@@ -70,6 +88,9 @@ cudaError_t cudaLaunchKernelExC(const cudaLaunchConfig_t* config, const void* fu
         return real_cudaLaunchKernelExC(config, func, args);
     cudaLaunchConfig_t cfg = *config;
     cfg.stream = (cudaStream_t)g.stream;
+    LaunchInfo li{func, {cfg.gridDim.x, cfg.gridDim.y, cfg.gridDim.z}, {cfg.blockDim.x, cfg.blockDim.y, cfg.blockDim.z},
+                  cfg.dynamicSmemBytes};
+    g.launch = &li;
     cudaError_t e = real_cudaLaunchKernelExC(&cfg, func, args);
     gate_end(&g);
     return e;

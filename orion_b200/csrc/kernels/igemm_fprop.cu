@@ -222,6 +222,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                                     else x += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[base + j]);
                                 }
                                 if (p.relu) x = fmaxf(x, 0.f);
+                                if (p.relu == 2) x = fminf(x, 6.f);
                                 v[j] = x;
                             }
                         }

@@ -23,6 +23,14 @@
 //   void    iter_done(int client, int iter)   request `iter` complete: publish and unlock
 //   void    stop(int client, bool locked)     ask a best-effort client to stop
 //   bool    stop_ack(int client)        client acknowledged the stop
+//   bool    client_blocked(int client, int iter)
+//                                       live runs only: the client already waits for request
+//                                       `iter` to complete and has nothing queued.  If that
+//                                       happens before the profile's op count was reached, the
+//                                       profile is longer than the real op sequence and the
+//                                       iteration is closed instead of deadlocking.  Replay
+//                                       environments return false; the reference has no such
+//                                       escape (it would hang).
 //
 // Quirks kept on purpose, because decisions must equal the reference's:
 //   * `size` restarts at 0 every poll and only sums ops admitted in that poll;
@@ -61,6 +69,7 @@ struct PolicyStats {
     uint64_t be_submits = 0;
     uint64_t be_rejects = 0;      // a best-effort head was seen and not released in that poll
     uint64_t queries = 0;
+    uint64_t forced_iter_ends = 0;   // iterations closed because the profile was longer than the op stream
 };
 
 class PolicyCore {
@@ -230,6 +239,11 @@ void PolicyCore::run_phase(Env& env, const PhaseArgs& a) {
         for (int i = 0; i < n; i++) {
             heads[i] = -1;
             if (seen[i] == num_kernels[i]) continue;
+            if (seen[i] > 0 && env.client_blocked(i, cur_iters[i])) {
+                seen[i] = num_kernels[i];
+                stats.forced_iter_ends++;
+                continue;
+            }
             int t = env.peek(i);
             if (t >= 0) {
                 heads[i] = t;

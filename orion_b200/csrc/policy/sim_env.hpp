@@ -168,6 +168,7 @@ public:
         if (!locked) after_unlock(k);
     }
     bool stop_ack(int i) const { return clients[i].stop_ack; }
+    bool client_blocked(int, int) const { return false; }
 
 private:
     const std::vector<ScriptOp>& seq_of(const Client& c) const {

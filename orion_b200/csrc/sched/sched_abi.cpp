@@ -168,6 +168,11 @@ struct LiveEnv {
     }
     void stop(int k, bool) { sh->client_stop[k].store(1, std::memory_order_release); }
     bool stop_ack(int i) { return sh->client_stop_ack[i].load(std::memory_order_acquire) != 0; }
+    bool client_blocked(int i, int iter) {
+        orion_ring& r = sh->rings[i];
+        return r.blocked_on.load(std::memory_order_acquire) == (int64_t)iter + 1 &&
+               r.tail.load(std::memory_order_acquire) == popped[i] && r.submitted.load(std::memory_order_acquire) == popped[i];
+    }
 };
 
 }  // namespace
@@ -333,6 +338,7 @@ void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files
         r.tail.store(0);
         r.submitted.store(0);
         r.granted.store(0);
+        r.blocked_on.store(0);
         delete[] sh->request_status[i];
         int len = num_iters[i] > 0 ? num_iters[i] : 0;
         sh->request_status[i] = new std::atomic<uint8_t>[(size_t)len + 1];
@@ -439,13 +445,14 @@ void orion_sched_shutdown(Scheduler* s) {
     if (s && s->sh) s->sh->active.store(0, std::memory_order_release);
 }
 
-// stats: [polls, hp_submits, be_submits, be_rejects, queries, join_timeouts, max_sms, green_be_sms]
+// stats: [polls, hp_submits, be_submits, be_rejects, queries, join_timeouts, max_sms, green_be_sms, forced_iter_ends]
 void orion_sched_stats(Scheduler* s, unsigned long long* out, int n) {
     if (!s || !out) return;
-    unsigned long long v[8] = {s->core.stats.polls,      s->core.stats.hp_submits, s->core.stats.be_submits,
+    unsigned long long v[9] = {s->core.stats.polls,      s->core.stats.hp_submits, s->core.stats.be_submits,
                                s->core.stats.be_rejects, s->core.stats.queries,    s->env.join_timeouts,
-                               (unsigned long long)s->core.max_sms, (unsigned long long)s->green.be_sms};
-    for (int i = 0; i < n && i < 8; i++) out[i] = v[i];
+                               (unsigned long long)s->core.max_sms, (unsigned long long)s->green.be_sms,
+                               s->core.stats.forced_iter_ends};
+    for (int i = 0; i < n && i < 9; i++) out[i] = v[i];
 }
 
 // Latency samples (ms) the scheduler measured for client `idx` (scheduler_eval.cpp:423-426).

@@ -1,0 +1,233 @@
+// PyTorch-side adapter: routes the ops of captured clients to the C-ABI kernels of
+// liborion_kernels.so.  Nothing here computes; torch only owns memory and streams.
+//
+// Two surfaces:
+//  1. Dispatcher overrides (CUDA key) for the ops that torch 2.x sends into cuDNN's
+//     graph API, where a C-level trap sees only an opaque execution plan:
+//       aten::convolution            -> ob200_conv2d_fprop   (cudnnConvolutionForward's role,
+//                                                             reference src/scheduler/utils_sched.cpp:284-296)
+//       aten::cudnn_batch_norm       -> ob200_bn_inference_f32 in eval mode
+//                                                            (cudnnBatchNormalizationForwardInference, :340-353)
+//     Shapes or layouts the kernels do not cover fall back to the stock ATen op one
+//     level below (at::_convolution, at::native_batch_norm); those launches still
+//     reach the scheduler through the cudaLaunchKernel / cuDNN traps.
+//  2. orion:: ops used by prepared inference models: convolution with the folded
+//     batch-norm scale/shift, residual add and ReLU applied in the kernel epilogue,
+//     pooling and the classifier GEMM.
+//
+// Every launch goes out on torch's current stream with `sm_quota` CTAs (a
+// per-thread setting: each client thread launches persistent kernels sized to the
+// SM budget its scheduler stream was given).
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include <atomic>
+
+extern "C" {
+int ob200_conv2d_fprop(const void* x, const void* w, void* y, const float* scale, const float* shift, const void* residual, int relu,
+                       int dtype, int Nb, int H, int W, int C, int Kout, int R, int S, int stride_h, int stride_w, int pad_h,
+                       int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
+int ob200_linear(const void* x, const void* w, void* y, const float* bias, int relu, int dtype, int M, int N, int K, int num_ctas,
+                 void* stream);
+int ob200_bn_inference_f32(const float* x, float* y, const float* gamma, const float* beta, const float* mean, const float* var,
+                           float eps, long long n_elems, int C, int relu, int num_ctas, void* stream);
+int ob200_binary_f32(const float* a, const float* b, float* y, long long n_elems, int mode, int num_ctas, void* stream);
+int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, int W, int C, int k, int stride, int pad, int num_ctas,
+                           void* stream);
+int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream);
+int ob200_sm_count(void);
+}
+
+namespace {
+
+thread_local int tls_quota = 0;
+std::atomic<int> g_overrides{1};
+std::atomic<long long> g_own_launches{0};
+std::atomic<long long> g_fallbacks{0};
+
+int quota() {
+    if (tls_quota > 0) return tls_quota;
+    static int sms = ob200_sm_count();
+    return sms > 0 ? sms : 148;
+}
+
+void* cur_stream() { return (void*)c10::cuda::getCurrentCUDAStream().stream(); }
+
+void check(int rc, const char* what) {
+    TORCH_CHECK(rc == 0, what, " failed with code ", rc);
+    g_own_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+int dtype_code(const at::Tensor& t) {
+    if (t.scalar_type() == at::kFloat) return 0;
+    if (t.scalar_type() == at::kBFloat16) return 1;
+    return -1;
+}
+
+bool is_nhwc(const at::Tensor& t) { return t.dim() == 4 && t.is_contiguous(at::MemoryFormat::ChannelsLast); }
+
+const float* fptr(const c10::optional<at::Tensor>& t) {
+    return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr;
+}
+
+// x, w: logical NCHW / KCRS tensors in channels-last memory (physical NHWC / KRSC).
+at::Tensor conv_core(const at::Tensor& x, const at::Tensor& w, const float* scale, const float* shift, const at::Tensor* residual,
+                     int act, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation) {
+    const int64_t Nb = x.size(0), C = x.size(1), H = x.size(2), W = x.size(3);
+    const int64_t K = w.size(0), R = w.size(2), S = w.size(3);
+    const int64_t P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) / stride[0] + 1;
+    const int64_t Q = (W + 2 * padding[1] - dilation[1] * (S - 1) - 1) / stride[1] + 1;
+    at::Tensor y = at::empty({Nb, K, P, Q}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
+    if (residual) TORCH_CHECK(residual->sizes() == y.sizes() && is_nhwc(*residual), "orion: residual must match the output (NHWC)");
+    check(ob200_conv2d_fprop(x.data_ptr(), w.data_ptr(), y.data_ptr(), scale, shift, residual ? residual->data_ptr() : nullptr,
+                             act, dtype_code(x), (int)Nb, (int)H, (int)W, (int)C, (int)K, (int)R, (int)S, (int)stride[0],
+                             (int)stride[1], (int)padding[0], (int)padding[1], (int)dilation[0], (int)dilation[1], quota(),
+                             cur_stream()),
+          "ob200_conv2d_fprop");
+    return y;
+}
+
+// ------------------------------------------------------------------ aten overrides
+at::Tensor convolution_override(const at::Tensor& input, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
+                                at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed,
+                                at::IntArrayRef output_padding, int64_t groups) {
+    const bool ok = g_overrides.load(std::memory_order_relaxed) && input.dim() == 4 && weight.dim() == 4 && !transposed &&
+                    groups == 1 && dtype_code(input) >= 0 && input.scalar_type() == weight.scalar_type() && stride.size() == 2 &&
+                    padding.size() == 2 && dilation.size() == 2 && input.numel() > 0 &&
+                    (!bias.has_value() || !bias->defined() || bias->scalar_type() == at::kFloat) &&
+                    (is_nhwc(weight) || is_nhwc(input));
+    if (!ok) {
+        g_fallbacks.fetch_add(1, std::memory_order_relaxed);
+        return at::_convolution(input, weight, bias, stride, padding, dilation, transposed, output_padding, groups,
+                                at::globalContext().benchmarkCuDNN(), at::globalContext().deterministicCuDNN(),
+                                at::globalContext().userEnabledCuDNN(), at::globalContext().allowTF32CuDNN());
+    }
+    at::Tensor x = is_nhwc(input) ? input : input.contiguous(at::MemoryFormat::ChannelsLast);
+    at::Tensor w = is_nhwc(weight) ? weight : weight.contiguous(at::MemoryFormat::ChannelsLast);
+    return conv_core(x, w, nullptr, fptr(bias), nullptr, 0, stride, padding, dilation);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_override(
+    const at::Tensor& input, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
+    const c10::optional<at::Tensor>& running_mean, const c10::optional<at::Tensor>& running_var, bool training, double momentum,
+    double eps) {
+    const bool ok = g_overrides.load(std::memory_order_relaxed) && !training && input.scalar_type() == at::kFloat && is_nhwc(input) &&
+                    running_mean.has_value() && running_mean->defined() && running_var.has_value() && running_var->defined() &&
+                    weight.defined() && weight.scalar_type() == at::kFloat && input.numel() > 0;
+    if (!ok) {
+        g_fallbacks.fetch_add(1, std::memory_order_relaxed);
+        auto r = at::native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps);
+        return std::make_tuple(std::get<0>(r), std::get<1>(r), std::get<2>(r), at::empty({0}, input.options().dtype(at::kByte)));
+    }
+    at::Tensor y = at::empty_like(input, at::MemoryFormat::ChannelsLast);
+    check(ob200_bn_inference_f32(input.data_ptr<float>(), y.data_ptr<float>(), weight.data_ptr<float>(), fptr(bias),
+                                 running_mean->data_ptr<float>(), running_var->data_ptr<float>(), (float)eps, input.numel(),
+                                 (int)input.size(1), 0, quota(), cur_stream()),
+          "ob200_bn_inference_f32");
+    at::Tensor none = at::empty({0}, input.options());
+    return std::make_tuple(y, none, none, at::empty({0}, input.options().dtype(at::kByte)));
+}
+
+// The training forward above saves mean / inverse std in native_batch_norm's format,
+// so the matching backward is native_batch_norm_backward.
+std::tuple<at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_backward_override(
+    const at::Tensor& input, const at::Tensor& grad_output, const at::Tensor& weight, const c10::optional<at::Tensor>& running_mean,
+    const c10::optional<at::Tensor>& running_var, const c10::optional<at::Tensor>& save_mean,
+    const c10::optional<at::Tensor>& save_var, double eps, const at::Tensor& reserve) {
+    (void)reserve;
+    const bool train = save_mean.has_value() && save_mean->defined() && save_mean->numel() > 0;
+    return at::native_batch_norm_backward(grad_output, input, weight, running_mean, running_var, save_mean, save_var, train, eps,
+                                          {true, true, true});
+}
+
+// ------------------------------------------------------------------ orion:: ops
+at::Tensor conv_bn_act(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& scale,
+                       const c10::optional<at::Tensor>& shift, const c10::optional<at::Tensor>& residual, int64_t act,
+                       at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 4 && w.dim() == 4 && dtype_code(x) >= 0 && x.scalar_type() == w.scalar_type(),
+                "orion::conv_bn_act: float32/bfloat16 4-D CUDA tensors expected");
+    TORCH_CHECK(is_nhwc(w), "orion::conv_bn_act: weight must be channels-last");
+    at::Tensor xin = is_nhwc(x) ? x : x.contiguous(at::MemoryFormat::ChannelsLast);
+    const at::Tensor* res = (residual.has_value() && residual->defined()) ? &*residual : nullptr;
+    return conv_core(xin, w, fptr(scale), fptr(shift), res, (int)act, stride, padding, dilation);
+}
+
+at::Tensor linear_op(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias, bool relu) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.is_contiguous() && w.is_contiguous() && dtype_code(x) >= 0 &&
+                    x.scalar_type() == w.scalar_type() && x.size(1) == w.size(1),
+                "orion::linear: contiguous [M,K] x [N,K] float32/bfloat16 expected");
+    at::Tensor y = at::empty({x.size(0), w.size(0)}, x.options());
+    check(ob200_linear(x.data_ptr(), w.data_ptr(), y.data_ptr(), fptr(bias), relu ? 1 : 0, dtype_code(x), (int)x.size(0),
+                       (int)w.size(0), (int)x.size(1), quota(), cur_stream()),
+          "ob200_linear");
+    return y;
+}
+
+at::Tensor maxpool_op(const at::Tensor& x, int64_t k, int64_t stride, int64_t pad) {
+    TORCH_CHECK(x.is_cuda() && is_nhwc(x) && x.scalar_type() == at::kFloat && x.size(1) % 4 == 0,
+                "orion::maxpool: channels-last float32 with C % 4 == 0 expected");
+    const int64_t P = (x.size(2) + 2 * pad - k) / stride + 1, Q = (x.size(3) + 2 * pad - k) / stride + 1;
+    at::Tensor y = at::empty({x.size(0), x.size(1), P, Q}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
+    check(ob200_maxpool_nhwc_f32(x.data_ptr<float>(), y.data_ptr<float>(), (int)x.size(0), (int)x.size(2), (int)x.size(3),
+                                 (int)x.size(1), (int)k, (int)stride, (int)pad, quota(), cur_stream()),
+          "ob200_maxpool_nhwc_f32");
+    return y;
+}
+
+at::Tensor avgpool_op(const at::Tensor& x) {
+    TORCH_CHECK(x.is_cuda() && is_nhwc(x) && x.scalar_type() == at::kFloat, "orion::avgpool: channels-last float32 expected");
+    at::Tensor y = at::empty({x.size(0), x.size(1)}, x.options().memory_format(at::MemoryFormat::Contiguous));
+    check(ob200_avgpool_nhwc_f32(x.data_ptr<float>(), y.data_ptr<float>(), (int)x.size(0), (int)(x.size(2) * x.size(3)),
+                                 (int)x.size(1), quota(), cur_stream()),
+          "ob200_avgpool_nhwc_f32");
+    return y;
+}
+
+at::Tensor add_act_op(const at::Tensor& a, const at::Tensor& b, bool relu) {
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kFloat && a.sizes() == b.sizes() && a.strides() == b.strides() &&
+                    a.is_non_overlapping_and_dense(),
+                "orion::add_act: two dense float32 tensors of one layout expected");
+    at::Tensor y = at::empty_like(a);
+    check(ob200_binary_f32(a.data_ptr<float>(), b.data_ptr<float>(), y.data_ptr<float>(), a.numel(), relu ? 2 : 1, quota(),
+                           cur_stream()),
+          "ob200_binary_f32");
+    return y;
+}
+
+int64_t set_sm_quota(int64_t n) {
+    int old = tls_quota;
+    tls_quota = (int)n;
+    return old;
+}
+int64_t set_overrides(int64_t on) { return g_overrides.exchange((int)on); }
+int64_t own_launches() { return g_own_launches.load(); }
+int64_t fallbacks() { return g_fallbacks.load(); }
+
+}  // namespace
+
+TORCH_LIBRARY(orion, m) {
+    m.def("conv_bn_act(Tensor x, Tensor w, Tensor? scale, Tensor? shift, Tensor? residual, int act, int[] stride, int[] padding, int[] dilation) -> Tensor");
+    m.def("linear(Tensor x, Tensor w, Tensor? bias, bool relu) -> Tensor");
+    m.def("maxpool(Tensor x, int k, int stride, int pad) -> Tensor");
+    m.def("avgpool(Tensor x) -> Tensor");
+    m.def("add_act(Tensor a, Tensor b, bool relu) -> Tensor");
+    m.def("set_sm_quota(int n) -> int", &set_sm_quota);
+    m.def("set_overrides(int on) -> int", &set_overrides);
+    m.def("own_launches() -> int", &own_launches);
+    m.def("fallbacks() -> int", &fallbacks);
+}
+
+TORCH_LIBRARY_IMPL(orion, CUDA, m) {
+    m.impl("conv_bn_act", &conv_bn_act);
+    m.impl("linear", &linear_op);
+    m.impl("maxpool", &maxpool_op);
+    m.impl("avgpool", &avgpool_op);
+    m.impl("add_act", &add_act_op);
+}
+
+TORCH_LIBRARY_IMPL(aten, CUDA, m) {
+    m.impl("convolution", &convolution_override);
+    m.impl("cudnn_batch_norm", &cudnn_batch_norm_override);
+    m.impl("cudnn_batch_norm_backward", &cudnn_batch_norm_backward_override);
+}

@@ -1,0 +1,199 @@
+"""PyTorch adapter: loads liborion_torch.so (dispatcher overrides + `torch.ops.orion.*`)
+and prepares inference models so that each conv + batch-norm (+ residual add)
+(+ ReLU/ReLU6) group runs as ONE launch of the implicit-GEMM kernel.
+
+`prepare_inference(model)` is the only call a client script adds; everything it
+builds still goes through the scheduler, because every launch of
+liborion_kernels.so passes the cudaLaunchKernel trap of the capture library.
+"""
+import operator
+import os
+
+import torch
+import torch.fx as fx
+import torch.nn as nn
+import torch.nn.functional as F
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_GLUE = os.path.join(_HERE, "lib", "liborion_torch.so")
+_loaded = False
+
+
+def load():
+    """Load the adapter; from then on aten::convolution / cudnn_batch_norm on CUDA
+    tensors in channels-last layout run on the orion kernels."""
+    global _loaded
+    if not _loaded:
+        if not os.path.exists(_GLUE):
+            raise RuntimeError("liborion_torch.so is not built; run `python -m orion_b200.build`")
+        torch.ops.load_library(_GLUE)
+        _loaded = True
+    return torch.ops.orion
+
+
+def set_sm_quota(n):
+    """CTA count of the persistent kernels launched by the calling thread."""
+    return load().set_sm_quota(int(n))
+
+
+def set_overrides(on):
+    return load().set_overrides(1 if on else 0)
+
+
+class FusedConv(nn.Module):
+    """conv -> (folded batch-norm) -> (+ residual) -> activation in one kernel launch."""
+
+    def __init__(self, conv, bn=None, act=0):
+        super().__init__()
+        assert conv.groups == 1 and conv.padding_mode == "zeros"
+        w = conv.weight.detach()
+        self.register_buffer("weight", w.contiguous(memory_format=torch.channels_last))
+        k = w.shape[0]
+        if bn is not None:
+            inv = torch.rsqrt(bn.running_var.detach().double() + bn.eps)
+            g = bn.weight.detach().double() if bn.weight is not None else torch.ones(k, dtype=torch.float64, device=w.device)
+            b = bn.bias.detach().double() if bn.bias is not None else torch.zeros(k, dtype=torch.float64, device=w.device)
+            scale = g * inv
+            shift = b - bn.running_mean.detach().double() * scale
+            if conv.bias is not None:
+                shift = shift + conv.bias.detach().double() * scale
+            self.register_buffer("scale", scale.float().contiguous())
+            self.register_buffer("shift", shift.float().contiguous())
+        else:
+            self.scale = None
+            if conv.bias is not None:
+                self.register_buffer("shift", conv.bias.detach().float().contiguous())
+            else:
+                self.shift = None
+        self.act = act
+        self.stride, self.padding, self.dilation = list(conv.stride), list(conv.padding), list(conv.dilation)
+
+    def forward(self, x, residual=None):
+        return torch.ops.orion.conv_bn_act(x, self.weight, self.scale, self.shift, residual, self.act, self.stride,
+                                           self.padding, self.dilation)
+
+
+class OrionMaxPool(nn.Module):
+    def __init__(self, k, stride, pad):
+        super().__init__()
+        self.k, self.stride, self.pad = k, stride, pad
+
+    def forward(self, x):
+        return torch.ops.orion.maxpool(x, self.k, self.stride, self.pad)
+
+
+class OrionAvgPool(nn.Module):
+    def forward(self, x):
+        n, c = x.shape[0], x.shape[1]
+        return torch.ops.orion.avgpool(x).view(n, c, 1, 1)
+
+
+class OrionLinear(nn.Module):
+    def __init__(self, lin):
+        super().__init__()
+        self.register_buffer("weight", lin.weight.detach().contiguous())
+        if lin.bias is not None:
+            self.register_buffer("bias", lin.bias.detach().float().contiguous())
+        else:
+            self.bias = None
+
+    def forward(self, x):
+        return torch.ops.orion.linear(x.contiguous(), self.weight, self.bias, False)
+
+
+def _one(v):
+    return v[0] if isinstance(v, (tuple, list)) else v
+
+
+def _act_of(node, mods):
+    """0 if `node` is not an activation the epilogue can apply, else 1 (ReLU) / 2 (ReLU6)."""
+    if node.op == "call_module":
+        m = mods.get(node.target)
+        if isinstance(m, nn.ReLU):
+            return 1
+        if isinstance(m, nn.ReLU6):
+            return 2
+        if isinstance(m, nn.Hardtanh) and m.min_val == 0 and m.max_val == 6:
+            return 2
+    if node.op == "call_function" and node.target in (F.relu, torch.relu):
+        return 1
+    if node.op == "call_function" and node.target is F.relu6:
+        return 2
+    if node.op == "call_method" and node.target in ("relu", "relu_"):
+        return 1
+    return 0
+
+
+def prepare_inference(model):
+    """Return an eval-mode copy of `model` (torchvision-style CNN, on its CUDA device,
+    float32) whose conv/bn/add/relu groups, pooling layers and classifier run on the
+    orion kernels.  Grouped (depthwise) convolutions keep their stock implementation."""
+    load()
+    model = model.eval()
+    gm = fx.symbolic_trace(model)
+    mods = dict(gm.named_modules())
+    g = gm.graph
+    counter = [0]
+
+    def add_module(m):
+        name = "orion_%d" % counter[0]
+        counter[0] += 1
+        gm.add_module(name, m)
+        return name
+
+    for node in list(g.nodes):
+        if node.op != "call_module":
+            continue
+        m = mods.get(node.target)
+        if isinstance(m, nn.Conv2d) and m.groups == 1 and m.padding_mode == "zeros" and isinstance(m.padding, tuple):
+            bn_node, bn = None, None
+            users = list(node.users)
+            if len(users) == 1 and users[0].op == "call_module" and isinstance(mods.get(users[0].target), nn.BatchNorm2d):
+                bn_node, bn = users[0], mods[users[0].target]
+            last = bn_node or node
+            act, act_node, res, add_node = 0, None, None, None
+            users = list(last.users)
+            if len(users) == 1:
+                u = users[0]
+                a = _act_of(u, mods)
+                if a:
+                    act, act_node = a, u
+                elif u.op == "call_function" and u.target in (operator.add, operator.iadd, torch.add) and len(u.args) == 2 \
+                        and not u.kwargs and all(isinstance(x, fx.Node) for x in u.args):
+                    other = u.args[1] if u.args[0] is last else u.args[0]
+                    if other is not last:
+                        add_node, res = u, other
+                        uu = list(u.users)
+                        if len(uu) == 1 and _act_of(uu[0], mods):
+                            act, act_node = _act_of(uu[0], mods), uu[0]
+            fused = FusedConv(m, bn, act)
+            name = add_module(fused)
+            anchor = act_node or add_node or last
+            with g.inserting_before(anchor):
+                new = g.call_module(name, (node.args[0],) if res is None else (node.args[0], res))
+            anchor.replace_all_uses_with(new)
+            for dead in (act_node, add_node, bn_node, node):
+                if dead is not None and len(dead.users) == 0:
+                    g.erase_node(dead)
+        elif isinstance(m, nn.MaxPool2d) and not m.ceil_mode and _one(m.dilation) == 1 and not m.return_indices:
+            name = add_module(OrionMaxPool(_one(m.kernel_size), _one(m.stride or m.kernel_size), _one(m.padding)))
+            with g.inserting_before(node):
+                new = g.call_module(name, node.args)
+            node.replace_all_uses_with(new)
+            g.erase_node(node)
+        elif isinstance(m, nn.AdaptiveAvgPool2d) and _one(m.output_size) == 1:
+            name = add_module(OrionAvgPool())
+            with g.inserting_before(node):
+                new = g.call_module(name, node.args)
+            node.replace_all_uses_with(new)
+            g.erase_node(node)
+        elif isinstance(m, nn.Linear):
+            name = add_module(OrionLinear(m))
+            with g.inserting_before(node):
+                new = g.call_module(name, node.args)
+            node.replace_all_uses_with(new)
+            g.erase_node(node)
+    g.lint()
+    gm.delete_all_unused_submodules()
+    gm.recompile()
+    return gm

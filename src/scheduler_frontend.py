@@ -44,9 +44,10 @@ class PyScheduler:
         return self._sched_lib.orion_sched_client_stream(self._scheduler, idx)
 
     def stats(self):
-        out = (ctypes.c_ulonglong * 8)()
-        self._sched_lib.orion_sched_stats(self._scheduler, out, 8)
-        keys = ("polls", "hp_submits", "be_submits", "be_rejects", "queries", "join_timeouts", "max_sms", "green_be_sms")
+        out = (ctypes.c_ulonglong * 9)()
+        self._sched_lib.orion_sched_stats(self._scheduler, out, 9)
+        keys = ("polls", "hp_submits", "be_submits", "be_rejects", "queries", "join_timeouts", "max_sms", "green_be_sms",
+                "forced_iter_ends")
         return dict(zip(keys, [int(v) for v in out]))
 
     def durations_ms(self, idx, cap=1 << 20):
@@ -103,6 +104,7 @@ class PyScheduler:
         barriers[0].wait()
         start = time.time()
         self._schedule(n, False, 0, *args)         # measured run
+        self.shutdown()                            # late calls of the clients (result read-back) run unscheduled
         barriers[0].wait()
         self._sync()
         self.total_time = time.time() - start
