@@ -1,0 +1,69 @@
+/* liborion_kernels.so — C ABI of the sm_100a workload kernels.
+ *
+ * Plain pointers and sizes only.  Every entry point launches on `stream`
+ * (a cudaStream_t) with at most `num_ctas` persistent CTAs (the SM quota granted to
+ * the caller) and returns 0 on success, a cudaError_t value (> 0) if the launch
+ * failed, or a negative number for invalid arguments.  Layouts: activations NHWC,
+ * filters KRSC (a torch tensor in channels_last memory format).  dtype: 0 = float32
+ * (computed as 3xTF32 with fp32 accumulation), 1 = bfloat16 (fp32 accumulation).
+ * There is no CPU fallback.
+ */
+#ifndef ORION_KERNELS_H
+#define ORION_KERNELS_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* y = act(conv(x, w) * scale[k] + shift[k] + residual).  Takes the place of the
+ * cudnnConvolutionForward call the reference replays (reference
+ * src/scheduler/utils_sched.cpp:284-296, trapped at src/cuda_capture/intercept_cudnn.cpp:6-62).
+ * scale / shift / residual may be NULL; relu: 0 none, 1 ReLU, 2 ReLU6.  Chooses the
+ * tile width and a split-K factor itself; split-K partial sums live in a scratch
+ * buffer that is allocated once per stream on first use. */
+int ob200_conv2d_fprop(const void* x, const void* w, void* y, const float* scale, const float* shift, const void* residual,
+                       int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S, int stride_h, int stride_w,
+                       int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
+
+/* Same with the tile width (bn: 64 or 128), the split-K factor and the scratch
+ * passed by the caller: scratch = tiles*128*bn floats, counters = tiles ints, both
+ * zero on entry (the kernel leaves them zero); unused when splits == 1. */
+int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, const float* scale, const float* shift, const void* residual,
+                          int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S, int stride_h, int stride_w,
+                          int pad_h, int pad_w, int dil_h, int dil_w, int bn, int splits, float* scratch, int* counters,
+                          int num_ctas, void* stream);
+
+/* The choice ob200_conv2d_fprop makes for a problem size. */
+int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out);
+
+/* y[M,N] = x[M,K] . w[N,K]^T + bias, optional ReLU.  Takes the place of cublasSgemm_v2
+ * (reference src/scheduler/utils_sched.cpp:490-501, trapped at src/cuda_capture/intercept_cublas.cpp:5-56). */
+int ob200_linear(const void* x, const void* w, void* y, const float* bias, int relu, int dtype, int M, int N, int K,
+                 int num_ctas, void* stream);
+
+/* Batch-norm inference over the innermost (channel) dimension.  Takes the place of
+ * cudnnBatchNormalizationForwardInference (reference src/scheduler/utils_sched.cpp:340-353). */
+int ob200_bn_inference_f32(const float* x, float* y, const float* gamma, const float* beta, const float* mean, const float* var,
+                           float eps, long long n_elems, int C, int relu, int num_ctas, void* stream);
+
+/* mode 0: y = relu(a); 1: y = a + b; 2: y = relu(a + b).  Takes the place of the
+ * at::native elementwise kernels that reach the reference through its cudaLaunchKernel
+ * trap (reference src/cuda_capture/intercept_temp.cpp:418-458). */
+int ob200_binary_f32(const float* a, const float* b, float* y, long long n_elems, int mode, int num_ctas, void* stream);
+
+/* NHWC max-pool / global average pool (same trap as above: max_pool_forward_nchw and
+ * the mean reduce kernel in the reference's profiles). */
+int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, int W, int C, int k, int stride, int pad, int num_ctas,
+                           void* stream);
+int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream);
+
+/* Device status word of the current device (synchronises the device): 0, or the code of
+ * the bounded wait a kernel gave up on.  Clears the word.  No counterpart in the reference. */
+int ob200_read_status(void);
+/* SM count of the current device.  No counterpart in the reference. */
+int ob200_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -12,6 +12,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <sys/syscall.h>
+#include <time.h>
 #include <unistd.h>
 
 #if defined(__x86_64__)
@@ -95,6 +96,19 @@ int client_index_of_stream(void* stream) {
     return -1;
 }
 
+static inline int64_t mono_ms() {
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (int64_t)ts.tv_sec * 1000 + ts.tv_nsec / 1000000;
+}
+static inline int64_t gate_timeout_ms() {
+    static int64_t v = [] {
+        const char* e = getenv("ORION_GATE_TIMEOUT_S");
+        return (int64_t)(e ? atoi(e) : 30) * 1000;
+    }();
+    return v;
+}
+
 static inline bool is_default_stream(void* s) {
     uintptr_t v = (uintptr_t)s;
     return v == 0 || v == 1 || v == 2;   // NULL, cudaStreamLegacy, cudaStreamPerThread
@@ -134,25 +148,43 @@ bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
     // Wait for the grant.  The high-priority client (last index) spins; best-effort
     // clients yield the core now and then so that they do not starve it.
     const bool hp = idx == sh.num_clients - 1;
+    const bool memop = orion_is_memop(type) != 0;
     uint32_t spins = 0;
+    int64_t t0 = 0;
+    bool self_granted = false;
     while (r.granted.load(std::memory_order_acquire) <= seq) {
+        bool take = false;
         if (!sh.active.load(std::memory_order_acquire)) {
-            // Scheduler detached while we were queued: run the call unscheduled.
-            r.granted.store(seq + 1, std::memory_order_release);
-            r.grant.stream = sh.client_stream[idx];
-            r.grant.event = nullptr;
-            break;
+            take = true;   // scheduler detached while we were queued: run the call unscheduled
+        } else if (memop && !sh.polling.load(std::memory_order_acquire)) {
+            take = true;   // nobody polls between two phases; memory operations need no decision
+        } else if ((++spins & 0xfffff) == 0) {
+            int64_t now = mono_ms();
+            if (!t0) t0 = now;
+            if (now - t0 > gate_timeout_ms()) {
+                fprintf(stderr, "orion: client %d waited more than %lld ms for a grant (record type %d, seq %llu, polling %d); "
+                                "running the call unscheduled\n", idx, (long long)gate_timeout_ms(), type,
+                        (unsigned long long)seq, sh.polling.load());
+                sh.wait_timeouts.fetch_add(1);
+                take = true;
+            }
+        }
+        if (take) {
+            uint64_t expect = seq;
+            if (r.granted.compare_exchange_strong(expect, seq + 1, std::memory_order_acq_rel)) self_granted = true;
+            break;   // if the exchange failed the scheduler granted meanwhile
         }
         ORION_PAUSE();
-        if (!hp && (++spins & 0x3ff) == 0) sched_yield();
+        if (!hp && (spins & 0x3ff) == 0) sched_yield();
     }
     tls_in_gate = true;
     g->idx = idx;
     g->seq = seq;
     g->type = type;
     g->tag = tag;
-    g->event = r.grant.event;
-    g->stream = is_default_stream(user_stream) ? r.grant.stream : user_stream;
+    g->event = self_granted ? nullptr : r.grant.event;
+    void* granted_stream = self_granted ? sh.client_stream[idx] : r.grant.stream;
+    g->stream = is_default_stream(user_stream) ? granted_stream : user_stream;
     return true;
 }
 
@@ -187,10 +219,21 @@ void block(int it) {
     const bool hp = idx == sh.num_clients - 1;
     uint32_t spins = 0;
     sh.rings[idx].blocked_on.store((int64_t)it + 1, std::memory_order_release);
+    int64_t t0 = 0;
     while (!st[it].load(std::memory_order_acquire)) {
         if (!sh.active.load(std::memory_order_acquire)) break;
         ORION_PAUSE();
-        if (!hp && (++spins & 0x3ff) == 0) sched_yield();
+        ++spins;
+        if (!hp && (spins & 0x3ff) == 0) sched_yield();
+        if ((spins & 0xfffff) == 0) {
+            int64_t now = mono_ms();
+            if (!t0) t0 = now;
+            if (now - t0 > 4 * gate_timeout_ms()) {
+                fprintf(stderr, "orion: client %d gave up waiting for request %d to complete\n", idx, it);
+                sh.wait_timeouts.fetch_add(1);
+                break;
+            }
+        }
     }
     sh.rings[idx].blocked_on.store(0, std::memory_order_release);
 }

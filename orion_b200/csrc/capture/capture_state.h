@@ -19,6 +19,10 @@
 //               the caller
 //   4. retire:  submitted.store(head+1, release); the scheduler joins on this
 //               before it queries an event of that client.
+// `granted` doubles as the consumer index of the ring and is advanced by
+// compare-and-swap: between two schedule() calls nobody polls, and a memory
+// operation queued then (for example the read-back of a result right after
+// block(it) returned) grants itself instead of waiting for the next phase.
 // The client never has more than one call between push and retire, which is the
 // reference's behaviour (its interposers spin until the queue is empty,
 // src/cuda_capture/utils_interc.cpp:53-64); the ring capacity leaves room for a
@@ -58,6 +62,8 @@ struct alignas(64) orion_ring {
 struct orion_shared {
     int abi_version;
     std::atomic<int> active;                 // scheduler attached: interposers queue instead of passing through
+    std::atomic<int> polling;                // the scheduler is inside schedule(); outside it, queued memory
+                                             // operations grant themselves (they bypass every policy rule anyway)
     int num_clients;
     std::atomic<int> epoch;                  // bumped whenever the thread table changes
     std::atomic<int32_t> thread_ids[ORION_MAX_THREADS];   // [0,N): clients, [N]: scheduler, rest: helper threads

@@ -104,7 +104,6 @@ struct LiveEnv {
     int n = 0;
     std::vector<void*> streams;
     std::vector<std::vector<void*>> events;
-    std::vector<uint64_t> popped;                       // records granted so far, per client
     std::vector<std::vector<uint64_t>> ev_seq;          // grant sequence behind each event slot
     std::vector<std::vector<int>> ev_owner;             // client whose launch records the slot
     uint64_t join_timeouts = 0;
@@ -117,9 +116,10 @@ struct LiveEnv {
 
     int peek(int i) {
         orion_ring& r = sh->rings[i];
+        uint64_t head = r.granted.load(std::memory_order_acquire);
         uint64_t tail = r.tail.load(std::memory_order_acquire);
-        if (tail <= popped[i]) return -1;
-        return r.recs[popped[i] % ORION_RING_CAP].type;
+        if (tail <= head) return -1;
+        return r.recs[head % ORION_RING_CAP].type;
     }
     int64_t now_us() { return wall_us(); }
     void submit(int i, int type, int stream, int evl, int evs) {
@@ -130,12 +130,14 @@ struct LiveEnv {
             cur_iter_ops[i].push_back(RecordedOp{type, last_pop_us[i] ? t - last_pop_us[i] : 0});
             last_pop_us[i] = t;
         }
+        uint64_t head = r.granted.load(std::memory_order_acquire);
         r.grant.stream = streams[stream];
         r.grant.event = events[evl][evs];
-        ev_seq[evl][evs] = popped[i] + 1;
+        ev_seq[evl][evs] = head + 1;
         ev_owner[evl][evs] = i;
-        popped[i] += 1;
-        r.granted.store(popped[i], std::memory_order_release);
+        // Fails only if the client granted itself a memory operation in the instant
+        // this phase started; that record is then already on its way.
+        r.granted.compare_exchange_strong(head, head + 1, std::memory_order_acq_rel);
     }
     bool query(int evl, int evs) {
         // The event is recorded by the client thread right after its launch; make sure
@@ -170,8 +172,9 @@ struct LiveEnv {
     bool stop_ack(int i) { return sh->client_stop_ack[i].load(std::memory_order_acquire) != 0; }
     bool client_blocked(int i, int iter) {
         orion_ring& r = sh->rings[i];
+        uint64_t head = r.granted.load(std::memory_order_acquire);
         return r.blocked_on.load(std::memory_order_acquire) == (int64_t)iter + 1 &&
-               r.tail.load(std::memory_order_acquire) == popped[i] && r.submitted.load(std::memory_order_acquire) == popped[i];
+               r.tail.load(std::memory_order_acquire) == head && r.submitted.load(std::memory_order_acquire) == head;
     }
 };
 
@@ -286,6 +289,7 @@ void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files
 
     // 1. thread table: clients, then this (scheduler) thread, then free helper slots
     sh->active.store(0);
+    sh->polling.store(0);
     sh->num_clients = num_clients;
     for (int i = 0; i < ORION_MAX_THREADS; i++) {
         sh->thread_ids[i].store(0);
@@ -357,7 +361,6 @@ void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files
     env.n = num_clients;
     env.streams.assign(num_clients, nullptr);
     env.events.assign(num_clients, {});
-    env.popped.assign(num_clients, 0);
     env.ev_seq.assign(num_clients, std::vector<uint64_t>(kEventsPerClient, 0));
     env.ev_owner.assign(num_clients, std::vector<int>(kEventsPerClient, -1));
     int lp = 0, hp = 0;
@@ -416,7 +419,9 @@ void* schedule(Scheduler* s, int num_clients, bool profile_mode, int iter, bool 
     a.depth = reef_depth;
     a.hp_limit = hp_limit;
     a.update_start = update_start;
+    s->sh->polling.store(1, std::memory_order_release);
     s->core.run_phase(s->env, a);
+    s->sh->polling.store(0, std::memory_order_release);
     s->phases_run++;
     if (s->core.error) {
         fprintf(stderr, "UNSUPPORTED OPERATION - ABORT\n");   // utils_sched.cpp:514-516
