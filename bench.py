@@ -1,0 +1,358 @@
+"""Headline benchmark: one high-priority (HP) inference client and one best-effort (BE)
+training client co-located on each GPU under the orion scheduler.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N=1): HP ResNet-50 inference, fp32, batch 4, N(0,1) 3x224x224 inputs, Poisson
+arrivals at 80 requests/s; BE ResNet-50 training, batch 32, SGD(momentum 0.9, lr 0.1),
+labels uniform in [0,1000); random init; synthetic data.  A step is one HP request;
+K = --steps measured HP requests after the launch protocol's 10 warm-up requests.
+
+Printed JSON (one line, rank 0):
+  value      BE training samples/s while co-located, inputs resident in HBM
+  e2e        the same through host buffers: every HP request copies its pinned batch to
+             the device and its logits back, every BE iteration copies its batch and
+             reads the loss back
+  hp         HP p50/p99 latency co-located and solo, and the p99 ratio (target <= 1.15)
+  be         BE samples/s solo and the co-located fraction (target >= 0.70)
+  roofline   the implicit-GEMM convolution kernel, timed here with CUDA events
+  cpu_baseline  the same workload in eager PyTorch on the host cores (bounded sample)
+With N > 1 (torchrun) every rank runs an independent replica on its own GPU; nothing is
+exchanged on the data path; `value` sums the ranks and the latency ratio is the worst rank.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "HP p99 latency (x solo) + BE train samples/s, co-located on one B200"
+HP_RPS = 80
+RESNET50_FWD_FLOP_B1 = 32.71e9 / 4   # conv + fc, 2*MAC, per image
+
+
+# ----------------------------------------------------------------------------- helpers
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d.get("hbm_gbs", 6650.0), "bf16_tflops": d.get("bf16_tflops", 1590.0), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi SM clock / throttle-reason samples during the timed region."""
+
+    def __init__(self, gpu):
+        self.gpu, self.proc, self.path = gpu, None, "/tmp/orion_clocks_%d_%s.csv" % (os.getpid(), str(gpu).replace("/", "_"))
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + q, "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 6:
+                    continue
+                try:
+                    sm.append(float(f[0]))
+                    mx.append(float(f[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            busy = sorted(x for x in sm if x > 0.5 * max(sm)) or sorted(sm)
+            out = {"sm_mhz": busy[len(busy) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def conv_layers_resnet50():
+    """(C, K, R, stride, pad, H) of every convolution of torchvision's ResNet-50, with the input size H=W."""
+    layers = [(3, 64, 7, 2, 3, 224)]
+    h, cin = 56, 64
+    for width, blocks, stride in ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2)):
+        for b in range(blocks):
+            s = stride if b == 0 else 1
+            layers.append((cin, width, 1, 1, 0, h))
+            layers.append((width, width, 3, s, 1, h))
+            hout = h // s
+            layers.append((width, width * 4, 1, 1, 0, hout))
+            if b == 0:
+                layers.append((cin, width * 4, 1, s, 0, h))
+            cin, h = width * 4, hout
+    return layers
+
+
+def kernel_roofline(batch, iters, warm):
+    """Replay every ResNet-50 convolution at `batch` through the implicit-GEMM kernel and time
+    the launches with CUDA events on their stream.  Inputs are rotated through a pool larger
+    than L2 so that no iteration finds its operands cached from the previous one."""
+    import torch
+    from orion_b200 import kernels as K
+    dev = torch.device("cuda", torch.cuda.current_device())
+    layers = conv_layers_resnet50()
+    flops = 0.0
+    work = []
+    for (c, k, r, s, p, h) in layers:
+        x = torch.randn(batch, h, h, c, device=dev)
+        w = torch.randn(k, r, r, c, device=dev) * (1.0 / (c * r * r) ** 0.5)
+        ho = (h + 2 * p - r) // s + 1
+        flops += 2.0 * batch * ho * ho * k * c * r * r
+        work.append((x, w, (s, s), (p, p)))
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
+    stream = torch.cuda.current_stream()
+    total_ms, launches = 0.0, 0
+    for it in range(warm + iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for (x, w, s, p) in work:
+            K.conv2d_nhwc(x, w, s, p)
+        e1.record(stream)
+        e1.synchronize()
+        if it >= warm:
+            total_ms += e0.elapsed_time(e1)
+            launches += len(work)
+    status = K.read_status()
+    if status != 0:
+        raise RuntimeError("a kernel reported a timed-out wait (status %d)" % status)
+    per_launch_flop = flops / len(work)
+    avg_launch_s = total_ms * 1e-3 / launches
+    return {"achieved_tflops": per_launch_flop / avg_launch_s / 1e12, "launches": launches, "avg_launch_us": avg_launch_s * 1e6,
+            "flop_per_launch": per_launch_flop}
+
+
+def cpu_baseline(sample_hp=12, sample_be=2):
+    """Eager PyTorch on the host cores: the reference's numeric path for this workload
+    (reference benchmarking/benchmark_suite/train_imagenet.py:111-116), on a bounded sample."""
+    import numpy as np
+    import torch
+    from torchvision import models
+    torch.manual_seed(42)
+    threads = torch.get_num_threads()
+    hp = models.resnet50(num_classes=1000).eval()
+    x = torch.randn(4, 3, 224, 224)
+    lat = []
+    with torch.no_grad():
+        for i in range(2 + sample_hp):
+            t = time.perf_counter()
+            hp(x)
+            if i >= 2:
+                lat.append(time.perf_counter() - t)
+    be = models.resnet50(num_classes=1000).train()
+    opt = torch.optim.SGD(be.parameters(), lr=0.1, momentum=0.9)
+    crit = torch.nn.CrossEntropyLoss()
+    xb, yb = torch.randn(32, 3, 224, 224), torch.randint(0, 1000, (32,))
+    t0 = None
+    for i in range(1 + sample_be):
+        if i == 1:
+            t0 = time.perf_counter()
+        opt.zero_grad()
+        crit(be(xb), yb).backward()
+        opt.step()
+    be_sps = 32 * sample_be / (time.perf_counter() - t0)
+    return {"value": be_sps, "unit": "samples/s", "cores": threads, "kind": "port",
+            "sample": "eager PyTorch fp32 on host cores, run one after the other: %d ResNet-50 b32 SGD steps (value) and %d "
+                      "ResNet-50 b4 forwards" % (sample_be, sample_hp),
+            "hp_p50_ms": float(np.percentile(lat, 50)) * 1e3, "hp_p99_ms": float(np.percentile(lat, 99)) * 1e3}
+
+
+def reference_policy_rate():
+    """Decisions/s of the reference scheduler (oracle/_ref, its own sources compiled unmodified)
+    and of this repository's policy core on the same arrival script, one core each."""
+    script = os.path.join(ROOT, "tests", "golden", "pair_open.script")
+    out = {}
+    ref = os.path.join(ROOT, "oracle", "_ref", "ref_replay")
+    try:
+        if os.path.exists(ref):
+            r = subprocess.run([ref, script, os.path.join(ROOT, "oracle", "_ref"), "-"], capture_output=True, text=True, timeout=120)
+            out["reference"] = json.loads(r.stdout.strip().splitlines()[-1])
+        own = os.path.join(ROOT, "orion_b200", "bin", "orion_replay")
+        if os.path.exists(own):
+            r = subprocess.run([own, script, "--repeat", "3"], capture_output=True, text=True, timeout=120)
+            out["orion_b200"] = json.loads(r.stdout.strip().splitlines()[-1])
+        if "reference" in out and "orion_b200" in out:
+            out["same_log"] = out["reference"]["log_fnv1a"] == out["orion_b200"]["log_fnv1a"]
+    except (OSError, ValueError, subprocess.SubprocessError, IndexError):
+        pass
+    return out
+
+
+# ----------------------------------------------------------------------------- the product arm
+def physical_gpu(local_rank):
+    """Device id to hand to child processes and nvidia-smi for this rank's GPU."""
+    vis = os.environ.get("ORION_PARENT_VISIBLE_DEVICES")
+    if vis is None:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        os.environ["ORION_PARENT_VISIBLE_DEVICES"] = vis
+    ids = [v for v in vis.split(",") if v != ""]
+    return ids[local_rank] if local_rank < len(ids) else str(local_rank)
+
+
+def run_replica(gpu, steps, out_dir, be_quota):
+    from orion_b200 import experiments as E
+    env = {"CUDA_VISIBLE_DEVICES": gpu}
+    if be_quota > 0:
+        env["ORION_BE_SM_QUOTA"] = be_quota
+    hp_prof = E.profile_client("resnet50_hp", os.path.join(out_dir, "profiles"), extra_env=env)
+    be_prof = E.profile_client("resnet50_be", os.path.join(out_dir, "profiles"), extra_env=env)
+    n_hp = steps + 10
+    hp_solo = E.run_launch_jobs([E.client_entry("resnet50_hp", hp_prof, n_hp, rps=HP_RPS)], os.path.join(out_dir, "hp_solo"),
+                                extra_env=env)
+    be_solo = E.run_launch_jobs([E.client_entry("resnet50_be", be_prof, 90)], os.path.join(out_dir, "be_solo"), extra_env=env)
+    # DUR_THRESHOLD the way the reference derived its 160 us: 2.5 % of the HP solo latency
+    # (reference benchmarking/benchmark_suite/utility_scripts/compute_average.py:42-44).
+    depth = int(os.environ.get("ORION_DUR_THRESHOLD_NS", 0)) or int(0.025 * hp_solo["clients"][0]["p50_latency"] * 1e6)
+    pair = [E.client_entry("resnet50_be", be_prof, 1000000), E.client_entry("resnet50_hp", hp_prof, n_hp, rps=HP_RPS)]
+    e2e = E.run_launch_jobs(pair, os.path.join(out_dir, "coloc_e2e"), depth=depth, extra_env=env)
+    env_res = dict(env)
+    env_res.update({"ORION_RESIDENT_INPUTS": 1, "ORION_READBACK": 0})
+    res = E.run_launch_jobs(pair, os.path.join(out_dir, "coloc_resident"), depth=depth, extra_env=env_res)
+    return {"hp_solo": hp_solo, "be_solo": be_solo, "e2e": e2e, "resident": res, "depth": depth,
+            "profile_rows": {"hp": hp_prof[3], "be": be_prof[3]}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1500)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", type=str, default="orion_b200")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        base = cpu_baseline(sample_hp=max(4, min(args.steps, 20)), sample_be=max(1, min(3, args.steps)))
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "samples/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["hp_p50_ms"], "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "ResNet-50 HP inference b4 + ResNet-50 BE training b32, eager PyTorch on host cores "
+                                       "(the reference's numeric path), run one after the other"},
+                "cpu_baseline": base, "hp": {"p50_ms": base["hp_p50_ms"], "p99_ms": base["hp_p99_ms"]},
+                "e2e": {"value": base["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "policy_decisions_per_s": reference_policy_rate()}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: the benchmark has no CPU fallback"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo")   # host-side barrier and gather only: the replicas exchange no data
+    from orion_b200 import build
+    build.build_all()
+
+    steps = max(args.steps, 20)
+    be_quota = int(os.environ.get("ORION_BE_SM_QUOTA", "0"))
+    out_dir = os.path.join(ROOT, "gpurun_out", "bench", "rank%d" % rank)
+    gpu = physical_gpu(local_rank)
+    sampler = ClockSampler(gpu)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    t0 = time.time()
+    rep = run_replica(gpu, steps, out_dir, be_quota)
+    torch.cuda.synchronize()
+    wall = time.time() - t0
+    clocks = sampler.stop()
+
+    def pick(run):
+        be, hp = run["clients"][0], run["clients"][1]
+        return be, hp
+
+    be_e2e, hp_e2e = pick(rep["e2e"])
+    be_res, hp_res = pick(rep["resident"])
+    hp_solo = rep["hp_solo"]["clients"][0]
+    be_solo = rep["be_solo"]["clients"][0]
+    local = {"be_sps": be_res["samples_per_s"], "be_sps_e2e": be_e2e["samples_per_s"], "be_solo_sps": be_solo["samples_per_s"],
+             "hp_p99": hp_e2e["p99_latency"], "hp_p50": hp_e2e["p50_latency"], "hp_solo_p99": hp_solo["p99_latency"],
+             "hp_solo_p50": hp_solo["p50_latency"], "hp_p99_resident": hp_res["p99_latency"],
+             "coloc_time": hp_res["total_time"], "launches": rep["resident"]["scheduler"].get("own_launches", 0),
+             "sched": rep["resident"]["scheduler"]["stats"], "wall": wall}
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, local)
+    else:
+        gathered = [local]
+    if rank != 0:
+        return 0
+
+    roof = kernel_roofline(batch=32, iters=5, warm=3)
+    peaks = read_peaks()
+    base = cpu_baseline()
+    worst = max(gathered, key=lambda g: g["hp_p99"] / g["hp_solo_p99"])
+    value = sum(g["be_sps"] for g in gathered)
+    e2e_value = sum(g["be_sps_e2e"] for g in gathered)
+    step_time = max(g["coloc_time"] for g in gathered)
+    line = {
+        "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": step_time * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "configs[1]: HP ResNet-50 inference fp32 b4 Poisson %d req/s x %d requests + BE ResNet-50 training "
+                               "b32 SGD(0.9, 0.1), one pair per GPU" % (HP_RPS, steps),
+                   "step": "one HP request (the BE client trains concurrently until the HP client is done)",
+                   "protocol_warmup_requests": 10, "algo": "orion", "dur_threshold_ns": rep["depth"],
+                   "be_sm_quota": be_quota or None, "profile_rows": rep["profile_rows"],
+                   "l2": "roofline replay rotates through >126 MB between iterations; co-location inputs exceed L2 per BE step"},
+        "hp": {"p99_ms": worst["hp_p99"], "p50_ms": worst["hp_p50"], "solo_p99_ms": worst["hp_solo_p99"],
+               "solo_p50_ms": worst["hp_solo_p50"], "p99_x_solo": worst["hp_p99"] / worst["hp_solo_p99"],
+               "p99_ms_resident": worst["hp_p99_resident"], "target_x_solo": 1.15},
+        "be": {"samples_per_s": value, "solo_samples_per_s": sum(g["be_solo_sps"] for g in gathered),
+               "fraction_of_solo": value / max(1e-9, sum(g["be_solo_sps"] for g in gathered)), "target_fraction": 0.70},
+        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": 4 * 3 * 224 * 224 * 4,
+                "d2h_bytes_per_step": 4 * 1000 * 4,
+                "be_h2d_bytes_per_iteration": 32 * 3 * 224 * 224 * 4 + 32 * 8, "be_d2h_bytes_per_iteration": 4,
+                "hp_p99_x_solo": worst["hp_p99"] / worst["hp_solo_p99"]},
+        "gpu_launches": int(sum(g["launches"] for g in gathered)),
+        "scheduler": gathered[0]["sched"],
+        "roofline": {"bound": "tensor", "achieved": roof["achieved_tflops"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": roof["achieved_tflops"] / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "igemm_fprop_kernel<float> (3xTF32), all 53 ResNet-50 convolutions at batch 32",
+                     "avg_launch_us": roof["avg_launch_us"], "launches_timed": roof["launches"],
+                     "note": "peak is the bf16 dense figure; fp32 runs three TF32 MMAs per product"},
+        "cpu_baseline": base,
+        "clocks": clocks,
+        "wall_s": wall,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

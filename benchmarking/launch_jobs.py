@@ -94,9 +94,15 @@ def launch_jobs(config_dict_list, input_args, run_eval, config_dir="."):
         t.join()
     sched_thread.join()
     out_dir = os.environ.get("ORION_OUT_DIR", ".")
+    info = {"stats": py_scheduler.stats(), "total_time": py_scheduler.total_time,
+            "hp_latency_ms_scheduler_side": py_scheduler.durations_ms(num_clients - 1)[-5000:]}
+    try:   # launches of the orion kernels made through the PyTorch adapter in this process
+        info["own_launches"] = int(torch.ops.orion.own_launches())
+        info["fallbacks"] = int(torch.ops.orion.fallbacks())
+    except (AttributeError, RuntimeError):
+        pass
     with open(os.path.join(out_dir, "scheduler.json"), "w") as f:
-        json.dump({"stats": py_scheduler.stats(), "total_time": py_scheduler.total_time,
-                   "hp_latency_ms_scheduler_side": py_scheduler.durations_ms(num_clients - 1)[-5000:]}, f)
+        json.dump(info, f)
     return py_scheduler
 
 

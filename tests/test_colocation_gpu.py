@@ -1,0 +1,41 @@
+"""End to end on one GPU: profile both clients, run HP solo and the HP/BE pair under the scheduler
+through benchmarking/launch_jobs.py with the capture library preloaded."""
+import os
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_profile_then_colocate(built, tmp_path):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from orion_b200 import experiments as E
+    out = str(tmp_path)
+    env = {"ORION_GATE_TIMEOUT_S": 15}
+    hp = E.profile_client("resnet50_hp", os.path.join(out, "profiles"), timeout=240)
+    be = E.profile_client("resnet50_be", os.path.join(out, "profiles"), timeout=240)
+    assert hp[3] == 53 + 3, "prepared ResNet-50 inference is 56 launches per request"
+    assert be[3] > 400
+    with open(hp[2]) as f:
+        assert f.readline().strip() == "Name,Profile,Memory_footprint,SM_usage,Duration"
+        rows = [l.rstrip("\n").split(",") for l in f]
+    assert all(len(r) == 5 for r in rows)
+    assert sum(1 for r in rows if "igemm" in r[0] and r[1] == "1") == 54
+
+    solo = E.run_launch_jobs([E.client_entry("resnet50_hp", hp, 130, rps=80)], os.path.join(out, "solo"), extra_env=env, timeout=180)
+    hp_solo = solo["clients"][0]
+    assert hp_solo["iterations"] == 130 and 0 < hp_solo["p50_latency"] < 50
+    assert solo["scheduler"]["stats"]["join_timeouts"] == 0
+
+    pair = [E.client_entry("resnet50_be", be, 100000), E.client_entry("resnet50_hp", hp, 130, rps=80)]
+    depth = int(0.025 * hp_solo["p50_latency"] * 1e6)
+    co = E.run_launch_jobs(pair, os.path.join(out, "pair"), depth=depth, extra_env=env, timeout=240)
+    be_c, hp_c = co["clients"]
+    assert hp_c["iterations"] == 130
+    assert be_c["iterations"] >= 11 and be_c["samples_per_s"] > 0
+    st = co["scheduler"]["stats"]
+    assert st["hp_submits"] > 0 and st["be_submits"] > 0 and st["join_timeouts"] == 0
+    assert co["scheduler"]["own_launches"] > 130 * 50
+    assert hp_c["p99_latency"] < 20 * hp_solo["p99_latency"]

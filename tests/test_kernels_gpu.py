@@ -1,0 +1,148 @@
+"""Parity of the sm_100a kernels against the CPU oracle, through the C ABI.
+
+Tolerances are the benchmark specification's: float32 relative 1e-4, bfloat16 relative 2e-2
+(relative to the largest magnitude of the expected tensor)."""
+import pytest
+import torch
+
+from oracle import numeric_oracle as O
+
+pytestmark = pytest.mark.gpu
+FP32_TOL, BF16_TOL = 1e-4, 2e-2
+
+
+@pytest.fixture(scope="module")
+def K(built):
+    from orion_b200 import kernels
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; the kernels have no CPU fallback")
+    torch.manual_seed(1234)
+    return kernels
+
+
+def _conv(K, Nb, H, W, C, Ko, R, stride, pad, dtype=torch.float32, dil=1, **kw):
+    x = torch.randn(Nb, H, W, C, device="cuda", dtype=dtype)
+    w = (torch.randn(Ko, R, R, C, device="cuda") / (C * R * R) ** 0.5).to(dtype)
+    y = K.conv2d_nhwc(x, w, (stride, stride), (pad, pad), (dil, dil), **kw)
+    assert K.read_status() == 0
+    want = O.conv2d_nhwc(x, w, (stride, stride), (pad, pad), (dil, dil),
+                         scale=kw.get("scale"), shift=kw.get("shift"), residual=kw.get("residual"),
+                         act=2 if kw.get("relu") == 2 else int(bool(kw.get("relu"))))
+    return O.rel_err(y, want)
+
+
+RESNET_SHAPES = [
+    (4, 224, 224, 3, 64, 7, 2, 3),      # stem: C=3 takes the scalar gather path
+    (4, 56, 56, 64, 64, 1, 1, 0), (4, 56, 56, 64, 64, 3, 1, 1), (4, 56, 56, 64, 256, 1, 1, 0),
+    (4, 56, 56, 256, 128, 1, 1, 0), (4, 56, 56, 128, 128, 3, 2, 1), (4, 56, 56, 256, 512, 1, 2, 0),
+    (4, 28, 28, 512, 256, 1, 1, 0), (4, 28, 28, 256, 256, 3, 2, 1), (4, 14, 14, 256, 1024, 1, 1, 0),
+    (4, 14, 14, 1024, 512, 1, 1, 0), (4, 14, 14, 512, 512, 3, 2, 1), (4, 7, 7, 512, 2048, 1, 1, 0),
+    (4, 7, 7, 2048, 512, 1, 1, 0), (4, 7, 7, 512, 512, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("shape", RESNET_SHAPES)
+def test_conv_fp32_resnet50_shapes(K, shape):
+    assert _conv(K, *shape) < FP32_TOL
+
+
+@pytest.mark.parametrize("shape", [(2, 9, 11, 24, 40, 3, 1, 1), (1, 5, 5, 16, 8, 1, 1, 0), (3, 17, 13, 36, 100, 3, 2, 1),
+                                   (2, 12, 12, 20, 72, 5, 1, 2), (1, 1, 1, 8, 8, 1, 1, 0), (2, 10, 10, 7, 19, 3, 1, 1)])
+def test_conv_fp32_ragged_shapes(K, shape):
+    """Row, column and channel tails; channel counts that are not a multiple of 4 (scalar loads and stores)."""
+    assert _conv(K, *shape) < FP32_TOL
+
+
+def test_conv_dilation_and_empty_batch(K):
+    assert _conv(K, 2, 16, 16, 32, 32, 3, 1, 2, dil=2) < FP32_TOL
+    x = torch.empty(0, 8, 8, 16, device="cuda")
+    w = torch.randn(8, 3, 3, 16, device="cuda")
+    assert K.conv2d_nhwc(x, w, (1, 1), (1, 1)).shape == (0, 8, 8, 8)
+
+
+def test_conv_fused_epilogue(K):
+    Ko = 96
+    scale, shift = torch.rand(Ko, device="cuda") + 0.5, torch.randn(Ko, device="cuda")
+    res = torch.randn(2, 14, 14, Ko, device="cuda")
+    for relu in (0, 1, 2):
+        assert _conv(K, 2, 14, 14, 64, Ko, 3, 1, 1, scale=scale, shift=shift, residual=res, relu=relu) < FP32_TOL
+
+
+@pytest.mark.parametrize("bn,splits", [(128, 1), (64, 1), (128, 4), (64, 3), (64, 16)])
+def test_conv_tile_width_and_split_k(K, bn, splits):
+    """Split-K through caller-provided scratch; the kernel must leave scratch and counters zero."""
+    x = torch.randn(4, 7, 7, 512, device="cuda")
+    w = torch.randn(512, 3, 3, 512, device="cuda") / 68.0
+    shift = torch.randn(512, device="cuda")
+    want = O.conv2d_nhwc(x, w, (1, 1), (1, 1), shift=shift, act=1)
+    y = K.conv2d_nhwc(x, w, (1, 1), (1, 1), shift=shift, relu=True, bn=bn, splits=splits)
+    assert K.read_status() == 0
+    assert O.rel_err(y, want) < FP32_TOL
+
+
+def test_conv_result_does_not_depend_on_the_sm_quota(K):
+    """A persistent grid of any size walks the same tiles: without split-K the output is bit-identical."""
+    x = torch.randn(4, 28, 28, 128, device="cuda")
+    w = torch.randn(128, 3, 3, 128, device="cuda") / 34.0
+    ref = K.conv2d_nhwc(x, w, (1, 1), (1, 1), bn=128, splits=1, num_ctas=148)
+    for q in (1, 8, 37, 64):
+        assert torch.equal(K.conv2d_nhwc(x, w, (1, 1), (1, 1), bn=128, splits=1, num_ctas=q), ref)
+    assert K.read_status() == 0
+
+
+def test_conv_is_linear_at_training_batch_size(K):
+    """Size-independent property at the BE batch size (32): conv(a*x1 + x2) = a*conv(x1) + conv(x2)."""
+    x1 = torch.randn(32, 56, 56, 64, device="cuda")
+    x2 = torch.randn(32, 56, 56, 64, device="cuda")
+    w = torch.randn(64, 3, 3, 64, device="cuda") / 24.0
+    f = lambda x: K.conv2d_nhwc(x, w, (1, 1), (1, 1))
+    lhs = f(2.5 * x1 + x2)
+    rhs = 2.5 * f(x1) + f(x2)
+    assert ((lhs - rhs).abs().max() / rhs.abs().max()).item() < 2e-5
+    assert K.read_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(2, 14, 14, 64, 64, 3, 1, 1), (4, 28, 28, 128, 256, 1, 1, 0), (1, 9, 9, 24, 40, 3, 2, 1)])
+def test_conv_bf16(K, shape):
+    assert _conv(K, *shape, dtype=torch.bfloat16) < BF16_TOL
+
+
+@pytest.mark.parametrize("M,N,Kd", [(4, 1000, 2048), (128, 128, 32), (300, 200, 136), (3072, 768, 768), (1, 10, 5)])
+def test_linear_fp32(K, M, N, Kd):
+    x, w, b = torch.randn(M, Kd, device="cuda"), torch.randn(N, Kd, device="cuda") / Kd ** 0.5, torch.randn(N, device="cuda")
+    y = K.linear(x, w, bias=b)
+    assert K.read_status() == 0
+    assert O.rel_err(y, O.linear(x, w, b)) < FP32_TOL
+
+
+@pytest.mark.parametrize("M,N,Kd", [(3072, 3072, 768), (257, 130, 72)])
+def test_linear_bf16(K, M, N, Kd):
+    x = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, Kd, device="cuda") / Kd ** 0.5).to(torch.bfloat16)
+    y = K.linear(x, w, relu=True)
+    assert K.read_status() == 0
+    assert O.rel_err(y, O.linear(x, w, relu=True)) < BF16_TOL
+
+
+@pytest.mark.parametrize("shape", [(4, 56, 56, 64), (2, 7, 7, 2048), (3, 5, 5, 6), (1, 1, 1, 4)])
+def test_bn_inference(K, shape):
+    C = shape[-1]
+    x = torch.randn(*shape, device="cuda")
+    g, b, m = torch.rand(C, device="cuda") + 0.5, torch.randn(C, device="cuda"), torch.randn(C, device="cuda")
+    v = torch.rand(C, device="cuda") + 0.1
+    for relu in (False, True):
+        y = K.bn_inference(x, g, b, m, v, 1e-5, relu=relu)
+        assert O.rel_err(y, O.bn_inference(x, g, b, m, v, 1e-5, relu)) < 1e-5
+
+
+def test_elementwise_and_pooling(K):
+    a, b = torch.randn(4, 56, 56, 256, device="cuda"), torch.randn(4, 56, 56, 256, device="cuda")
+    assert torch.equal(K.binary(a, mode=0), torch.relu(a))
+    assert torch.equal(K.binary(a, b, mode=1), a + b)
+    assert torch.equal(K.binary(a, b, mode=2), torch.relu(a + b))
+    odd = torch.randn(1031, device="cuda")
+    assert torch.equal(K.binary(odd, odd, mode=2), torch.relu(odd + odd))          # tail that is not a multiple of 4
+    x = torch.randn(4, 112, 112, 64, device="cuda")
+    assert torch.equal(K.maxpool_nhwc(x, 3, 2, 1).double().cpu(), O.maxpool_nhwc(x, 3, 2, 1))
+    z = torch.randn(4, 7, 7, 2048, device="cuda")
+    assert O.rel_err(K.avgpool_nhwc(z), O.avgpool_nhwc(z)) < 1e-6

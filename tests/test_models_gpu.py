@@ -1,0 +1,73 @@
+"""Whole-model parity: torchvision models running on the orion kernels (through the dispatcher
+overrides, and as prepared models with fused epilogues) against eager PyTorch in float32 on the
+CPU — the reference's numeric path.  Tolerance: fp32 relative 1e-4 (benchmark specification)."""
+import pytest
+import torch
+import torchvision
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(built):
+    from orion_b200 import torch_ops
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    torch_ops.load()
+    return torch_ops
+
+
+def _rel(a, b):
+    return ((a.double().cpu() - b.double().cpu()).abs().max() / b.double().abs().max()).item()
+
+
+@pytest.mark.parametrize("name", ["resnet50", "mobilenet_v2", "resnet101"])
+def test_inference_matches_cpu_fp32(ops, name):
+    torch.manual_seed(42)
+    model = torchvision.models.__dict__[name](num_classes=1000).eval()
+    x = torch.randn(4, 3, 224, 224)
+    with torch.no_grad():
+        want = model(x)
+        cuda_model = model.cuda().to(memory_format=torch.channels_last)
+        xc = x.cuda().contiguous(memory_format=torch.channels_last)
+        before = int(torch.ops.orion.own_launches())
+        via_overrides = cuda_model(xc)
+        mid = int(torch.ops.orion.own_launches())
+        prepared = ops.prepare_inference(cuda_model)
+        via_prepared = prepared(xc)
+        after = int(torch.ops.orion.own_launches())
+    from orion_b200 import kernels
+    assert kernels.read_status() == 0
+    assert mid > before and after > mid, "the orion kernels did not run"
+    assert _rel(via_overrides, want) < 1e-4
+    assert _rel(via_prepared, want) < 1e-4
+    if name == "resnet50":
+        assert after - mid == 53 + 3      # 53 fused convolutions, max-pool, average pool, classifier: one launch each
+
+
+def test_training_step_runs_on_overridden_forward_convolutions(ops):
+    """BE-style training: forward convolutions on the orion kernel, backward on the stock ops;
+    the loss must follow the stock path closely for a few SGD steps."""
+    def run(override):
+        torch.manual_seed(7)
+        ops.set_overrides(override)
+        m = torchvision.models.resnet18(num_classes=10).cuda().to(memory_format=torch.channels_last).train()
+        opt = torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9)
+        x = torch.randn(8, 3, 64, 64, device="cuda").contiguous(memory_format=torch.channels_last)
+        y = torch.randint(0, 10, (8,), device="cuda")
+        losses = []
+        for _ in range(4):
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(m(x), y)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        return losses
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ours, stock = run(True), run(False)
+    finally:
+        ops.set_overrides(True)
+    for a, b in zip(ours, stock):
+        assert abs(a - b) / abs(b) < 5e-3

@@ -1,0 +1,107 @@
+"""Live scheduler + capture library on the host: client threads queue ops through the
+lock-free rings, the scheduler thread grants them (ORION_FAKE_GPU=1: every event is
+complete at once).  Each scenario runs in a child process because the libraries keep
+process-wide state."""
+import json
+import os
+import subprocess
+import sys
+import textwrap
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+DRIVER = textwrap.dedent('''
+    import ctypes, json, sys, threading, time
+    sys.path.insert(0, %(root)r)
+    from src.scheduler_frontend import PyScheduler
+    cap = ctypes.CDLL(%(root)r + "/orion_b200/lib/liborion_capture.so", mode=ctypes.RTLD_GLOBAL)
+    sched = ctypes.CDLL(%(root)r + "/orion_b200/lib/liborion_sched.so")
+    cap.stop.restype = ctypes.c_bool
+    cfg = json.loads(sys.argv[1])
+    N = len(cfg["clients"])
+    barriers = [threading.Barrier(N + 1)]
+    done = [0] * N
+    wrong = []
+    def client(i):
+        c = cfg["clients"][i]
+        barriers[0].wait()
+        it = 0
+        while it < c["iters"]:
+            for t in c["ops"]:
+                got = cap.orion_capture_op(t)
+                if got != i: wrong.append((i, got))
+            cap.block(it)
+            for t in c.get("after", []):
+                cap.orion_capture_op(t)
+            it += 1
+            done[i] = it
+            if it == 1 or it == 10: barriers[0].wait()
+            if cap.stop(): break
+        barriers[0].wait()
+    ths = [threading.Thread(target=client, args=(i,)) for i in range(N)]
+    for t in ths: t.start()
+    ps = PyScheduler(sched, N)
+    st = threading.Thread(target=ps.run_scheduler, args=(
+        barriers, [t.native_id for t in ths], ["m"] * N, [c["profile"] for c in cfg["clients"]], [None] * N,
+        [c["num_kernels"] for c in cfg["clients"]], [None] * N, [c["iters"] for c in cfg["clients"]], True, True,
+        cfg.get("reef", False), False, cfg.get("depth", 160000), 1, 1, [c["train"] for c in cfg["clients"]]))
+    t0 = time.time(); st.start()
+    for t in ths: t.join()
+    st.join()
+    print(json.dumps({"done": done, "wrong": wrong, "stats": ps.stats(), "secs": time.time() - t0,
+                      "hp_samples": len(ps.durations_ms(N - 1))}))
+''')
+
+
+def _run(cfg, env_extra=None, timeout=120):
+    env = dict(os.environ, ORION_FAKE_GPU="1", ORION_GATE_TIMEOUT_S="5")
+    env.update(env_extra or {})
+    out = subprocess.run([sys.executable, "-c", DRIVER % {"root": ROOT}, json.dumps(cfg)], capture_output=True, text=True,
+                         timeout=timeout, env=env)
+    assert out.returncode == 0, out.stderr[-3000:]
+    return json.loads(out.stdout.strip().splitlines()[-1])
+
+
+def _profile(tmp_path, name, rows):
+    p = tmp_path / name
+    p.write_text("Name,Profile,Memory_footprint,SM_usage,Duration\n" + "".join("k,%d,0,%d,%d\n" % r for r in rows))
+    return str(p)
+
+
+def test_pair_runs_to_completion_and_best_effort_is_stopped(built, tmp_path):
+    be = _profile(tmp_path, "be", [(1, 40, 9000), (0, 200, 5000), (-1, 30, 3000)] * 10)
+    hp = _profile(tmp_path, "hp", [(1, 60, 8000), (0, 20, 2000)] * 6)
+    r = _run({"clients": [{"profile": be, "num_kernels": 30, "iters": 100000, "train": True, "ops": [1] + [0] * 30},
+                          {"profile": hp, "num_kernels": 12, "iters": 60, "train": False, "ops": [1] + [0] * 12, "after": [1]}],
+              "depth": 20000})
+    assert r["done"][1] == 60 and 10 <= r["done"][0] < 100000
+    assert not r["wrong"]
+    s = r["stats"]
+    assert s["hp_submits"] == 60 * 14 - 1 or s["hp_submits"] >= 60 * 13          # 12 kernels + copies per request
+    assert s["be_submits"] >= 10 * 31 and s["join_timeouts"] == 0 and s["forced_iter_ends"] == 0
+    assert r["hp_samples"] == 60
+
+
+def test_single_client_and_reef_policy(built, tmp_path):
+    p = _profile(tmp_path, "p", [(1, 10, 1000)] * 5)
+    r = _run({"clients": [{"profile": p, "num_kernels": 5, "iters": 15, "train": False, "ops": [0] * 5}]})
+    assert r["done"] == [15] and r["stats"]["hp_submits"] == 75
+    be = _profile(tmp_path, "be", [(1, 100, 500)] * 4)
+    r = _run({"reef": True, "depth": 3, "clients": [{"profile": be, "num_kernels": 4, "iters": 100000, "train": True, "ops": [0] * 4},
+                                                     {"profile": p, "num_kernels": 5, "iters": 30, "train": False, "ops": [0] * 5}]})
+    assert r["done"][1] == 30 and r["done"][0] >= 10
+
+
+def test_profile_longer_than_the_op_stream_does_not_deadlock(built, tmp_path):
+    """The client issues 4 ops per request, the profile announces 6: the scheduler closes the
+    request when the client is already waiting for it (the reference would hang here)."""
+    p = _profile(tmp_path, "p", [(1, 10, 1000)] * 6)
+    r = _run({"clients": [{"profile": p, "num_kernels": 6, "iters": 14, "train": False, "ops": [0] * 4}]})
+    assert r["done"] == [14]
+    assert r["stats"]["forced_iter_ends"] == 14
+
+
+def test_profile_shorter_than_the_op_stream_keeps_running(built, tmp_path):
+    p = _profile(tmp_path, "p", [(1, 10, 1000)] * 3)
+    r = _run({"clients": [{"profile": p, "num_kernels": 3, "iters": 13, "train": False, "ops": [0] * 5}]}, timeout=180)
+    assert r["done"] == [13]
