@@ -109,6 +109,7 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
         quota = int(os.environ.get("ORION_BE_SM_QUOTA", "0")) if train else 0
         if quota > 0:
             torch_ops.set_sm_quota(quota)
+        import contextlib
         model = models.__dict__[model_name](num_classes=1000)
         model = model.to(local_rank).to(memory_format=torch.channels_last)
         if train:
@@ -138,13 +139,15 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
                     gpu_data = data.to(local_rank, non_blocking=True).contiguous(memory_format=torch.channels_last)
                     gpu_target = target.to(local_rank, non_blocking=True)
                 optimizer.zero_grad()
-                output = model(gpu_data)
-                loss = criterion(output, gpu_target)
+                # iteration 0 overlaps with other clients preparing their models (see TRACE_LOCK)
+                with (torch_ops.TRACE_LOCK if batch_idx == 0 else contextlib.nullcontext()):
+                    output = model(gpu_data)
+                    loss = criterion(output, gpu_target)
                 loss.backward()
                 optimizer.step()
                 backend_lib.block(batch_idx)
                 if readback:
-                    result = float(loss)
+                    result = float(loss.detach())
                 timings.append(time.time() - start_iter)
                 batch_idx += 1
                 if batch_idx == 1 or batch_idx == 10:
@@ -162,7 +165,8 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
                         continue
                     if not resident:
                         gpu_data = data.to(local_rank, non_blocking=True).contiguous(memory_format=torch.channels_last)
-                    output = model(gpu_data)
+                    with (torch_ops.TRACE_LOCK if batch_idx == 0 else contextlib.nullcontext()):
+                        output = model(gpu_data)
                     backend_lib.block(batch_idx)
                     if readback:
                         result = output.cpu()   # a plain device-to-host copy: no extra kernel in the op stream

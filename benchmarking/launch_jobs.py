@@ -71,6 +71,18 @@ def launch_jobs(config_dict_list, input_args, run_eval, config_dir="."):
     num_iters = [c["num_iters"] for c in config_dict_list]
     train_list = [c["args"]["train"] for c in config_dict_list]
 
+    def guarded(fn, kwargs):
+        # A client that dies would leave the others waiting at a barrier for ever: end the run instead.
+        try:
+            fn(**kwargs)
+        except BaseException:
+            import traceback
+            traceback.print_exc()
+            sys.stderr.write("orion: a client thread failed; aborting the run\n")
+            sys.stderr.flush()
+            py_scheduler.shutdown()
+            os._exit(3)
+
     threads, tids = [], []
     for i, c in enumerate(config_dict_list):
         if c["arch"] not in function_dict:
@@ -78,7 +90,7 @@ def launch_jobs(config_dict_list, input_args, run_eval, config_dir="."):
         kwargs = dict(c["args"])
         kwargs.update({"num_iters": num_iters[i], "local_rank": 0, "barriers": barriers, "client_barrier": client_barrier,
                        "tid": i})
-        t = threading.Thread(target=function_dict[c["arch"]], kwargs=kwargs)
+        t = threading.Thread(target=guarded, args=(function_dict[c["arch"]], kwargs))
         t.start()
         tids.append(t.native_id)
         threads.append(t)

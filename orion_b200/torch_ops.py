@@ -8,6 +8,7 @@ liborion_kernels.so passes the cudaLaunchKernel trap of the capture library.
 """
 import operator
 import os
+import threading
 
 import torch
 import torch.fx as fx
@@ -17,6 +18,10 @@ import torch.nn.functional as F
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _GLUE = os.path.join(_HERE, "lib", "liborion_torch.so")
 _loaded = False
+# torch.fx.symbolic_trace patches nn.Module.__call__ process-wide while it runs.  Client threads
+# of one process therefore take this lock around everything that calls a module during their
+# first iteration (when models are prepared), and prepare_inference holds it while tracing.
+TRACE_LOCK = threading.RLock()
 
 
 def load():
@@ -130,7 +135,8 @@ def prepare_inference(model):
     orion kernels.  Grouped (depthwise) convolutions keep their stock implementation."""
     load()
     model = model.eval()
-    gm = fx.symbolic_trace(model)
+    with TRACE_LOCK:
+        gm = fx.symbolic_trace(model)
     mods = dict(gm.named_modules())
     g = gm.graph
     counter = [0]
