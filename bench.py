@@ -94,60 +94,11 @@ class ClockSampler:
         return out
 
 
-def conv_layers_resnet50():
-    """(C, K, R, stride, pad, H) of every convolution of torchvision's ResNet-50, with the input size H=W."""
-    layers = [(3, 64, 7, 2, 3, 224)]
-    h, cin = 56, 64
-    for width, blocks, stride in ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2)):
-        for b in range(blocks):
-            s = stride if b == 0 else 1
-            layers.append((cin, width, 1, 1, 0, h))
-            layers.append((width, width, 3, s, 1, h))
-            hout = h // s
-            layers.append((width, width * 4, 1, 1, 0, hout))
-            if b == 0:
-                layers.append((cin, width * 4, 1, s, 0, h))
-            cin, h = width * 4, hout
-    return layers
-
-
 def kernel_roofline(batch, iters, warm):
-    """Replay every ResNet-50 convolution at `batch` through the implicit-GEMM kernel and time
-    the launches with CUDA events on their stream.  Inputs are rotated through a pool larger
-    than L2 so that no iteration finds its operands cached from the previous one."""
-    import torch
-    from orion_b200 import kernels as K
-    dev = torch.device("cuda", torch.cuda.current_device())
-    layers = conv_layers_resnet50()
-    flops = 0.0
-    work = []
-    for (c, k, r, s, p, h) in layers:
-        x = torch.randn(batch, h, h, c, device=dev)
-        w = torch.randn(k, r, r, c, device=dev) * (1.0 / (c * r * r) ** 0.5)
-        ho = (h + 2 * p - r) // s + 1
-        flops += 2.0 * batch * ho * ho * k * c * r * r
-        work.append((x, w, (s, s), (p, p)))
-    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
-    stream = torch.cuda.current_stream()
-    total_ms, launches = 0.0, 0
-    for it in range(warm + iters):
-        flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for (x, w, s, p) in work:
-            K.conv2d_nhwc(x, w, s, p)
-        e1.record(stream)
-        e1.synchronize()
-        if it >= warm:
-            total_ms += e0.elapsed_time(e1)
-            launches += len(work)
-    status = K.read_status()
-    if status != 0:
-        raise RuntimeError("a kernel reported a timed-out wait (status %d)" % status)
-    per_launch_flop = flops / len(work)
-    avg_launch_s = total_ms * 1e-3 / launches
-    return {"achieved_tflops": per_launch_flop / avg_launch_s / 1e12, "launches": launches, "avg_launch_us": avg_launch_s * 1e6,
-            "flop_per_launch": per_launch_flop}
+    """All 53 ResNet-50 convolutions at `batch` through the implicit-GEMM kernel, timed with CUDA
+    events on the launching stream (orion_b200/kernel_replay.py; L2 is flushed between iterations)."""
+    from orion_b200 import kernel_replay
+    return kernel_replay.replay(kernel_replay.conv_layers_resnet50(), batch, iters, warm)
 
 
 def cpu_baseline(sample_hp=12, sample_be=2):
