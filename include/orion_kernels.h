@@ -33,6 +33,21 @@ int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, const float* sc
                           int pad_h, int pad_w, int dil_h, int dil_w, int bn, int splits, float* scratch, int* counters,
                           int num_ctas, void* stream);
 
+/* No counterpart in the reference.  ob200_conv2d_fprop_ex for callers that cannot allocate device
+ * memory at the moment of the call — code running under stream capture, inside an allocator or
+ * framework hook where a cudaMalloc would re-enter the allocator, or an embedder that hands out all
+ * device memory up front.  The split-K scratch is a fixed 8 MiB (+1 KiB of tile counters) array
+ * compiled into the library (held by every GPU that loads it, until exit); the call performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.  Limits: tiles*128*bn floats must fit
+ * in 2 Mi floats and tiles (ceil(M/128)*ceil(Kout/bn)) in 256, else the call returns -3 and launches
+ * nothing.  All calls share the array: each call clears the part it uses on `stream` first, and calls
+ * that overlap on the GPU without an ordering between their streams race on it.  The first call on a
+ * device resolves the array's device address (not a stream operation): make it before any capture. */
+int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y, const float* scale, const float* shift,
+                               const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
+                               int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn, int splits,
+                               int num_ctas, void* stream);
+
 /* The choice ob200_conv2d_fprop makes for a problem size. */
 int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out);
 
