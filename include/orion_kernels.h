@@ -75,6 +75,11 @@ int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int 
 /* Device status word of the current device (synchronises the device): 0, or the code of
  * the bounded wait a kernel gave up on.  Clears the word.  No counterpart in the reference. */
 int ob200_read_status(void);
+/* Tuning aid, no counterpart in the reference: `dev_buf` (8 long longs in device memory, or NULL to
+ * switch off) receives from CTA 0 of every implicit-GEMM launch the cycles each warp role spent
+ * waiting: [0] epilogue, [1] MMA on operands, [2] MMA on a free accumulator, [3] splitter,
+ * [4] producer, [5] whole kernel. */
+void ob200_set_debug_buffer(long long* dev_buf);
 /* SM count of the current device.  No counterpart in the reference. */
 int ob200_sm_count(void);
 

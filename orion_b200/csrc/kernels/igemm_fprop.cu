@@ -12,10 +12,12 @@
 //   warps 0-3   epilogue: tcgen05.ld the fp32 accumulator, apply scale/shift,
 //               residual and ReLU, store NHWC rows
 //   warp  4     allocates TMEM, one lane issues tcgen05.mma and tcgen05.commit
-//   warps 5-12  two producer groups of 128 threads that alternate over k-blocks:
-//               gather one 128-byte row slice of the im2col matrix (zero-filled at
-//               the image border) and of the filter per thread, and write them
-//               into shared memory in the 128-byte-swizzled K-major layout
+//   warps 5-8   splitters (fp32 only): split the raw operand rows in shared memory into
+//               TF32 high parts (in place) and exact remainders (second buffer)
+//   warps 9-12  producers, one thread per operand row: cp.async 16-byte copies of one
+//               128-byte row slice of the im2col matrix (zero-filled at the image
+//               border) and of the filter, straight into the 128-byte-swizzled
+//               K-major stage buffers, several stages ahead of the MMA
 // fp32 inputs run as 3xTF32: each value is split into a TF32-rounded high part and
 // the exact remainder, and lo*hi + hi*lo + hi*hi accumulate in fp32, which keeps
 // the result within ~1e-6 relative of an fp32 reference.  bf16 inputs use one
@@ -41,8 +43,9 @@ namespace ob200 {
 constexpr int BM = 128;
 constexpr int EPI_WARPS = 4;
 constexpr int MMA_WARP = 4;
-constexpr int PROD_GROUPS = 2;
-constexpr int NTHREADS = (EPI_WARPS + 1 + 4 * PROD_GROUPS) * 32;   // 416
+constexpr int SPLIT_WARPS = 4;
+constexpr int PROD_WARPS = 4;
+constexpr int NTHREADS = (EPI_WARPS + 1 + SPLIT_WARPS + PROD_WARPS) * 32;   // 416
 
 template <typename T, int BN>
 struct Cfg {
@@ -53,11 +56,13 @@ struct Cfg {
     static constexpr int B_BYTES = BN * 128;
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (kSplit ? 2 : 1);
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int EPI_BYTES = EPI_WARPS * 32 * 36 * 4;   // per-warp transpose tiles of the epilogue
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 512 /*barriers*/;
     static constexpr int TMEM_COLS = 2 * BN;
 };
 
 struct SharedCtl {
+    uint64_t raw_full[8];
     uint64_t full[8];
     uint64_t empty[8];
     uint64_t tmem_full[2];
@@ -97,6 +102,26 @@ __device__ __forceinline__ void st_chunk(uint8_t* hi, uint8_t*, uint32_t off, co
     *reinterpret_cast<uint4*>(hi + off) = v;
 }
 
+// In place: TF32-rounded high parts; second buffer: exact remainders.
+__device__ __forceinline__ void split_chunk(uint8_t* hi, uint8_t* lo) {
+    const float4 v = *reinterpret_cast<const float4*>(hi);
+    float4 h, l;
+    h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
+    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+    *reinterpret_cast<float4*>(hi) = h;
+    *reinterpret_cast<float4*>(lo) = l;
+}
+
+// 16-byte asynchronous global->shared copy; `ok == false` writes zeros and reads nothing.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool ok) {
+    const int bytes = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// The mbarrier receives one arrival from this thread once all its earlier cp.async copies have landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void set_elem(float4& v, int i, float x) {
     if (i == 0) v.x = x; else if (i == 1) v.y = x; else if (i == 2) v.z = x; else v.w = x;
 }
@@ -106,13 +131,106 @@ __device__ __forceinline__ void set_elem(uint4& v, int i, __nv_bfloat16 x) {
     *w |= bits;
 }
 
+constexpr int EPI_LD = 36;   // floats per staged accumulator row: 16-byte aligned, conflict-free both ways
+
+struct EpiCoef {
+    float4 scale, shift;
+};
+
+// Per-channel multiplier / addend of four consecutive output channels starting at n.
+template <typename T>
+__device__ __forceinline__ EpiCoef load_coef(const IgemmParams& p, int n) {
+    EpiCoef c;
+    c.scale = make_float4(1.f, 1.f, 1.f, 1.f);
+    c.shift = make_float4(0.f, 0.f, 0.f, 0.f);
+    float* sc = &c.scale.x;
+    float* sh = &c.shift.x;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        if (n + e < p.Kout) {
+            if (p.scale) sc[e] = __ldg(p.scale + n + e);
+            if (p.shift) sh[e] = __ldg(p.shift + n + e);
+        }
+    }
+    return c;
+}
+
+// Epilogue of four consecutive channels of output row m: affine, residual, activation, store.
+template <typename T>
+__device__ __forceinline__ void store_out(const IgemmParams& p, const EpiCoef& c, float4 v, long long m, int n) {
+    if (n >= p.Kout) return;
+    const long long base = m * p.Kout + n;
+    float x[4] = {v.x * c.scale.x + c.shift.x, v.y * c.scale.y + c.shift.y, v.z * c.scale.z + c.shift.z, v.w * c.scale.w + c.shift.w};
+    const bool full = (n + 3 < p.Kout) && ((p.Kout & 3) == 0);
+    if (p.residual) {
+        if (sizeof(T) == 4) {
+            const float* res = reinterpret_cast<const float*>(p.residual) + base;
+            if (full) {
+                const float4 q = __ldg(reinterpret_cast<const float4*>(res));
+                x[0] += q.x; x[1] += q.y; x[2] += q.z; x[3] += q.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (n + e < p.Kout) x[e] += __ldg(res + e);
+            }
+        } else {
+            const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(p.residual) + base;
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (n + e < p.Kout) x[e] += __bfloat162float(res[e]);
+        }
+    }
+    if (p.relu) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) x[e] = fmaxf(x[e], 0.f);
+        if (p.relu == 2) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) x[e] = fminf(x[e], 6.f);
+        }
+    }
+    if (sizeof(T) == 4) {
+        float* y = reinterpret_cast<float*>(p.y) + base;
+        if (full) {
+            *reinterpret_cast<float4*>(y) = make_float4(x[0], x[1], x[2], x[3]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (n + e < p.Kout) y[e] = x[e];
+        }
+    } else {
+        __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + base;
+        if (full) {
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(x[0], x[1]);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(x[2], x[3]);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&t0);
+            o.y = *reinterpret_cast<uint32_t*>(&t1);
+            *reinterpret_cast<uint2*>(y) = o;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (n + e < p.Kout) y[e] = __float2bfloat16(x[e]);
+        }
+    }
+}
+
+// mbar_wait that also adds the cycles spent waiting to `acc` (role-level wait breakdown for tuning).
+__device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long& acc) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(bar, parity, abort_flag);
+    acc += clock64() - t0;
+    return ok;
+}
+
 template <typename T, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmParams p) {
     using C = Cfg<T, BN>;
     using Chunk = typename ChunkOf<T>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + C::STAGES * C::STAGE_BYTES);
+    float* epi_stage = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);
+    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + C::STAGES * C::STAGE_BYTES + C::EPI_BYTES);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -120,7 +238,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
 
     if (tid == 0) {
         for (int s = 0; s < C::STAGES; s++) {
-            mbar_init(&ctl->full[s], 4);       // one elected lane per producer warp of the owning group
+            mbar_init(&ctl->raw_full[s], PROD_WARPS * 32);   // every producer thread, when its copies have landed
+            mbar_init(&ctl->full[s], SPLIT_WARPS);           // one elected lane per splitter warp
             mbar_init(&ctl->empty[s], 1);      // tcgen05.commit
         }
         for (int b = 0; b < 2; b++) {
@@ -144,6 +263,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
     const int tiles = p.tiles_m * p.tiles_n;
     const int units = tiles * p.splits;
     const int SC = p.S * p.C;
+    long long waited = 0;
+    const long long t_start = clock64();
 
     if (warp < EPI_WARPS) {
         // ------------------------------------------------------------ epilogue
@@ -152,124 +273,86 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             const int tile = u / p.splits;
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const int ab = local & 1;
-            if (!mbar_wait(&ctl->tmem_full[ab], (local >> 1) & 1, abort_flag)) {
+            if (!timed_wait(&ctl->tmem_full[ab], (local >> 1) & 1, abort_flag, waited)) {
                 if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_FULL); }
                 break;
             }
             tc_fence_after_sync();
-            const int row = warp * 32 + lane;
-            const long long m = (long long)tm * BM + row;
-            const bool row_ok = m < p.M;
-            bool finalize = true;
-            float* part = nullptr;
-            if (p.splits > 1) {
-                // Add this unit's partial tile into the fp32 scratch; the last unit of the tile finalises.
-                part = p.scratch + ((long long)tile * BM + row) * BN;
+            // Accumulator rows sit one per lane; a per-warp shared-memory tile turns them so that
+            // eight consecutive lanes own 32 consecutive output channels of one row, which makes
+            // every global access below a full 128-byte line.
+            float* stage = epi_stage + warp * (32 * EPI_LD);
+            const int sub = lane >> 3;          // row within a group of four
+            const int cc = (lane & 7) * 4;      // first of this lane's four channels within the 32-channel chunk
+            const long long tile_row0 = (long long)tm * BM + warp * 32;
 #pragma unroll 1
-                for (int cb = 0; cb < BN / 32; cb++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * BN + cb * 32, r);
-                    tmem_ld_wait();
-                    if (row_ok) {
+            for (int cb = 0; cb < BN / 32; cb++) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * BN + cb * 32, r);
+                tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; j++) atomicAdd(part + cb * 32 + j, __uint_as_float(r[j]));
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) =
+                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                __syncwarp();
+                const int n = tn * BN + cb * 32 + cc;
+                if (p.splits > 1) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int rr = i * 4 + sub;
+                        if (tile_row0 + rr < p.M) {
+                            const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc);
+                            float* part = p.scratch + ((long long)tile * BM + warp * 32 + rr) * BN + cb * 32 + cc;
+                            atomicAdd(part + 0, v.x); atomicAdd(part + 1, v.y); atomicAdd(part + 2, v.z); atomicAdd(part + 3, v.w);
+                        }
+                    }
+                } else {
+                    const EpiCoef coef = load_coef<T>(p, n);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int rr = i * 4 + sub;
+                        const long long m = tile_row0 + rr;
+                        if (m < p.M) store_out<T>(p, coef, *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc), m, n);
                     }
                 }
-                __threadfence();
                 __syncwarp();
-                // All four epilogue warps must have added their rows before the unit counts as arrived.
+            }
+            if (p.splits > 1) {
+                // The unit that arrives last on the tile's counter applies the epilogue to the sums.
+                __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (tid == 0) {
                     int prev = atomicAdd(p.counters + tile, 1);
                     ctl->last_flag = (prev == p.splits - 1);
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                finalize = ctl->last_flag != 0;
-                __threadfence();
-            }
-            if (finalize) {
+                if (ctl->last_flag) {
+                    __threadfence();
 #pragma unroll 1
-                for (int cb = 0; cb < BN / 32; cb++) {
-                    float v[32];
-                    if (p.splits > 1) {
+                    for (int cb = 0; cb < BN / 32; cb++) {
+                        const int n = tn * BN + cb * 32 + cc;
+                        const EpiCoef coef = load_coef<T>(p, n);
 #pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = row_ok ? __ldcg(part + cb * 32 + j) : 0.f;
-                        // leave the scratch zeroed for the next launch
-                        if (row_ok) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(part + cb * 32 + j) = make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                    } else {
-                        uint32_t r[32];
-                        tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * BN + cb * 32, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-                    }
-                    if (row_ok) {
-                        const int n0 = tn * BN + cb * 32;
-                        const long long base = m * p.Kout + n0;
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int n = n0 + j;
-                            if (n < p.Kout) {
-                                float x = v[j];
-                                if (p.scale) x *= __ldg(p.scale + n);
-                                if (p.shift) x += __ldg(p.shift + n);
-                                if (p.residual) {
-                                    if (sizeof(T) == 4) x += __ldg(reinterpret_cast<const float*>(p.residual) + base + j);
-                                    else x += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[base + j]);
-                                }
-                                if (p.relu) x = fmaxf(x, 0.f);
-                                if (p.relu == 2) x = fminf(x, 6.f);
-                                v[j] = x;
-                            }
-                        }
-                        if (sizeof(T) == 4) {
-                            float* y = reinterpret_cast<float*>(p.y) + base;
-                            if ((p.Kout & 3) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    if (n0 + j < p.Kout)
-                                        *reinterpret_cast<float4*>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++)
-                                    if (n0 + j < p.Kout) y[j] = v[j];
-                            }
-                        } else {
-                            __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + base;
-                            if ((p.Kout & 7) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    if (n0 + j < p.Kout) {
-                                        uint4 o;
-                                        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                                        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                                        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                                        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                                        o.x = *reinterpret_cast<uint32_t*>(&t0);
-                                        o.y = *reinterpret_cast<uint32_t*>(&t1);
-                                        o.z = *reinterpret_cast<uint32_t*>(&t2);
-                                        o.w = *reinterpret_cast<uint32_t*>(&t3);
-                                        *reinterpret_cast<uint4*>(y + j) = o;
-                                    }
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++)
-                                    if (n0 + j < p.Kout) y[j] = __float2bfloat16(v[j]);
+                        for (int i = 0; i < 8; i++) {
+                            const int rr = i * 4 + sub;
+                            const long long m = tile_row0 + rr;
+                            if (m < p.M) {
+                                float4* part = reinterpret_cast<float4*>(p.scratch + ((long long)tile * BM + warp * 32 + rr) * BN + cb * 32 + cc);
+                                const float4 v = __ldcg(part);
+                                *part = make_float4(0.f, 0.f, 0.f, 0.f);   // leave the scratch zeroed for the next launch
+                                store_out<T>(p, coef, v, m, n);
                             }
                         }
                     }
+                    if (tid == 0) p.counters[tile] = 0;
                 }
-                if (p.splits > 1 && tid == 0) p.counters[tile] = 0;   // ready for the next launch
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is rewritten by the next unit
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->tmem_empty[ab]);
         }
+        if (p.debug && blockIdx.x == 0 && tid == 0) p.debug[0] = waited;
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issue
         if (lane == 0) {
@@ -277,12 +360,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             uint32_t it = 0;
             int local = 0;
             bool dead = false;
+            long long waited2 = 0;
             for (int u = blockIdx.x; u < units && !dead; u += gridDim.x, local++) {
                 const int split = u % p.splits;
                 const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
                 const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
                 const int ab = local & 1;
-                if (!mbar_wait(&ctl->tmem_empty[ab], ((local >> 1) & 1) ^ 1, abort_flag)) {
+                if (!timed_wait(&ctl->tmem_empty[ab], ((local >> 1) & 1) ^ 1, abort_flag, waited2)) {
                     if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_EMPTY); }
                     break;
                 }
@@ -290,11 +374,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                 const uint32_t d = tmem_base + ab * BN;
                 for (int kb = kb_begin; kb < kb_end; kb++, it++) {
                     const int s = it % C::STAGES;
-                    if (!mbar_wait(&ctl->full[s], (it / C::STAGES) & 1, abort_flag)) {
+                    // fp32: operands are ready when the splitters are done; bf16: when the copies have landed
+                    if (!timed_wait(C::kSplit ? &ctl->full[s] : &ctl->raw_full[s], (it / C::STAGES) & 1, abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_FULL); }
                         dead = true;
                         break;
                     }
+                    if (!C::kSplit) fence_proxy_async_smem();   // cp.async wrote through the generic proxy
                     tc_fence_after_sync();
                     const uint32_t base = smem_u32(smem + s * C::STAGE_BYTES);
                     if (C::kSplit) {
@@ -322,15 +408,57 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                 }
                 if (!dead) umma_commit(&ctl->tmem_full[ab]);
             }
+            if (p.debug && blockIdx.x == 0) { p.debug[1] = waited; p.debug[2] = waited2; }
+        }
+    } else if (warp < MMA_WARP + 1 + SPLIT_WARPS) {
+        // ------------------------------------------------------------ splitters (fp32 only)
+        // Turn the raw fp32 operand rows the producers copied into shared memory into the
+        // TF32-rounded high parts (in place) and the exact remainders (second buffer).
+        if (C::kSplit) {
+            const int row = (warp - (MMA_WARP + 1)) * 32 + lane;   // 0..127
+            uint32_t it = 0;
+            bool dead = false;
+            for (int u = blockIdx.x; u < units && !dead; u += gridDim.x) {
+                const int split = u % p.splits;
+                const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
+                const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
+                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+                    const int s = it % C::STAGES;
+                    if (!timed_wait(&ctl->raw_full[s], (it / C::STAGES) & 1, abort_flag, waited)) {
+                        if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_FULL); }
+                        dead = true;
+                        break;
+                    }
+                    uint8_t* st = smem + s * C::STAGE_BYTES;
+                    uint8_t* a_hi = st;
+                    uint8_t* a_lo = st + C::A_BYTES;
+                    uint8_t* b_hi = st + 2 * C::A_BYTES;
+                    uint8_t* b_lo = b_hi + C::B_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint32_t off = sw128_offset((uint32_t)row, (uint32_t)j);
+                        split_chunk(a_hi + off, a_lo + off);
+                        if (row < BN) split_chunk(b_hi + off, b_lo + off);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ctl->full[s]);
+                }
+            }
+            if (p.debug && blockIdx.x == 0 && row == 0) p.debug[3] = waited;
         }
     } else {
         // ------------------------------------------------------------ producers
-        const int pw = warp - (MMA_WARP + 1);       // 0..7
-        const int group = pw >> 2;                  // producer group
-        const int row = (pw & 3) * 32 + lane;       // 0..127: A row, and B row when < BN
+        // Asynchronous 16-byte copies (zero-filled outside the image) straight into the swizzled
+        // stage buffers, several stages ahead of the MMA.  Eight consecutive threads copy the
+        // eight 16-byte chunks of one operand row, so a warp instruction reads four full 128-byte
+        // lines; each thread serves rows (t/8), (t/8)+16, ... of the tile with its fixed chunk t%8.
+        const int pt = (warp - (MMA_WARP + 1 + SPLIT_WARPS)) * 32 + lane;   // 0..127
         const T* __restrict__ X = reinterpret_cast<const T*>(p.x);
         const T* __restrict__ Wt = reinterpret_cast<const T*>(p.w);
         const bool vec = (p.C % C::EPC) == 0;
+        const int chunk = pt & 7;
+        const int row0 = pt >> 3;   // 0..15
         uint32_t it = 0;
         bool dead = false;
         for (int u = blockIdx.x; u < units && !dead; u += gridDim.x) {
@@ -338,84 +466,118 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
             const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
-            const long long m = (long long)tm * BM + row;
-            const bool m_ok = m < p.M;
-            int n_img = 0, h_base = 0, w_base = 0;
-            if (m_ok) {
+            if (vec) {
+                long long xbase[8];   // element offset of the image of row i, -1 when the row is past M
+                int hb[8], wb[8];
                 const int pq = p.P * p.Q;
-                n_img = (int)(m / pq);
-                const int rem = (int)(m - (long long)n_img * pq);
-                const int op = rem / p.Q, oq = rem - op * p.Q;
-                h_base = op * p.stride_h - p.pad_h;
-                w_base = oq * p.stride_w - p.pad_w;
-            }
-            const int kout = tn * BN + row;
-            const bool b_ok = row < BN && kout < p.Kout;
-            for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                if ((int)(it % PROD_GROUPS) != group) continue;
-                const int s = it % C::STAGES;
-                const int r = kb / p.kblocks_per_r;
-                const int kk0 = (kb - r * p.kblocks_per_r) * C::BK;
-                const int h = h_base + r * p.dil_h;
-                const bool h_ok = m_ok && h >= 0 && h < p.H;
-                Chunk a[8], b[8];
-                const T* xrow = X + ((long long)n_img * p.H + (h_ok ? h : 0)) * p.W * p.C;
-                const T* wrow = Wt + ((long long)(b_ok ? kout : 0) * p.R + r) * SC;
-                if (vec) {
-                    int ts = kk0 / p.C, tc = kk0 - ts * p.C;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int kk = kk0 + j * C::EPC;
-                        const int w = w_base + ts * p.dil_w;
-                        const bool ok = h_ok && kk < SC && w >= 0 && w < p.W;
-                        ld_chunk(xrow + (long long)(ok ? w : 0) * p.C + tc, ok, a[j]);
-                        ld_chunk(wrow + kk, b_ok && kk < SC, b[j]);
-                        tc += C::EPC;
-                        if (tc >= p.C) { tc -= p.C; ts++; }
+                for (int i = 0; i < 8; i++) {
+                    const long long m = (long long)tm * BM + i * 16 + row0;
+                    xbase[i] = -1;
+                    hb[i] = wb[i] = 0;
+                    if (m < p.M) {
+                        const int n_img = (int)(m / pq);
+                        const int rem = (int)(m - (long long)n_img * pq);
+                        const int op = rem / p.Q, oq = rem - op * p.Q;
+                        xbase[i] = (long long)n_img * p.H * p.W * p.C;
+                        hb[i] = op * p.stride_h - p.pad_h;
+                        wb[i] = oq * p.stride_w - p.pad_w;
                     }
-                } else {
-                    int ts = kk0 / p.C, tc = kk0 - ts * p.C;
+                }
+                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+                    const int s = it % C::STAGES;
+                    const int r = kb / p.kblocks_per_r;
+                    const int kk = (kb - r * p.kblocks_per_r) * C::BK + chunk * C::EPC;
+                    const bool k_ok = kk < SC;
+                    const int ts = kk / p.C, tc = kk - ts * p.C;
+                    if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                        if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
+                        dead = true;
+                        break;
+                    }
+                    uint8_t* st = smem + s * C::STAGE_BYTES;
+                    const uint32_t a_dst = smem_u32(st);
+                    const uint32_t b_dst = smem_u32(st + (C::kSplit ? 2 : 1) * C::A_BYTES);
 #pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int row = i * 16 + row0;
+                        const int h = hb[i] + r * p.dil_h;
+                        const int w = wb[i] + ts * p.dil_w;
+                        const bool ok = k_ok && xbase[i] >= 0 && h >= 0 && h < p.H && w >= 0 && w < p.W;
+                        const T* src = ok ? X + xbase[i] + ((long long)h * p.W + w) * p.C + tc : X;
+                        cp_async_16(a_dst + sw128_offset((uint32_t)row, (uint32_t)chunk), src, ok);
+                    }
+#pragma unroll
+                    for (int i = 0; i < BN / 16; i++) {
+                        const int row = i * 16 + row0;
+                        const int kout = tn * BN + row;
+                        const bool ok = k_ok && kout < p.Kout;
+                        const T* src = ok ? Wt + ((long long)kout * p.R + r) * SC + kk : Wt;
+                        cp_async_16(b_dst + sw128_offset((uint32_t)row, (uint32_t)chunk), src, ok);
+                    }
+                    cp_async_arrive_noinc(&ctl->raw_full[s]);
+                }
+            } else {
+                // Channel counts that are not a multiple of the 16-byte chunk (the 3-channel stem):
+                // scalar gather, one thread per operand row.
+                const int row = pt;
+                const long long m = (long long)tm * BM + row;
+                const bool m_ok = m < p.M;
+                int n_img = 0, h_base = 0, w_base = 0;
+                if (m_ok) {
+                    const int pq = p.P * p.Q;
+                    n_img = (int)(m / pq);
+                    const int rem = (int)(m - (long long)n_img * pq);
+                    const int op = rem / p.Q, oq = rem - op * p.Q;
+                    h_base = op * p.stride_h - p.pad_h;
+                    w_base = oq * p.stride_w - p.pad_w;
+                }
+                const int kout = tn * BN + row;
+                const bool b_ok = row < BN && kout < p.Kout;
+                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+                    const int s = it % C::STAGES;
+                    const int r = kb / p.kblocks_per_r;
+                    const int kk0 = (kb - r * p.kblocks_per_r) * C::BK;
+                    const int h = h_base + r * p.dil_h;
+                    const bool h_ok = m_ok && h >= 0 && h < p.H;
+                    const T* xrow = X + ((long long)n_img * p.H + (h_ok ? h : 0)) * p.W * p.C;
+                    const T* wrow = Wt + ((long long)(b_ok ? kout : 0) * p.R + r) * SC;
+                    if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                        if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
+                        dead = true;
+                        break;
+                    }
+                    uint8_t* st = smem + s * C::STAGE_BYTES;
+                    uint8_t* a_dst = st;
+                    uint8_t* b_dst = st + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                    int ts = kk0 / p.C, tc = kk0 - ts * p.C;
+#pragma unroll 1
                     for (int j = 0; j < 8; j++) {
-                        Chunk av, bv;
-                        ld_chunk((const T*)nullptr, false, av);
-                        ld_chunk((const T*)nullptr, false, bv);
+                        const uint32_t off = sw128_offset((uint32_t)row, (uint32_t)j);
 #pragma unroll
                         for (int e = 0; e < C::EPC; e++) {
                             const int kk = kk0 + j * C::EPC + e;
                             const int w = w_base + ts * p.dil_w;
-                            if (h_ok && kk < SC && w >= 0 && w < p.W) set_elem(av, e, xrow[(long long)w * p.C + tc]);
-                            if (b_ok && kk < SC) set_elem(bv, e, wrow[kk]);
+                            T av = T(0.f), bv = T(0.f);
+                            if (h_ok && kk < SC && w >= 0 && w < p.W) av = xrow[(long long)w * p.C + tc];
+                            if (b_ok && kk < SC) bv = wrow[kk];
+                            reinterpret_cast<T*>(a_dst + off)[e] = av;
+                            if (row < BN) reinterpret_cast<T*>(b_dst + off)[e] = bv;
                             tc++;
                             if (tc >= p.C) { tc = 0; ts++; }
                         }
-                        a[j] = av;
-                        b[j] = bv;
                     }
+                    if (!C::kSplit) fence_proxy_async_smem();
+                    mbar_arrive(&ctl->raw_full[s]);
                 }
-                if (!mbar_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag)) {
-                    if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
-                    dead = true;
-                    break;
-                }
-                uint8_t* st = smem + s * C::STAGE_BYTES;
-                uint8_t* a_hi = st;
-                uint8_t* a_lo = st + C::A_BYTES;
-                uint8_t* b_hi = st + (C::kSplit ? 2 : 1) * C::A_BYTES;
-                uint8_t* b_lo = b_hi + C::B_BYTES;
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const uint32_t off = sw128_offset((uint32_t)row, (uint32_t)j);
-                    st_chunk(a_hi, a_lo, off, a[j]);
-                    if (row < BN) st_chunk(b_hi, b_lo, off, b[j]);
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&ctl->full[s]);
             }
         }
     }
 
+    if (p.debug && blockIdx.x == 0) {
+        if (warp == MMA_WARP + 1 + SPLIT_WARPS && lane == 0) p.debug[4] = waited;   // producer warp 0
+        if (tid == 0) p.debug[5] = clock64() - t_start;
+    }
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();

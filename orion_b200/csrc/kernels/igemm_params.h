@@ -15,6 +15,7 @@ typedef struct IgemmParams {
     float* scratch;         /* split-K partial sums, zero on entry, zero on exit */
     int* counters;          /* split-K arrival counters, one per tile, zero on entry and exit */
     int* status;            /* optional device word that receives an error code */
+    long long* debug;       /* optional: 8 cycle counters written by CTA 0 (role wait times) */
     int relu;               /* 0 none, 1 ReLU, 2 ReLU6 */
     int dtype;              /* 0 = fp32 (3xTF32), 1 = bf16 */
     int Nb, H, W, C, Kout, R, S, P, Q;

@@ -24,6 +24,8 @@ std::mutex g_mu;
 std::unordered_map<uint64_t, Scratch> g_scratch;        // key: device << 48 ^ stream
 std::unordered_map<int, int*> g_status;                 // per device
 
+long long* g_debug = nullptr;   // optional role-wait counters, see ob200_set_debug_buffer
+
 int* status_word(int dev) {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_status.find(dev);
@@ -109,6 +111,7 @@ extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, cons
     if (splits < 1 || splits > p.num_kblocks) return -1;
     p.splits = splits;
     p.status = status_word(dev);
+    p.debug = g_debug;
     if (splits > 1) {
         if (!scratch || !counters) return -1;
         p.scratch = scratch;
@@ -165,6 +168,11 @@ extern "C" int ob200_read_status(void) {
     if (v) cudaMemset(p, 0, sizeof v);
     return v;
 }
+
+// Tuning aid: device buffer of 8 long longs that receives, from CTA 0 of every implicit-GEMM launch,
+// the cycles each warp role spent waiting: [0] epilogue, [1] MMA on operands, [2] MMA on a free
+// accumulator, [3] splitter, [4] producer, [5] whole kernel.  NULL switches it off.
+extern "C" void ob200_set_debug_buffer(long long* dev_buf) { g_debug = dev_buf; }
 
 extern "C" int ob200_sm_count(void) {
     int dev = 0, n = 0;
