@@ -14,7 +14,7 @@
 //   warp  4     allocates TMEM, one lane issues tcgen05.mma and tcgen05.commit
 //   warps 5-8   splitters (fp32 only): split the raw operand rows in shared memory into
 //               TF32 high parts (in place) and exact remainders (second buffer)
-//   warps 9-12  producers, one thread per operand row: cp.async 16-byte copies of one
+//   warps 9-16  producers: cp.async 16-byte copies of one
 //               128-byte row slice of the im2col matrix (zero-filled at the image
 //               border) and of the filter, straight into the 128-byte-swizzled
 //               K-major stage buffers, several stages ahead of the MMA
@@ -44,8 +44,8 @@ constexpr int BM = 128;
 constexpr int EPI_WARPS = 4;
 constexpr int MMA_WARP = 4;
 constexpr int SPLIT_WARPS = 4;
-constexpr int PROD_WARPS = 4;
-constexpr int NTHREADS = (EPI_WARPS + 1 + SPLIT_WARPS + PROD_WARPS) * 32;   // 416
+constexpr int PROD_WARPS = 8;
+constexpr int NTHREADS = (EPI_WARPS + 1 + SPLIT_WARPS + PROD_WARPS) * 32;   // 544
 
 template <typename T, int BN>
 struct Cfg {
@@ -216,8 +216,7 @@ __device__ __forceinline__ void store_out(const IgemmParams& p, const EpiCoef& c
 
 // mbar_wait that also adds the cycles spent waiting to `acc` (role-level wait breakdown for tuning).
 __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long& acc) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
+    const long long t0 = clock64();   // the first try_wait may already suspend the thread for a while
     const bool ok = mbar_wait(bar, parity, abort_flag);
     acc += clock64() - t0;
     return ok;
@@ -415,7 +414,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
         // Turn the raw fp32 operand rows the producers copied into shared memory into the
         // TF32-rounded high parts (in place) and the exact remainders (second buffer).
         if (C::kSplit) {
-            const int row = (warp - (MMA_WARP + 1)) * 32 + lane;   // 0..127
+            const int st_id = (warp - (MMA_WARP + 1)) * 32 + lane;   // 0..127
+            const int row = st_id;                                    // operand row
             uint32_t it = 0;
             bool dead = false;
             for (int u = blockIdx.x; u < units && !dead; u += gridDim.x) {
@@ -445,7 +445,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     if (lane == 0) mbar_arrive(&ctl->full[s]);
                 }
             }
-            if (p.debug && blockIdx.x == 0 && row == 0) p.debug[3] = waited;
+            if (p.debug && blockIdx.x == 0 && st_id == 0) p.debug[3] = waited;
         }
     } else {
         // ------------------------------------------------------------ producers
@@ -453,12 +453,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
         // stage buffers, several stages ahead of the MMA.  Eight consecutive threads copy the
         // eight 16-byte chunks of one operand row, so a warp instruction reads four full 128-byte
         // lines; each thread serves rows (t/8), (t/8)+16, ... of the tile with its fixed chunk t%8.
-        const int pt = (warp - (MMA_WARP + 1 + SPLIT_WARPS)) * 32 + lane;   // 0..127
+        const int pt = (warp - (MMA_WARP + 1 + SPLIT_WARPS)) * 32 + lane;   // 0..255
         const T* __restrict__ X = reinterpret_cast<const T*>(p.x);
         const T* __restrict__ Wt = reinterpret_cast<const T*>(p.w);
         const bool vec = (p.C % C::EPC) == 0;
+        constexpr int RPT = BM / 32;            // A rows per thread
         const int chunk = pt & 7;
-        const int row0 = pt >> 3;   // 0..15
+        const int row0 = pt >> 3;               // 0..31; this thread serves rows row0 + 32*i
+        // (row & 7) == (row0 & 7) for all of them, so the swizzled chunk position is a per-thread constant
+        const uint32_t sw_off = (uint32_t)row0 * 128u + (uint32_t)((chunk ^ (row0 & 7)) << 4);
         uint32_t it = 0;
         bool dead = false;
         for (int u = blockIdx.x; u < units && !dead; u += gridDim.x) {
@@ -467,22 +470,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
             const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
             if (vec) {
-                long long xbase[8];   // element offset of the image of row i, -1 when the row is past M
-                int hb[8], wb[8];
+                const T* xpix[RPT];   // address of the (possibly out-of-image) top-left tap pixel of row i; null past M
+                int hb[RPT], wb[RPT];
                 const int pq = p.P * p.Q;
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const long long m = (long long)tm * BM + i * 16 + row0;
-                    xbase[i] = -1;
+                for (int i = 0; i < RPT; i++) {
+                    const long long m = (long long)tm * BM + i * 32 + row0;
+                    xpix[i] = nullptr;
                     hb[i] = wb[i] = 0;
                     if (m < p.M) {
                         const int n_img = (int)(m / pq);
                         const int rem = (int)(m - (long long)n_img * pq);
                         const int op = rem / p.Q, oq = rem - op * p.Q;
-                        xbase[i] = (long long)n_img * p.H * p.W * p.C;
                         hb[i] = op * p.stride_h - p.pad_h;
                         wb[i] = oq * p.stride_w - p.pad_w;
+                        xpix[i] = X + (((long long)n_img * p.H + hb[i]) * p.W + wb[i]) * p.C;
                     }
+                }
+                const T* wrow[BN / 32];
+#pragma unroll
+                for (int i = 0; i < BN / 32; i++) {
+                    const int kout = tn * BN + i * 32 + row0;
+                    wrow[i] = kout < p.Kout ? Wt + (long long)kout * p.R * SC : nullptr;
                 }
                 for (int kb = kb_begin; kb < kb_end; kb++, it++) {
                     const int s = it % C::STAGES;
@@ -490,39 +499,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     const int kk = (kb - r * p.kblocks_per_r) * C::BK + chunk * C::EPC;
                     const bool k_ok = kk < SC;
                     const int ts = kk / p.C, tc = kk - ts * p.C;
+                    const int dh = r * p.dil_h, dw = ts * p.dil_w;
+                    const long long xoff = ((long long)dh * p.W + dw) * p.C + tc;   // same for every row of the tile
+                    const long long woff = (long long)r * SC + kk;
                     if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                         dead = true;
                         break;
                     }
-                    uint8_t* st = smem + s * C::STAGE_BYTES;
-                    const uint32_t a_dst = smem_u32(st);
-                    const uint32_t b_dst = smem_u32(st + (C::kSplit ? 2 : 1) * C::A_BYTES);
+                    const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES) + sw_off;
+                    const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int row = i * 16 + row0;
-                        const int h = hb[i] + r * p.dil_h;
-                        const int w = wb[i] + ts * p.dil_w;
-                        const bool ok = k_ok && xbase[i] >= 0 && h >= 0 && h < p.H && w >= 0 && w < p.W;
-                        const T* src = ok ? X + xbase[i] + ((long long)h * p.W + w) * p.C + tc : X;
-                        cp_async_16(a_dst + sw128_offset((uint32_t)row, (uint32_t)chunk), src, ok);
+                    for (int i = 0; i < RPT; i++) {
+                        const int h = hb[i] + dh, w = wb[i] + dw;
+                        const bool ok = k_ok && xpix[i] != nullptr && (unsigned)h < (unsigned)p.H && (unsigned)w < (unsigned)p.W;
+                        cp_async_16(a_dst + i * 4096, ok ? (const void*)(xpix[i] + xoff) : (const void*)X, ok);
                     }
 #pragma unroll
-                    for (int i = 0; i < BN / 16; i++) {
-                        const int row = i * 16 + row0;
-                        const int kout = tn * BN + row;
-                        const bool ok = k_ok && kout < p.Kout;
-                        const T* src = ok ? Wt + ((long long)kout * p.R + r) * SC + kk : Wt;
-                        cp_async_16(b_dst + sw128_offset((uint32_t)row, (uint32_t)chunk), src, ok);
+                    for (int i = 0; i < BN / 32; i++) {
+                        const bool ok = k_ok && wrow[i] != nullptr;
+                        cp_async_16(b_dst + i * 4096, ok ? (const void*)(wrow[i] + woff) : (const void*)Wt, ok);
                     }
                     cp_async_arrive_noinc(&ctl->raw_full[s]);
                 }
             } else {
                 // Channel counts that are not a multiple of the 16-byte chunk (the 3-channel stem):
                 // scalar gather, one thread per operand row.
-                const int row = pt;
+                const int row = pt & 127;
+                const bool worker = pt < 128;   // one thread per operand row; the other producer warps only arrive
                 const long long m = (long long)tm * BM + row;
-                const bool m_ok = m < p.M;
+                const bool m_ok = worker && m < p.M;
                 int n_img = 0, h_base = 0, w_base = 0;
                 if (m_ok) {
                     const int pq = p.P * p.Q;
@@ -533,7 +539,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     w_base = oq * p.stride_w - p.pad_w;
                 }
                 const int kout = tn * BN + row;
-                const bool b_ok = row < BN && kout < p.Kout;
+                const bool b_ok = worker && row < BN && kout < p.Kout;
                 for (int kb = kb_begin; kb < kb_end; kb++, it++) {
                     const int s = it % C::STAGES;
                     const int r = kb / p.kblocks_per_r;
@@ -552,7 +558,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     uint8_t* b_dst = st + (C::kSplit ? 2 : 1) * C::A_BYTES;
                     int ts = kk0 / p.C, tc = kk0 - ts * p.C;
 #pragma unroll 1
-                    for (int j = 0; j < 8; j++) {
+                    for (int j = 0; j < (worker ? 8 : 0); j++) {
                         const uint32_t off = sw128_offset((uint32_t)row, (uint32_t)j);
 #pragma unroll
                         for (int e = 0; e < C::EPC; e++) {
