@@ -51,6 +51,32 @@ int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y, const floa
 /* The choice ob200_conv2d_fprop makes for a problem size. */
 int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out);
 
+/* Data gradient of the convolution, dx [Nb,H,W,C] from dy [Nb,P,Q,Kout] and the re-laid-out filter
+ * wt [C,R,S,Kout] (ob200_filter_transpose).  Takes the place of cudnnConvolutionBackwardData
+ * (reference src/scheduler/utils_sched.cpp:439-464, trapped at src/cuda_capture/intercept_cudnn.cpp:482-558). */
+int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
+                       int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
+/* w [K, R*S, C] -> wt [C, R*S, K]; elem_bytes 4 or 2.  No counterpart in the reference (cuDNN re-lays filters internally). */
+int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream);
+
+/* Batch-norm training forward over [rows, C] float32 (C % 4 == 0): batch statistics, normalisation,
+ * running-statistics update; save_mean / save_invstd feed the backward pass.  `sums` is a scratch of
+ * 2*C doubles that must be zero on entry.  Takes the place of cudnnBatchNormalizationForwardTrainingEx
+ * (reference src/scheduler/utils_sched.cpp:297-339). */
+int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
+                               float* running_var, float* save_mean, float* save_invstd, double* sums, float eps, float momentum,
+                               long long rows, int C, int num_ctas, void* stream);
+/* Batch-norm backward: dx, dgamma, dbeta (the last two may be NULL); `sums` as above.  Takes the place of
+ * cudnnBatchNormalizationBackwardEx (reference src/scheduler/utils_sched.cpp:398-438). */
+int ob200_bn_backward_f32(const float* dy, const float* x, float* dx, const float* gamma, const float* save_mean,
+                          const float* save_invstd, float* dgamma, float* dbeta, double* sums, long long rows, int C, int num_ctas,
+                          void* stream);
+/* dx = dy where y > 0, else 0 (threshold_backward kernels behind the reference's cudaLaunchKernel trap). */
+int ob200_relu_backward_f32(const float* dy, const float* y, float* dx, long long n, int num_ctas, void* stream);
+/* torch.optim.SGD step with momentum on one parameter tensor (the foreach kernels behind the same trap). */
+int ob200_sgd_momentum_f32(float* p, const float* g, float* m, long long n, float lr, float mu, float wd, int nesterov,
+                           int first_step, int num_ctas, void* stream);
+
 /* y[M,N] = x[M,K] . w[N,K]^T + bias, optional ReLU.  Takes the place of cublasSgemm_v2
  * (reference src/scheduler/utils_sched.cpp:490-501, trapped at src/cuda_capture/intercept_cublas.cpp:5-56). */
 int ob200_linear(const void* x, const void* w, void* y, const float* bias, int relu, int dtype, int M, int N, int K,

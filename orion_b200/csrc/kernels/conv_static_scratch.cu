@@ -94,6 +94,7 @@ extern "C" int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y,
     p.tiles_n = (Kout + bn - 1) / bn;
     if (splits < 1 || splits > p.num_kblocks) return -1;
     p.splits = splits;
+    igemm_set_fprop(&p);
 
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const unsigned long long need = (unsigned long long)tiles * 128ull * (unsigned long long)bn;

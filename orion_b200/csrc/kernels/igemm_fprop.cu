@@ -1,5 +1,6 @@
-// Implicit-GEMM forward convolution and linear layer on the 5th-generation tensor
-// cores (tcgen05.mma, accumulators in TMEM), for NHWC activations and KRSC weights.
+// Implicit-GEMM convolution (forward and data gradient) and linear layer on the
+// 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM), for NHWC
+// activations and KRSC weights.
 //
 //   Y[m, k] = epilogue( sum_{r,s,c} X[n, p*sh - ph + r*dh, q*sw - pw + s*dw, c] * Wt[k, r, s, c] )
 //   m = (n*P + p)*Q + q;   GEMM view: M = N*P*Q rows, N = K_out columns, K = R*S*C.
@@ -470,9 +471,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
             const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
             if (vec) {
-                const T* xpix[RPT];   // address of the (possibly out-of-image) top-left tap pixel of row i; null past M
+                // Unit-divisor gathers (forward convolution, stride-1 data gradient): xpix is the address of
+                // the (possibly out-of-image) tap-0 pixel of row i, and a tap adds a row-independent offset.
+                // Strided data gradients keep the image base and compute the pixel per tap.  Null past M.
+                const bool unit = p.div_h == 1 && p.div_w == 1;
+                const T* xpix[RPT];
                 int hb[RPT], wb[RPT];
-                const int pq = p.P * p.Q;
+                const int pq = p.OH * p.OW;
 #pragma unroll
                 for (int i = 0; i < RPT; i++) {
                     const long long m = (long long)tm * BM + i * 32 + row0;
@@ -481,10 +486,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     if (m < p.M) {
                         const int n_img = (int)(m / pq);
                         const int rem = (int)(m - (long long)n_img * pq);
-                        const int op = rem / p.Q, oq = rem - op * p.Q;
-                        hb[i] = op * p.stride_h - p.pad_h;
-                        wb[i] = oq * p.stride_w - p.pad_w;
-                        xpix[i] = X + (((long long)n_img * p.H + hb[i]) * p.W + wb[i]) * p.C;
+                        const int op = rem / p.OW, oq = rem - op * p.OW;
+                        hb[i] = op * p.bmul_h + p.badd_h;
+                        wb[i] = oq * p.bmul_w + p.badd_w;
+                        xpix[i] = X + (long long)n_img * p.IH * p.IW * p.C + (unit ? ((long long)hb[i] * p.IW + wb[i]) * p.C : 0);
                     }
                 }
                 const T* wrow[BN / 32];
@@ -499,8 +504,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     const int kk = (kb - r * p.kblocks_per_r) * C::BK + chunk * C::EPC;
                     const bool k_ok = kk < SC;
                     const int ts = kk / p.C, tc = kk - ts * p.C;
-                    const int dh = r * p.dil_h, dw = ts * p.dil_w;
-                    const long long xoff = ((long long)dh * p.W + dw) * p.C + tc;   // same for every row of the tile
+                    const int dh = r * p.step_h, dw = ts * p.step_w;
+                    const long long xoff = ((long long)dh * p.IW + dw) * p.C + tc;   // same for every row of the tile
                     const long long woff = (long long)r * SC + kk;
                     if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
@@ -509,11 +514,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     }
                     const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES) + sw_off;
                     const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                    if (unit) {
 #pragma unroll
-                    for (int i = 0; i < RPT; i++) {
-                        const int h = hb[i] + dh, w = wb[i] + dw;
-                        const bool ok = k_ok && xpix[i] != nullptr && (unsigned)h < (unsigned)p.H && (unsigned)w < (unsigned)p.W;
-                        cp_async_16(a_dst + i * 4096, ok ? (const void*)(xpix[i] + xoff) : (const void*)X, ok);
+                        for (int i = 0; i < RPT; i++) {
+                            const int h = hb[i] + dh, w = wb[i] + dw;
+                            const bool ok = k_ok && xpix[i] != nullptr && (unsigned)h < (unsigned)p.IH && (unsigned)w < (unsigned)p.IW;
+                            cp_async_16(a_dst + i * 4096, ok ? (const void*)(xpix[i] + xoff) : (const void*)X, ok);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < RPT; i++) {
+                            const int hn = hb[i] + dh, wn = wb[i] + dw;
+                            const int h = hn / p.div_h, w = wn / p.div_w;
+                            const bool ok = k_ok && xpix[i] != nullptr && hn >= 0 && wn >= 0 && h * p.div_h == hn && w * p.div_w == wn &&
+                                            h < p.IH && w < p.IW;
+                            cp_async_16(a_dst + i * 4096, ok ? (const void*)(xpix[i] + ((long long)h * p.IW + w) * p.C + tc) : (const void*)X, ok);
+                        }
                     }
 #pragma unroll
                     for (int i = 0; i < BN / 32; i++) {
@@ -531,12 +547,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                 const bool m_ok = worker && m < p.M;
                 int n_img = 0, h_base = 0, w_base = 0;
                 if (m_ok) {
-                    const int pq = p.P * p.Q;
+                    const int pq = p.OH * p.OW;
                     n_img = (int)(m / pq);
                     const int rem = (int)(m - (long long)n_img * pq);
-                    const int op = rem / p.Q, oq = rem - op * p.Q;
-                    h_base = op * p.stride_h - p.pad_h;
-                    w_base = oq * p.stride_w - p.pad_w;
+                    const int op = rem / p.OW, oq = rem - op * p.OW;
+                    h_base = op * p.bmul_h + p.badd_h;
+                    w_base = oq * p.bmul_w + p.badd_w;
                 }
                 const int kout = tn * BN + row;
                 const bool b_ok = worker && row < BN && kout < p.Kout;
@@ -544,9 +560,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     const int s = it % C::STAGES;
                     const int r = kb / p.kblocks_per_r;
                     const int kk0 = (kb - r * p.kblocks_per_r) * C::BK;
-                    const int h = h_base + r * p.dil_h;
-                    const bool h_ok = m_ok && h >= 0 && h < p.H;
-                    const T* xrow = X + ((long long)n_img * p.H + (h_ok ? h : 0)) * p.W * p.C;
+                    const int hn = h_base + r * p.step_h;
+                    const int h = hn / p.div_h;
+                    const bool h_ok = m_ok && hn >= 0 && h * p.div_h == hn && h < p.IH;
+                    const T* xrow = X + ((long long)n_img * p.IH + (h_ok ? h : 0)) * p.IW * p.C;
                     const T* wrow = Wt + ((long long)(b_ok ? kout : 0) * p.R + r) * SC;
                     if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
@@ -563,9 +580,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
 #pragma unroll
                         for (int e = 0; e < C::EPC; e++) {
                             const int kk = kk0 + j * C::EPC + e;
-                            const int w = w_base + ts * p.dil_w;
+                            const int wn = w_base + ts * p.step_w;
+                            const int w = wn / p.div_w;
                             T av = T(0.f), bv = T(0.f);
-                            if (h_ok && kk < SC && w >= 0 && w < p.W) av = xrow[(long long)w * p.C + tc];
+                            if (h_ok && kk < SC && wn >= 0 && w * p.div_w == wn && w < p.IW) av = xrow[(long long)w * p.C + tc];
                             if (b_ok && kk < SC) bv = wrow[kk];
                             reinterpret_cast<T*>(a_dst + off)[e] = av;
                             if (row < BN) reinterpret_cast<T*>(b_dst + off)[e] = bv;

@@ -25,7 +25,31 @@ typedef struct IgemmParams {
     int num_kblocks;        /* R * kblocks_per_r */
     int tiles_m, tiles_n;
     int splits;             /* split-K factor, <= num_kblocks */
+    /* Gather geometry (filled by igemm_set_fprop / igemm_set_dgrad).  GEMM row m = (n*OH + oh)*OW + ow;
+     * for tap (r, s) the source pixel of tensor x [Nb, IH, IW, C] is
+     *   ih = (oh*bmul_h + badd_h + r*step_h) / div_h   (valid only if the division is exact), same for w. */
+    int OH, OW, IH, IW;
+    int bmul_h, bmul_w, badd_h, badd_w, step_h, step_w, div_h, div_w;
 } IgemmParams;
+
+/* Forward convolution: rows are output pixels (P x Q), the source is the input image. */
+static inline void igemm_set_fprop(IgemmParams* p) {
+    p->OH = p->P; p->OW = p->Q; p->IH = p->H; p->IW = p->W;
+    p->bmul_h = p->stride_h; p->bmul_w = p->stride_w;
+    p->badd_h = -p->pad_h; p->badd_w = -p->pad_w;
+    p->step_h = p->dil_h; p->step_w = p->dil_w;
+    p->div_h = 1; p->div_w = 1;
+}
+
+/* Data gradient: rows are input pixels (H x W), the source is dy [Nb, P, Q, C] (C = the
+ * convolution's output channels), and tap (r, s) reads dy at ((h + pad - r*dil) / stride). */
+static inline void igemm_set_dgrad(IgemmParams* p, int conv_H, int conv_W, int conv_P, int conv_Q) {
+    p->OH = conv_H; p->OW = conv_W; p->IH = conv_P; p->IW = conv_Q;
+    p->bmul_h = 1; p->bmul_w = 1;
+    p->badd_h = p->pad_h; p->badd_w = p->pad_w;
+    p->step_h = -p->dil_h; p->step_w = -p->dil_w;
+    p->div_h = p->stride_h; p->div_w = p->stride_w;
+}
 
 int ob200_igemm_launch(const IgemmParams* params, int bn, int num_ctas, void* stream);
 

@@ -110,6 +110,7 @@ extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, cons
     p.tiles_n = (Kout + bn - 1) / bn;
     if (splits < 1 || splits > p.num_kblocks) return -1;
     p.splits = splits;
+    igemm_set_fprop(&p);
     p.status = status_word(dev);
     p.debug = g_debug;
     if (splits > 1) {
@@ -147,6 +148,62 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
     }
     return ob200_conv2d_fprop_ex(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h,
                                  pad_w, dil_h, dil_w, bn, splits, scratch, counters, num_ctas, stream);
+}
+
+// Data gradient of the convolution: dx[n,h,w,c] = sum_{r,s,k} dy[n,(h+pad-r*dil)/stride,(w+pad-s*dil)/stride,k] * w[k,r,s,c]
+// over the taps whose division is exact.  wt is the filter re-laid out as [C, R, S, Kout]
+// (ob200_filter_transpose).  Same kernel as the forward pass, with the gather geometry of
+// igemm_set_dgrad: GEMM rows are input pixels, the reduction runs over (r, s, k).
+extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R,
+                                  int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas,
+                                  void* stream) {
+    if (dtype != 0 && dtype != 1) return -1;
+    if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || Kout <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
+        dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0)
+        return -1;
+    if (Nb == 0) return 0;
+    const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / stride_h + 1;
+    const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / stride_w + 1;
+    if (P <= 0 || Q <= 0) return -1;
+    if (((uintptr_t)dy | (uintptr_t)wt | (uintptr_t)dx) % 16) return -2;
+    const long long M = (long long)Nb * H * W;
+    if (M > 0x7fffffffLL) return -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int bn = 128, splits = 1;
+    ob200_plan_conv(dtype, M, C, R, S, Kout, num_ctas, &bn, &splits);
+    IgemmParams p;
+    memset(&p, 0, sizeof p);
+    p.x = dy; p.w = wt; p.y = dx;
+    p.dtype = dtype;
+    p.Nb = Nb; p.H = H; p.W = W; p.P = P; p.Q = Q; p.R = R; p.S = S;
+    p.C = Kout;      // reduction channels: those of dy
+    p.Kout = C;      // GEMM columns: the channels of dx
+    p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
+    p.M = (int)M;
+    const int bk = dtype == 0 ? 32 : 64;
+    p.kblocks_per_r = (S * Kout + bk - 1) / bk;
+    p.num_kblocks = R * p.kblocks_per_r;
+    p.tiles_m = (int)((M + 127) / 128);
+    p.tiles_n = (C + bn - 1) / bn;
+    if (splits > p.num_kblocks) splits = p.num_kblocks;
+    p.status = status_word(dev);
+    p.debug = g_debug;
+    if (splits > 1) {
+        const long long tiles = (long long)p.tiles_m * p.tiles_n;
+        Scratch* sc = scratch_for(dev, (cudaStream_t)stream);
+        if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
+            splits = 1;
+        } else {
+            p.scratch = sc->partial;
+            p.counters = sc->counters;
+        }
+    }
+    p.splits = splits;
+    igemm_set_dgrad(&p, H, W, P, Q);
+    const long long units = (long long)p.tiles_m * p.tiles_n * splits;
+    const int grid = units < num_ctas ? (int)units : num_ctas;
+    return ob200_igemm_launch(&p, bn, grid, stream);
 }
 
 // y[M, N] = x[M, K] . w[N, K]^T (+ bias) (+ ReLU): a 1x1 convolution over M "pixels".

@@ -19,6 +19,7 @@
 // per-thread setting: each client thread launches persistent kernels sized to the
 // SM budget its scheduler stream was given).
 #include <ATen/ATen.h>
+#include <ATen/NativeFunctions.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
@@ -37,6 +38,15 @@ int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, int W, int C
                            void* stream);
 int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream);
 int ob200_sm_count(void);
+int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
+                       int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
+int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream);
+int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
+                               float* running_var, float* save_mean, float* save_invstd, double* sums, float eps, float momentum,
+                               long long rows, int C, int num_ctas, void* stream);
+int ob200_bn_backward_f32(const float* dy, const float* x, float* dx, const float* gamma, const float* save_mean,
+                          const float* save_invstd, float* dgamma, float* dbeta, double* sums, long long rows, int C, int num_ctas,
+                          void* stream);
 }
 
 namespace {
@@ -115,6 +125,23 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_over
     const bool ok = g_overrides.load(std::memory_order_relaxed) && !training && input.scalar_type() == at::kFloat && is_nhwc(input) &&
                     running_mean.has_value() && running_mean->defined() && running_var.has_value() && running_var->defined() &&
                     weight.defined() && weight.scalar_type() == at::kFloat && input.numel() > 0;
+    const bool train_ok = g_overrides.load(std::memory_order_relaxed) && training && input.scalar_type() == at::kFloat &&
+                          is_nhwc(input) && input.size(1) % 4 == 0 && weight.defined() && weight.scalar_type() == at::kFloat &&
+                          input.numel() > 0;
+    if (train_ok) {
+        // cudnnBatchNormalizationForwardTrainingEx's role: batch statistics, normalise, update running statistics.
+        const int64_t C = input.size(1);
+        at::Tensor y = at::empty_like(input, at::MemoryFormat::ChannelsLast);
+        at::Tensor save_mean = at::empty({C}, input.options()), save_invstd = at::empty({C}, input.options());
+        at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
+        float* rm = (running_mean.has_value() && running_mean->defined()) ? running_mean->data_ptr<float>() : nullptr;
+        float* rv = (running_var.has_value() && running_var->defined()) ? running_var->data_ptr<float>() : nullptr;
+        check(ob200_bn_train_forward_f32(input.data_ptr<float>(), y.data_ptr<float>(), weight.data_ptr<float>(), fptr(bias), rm, rv,
+                                         save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(), sums.data_ptr<double>(), (float)eps,
+                                         (float)momentum, input.numel() / C, (int)C, quota(), cur_stream()),
+              "ob200_bn_train_forward_f32");
+        return std::make_tuple(y, save_mean, save_invstd, at::empty({0}, input.options().dtype(at::kByte)));
+    }
     if (!ok) {
         g_fallbacks.fetch_add(1, std::memory_order_relaxed);
         auto r = at::native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps);
@@ -137,8 +164,60 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_backward_overrid
     const c10::optional<at::Tensor>& save_var, double eps, const at::Tensor& reserve) {
     (void)reserve;
     const bool train = save_mean.has_value() && save_mean->defined() && save_mean->numel() > 0;
+    if (g_overrides.load(std::memory_order_relaxed) && train && input.scalar_type() == at::kFloat && is_nhwc(input) &&
+        is_nhwc(grad_output) && input.size(1) % 4 == 0 && weight.defined() && save_var.has_value() && save_var->defined() &&
+        input.numel() > 0) {
+        const int64_t C = input.size(1);
+        at::Tensor dx = at::empty_like(input, at::MemoryFormat::ChannelsLast);
+        at::Tensor dgamma = at::empty({C}, input.options()), dbeta = at::empty({C}, input.options());
+        at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
+        check(ob200_bn_backward_f32(grad_output.data_ptr<float>(), input.data_ptr<float>(), dx.data_ptr<float>(),
+                                    weight.data_ptr<float>(), save_mean->data_ptr<float>(), save_var->data_ptr<float>(),
+                                    dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), sums.data_ptr<double>(), input.numel() / C, (int)C,
+                                    quota(), cur_stream()),
+              "ob200_bn_backward_f32");
+        return std::make_tuple(dx, dgamma, dbeta);
+    }
+    g_fallbacks.fetch_add(1, std::memory_order_relaxed);
     return at::native_batch_norm_backward(grad_output, input, weight, running_mean, running_var, save_mean, save_var, train, eps,
                                           {true, true, true});
+}
+
+// cudnnConvolutionBackwardData's role goes to the orion data-gradient kernel; the filter and bias
+// gradients stay with the stock implementation (reference src/scheduler/utils_sched.cpp:439-489).
+std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_override(
+    const at::Tensor& grad_output, const at::Tensor& input, const at::Tensor& weight, at::OptionalIntArrayRef bias_sizes,
+    at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, at::IntArrayRef output_padding,
+    int64_t groups, std::array<bool, 3> output_mask) {
+    const bool ok = g_overrides.load(std::memory_order_relaxed) && output_mask[0] && input.dim() == 4 && weight.dim() == 4 &&
+                    !transposed && groups == 1 && dtype_code(input) >= 0 && input.scalar_type() == weight.scalar_type() &&
+                    grad_output.scalar_type() == input.scalar_type() && stride.size() == 2 && padding.size() == 2 &&
+                    dilation.size() == 2 && input.numel() > 0 && is_nhwc(weight) && weight.size(0) % (dtype_code(input) == 0 ? 4 : 8) == 0;
+    if (!ok) {
+        g_fallbacks.fetch_add(1, std::memory_order_relaxed);
+        return at::native::convolution_backward(grad_output, input, weight, bias_sizes, stride, padding, dilation, transposed,
+                                                output_padding, groups, output_mask);
+    }
+    at::Tensor dy = is_nhwc(grad_output) ? grad_output : grad_output.contiguous(at::MemoryFormat::ChannelsLast);
+    const int64_t Nb = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3);
+    const int64_t K = weight.size(0), R = weight.size(2), S = weight.size(3);
+    at::Tensor wt = at::empty({C, K, R, S}, weight.options().memory_format(at::MemoryFormat::ChannelsLast));   // physical [C,R,S,K]
+    check(ob200_filter_transpose(weight.data_ptr(), wt.data_ptr(), (int)K, (int)(R * S), (int)C, (int)weight.element_size(),
+                                 cur_stream()),
+          "ob200_filter_transpose");
+    at::Tensor dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::ChannelsLast));
+    check(ob200_conv2d_dgrad(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), dtype_code(input), (int)Nb, (int)H, (int)W, (int)C, (int)K,
+                             (int)R, (int)S, (int)stride[0], (int)stride[1], (int)padding[0], (int)padding[1], (int)dilation[0],
+                             (int)dilation[1], quota(), cur_stream()),
+          "ob200_conv2d_dgrad");
+    at::Tensor dw, db;
+    if (output_mask[1] || output_mask[2]) {
+        auto rest = at::native::convolution_backward(dy, input, weight, bias_sizes, stride, padding, dilation, transposed,
+                                                     output_padding, groups, {false, output_mask[1], output_mask[2]});
+        dw = std::get<1>(rest);
+        db = std::get<2>(rest);
+    }
+    return std::make_tuple(dx, dw, db);
 }
 
 // ------------------------------------------------------------------ orion:: ops
@@ -230,4 +309,5 @@ TORCH_LIBRARY_IMPL(aten, CUDA, m) {
     m.impl("convolution", &convolution_override);
     m.impl("cudnn_batch_norm", &cudnn_batch_norm_override);
     m.impl("cudnn_batch_norm_backward", &cudnn_batch_norm_backward_override);
+    m.impl("convolution_backward", &convolution_backward_override);
 }

@@ -30,6 +30,15 @@ def lib():
         L.ob200_binary_f32.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_int, c_void_p]
         L.ob200_maxpool_nhwc_f32.argtypes = [c_void_p] * 2 + [c_int] * 7 + [c_int, c_void_p]
         L.ob200_avgpool_nhwc_f32.argtypes = [c_void_p] * 2 + [c_int] * 3 + [c_int, c_void_p]
+        L.ob200_conv2d_dgrad.argtypes = [c_void_p] * 3 + [c_int] * 14 + [c_int, c_void_p]
+        L.ob200_filter_transpose.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        L.ob200_bn_train_forward_f32.argtypes = [c_void_p] * 9 + [c_float, c_float, c_ll, c_int, c_int, c_void_p]
+        L.ob200_bn_backward_f32.argtypes = [c_void_p] * 9 + [c_ll, c_int, c_int, c_void_p]
+        L.ob200_relu_backward_f32.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_void_p]
+        L.ob200_sgd_momentum_f32.argtypes = [c_void_p] * 3 + [c_ll, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]
+        for name in ("ob200_conv2d_dgrad", "ob200_filter_transpose", "ob200_bn_train_forward_f32", "ob200_bn_backward_f32",
+                     "ob200_relu_backward_f32", "ob200_sgd_momentum_f32"):
+            getattr(L, name).restype = c_int
         for name in ("ob200_conv2d_fprop", "ob200_conv2d_fprop_ex", "ob200_linear", "ob200_plan_conv", "ob200_bn_inference_f32",
                      "ob200_binary_f32", "ob200_maxpool_nhwc_f32", "ob200_avgpool_nhwc_f32", "ob200_read_status",
                      "ob200_sm_count"):
@@ -142,3 +151,65 @@ def avgpool_nhwc(x, num_ctas=None):
     _check(lib().ob200_avgpool_nhwc_f32(_ptr(x), _ptr(y), Nb, H * W, C, num_ctas or sm_count(), _stream()),
            "ob200_avgpool_nhwc_f32")
     return y
+
+
+def filter_transpose(w):
+    """w: [K, R, S, C] -> [C, R, S, K] (the layout ob200_conv2d_dgrad reads)."""
+    K, R, S, C = w.shape
+    wt = torch.empty((C, R, S, K), device=w.device, dtype=w.dtype)
+    _check(lib().ob200_filter_transpose(_ptr(w), _ptr(wt), K, R * S, C, w.element_size(), _stream()), "ob200_filter_transpose")
+    return wt
+
+
+def conv2d_dgrad_nhwc(dy, w, input_hw, stride=(1, 1), padding=(0, 0), dilation=(1, 1), num_ctas=None):
+    """dy: [N, P, Q, K], w: [K, R, S, C] -> dx [N, H, W, C]."""
+    assert dy.is_contiguous() and w.is_contiguous() and dy.dtype == w.dtype
+    Nb, P, Q, K = dy.shape
+    K2, R, S, C = w.shape
+    assert K == K2
+    H, W = input_hw
+    wt = filter_transpose(w)
+    dx = torch.empty((Nb, H, W, C), device=dy.device, dtype=dy.dtype)
+    _check(lib().ob200_conv2d_dgrad(_ptr(dy), _ptr(wt), _ptr(dx), _dtype_code(dy), Nb, H, W, C, K, R, S, stride[0], stride[1],
+                                    padding[0], padding[1], dilation[0], dilation[1], num_ctas or sm_count(), _stream()),
+           "ob200_conv2d_dgrad")
+    return dx
+
+
+def bn_train_forward(x, gamma, beta, running_mean, running_var, eps, momentum, num_ctas=None):
+    """x: [..., C] float32 -> (y, save_mean, save_invstd); running stats are updated in place."""
+    assert x.is_contiguous() and x.dtype == torch.float32
+    C = x.shape[-1]
+    rows = x.numel() // C
+    y = torch.empty_like(x)
+    save_mean = torch.empty(C, device=x.device)
+    save_invstd = torch.empty(C, device=x.device)
+    sums = torch.zeros(2 * C, device=x.device, dtype=torch.float64)
+    _check(lib().ob200_bn_train_forward_f32(_ptr(x), _ptr(y), _ptr(gamma), _ptr(beta), _ptr(running_mean), _ptr(running_var),
+                                            _ptr(save_mean), _ptr(save_invstd), _ptr(sums), float(eps), float(momentum), rows, C,
+                                            num_ctas or sm_count(), _stream()), "ob200_bn_train_forward_f32")
+    return y, save_mean, save_invstd
+
+
+def bn_backward(dy, x, gamma, save_mean, save_invstd, num_ctas=None):
+    assert dy.is_contiguous() and x.is_contiguous()
+    C = x.shape[-1]
+    rows = x.numel() // C
+    dx = torch.empty_like(x)
+    dgamma, dbeta = torch.empty(C, device=x.device), torch.empty(C, device=x.device)
+    sums = torch.zeros(2 * C, device=x.device, dtype=torch.float64)
+    _check(lib().ob200_bn_backward_f32(_ptr(dy), _ptr(x), _ptr(dx), _ptr(gamma), _ptr(save_mean), _ptr(save_invstd), _ptr(dgamma),
+                                       _ptr(dbeta), _ptr(sums), rows, C, num_ctas or sm_count(), _stream()), "ob200_bn_backward_f32")
+    return dx, dgamma, dbeta
+
+
+def relu_backward(dy, y, num_ctas=None):
+    dx = torch.empty_like(dy)
+    _check(lib().ob200_relu_backward_f32(_ptr(dy), _ptr(y), _ptr(dx), dy.numel(), num_ctas or sm_count(), _stream()),
+           "ob200_relu_backward_f32")
+    return dx
+
+
+def sgd_momentum_(p, g, m, lr, mu, wd=0.0, nesterov=False, first_step=False, num_ctas=None):
+    _check(lib().ob200_sgd_momentum_f32(_ptr(p), _ptr(g), _ptr(m), p.numel(), lr, mu, wd, int(nesterov), int(first_step),
+                                        num_ctas or sm_count(), _stream()), "ob200_sgd_momentum_f32")

@@ -1,0 +1,96 @@
+"""Parity of the training-side kernels (data-gradient convolution, batch-norm training forward
+and backward, ReLU backward, SGD update) against float64 CPU references, through the C ABI.
+Tolerance: float32 relative 1e-4 of the largest expected magnitude (benchmark specification)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import numeric_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def K(built):
+    from orion_b200 import kernels
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; the kernels have no CPU fallback")
+    torch.manual_seed(4321)
+    return kernels
+
+
+def _dgrad_ref(dy, w, hw, stride, pad, dil):
+    """cudnnConvolutionBackwardData by definition: the gradient of conv2d with respect to its input."""
+    dyd = dy.detach().double().cpu().permute(0, 3, 1, 2)
+    wd = w.detach().double().cpu().permute(0, 3, 1, 2)
+    n, c = dy.shape[0], w.shape[3]
+    dx = torch.nn.grad.conv2d_input((n, c, hw[0], hw[1]), wd, dyd, stride=stride, padding=pad, dilation=dil)
+    return dx.permute(0, 2, 3, 1).contiguous()
+
+
+@pytest.mark.parametrize("shape", [
+    (4, 56, 56, 64, 64, 3, 1, 1), (4, 56, 56, 64, 256, 1, 1, 0), (4, 56, 56, 128, 128, 3, 2, 1), (4, 56, 56, 256, 512, 1, 2, 0),
+    (4, 14, 14, 256, 256, 3, 1, 1), (4, 7, 7, 512, 512, 3, 1, 1), (2, 11, 9, 24, 40, 3, 2, 1), (2, 12, 12, 16, 20, 5, 1, 2),
+    (1, 224, 224, 3, 64, 7, 2, 3), (2, 16, 16, 32, 32, 3, 1, 2),
+])
+def test_conv_dgrad_fp32(K, shape):
+    Nb, H, W, C, Ko, R, stride, pad = shape
+    dil = 2 if shape == (2, 16, 16, 32, 32, 3, 1, 2) else 1
+    P = (H + 2 * pad - dil * (R - 1) - 1) // stride + 1
+    Q = (W + 2 * pad - dil * (R - 1) - 1) // stride + 1
+    dy = torch.randn(Nb, P, Q, Ko, device="cuda")
+    w = torch.randn(Ko, R, R, C, device="cuda") / (Ko * R * R) ** 0.5
+    dx = K.conv2d_dgrad_nhwc(dy, w, (H, W), (stride, stride), (pad, pad), (dil, dil))
+    assert K.read_status() == 0
+    assert O.rel_err(dx, _dgrad_ref(dy, w, (H, W), stride, pad, dil)) < TOL
+
+
+def test_conv_dgrad_bf16_and_filter_transpose(K):
+    w = torch.randn(40, 3, 3, 24, device="cuda")
+    assert torch.equal(K.filter_transpose(w), w.permute(3, 1, 2, 0).contiguous())
+    dy = torch.randn(2, 14, 14, 64, device="cuda", dtype=torch.bfloat16)
+    wb = (torch.randn(64, 3, 3, 64, device="cuda") / 24.0).to(torch.bfloat16)
+    dx = K.conv2d_dgrad_nhwc(dy, wb, (14, 14), (1, 1), (1, 1))
+    assert O.rel_err(dx, _dgrad_ref(dy, wb, (14, 14), 1, 1, 1)) < 2e-2
+
+
+@pytest.mark.parametrize("shape", [(32, 56, 56, 64), (4, 7, 7, 2048), (3, 5, 5, 24), (2, 3, 2, 8)])
+def test_bn_training_forward_and_backward(K, shape):
+    C = shape[-1]
+    x = (torch.randn(*shape, device="cuda") * 2.0 + 0.7)
+    g, b = torch.rand(C, device="cuda") + 0.5, torch.randn(C, device="cuda")
+    rm, rv = torch.randn(C, device="cuda"), torch.rand(C, device="cuda") + 0.5
+    rm_ref, rv_ref = rm.double().cpu().clone(), rv.double().cpu().clone()
+    xd = x.double().cpu().reshape(-1, C).requires_grad_(True)
+    want = F.batch_norm(xd, rm_ref, rv_ref, g.double().cpu(), b.double().cpu(), True, 0.1, 1e-5)
+    y, mean, invstd = K.bn_train_forward(x, g, b, rm, rv, 1e-5, 0.1)
+    assert O.rel_err(y.reshape(-1, C), want.detach()) < 1e-5
+    assert O.rel_err(mean, xd.detach().mean(0)) < 1e-5
+    assert O.rel_err(invstd, 1.0 / torch.sqrt(xd.detach().var(0, unbiased=False) + 1e-5)) < 1e-5
+    assert O.rel_err(rm, rm_ref) < 1e-5 and O.rel_err(rv, rv_ref) < 1e-5          # running statistics updated in place
+    dy = torch.randn(*shape, device="cuda")
+    gd, bd = g.double().cpu().requires_grad_(True), b.double().cpu().requires_grad_(True)
+    out = F.batch_norm(xd, None, None, gd, bd, True, 0.1, 1e-5)
+    out.backward(dy.double().cpu().reshape(-1, C))
+    dx, dgamma, dbeta = K.bn_backward(dy, x, g, mean, invstd)
+    assert O.rel_err(dx.reshape(-1, C), xd.grad) < 1e-4
+    assert O.rel_err(dgamma, gd.grad) < 1e-4 and O.rel_err(dbeta, bd.grad) < 1e-4
+
+
+def test_relu_backward_and_sgd(K):
+    y = torch.randn(4, 28, 28, 130, device="cuda")
+    dy = torch.randn_like(y)
+    assert torch.equal(K.relu_backward(dy, y), torch.where(y > 0, dy, torch.zeros_like(dy)))
+    odd = torch.randn(1001, device="cuda")
+    assert torch.equal(K.relu_backward(odd, odd), torch.where(odd > 0, odd, torch.zeros_like(odd)))
+    p = torch.randn(100003, device="cuda")
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.SGD([ref_p], lr=0.1, momentum=0.9, weight_decay=1e-4)
+    m = torch.zeros_like(p)
+    for step in range(3):
+        gstep = torch.randn_like(p)
+        ref_p.grad = gstep.clone()
+        opt.step()
+        K.sgd_momentum_(p, gstep, m, 0.1, 0.9, 1e-4, first_step=(step == 0))
+    assert (p - ref_p.detach()).abs().max().item() < 1e-5
