@@ -109,6 +109,8 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
         quota = int(os.environ.get("ORION_BE_SM_QUOTA", "0")) if train else 0
         if quota > 0:
             torch_ops.set_sm_quota(quota)
+        if train and os.environ.get("ORION_TRAIN_TF32", "0") == "1":
+            torch.ops.orion.set_tf32(1)   # training convolutions in one TF32 pass, like stock cuDNN's default
         import contextlib
         model = models.__dict__[model_name](num_classes=1000)
         model = model.to(local_rank).to(memory_format=torch.channels_last)

@@ -5,7 +5,9 @@
  * the caller) and returns 0 on success, a cudaError_t value (> 0) if the launch
  * failed, or a negative number for invalid arguments.  Layouts: activations NHWC,
  * filters KRSC (a torch tensor in channels_last memory format).  dtype: 0 = float32
- * (computed as 3xTF32 with fp32 accumulation), 1 = bfloat16 (fp32 accumulation).
+ * (computed as 3xTF32 with fp32 accumulation, ~1e-6 relative error), 1 = bfloat16 (fp32
+ * accumulation), 2 = float32 data multiplied in a single TF32 pass (10-bit mantissa products:
+ * what cuDNN does by default on tensor cores; about three times less tensor work).
  * There is no CPU fallback.
  */
 #ifndef ORION_KERNELS_H

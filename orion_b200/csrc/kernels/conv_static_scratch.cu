@@ -68,7 +68,7 @@ extern "C" int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y,
                                           const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R,
                                           int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn,
                                           int splits, int num_ctas, void* stream) {
-    if (dtype != 0 && dtype != 1) return -1;
+    if (dtype < 0 || dtype > 2) return -1;
     if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || Kout <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
         dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0 || (bn != 64 && bn != 128))
         return -1;
@@ -79,7 +79,7 @@ extern "C" int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y,
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)residual) % 16) return -2;
     const long long M = (long long)Nb * P * Q;
     if (M > 0x7fffffffLL) return -1;
-    const int bk = dtype == 0 ? 32 : 64;
+    const int bk = dtype == 1 ? 64 : 32;
 
     IgemmParams p;
     memset(&p, 0, sizeof p);

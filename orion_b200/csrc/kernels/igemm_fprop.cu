@@ -19,7 +19,7 @@
 //               128-byte row slice of the im2col matrix (zero-filled at the image
 //               border) and of the filter, straight into the 128-byte-swizzled
 //               K-major stage buffers, several stages ahead of the MMA
-// fp32 inputs run as 3xTF32: each value is split into a TF32-rounded high part and
+// fp32 inputs run as 3xTF32 (dtype 0; dtype 2 = one TF32 pass, no splitters): each value is split into a TF32-rounded high part and
 // the exact remainder, and lo*hi + hi*lo + hi*hi accumulate in fp32, which keeps
 // the result within ~1e-6 relative of an fp32 reference.  bf16 inputs use one
 // kind::f16 MMA per k-step.
@@ -48,9 +48,9 @@ constexpr int SPLIT_WARPS = 4;
 constexpr int PROD_WARPS = 8;
 constexpr int NTHREADS = (EPI_WARPS + 1 + SPLIT_WARPS + PROD_WARPS) * 32;   // 544
 
-template <typename T, int BN>
+template <typename T, int BN, int PASSES>
 struct Cfg {
-    static constexpr bool kSplit = sizeof(T) == 4;            // 3xTF32
+    static constexpr bool kSplit = sizeof(T) == 4 && PASSES == 3;   // 3xTF32; PASSES == 1 is plain TF32
     static constexpr int BK = 128 / sizeof(T);                // elements per 128-byte row
     static constexpr int EPC = 16 / sizeof(T);                // elements per 16-byte chunk
     static constexpr int A_BYTES = BM * 128;
@@ -223,9 +223,9 @@ __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volat
     return ok;
 }
 
-template <typename T, int BN>
+template <typename T, int BN, int PASSES>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmParams p) {
-    using C = Cfg<T, BN>;
+    using C = Cfg<T, BN, PASSES>;
     using Chunk = typename ChunkOf<T>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issue
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(C::kSplit ? 2 : 1, BM, BN);
+            constexpr uint32_t idesc = umma_idesc(sizeof(T) == 4 ? 2 : 1, BM, BN);
             uint32_t it = 0;
             int local = 0;
             bool dead = false;
@@ -401,7 +401,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
 #pragma unroll
                         for (int ks = 0; ks < 4; ks++) {
                             const uint64_t o = (uint64_t)(ks * 2);
-                            umma_f16(d, a + o, b + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
+                            if (sizeof(T) == 4) umma_tf32(d, a + o, b + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
+                            else umma_f16(d, a + o, b + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&ctl->empty[s]);   // frees the stage once these MMAs have read it
@@ -612,18 +613,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
     }
 }
 
-template <typename T, int BN>
+template <typename T, int BN, int PASSES>
 static cudaError_t launch_cfg(const IgemmParams& p, int num_ctas, cudaStream_t stream) {
-    using C = Cfg<T, BN>;
+    using C = Cfg<T, BN, PASSES>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_fprop_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_fprop_kernel<T, BN, PASSES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    igemm_fprop_kernel<T, BN><<<num_ctas, NTHREADS, C::SMEM_BYTES, stream>>>(p);
+    igemm_fprop_kernel<T, BN, PASSES><<<num_ctas, NTHREADS, C::SMEM_BYTES, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -634,9 +635,11 @@ extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_cta
     IgemmParams p = *params;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (p.dtype == 0) {
-        return (int)(bn == 64 ? launch_cfg<float, 64>(p, num_ctas, s) : launch_cfg<float, 128>(p, num_ctas, s));
+        return (int)(bn == 64 ? launch_cfg<float, 64, 3>(p, num_ctas, s) : launch_cfg<float, 128, 3>(p, num_ctas, s));
     } else if (p.dtype == 1) {
-        return (int)(bn == 64 ? launch_cfg<__nv_bfloat16, 64>(p, num_ctas, s) : launch_cfg<__nv_bfloat16, 128>(p, num_ctas, s));
+        return (int)(bn == 64 ? launch_cfg<__nv_bfloat16, 64, 1>(p, num_ctas, s) : launch_cfg<__nv_bfloat16, 128, 1>(p, num_ctas, s));
+    } else if (p.dtype == 2) {   // float32 data, one TF32 pass (the precision cuDNN uses by default on tensor cores)
+        return (int)(bn == 64 ? launch_cfg<float, 64, 1>(p, num_ctas, s) : launch_cfg<float, 128, 1>(p, num_ctas, s));
     }
     return -1;
 }

@@ -17,7 +17,7 @@ typedef struct IgemmParams {
     int* status;            /* optional device word that receives an error code */
     long long* debug;       /* optional: 8 cycle counters written by CTA 0 (role wait times) */
     int relu;               /* 0 none, 1 ReLU, 2 ReLU6 */
-    int dtype;              /* 0 = fp32 (3xTF32), 1 = bf16 */
+    int dtype;              /* 0 = fp32 (3xTF32), 1 = bf16, 2 = fp32 data with a single TF32 pass */
     int Nb, H, W, C, Kout, R, S, P, Q;
     int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
     int M;                  /* Nb*P*Q */

@@ -57,7 +57,7 @@ Scratch* scratch_for(int dev, cudaStream_t s) {
 }  // namespace
 
 extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out) {
-    const int bk = dtype == 0 ? 32 : 64;
+    const int bk = dtype == 1 ? 64 : 32;
     const int kblocks = R * ((S * C + bk - 1) / bk);
     const int tiles_m = (int)((M + 127) / 128);
     int bn = 128;
@@ -81,7 +81,7 @@ extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, cons
                                      const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R,
                                      int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn,
                                      int splits, float* scratch, int* counters, int num_ctas, void* stream) {
-    if (dtype != 0 && dtype != 1) return -1;
+    if (dtype < 0 || dtype > 2) return -1;
     if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || Kout <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
         dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0)
         return -1;
@@ -89,7 +89,7 @@ extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, cons
     const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / stride_h + 1;
     const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / stride_w + 1;
     if (P <= 0 || Q <= 0) return -1;
-    const int elem = dtype == 0 ? 4 : 2;
+    const int elem = dtype == 1 ? 2 : 4;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)residual) % 16) return -2;   // 128-bit accesses
     int dev = 0;
     cudaGetDevice(&dev);
@@ -157,7 +157,7 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
 extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R,
                                   int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas,
                                   void* stream) {
-    if (dtype != 0 && dtype != 1) return -1;
+    if (dtype < 0 || dtype > 2) return -1;
     if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || Kout <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
         dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0)
         return -1;
@@ -181,7 +181,7 @@ extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int 
     p.Kout = C;      // GEMM columns: the channels of dx
     p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
     p.M = (int)M;
-    const int bk = dtype == 0 ? 32 : 64;
+    const int bk = dtype == 1 ? 64 : 32;
     p.kblocks_per_r = (S * Kout + bk - 1) / bk;
     p.num_kblocks = R * p.kblocks_per_r;
     p.tiles_m = (int)((M + 127) / 128);

@@ -69,10 +69,19 @@ void check(int rc, const char* what) {
     g_own_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
+std::atomic<int> g_tf32{0};   // 1: float32 convolutions run as one TF32 pass (cuDNN's default precision)
+
 int dtype_code(const at::Tensor& t) {
     if (t.scalar_type() == at::kFloat) return 0;
     if (t.scalar_type() == at::kBFloat16) return 1;
     return -1;
+}
+
+// Kernel dtype for the dispatcher overrides (the path training clients take): float32 may be
+// switched to a single TF32 pass; prepared inference models always keep full float32 accuracy.
+int override_dtype_code(const at::Tensor& t) {
+    int c = dtype_code(t);
+    return (c == 0 && g_tf32.load(std::memory_order_relaxed)) ? 2 : c;
 }
 
 bool is_nhwc(const at::Tensor& t) { return t.dim() == 4 && t.is_contiguous(at::MemoryFormat::ChannelsLast); }
@@ -83,7 +92,7 @@ const float* fptr(const c10::optional<at::Tensor>& t) {
 
 // x, w: logical NCHW / KCRS tensors in channels-last memory (physical NHWC / KRSC).
 at::Tensor conv_core(const at::Tensor& x, const at::Tensor& w, const float* scale, const float* shift, const at::Tensor* residual,
-                     int act, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation) {
+                     int act, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int dtype) {
     const int64_t Nb = x.size(0), C = x.size(1), H = x.size(2), W = x.size(3);
     const int64_t K = w.size(0), R = w.size(2), S = w.size(3);
     const int64_t P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) / stride[0] + 1;
@@ -91,7 +100,7 @@ at::Tensor conv_core(const at::Tensor& x, const at::Tensor& w, const float* scal
     at::Tensor y = at::empty({Nb, K, P, Q}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
     if (residual) TORCH_CHECK(residual->sizes() == y.sizes() && is_nhwc(*residual), "orion: residual must match the output (NHWC)");
     check(ob200_conv2d_fprop(x.data_ptr(), w.data_ptr(), y.data_ptr(), scale, shift, residual ? residual->data_ptr() : nullptr,
-                             act, dtype_code(x), (int)Nb, (int)H, (int)W, (int)C, (int)K, (int)R, (int)S, (int)stride[0],
+                             act, dtype, (int)Nb, (int)H, (int)W, (int)C, (int)K, (int)R, (int)S, (int)stride[0],
                              (int)stride[1], (int)padding[0], (int)padding[1], (int)dilation[0], (int)dilation[1], quota(),
                              cur_stream()),
           "ob200_conv2d_fprop");
@@ -115,7 +124,7 @@ at::Tensor convolution_override(const at::Tensor& input, const at::Tensor& weigh
     }
     at::Tensor x = is_nhwc(input) ? input : input.contiguous(at::MemoryFormat::ChannelsLast);
     at::Tensor w = is_nhwc(weight) ? weight : weight.contiguous(at::MemoryFormat::ChannelsLast);
-    return conv_core(x, w, nullptr, fptr(bias), nullptr, 0, stride, padding, dilation);
+    return conv_core(x, w, nullptr, fptr(bias), nullptr, 0, stride, padding, dilation, override_dtype_code(x));
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_override(
@@ -192,7 +201,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_override(
     const bool ok = g_overrides.load(std::memory_order_relaxed) && output_mask[0] && input.dim() == 4 && weight.dim() == 4 &&
                     !transposed && groups == 1 && dtype_code(input) >= 0 && input.scalar_type() == weight.scalar_type() &&
                     grad_output.scalar_type() == input.scalar_type() && stride.size() == 2 && padding.size() == 2 &&
-                    dilation.size() == 2 && input.numel() > 0 && is_nhwc(weight) && weight.size(0) % (dtype_code(input) == 0 ? 4 : 8) == 0;
+                    dilation.size() == 2 && input.numel() > 0 && is_nhwc(weight) && weight.size(0) % (input.scalar_type() == at::kFloat ? 4 : 8) == 0;
     if (!ok) {
         g_fallbacks.fetch_add(1, std::memory_order_relaxed);
         return at::native::convolution_backward(grad_output, input, weight, bias_sizes, stride, padding, dilation, transposed,
@@ -206,7 +215,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_override(
                                  cur_stream()),
           "ob200_filter_transpose");
     at::Tensor dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::ChannelsLast));
-    check(ob200_conv2d_dgrad(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), dtype_code(input), (int)Nb, (int)H, (int)W, (int)C, (int)K,
+    check(ob200_conv2d_dgrad(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), override_dtype_code(input), (int)Nb, (int)H, (int)W, (int)C, (int)K,
                              (int)R, (int)S, (int)stride[0], (int)stride[1], (int)padding[0], (int)padding[1], (int)dilation[0],
                              (int)dilation[1], quota(), cur_stream()),
           "ob200_conv2d_dgrad");
@@ -229,7 +238,7 @@ at::Tensor conv_bn_act(const at::Tensor& x, const at::Tensor& w, const c10::opti
     TORCH_CHECK(is_nhwc(w), "orion::conv_bn_act: weight must be channels-last");
     at::Tensor xin = is_nhwc(x) ? x : x.contiguous(at::MemoryFormat::ChannelsLast);
     const at::Tensor* res = (residual.has_value() && residual->defined()) ? &*residual : nullptr;
-    return conv_core(xin, w, fptr(scale), fptr(shift), res, (int)act, stride, padding, dilation);
+    return conv_core(xin, w, fptr(scale), fptr(shift), res, (int)act, stride, padding, dilation, dtype_code(xin));
 }
 
 at::Tensor linear_op(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias, bool relu) {
@@ -280,6 +289,7 @@ int64_t set_sm_quota(int64_t n) {
     return old;
 }
 int64_t set_overrides(int64_t on) { return g_overrides.exchange((int)on); }
+int64_t set_tf32(int64_t on) { return g_tf32.exchange((int)on); }
 int64_t own_launches() { return g_own_launches.load(); }
 int64_t fallbacks() { return g_fallbacks.load(); }
 
@@ -293,6 +303,7 @@ TORCH_LIBRARY(orion, m) {
     m.def("add_act(Tensor a, Tensor b, bool relu) -> Tensor");
     m.def("set_sm_quota(int n) -> int", &set_sm_quota);
     m.def("set_overrides(int on) -> int", &set_overrides);
+    m.def("set_tf32(int on) -> int", &set_tf32);
     m.def("own_launches() -> int", &own_launches);
     m.def("fallbacks() -> int", &fallbacks);
 }

@@ -33,7 +33,8 @@ def replay(layers, batch, iters, warm, dtype="float32", flush_mb=160):
     import torch
     from orion_b200 import kernels as K
     dev = torch.device("cuda", torch.cuda.current_device())
-    tdtype = getattr(torch, dtype)
+    tf32 = dtype == "tf32"
+    tdtype = torch.float32 if tf32 else getattr(torch, dtype)
     flops, work = 0.0, []
     for (c, k, r, s, p, h) in layers:
         x = torch.randn(batch, h, h, c, device=dev).to(tdtype)
@@ -50,7 +51,7 @@ def replay(layers, batch, iters, warm, dtype="float32", flush_mb=160):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for (x, w, s, p) in work:
-            K.conv2d_nhwc(x, w, s, p)
+            K.conv2d_nhwc(x, w, s, p, tf32=tf32)
         e1.record(stream)
         e1.synchronize()
         if it >= warm:
@@ -72,7 +73,7 @@ def main():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warm", type=int, default=3)
-    ap.add_argument("--dtype", default="float32")
+    ap.add_argument("--dtype", default="float32", help="float32 (3xTF32), tf32 (float32 data, one TF32 pass) or bfloat16")
     ap.add_argument("--no-flush", action="store_true")
     a = ap.parse_args()
     if a.case:

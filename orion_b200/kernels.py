@@ -78,7 +78,7 @@ def read_status():
 
 
 def conv2d_nhwc(x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, shift=None, residual=None, relu=False,
-                num_ctas=None, bn=None, splits=None, out=None):
+                num_ctas=None, bn=None, splits=None, out=None, tf32=False):
     """x: [N, H, W, C] contiguous, w: [K, R, S, C] contiguous -> [N, P, Q, K]."""
     assert x.is_cuda and x.is_contiguous() and w.is_contiguous() and x.dtype == w.dtype
     Nb, H, W, C = x.shape
@@ -88,7 +88,8 @@ def conv2d_nhwc(x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None
     Q = (W + 2 * padding[1] - dilation[1] * (S - 1) - 1) // stride[1] + 1
     y = out if out is not None else torch.empty((Nb, P, Q, K), device=x.device, dtype=x.dtype)
     n = num_ctas or sm_count()
-    args = [_ptr(x), _ptr(w), _ptr(y), _ptr(scale), _ptr(shift), _ptr(residual), int(relu), _dtype_code(x), Nb, H, W, C, K, R, S,
+    code = 2 if (tf32 and x.dtype == torch.float32) else _dtype_code(x)
+    args = [_ptr(x), _ptr(w), _ptr(y), _ptr(scale), _ptr(shift), _ptr(residual), int(relu), code, Nb, H, W, C, K, R, S,
             stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1]]
     if bn is None and splits is None:
         _check(lib().ob200_conv2d_fprop(*args, n, _stream()), "ob200_conv2d_fprop")

@@ -146,3 +146,16 @@ def test_elementwise_and_pooling(K):
     assert torch.equal(K.maxpool_nhwc(x, 3, 2, 1).double().cpu(), O.maxpool_nhwc(x, 3, 2, 1))
     z = torch.randn(4, 7, 7, 2048, device="cuda")
     assert O.rel_err(K.avgpool_nhwc(z), O.avgpool_nhwc(z)) < 1e-6
+
+
+@pytest.mark.parametrize("shape", [(4, 28, 28, 128, 128, 3, 1, 1), (4, 56, 56, 64, 256, 1, 1, 0)])
+def test_conv_single_pass_tf32_mode(K, shape):
+    """dtype 2: float32 data, products in one TF32 pass (10-bit mantissa).  Expected error ~1e-3, far
+    above the fp32 tolerance — which is why it is opt-in — and far below a wrong result."""
+    Nb, H, W, C, Ko, R, stride, pad = shape
+    x = torch.randn(Nb, H, W, C, device="cuda")
+    w = torch.randn(Ko, R, R, C, device="cuda") / (C * R * R) ** 0.5
+    y = K.conv2d_nhwc(x, w, (stride, stride), (pad, pad), tf32=True)
+    assert K.read_status() == 0
+    err = O.rel_err(y, O.conv2d_nhwc(x, w, (stride, stride), (pad, pad)))
+    assert 1e-5 < err < 5e-3
