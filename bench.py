@@ -108,6 +108,10 @@ def cpu_baseline(sample_hp=12, sample_be=2):
     import torch
     from torchvision import models
     torch.manual_seed(42)
+    try:   # use every core this process may run on (torchrun exports OMP_NUM_THREADS=1)
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     threads = torch.get_num_threads()
     hp = models.resnet50(num_classes=1000).eval()
     x = torch.randn(4, 3, 224, 224)

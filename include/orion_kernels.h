@@ -84,6 +84,12 @@ int ob200_sgd_momentum_f32(float* p, const float* g, float* m, long long n, floa
 int ob200_linear(const void* x, const void* w, void* y, const float* bias, int relu, int dtype, int M, int N, int K,
                  int num_ctas, void* stream);
 
+/* `batch` independent GEMMs of one shape, operands stride_* elements apart (strides multiples of 16 bytes).
+ * Takes the place of cublasSgemmStridedBatched (reference src/scheduler/utils_sched.cpp:502-513, trapped at
+ * src/cuda_capture/intercept_cublas.cpp:114-170): attention scores Q.K^T and, with V pre-transposed, P.V. */
+int ob200_linear_batched(const void* x, const void* w, void* y, int dtype, int batch, int M, int N, int K, long long stride_x,
+                         long long stride_w, long long stride_y, int num_ctas, void* stream);
+
 /* Batch-norm inference over the innermost (channel) dimension.  Takes the place of
  * cudnnBatchNormalizationForwardInference (reference src/scheduler/utils_sched.cpp:340-353). */
 int ob200_bn_inference_f32(const float* x, float* y, const float* gamma, const float* beta, const float* mean, const float* var,
@@ -99,6 +105,18 @@ int ob200_binary_f32(const float* a, const float* b, float* y, long long n_elems
 int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, int W, int C, int k, int stride, int pad, int num_ctas,
                            void* stream);
 int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream);
+
+/* Row kernels of the transformer clients; dtype 0 = float32, 1 = bfloat16 (float32 math), D a multiple of
+ * 4 / 8 elements.  They take the place of the at::native kernels that reach the reference through its
+ * cudaLaunchKernel trap (reference src/cuda_capture/intercept_temp.cpp:418-458): vectorized_layer_norm_kernel,
+ * softmax_warp_forward, the bias + GELU elementwise kernels, and the optimizer's elementwise update kernels. */
+int ob200_layernorm(const void* x, void* y, const float* gamma, const float* beta, float* mean_out, float* rstd_out,
+                    long long rows, int D, float eps, int dtype, int num_ctas, void* stream);
+int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, int dtype, int num_ctas, void* stream);
+int ob200_bias_gelu(const void* x, void* y, const float* bias, long long rows, int D, int dtype, int num_ctas, void* stream);
+/* torch.optim.AdamW step number `step` (>= 1) on one float32 tensor. */
+int ob200_adamw_f32(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, int step, int num_ctas, void* stream);
 
 /* Device status word of the current device (synchronises the device): 0, or the code of
  * the bounded wait a kernel gave up on.  Clears the word.  No counterpart in the reference. */

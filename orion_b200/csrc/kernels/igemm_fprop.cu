@@ -158,9 +158,9 @@ __device__ __forceinline__ EpiCoef load_coef(const IgemmParams& p, int n) {
 
 // Epilogue of four consecutive channels of output row m: affine, residual, activation, store.
 template <typename T>
-__device__ __forceinline__ void store_out(const IgemmParams& p, const EpiCoef& c, float4 v, long long m, int n) {
+__device__ __forceinline__ void store_out(const IgemmParams& p, const EpiCoef& c, float4 v, long long m, int n, long long y_off) {
     if (n >= p.Kout) return;
-    const long long base = m * p.Kout + n;
+    const long long base = y_off + m * p.Kout + n;
     float x[4] = {v.x * c.scale.x + c.shift.x, v.y * c.scale.y + c.shift.y, v.z * c.scale.z + c.shift.z, v.w * c.scale.w + c.shift.w};
     const bool full = (n + 3 < p.Kout) && ((p.Kout & 3) == 0);
     if (p.residual) {
@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int* abort_flag = &ctl->abort_flag;
 
-    const int tiles = p.tiles_m * p.tiles_n;
+    const int tiles_per_problem = p.tiles_m * p.tiles_n;
+    const int tiles = tiles_per_problem * (p.batch > 1 ? p.batch : 1);
     const int units = tiles * p.splits;
     const int SC = p.S * p.C;
     long long waited = 0;
@@ -271,7 +272,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
         int local = 0;
         for (int u = blockIdx.x; u < units; u += gridDim.x, local++) {
             const int tile = u / p.splits;
-            const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+            const int bidx = tile / tiles_per_problem;
+            const int tloc = tile - bidx * tiles_per_problem;
+            const int tm = tloc / p.tiles_n, tn = tloc % p.tiles_n;
+            const long long y_off = (long long)bidx * p.batch_stride_y;
             const int ab = local & 1;
             if (!timed_wait(&ctl->tmem_full[ab], (local >> 1) & 1, abort_flag, waited)) {
                 if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_FULL); }
@@ -312,7 +316,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                     for (int i = 0; i < 8; i++) {
                         const int rr = i * 4 + sub;
                         const long long m = tile_row0 + rr;
-                        if (m < p.M) store_out<T>(p, coef, *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc), m, n);
+                        if (m < p.M) store_out<T>(p, coef, *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc), m, n, y_off);
                     }
                 }
                 __syncwarp();
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
                                 float4* part = reinterpret_cast<float4*>(p.scratch + ((long long)tile * BM + warp * 32 + rr) * BN + cb * 32 + cc);
                                 const float4 v = __ldcg(part);
                                 *part = make_float4(0.f, 0.f, 0.f, 0.f);   // leave the scratch zeroed for the next launch
-                                store_out<T>(p, coef, v, m, n);
+                                store_out<T>(p, coef, v, m, n, y_off);
                             }
                         }
                     }
@@ -456,8 +460,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
         // eight 16-byte chunks of one operand row, so a warp instruction reads four full 128-byte
         // lines; each thread serves rows (t/8), (t/8)+16, ... of the tile with its fixed chunk t%8.
         const int pt = (warp - (MMA_WARP + 1 + SPLIT_WARPS)) * 32 + lane;   // 0..255
-        const T* __restrict__ X = reinterpret_cast<const T*>(p.x);
-        const T* __restrict__ Wt = reinterpret_cast<const T*>(p.w);
+        const T* __restrict__ X0 = reinterpret_cast<const T*>(p.x);
+        const T* __restrict__ W0 = reinterpret_cast<const T*>(p.w);
         const bool vec = (p.C % C::EPC) == 0;
         constexpr int RPT = BM / 32;            // A rows per thread
         const int chunk = pt & 7;
@@ -468,7 +472,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
         bool dead = false;
         for (int u = blockIdx.x; u < units && !dead; u += gridDim.x) {
             const int tile = u / p.splits, split = u % p.splits;
-            const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+            const int bidx = tile / tiles_per_problem;
+            const int tloc = tile - bidx * tiles_per_problem;
+            const int tm = tloc / p.tiles_n, tn = tloc % p.tiles_n;
+            const T* __restrict__ X = X0 + (long long)bidx * p.batch_stride_x;
+            const T* __restrict__ Wt = W0 + (long long)bidx * p.batch_stride_w;
             const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
             const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
             if (vec) {

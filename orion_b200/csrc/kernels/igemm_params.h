@@ -29,6 +29,11 @@ typedef struct IgemmParams {
      * for tap (r, s) the source pixel of tensor x [Nb, IH, IW, C] is
      *   ih = (oh*bmul_h + badd_h + r*step_h) / div_h   (valid only if the division is exact), same for w. */
     int OH, OW, IH, IW;
+    /* Batched GEMM: `batch` independent problems of one shape; tile index runs over (b, tile_m, tile_n)
+     * and problem b reads x + b*batch_stride_x, w + b*batch_stride_w, writes y + b*batch_stride_y
+     * (strides in elements).  batch <= 1 means a single problem. */
+    int batch;
+    long long batch_stride_x, batch_stride_w, batch_stride_y;
     int bmul_h, bmul_w, badd_h, badd_w, step_h, step_w, div_h, div_w;
 } IgemmParams;
 

@@ -213,6 +213,43 @@ extern "C" int ob200_linear(const void* x, const void* w, void* y, const float* 
     return ob200_conv2d_fprop(x, w, y, nullptr, bias, nullptr, relu, dtype, M, 1, 1, K, N, 1, 1, 1, 1, 0, 0, 1, 1, num_ctas, stream);
 }
 
+// `batch` independent GEMMs of one shape: y_b[M, N] = x_b[M, K] . w_b[N, K]^T, operands `stride_*` elements
+// apart.  Takes the place of cublasSgemmStridedBatched (attention scores and context products).
+extern "C" int ob200_linear_batched(const void* x, const void* w, void* y, int dtype, int batch, int M, int N, int K,
+                                    long long stride_x, long long stride_w, long long stride_y, int num_ctas, void* stream) {
+    if (dtype < 0 || dtype > 2 || batch < 0 || M < 0 || N <= 0 || K <= 0 || num_ctas <= 0) return -1;
+    if (batch == 0 || M == 0) return 0;
+    const int elem = dtype == 1 ? 2 : 4;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) % 16) return -2;
+    if ((stride_x * elem) % 16 || (stride_w * elem) % 16 || (stride_y * elem) % 16) return -2;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    IgemmParams p;
+    memset(&p, 0, sizeof p);
+    p.x = x; p.w = w; p.y = y;
+    p.dtype = dtype;
+    p.Nb = M; p.H = p.W = p.P = p.Q = p.R = p.S = 1;
+    p.C = K; p.Kout = N;
+    p.stride_h = p.stride_w = p.dil_h = p.dil_w = 1;
+    p.M = M;
+    const int bk = 128 / elem;
+    p.kblocks_per_r = (K + bk - 1) / bk;
+    p.num_kblocks = p.kblocks_per_r;
+    const int bn = N <= 64 ? 64 : 128;
+    p.tiles_m = (M + 127) / 128;
+    p.tiles_n = (N + bn - 1) / bn;
+    p.splits = 1;
+    p.status = status_word(dev);
+    p.debug = g_debug;
+    p.batch = batch;
+    p.batch_stride_x = stride_x; p.batch_stride_w = stride_w; p.batch_stride_y = stride_y;
+    igemm_set_fprop(&p);
+    const long long units = (long long)p.tiles_m * p.tiles_n * batch;
+    if (units > 0x7fffffffLL) return -1;
+    const int grid = units < num_ctas ? (int)units : num_ctas;
+    return ob200_igemm_launch(&p, bn, grid, stream);
+}
+
 // Reads and clears the device status word of the current device (synchronises the
 // device).  0 = no kernel reported a timed-out wait since the last call.
 extern "C" int ob200_read_status(void) {

@@ -36,6 +36,14 @@ def lib():
         L.ob200_bn_backward_f32.argtypes = [c_void_p] * 9 + [c_ll, c_int, c_int, c_void_p]
         L.ob200_relu_backward_f32.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_void_p]
         L.ob200_sgd_momentum_f32.argtypes = [c_void_p] * 3 + [c_ll, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]
+        L.ob200_layernorm.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_float, c_int, c_int, c_void_p]
+        L.ob200_softmax.argtypes = [c_void_p] * 2 + [c_ll, c_int, c_float, c_int, c_int, c_void_p]
+        L.ob200_bias_gelu.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_int, c_int, c_void_p]
+        L.ob200_adamw_f32.argtypes = [c_void_p] * 4 + [c_ll] + [c_float] * 5 + [c_int, c_int, c_void_p]
+        for name in ("ob200_layernorm", "ob200_softmax", "ob200_bias_gelu", "ob200_adamw_f32"):
+            getattr(L, name).restype = c_int
+        L.ob200_linear_batched.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_ll] * 3 + [c_int, c_void_p]
+        L.ob200_linear_batched.restype = c_int
         for name in ("ob200_conv2d_dgrad", "ob200_filter_transpose", "ob200_bn_train_forward_f32", "ob200_bn_backward_f32",
                      "ob200_relu_backward_f32", "ob200_sgd_momentum_f32"):
             getattr(L, name).restype = c_int
@@ -214,3 +222,49 @@ def relu_backward(dy, y, num_ctas=None):
 def sgd_momentum_(p, g, m, lr, mu, wd=0.0, nesterov=False, first_step=False, num_ctas=None):
     _check(lib().ob200_sgd_momentum_f32(_ptr(p), _ptr(g), _ptr(m), p.numel(), lr, mu, wd, int(nesterov), int(first_step),
                                         num_ctas or sm_count(), _stream()), "ob200_sgd_momentum_f32")
+
+
+def linear_batched(x, w, num_ctas=None, tf32=False):
+    """x: [B, M, K], w: [B, N, K] -> [B, M, N] (y_b = x_b . w_b^T)."""
+    assert x.is_contiguous() and w.is_contiguous() and x.dtype == w.dtype and x.shape[0] == w.shape[0]
+    B, M, K = x.shape
+    N = w.shape[1]
+    y = torch.empty((B, M, N), device=x.device, dtype=x.dtype)
+    code = 2 if (tf32 and x.dtype == torch.float32) else _dtype_code(x)
+    _check(lib().ob200_linear_batched(_ptr(x), _ptr(w), _ptr(y), code, B, M, N, K, M * K, N * K, M * N, num_ctas or sm_count(),
+                                      _stream()), "ob200_linear_batched")
+    return y
+
+
+def layernorm(x, gamma, beta, eps=1e-5, num_ctas=None):
+    """LayerNorm over the last dimension; x float32 or bfloat16, gamma/beta float32."""
+    assert x.is_contiguous()
+    D = x.shape[-1]
+    y = torch.empty_like(x)
+    _check(lib().ob200_layernorm(_ptr(x), _ptr(y), _ptr(gamma), _ptr(beta), None, None, x.numel() // D, D, float(eps), _dtype_code(x),
+                                 num_ctas or sm_count(), _stream()), "ob200_layernorm")
+    return y
+
+
+def softmax(x, scale=1.0, num_ctas=None):
+    """softmax(x * scale) over the last dimension."""
+    assert x.is_contiguous()
+    D = x.shape[-1]
+    y = torch.empty_like(x)
+    _check(lib().ob200_softmax(_ptr(x), _ptr(y), x.numel() // D, D, float(scale), _dtype_code(x), num_ctas or sm_count(), _stream()),
+           "ob200_softmax")
+    return y
+
+
+def bias_gelu(x, bias=None, num_ctas=None):
+    assert x.is_contiguous()
+    D = x.shape[-1]
+    y = torch.empty_like(x)
+    _check(lib().ob200_bias_gelu(_ptr(x), _ptr(y), _ptr(bias), x.numel() // D, D, _dtype_code(x), num_ctas or sm_count(), _stream()),
+           "ob200_bias_gelu")
+    return y
+
+
+def adamw_(p, g, m, v, step, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, num_ctas=None):
+    _check(lib().ob200_adamw_f32(_ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), lr, betas[0], betas[1], eps, weight_decay, step,
+                                 num_ctas or sm_count(), _stream()), "ob200_adamw_f32")

@@ -1,0 +1,74 @@
+"""Transformer-side kernels (LayerNorm, softmax, bias+GELU, AdamW, batched GEMM) against float64 CPU
+references.  Tolerances: float32 relative 1e-4, bfloat16 relative 2e-2 (benchmark specification)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import numeric_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K(built):
+    from orion_b200 import kernels
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; the kernels have no CPU fallback")
+    torch.manual_seed(777)
+    return kernels
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("rows,D", [(3072, 768), (8192, 1024), (5, 64), (1, 8)])
+def test_layernorm(K, rows, D, dtype, tol):
+    x = (torch.randn(rows, D, device="cuda") * 3 + 1).to(dtype)
+    g, b = torch.rand(D, device="cuda") + 0.5, torch.randn(D, device="cuda")
+    want = F.layer_norm(x.double().cpu(), (D,), g.double().cpu(), b.double().cpu(), 1e-5)
+    assert O.rel_err(K.layernorm(x, g, b, 1e-5), want) < tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("rows,D", [(96 * 384, 384), (1000, 512), (3, 8)])
+def test_softmax(K, rows, D, dtype, tol):
+    x = (torch.randn(rows, D, device="cuda") * 4).to(dtype)
+    want = F.softmax(x.double().cpu() * 0.125, dim=-1)
+    got = K.softmax(x, 0.125)
+    assert O.rel_err(got, want) < tol
+    assert (got.float().sum(-1) - 1).abs().max().item() < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+def test_bias_gelu(K, dtype, tol):
+    x = torch.randn(3072, 3072, device="cuda").to(dtype)
+    bias = torch.randn(3072, device="cuda")
+    want = F.gelu(x.double().cpu() + bias.double().cpu())
+    assert O.rel_err(K.bias_gelu(x, bias), want) < tol
+
+
+def test_adamw_matches_torch(K):
+    p = torch.randn(50001, device="cuda")
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=3e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    for step in range(1, 4):
+        g = torch.randn_like(p)
+        ref.grad = g.clone()
+        opt.step()
+        K.adamw_(p, g, m, v, step, 3e-4)
+    assert (p - ref.detach()).abs().max().item() < 1e-6
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+def test_batched_gemm_attention_shapes(K, dtype, tol):
+    """Q.K^T of BERT-base at batch 8: 96 problems of 384 x 384 x 64, and P.V with V transposed: 384 x 64 x 384."""
+    q = torch.randn(96, 384, 64, device="cuda").to(dtype)
+    k = torch.randn(96, 384, 64, device="cuda").to(dtype)
+    scores = K.linear_batched(q, k)
+    assert K.read_status() == 0
+    assert O.rel_err(scores, torch.bmm(q.double().cpu(), k.double().cpu().transpose(1, 2))) < tol
+    pr = torch.softmax(torch.randn(96, 384, 384, device="cuda"), -1).to(dtype)
+    vt = torch.randn(96, 64, 384, device="cuda").to(dtype)
+    ctx = K.linear_batched(pr, vt)
+    assert O.rel_err(ctx, torch.bmm(pr.double().cpu(), vt.double().cpu().transpose(1, 2))) < tol
+    odd = K.linear_batched(torch.randn(3, 130, 72, device="cuda"), torch.randn(3, 50, 72, device="cuda"))
+    assert odd.shape == (3, 130, 50) and K.read_status() == 0
