@@ -58,6 +58,11 @@ int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int n
  * (reference src/scheduler/utils_sched.cpp:439-464, trapped at src/cuda_capture/intercept_cudnn.cpp:482-558). */
 int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
+/* Filter gradient dw [Kout,R,S,C] (float32) from the layer input x [Nb,H,W,C] and dy [Nb,P,Q,Kout]; dtype 0 or 2
+ * (float32 data), C and Kout multiples of 4.  Takes the place of cudnnConvolutionBackwardFilter (reference
+ * src/scheduler/utils_sched.cpp:465-489, trapped at src/cuda_capture/intercept_cudnn.cpp:560-640). */
+int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
+                       int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
 /* w [K, R*S, C] -> wt [C, R*S, K]; elem_bytes 4 or 2.  No counterpart in the reference (cuDNN re-lays filters internally). */
 int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream);
 

@@ -289,6 +289,43 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             const int sub = lane >> 3;          // row within a group of four
             const int cc = (lane & 7) * 4;      // first of this lane's four channels within the 32-channel chunk
             const long long tile_row0 = (long long)tm * BM + warp * 32;
+            if (p.mode == 1) {
+                // Filter gradient: accumulator row = output channel k, columns = channels c of tap (r, s).
+                // The result lands in dw[k][r][s][c]; partial sums of different pixel ranges are added atomically.
+                const int tap = tn / p.ctiles, cblk = tn - tap * p.ctiles;
+                float* dw = reinterpret_cast<float*>(p.y);
+#pragma unroll 1
+                for (int cb = 0; cb < BN / 32; cb++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * BN + cb * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) =
+                            make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    __syncwarp();
+                    const int c = cblk * BN + cb * 32 + cc;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int rr = i * 4 + sub;
+                        const long long k = tile_row0 + rr;
+                        if (k < p.Kout && c < p.C) {
+                            const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc);
+                            float* dst = dw + ((long long)k * p.R * p.S + tap) * p.C + c;
+                            if (p.splits > 1) {
+                                atomicAdd(dst + 0, v.x); atomicAdd(dst + 1, v.y); atomicAdd(dst + 2, v.z); atomicAdd(dst + 3, v.w);
+                            } else {
+                                *reinterpret_cast<float4*>(dst) = v;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->tmem_empty[ab]);
+                continue;
+            }
 #pragma unroll 1
             for (int cb = 0; cb < BN / 32; cb++) {
                 uint32_t r[32];
@@ -479,6 +516,75 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             const T* __restrict__ Wt = W0 + (long long)bidx * p.batch_stride_w;
             const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
             const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
+            if (p.mode == 1) {
+                // Filter gradient (float32 data).  A k-block is 32 consecutive output pixels.  Both operands
+                // have the pixel index as their slow dimension in memory, so they are transposed on the way
+                // in: thread (prow, cg) loads, for pixel m = first + prow, every eighth 16-byte chunk of
+                // dy[m][k0..k0+127] and of x[pixel of m at this tile's tap][c0..c0+BN-1], and scatters the four
+                // values of a chunk to column m of four consecutive K-major operand rows.
+                if (sizeof(T) == 4) {
+                    const int tap = tn / p.ctiles, cblk = tn - tap * p.ctiles;
+                    const int fr = tap / p.S, fs = tap - fr * p.S;
+                    const int k0 = tm * BM, c0 = cblk * BN;
+                    const int pq = p.P * p.Q;
+                    const int prow = pt >> 3, cg = pt & 7;
+                    const float* __restrict__ DY = reinterpret_cast<const float*>(X);
+                    const float* __restrict__ IN = reinterpret_cast<const float*>(Wt);
+                    for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+                        const int s = it % C::STAGES;
+                        const long long m = (long long)kb * 32 + prow;
+                        const bool m_ok = m < p.M;
+                        const float* xsrc = nullptr;
+                        if (m_ok) {
+                            const int n_img = (int)(m / pq);
+                            const int rem = (int)(m - (long long)n_img * pq);
+                            const int op = rem / p.Q, oq = rem - op * p.Q;
+                            const int h = op * p.stride_h - p.pad_h + fr * p.dil_h;
+                            const int w = oq * p.stride_w - p.pad_w + fs * p.dil_w;
+                            if ((unsigned)h < (unsigned)p.H && (unsigned)w < (unsigned)p.W)
+                                xsrc = IN + (((long long)n_img * p.H + h) * p.W + w) * p.C;
+                        }
+                        float4 av[BM / 32], bv[BN / 32];
+#pragma unroll
+                        for (int i = 0; i < BM / 32; i++) {
+                            const int k = k0 + (cg + 8 * i) * 4;
+                            av[i] = (m_ok && k < p.Kout) ? __ldg(reinterpret_cast<const float4*>(DY + m * p.Kout + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int i = 0; i < BN / 32; i++) {
+                            const int c = c0 + (cg + 8 * i) * 4;
+                            bv[i] = (xsrc != nullptr && c < p.C) ? __ldg(reinterpret_cast<const float4*>(xsrc + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                            if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
+                            dead = true;
+                            break;
+                        }
+                        uint8_t* a_dst = smem + s * C::STAGE_BYTES;
+                        uint8_t* b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                        const uint32_t col_chunk = (uint32_t)prow >> 2, col_word = ((uint32_t)prow & 3u) * 4u;
+#pragma unroll
+                        for (int i = 0; i < BM / 32; i++) {
+                            const uint32_t row = (uint32_t)(cg + 8 * i) * 4u;
+                            const float e[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
+#pragma unroll
+                            for (int q = 0; q < 4; q++)
+                                *reinterpret_cast<float*>(a_dst + sw128_offset(row + q, col_chunk) + col_word) = e[q];
+                        }
+#pragma unroll
+                        for (int i = 0; i < BN / 32; i++) {
+                            const uint32_t row = (uint32_t)(cg + 8 * i) * 4u;
+                            const float e[4] = {bv[i].x, bv[i].y, bv[i].z, bv[i].w};
+#pragma unroll
+                            for (int q = 0; q < 4; q++)
+                                *reinterpret_cast<float*>(b_dst + sw128_offset(row + q, col_chunk) + col_word) = e[q];
+                        }
+                        if (!C::kSplit) fence_proxy_async_smem();
+                        mbar_arrive(&ctl->raw_full[s]);
+                    }
+                }
+                continue;
+            }
             if (vec) {
                 // Unit-divisor gathers (forward convolution, stride-1 data gradient): xpix is the address of
                 // the (possibly out-of-image) tap-0 pixel of row i, and a tap adds a row-independent offset.

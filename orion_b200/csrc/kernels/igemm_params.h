@@ -34,6 +34,14 @@ typedef struct IgemmParams {
      * (strides in elements).  batch <= 1 means a single problem. */
     int batch;
     long long batch_stride_x, batch_stride_w, batch_stride_y;
+    /* mode 0: forward / data gradient / GEMM (operands K-major).  mode 1: filter gradient:
+     *   dw[k][r][s][c] = sum over pixels m of dy[m][k] * x[pixel of m at tap (r,s)][c]
+     * with x = dy [Nb*P*Q, Kout], w = the layer input [Nb, H, W, C], y = dw (float32, accumulated with
+     * atomic adds when splits > 1, so it must be zero on entry then); the reduction runs over pixels (the
+     * producers transpose both operands into K-major tiles), tiles_m covers Kout and tiles_n covers
+     * (tap, channel block). */
+    int mode;
+    int ctiles;             /* filter gradient: channel blocks per tap, ceil(C / BN) */
     int bmul_h, bmul_w, badd_h, badd_w, step_h, step_w, div_h, div_w;
 } IgemmParams;
 

@@ -206,6 +206,59 @@ extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int 
     return ob200_igemm_launch(&p, bn, grid, stream);
 }
 
+// Filter gradient of the convolution: dw[k,r,s,c] = sum_{n,p,q} dy[n,p,q,k] * x[n, p*stride-pad+r*dil, q*stride-pad+s*dil, c].
+// float32 only (dtype 0: 3xTF32, 2: one TF32 pass); C and Kout multiples of 4.  The reduction over the
+// N*P*Q pixels is split across CTAs and summed with atomic adds, so dw is cleared on `stream` first.
+extern "C" int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int Nb, int H, int W, int C, int Kout, int R,
+                                  int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas,
+                                  void* stream) {
+    if (dtype != 0 && dtype != 2) return -1;
+    if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || Kout <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
+        dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0 || (C & 3) || (Kout & 3))
+        return -1;
+    const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / stride_h + 1;
+    const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / stride_w + 1;
+    if (P <= 0 || Q <= 0) return -1;
+    if (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dw) % 16) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t dw_bytes = (size_t)Kout * R * S * C * sizeof(float);
+    if (Nb == 0) return (int)cudaMemsetAsync(dw, 0, dw_bytes, s);
+    const long long Mpix = (long long)Nb * P * Q;
+    if (Mpix > 0x7fffffffLL) return -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    IgemmParams p;
+    memset(&p, 0, sizeof p);
+    p.mode = 1;
+    p.x = dy; p.w = x; p.y = dw;
+    p.dtype = dtype;
+    p.Nb = Nb; p.H = H; p.W = W; p.C = C; p.Kout = Kout; p.R = R; p.S = S; p.P = P; p.Q = Q;
+    p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
+    p.M = (int)Mpix;
+    const int bn = C > 64 ? 128 : 64;
+    p.ctiles = (C + bn - 1) / bn;
+    p.tiles_m = (Kout + 127) / 128;
+    p.tiles_n = R * S * p.ctiles;
+    p.kblocks_per_r = (int)((Mpix + 31) / 32);
+    p.num_kblocks = p.kblocks_per_r;
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    long long splits = (2LL * num_ctas + tiles - 1) / tiles;       // about two units per granted SM
+    if (splits > p.num_kblocks / 2) splits = p.num_kblocks / 2;    // at least two k-blocks per unit
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    p.splits = (int)splits;
+    p.status = status_word(dev);
+    p.debug = g_debug;
+    igemm_set_fprop(&p);
+    if (p.splits > 1) {
+        cudaError_t e = cudaMemsetAsync(dw, 0, dw_bytes, s);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const long long units = tiles * p.splits;
+    const int grid = units < num_ctas ? (int)units : num_ctas;
+    return ob200_igemm_launch(&p, bn, grid, stream);
+}
+
 // y[M, N] = x[M, K] . w[N, K]^T (+ bias) (+ ReLU): a 1x1 convolution over M "pixels".
 extern "C" int ob200_linear(const void* x, const void* w, void* y, const float* bias, int relu, int dtype, int M, int N, int K,
                             int num_ctas, void* stream) {

@@ -41,6 +41,8 @@ int ob200_sm_count(void);
 int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
 int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream);
+int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
+                       int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
 int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
                                float* running_var, float* save_mean, float* save_invstd, double* sums, float eps, float momentum,
                                long long rows, int C, int num_ctas, void* stream);
@@ -192,39 +194,57 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_backward_overrid
                                           {true, true, true});
 }
 
-// cudnnConvolutionBackwardData's role goes to the orion data-gradient kernel; the filter and bias
-// gradients stay with the stock implementation (reference src/scheduler/utils_sched.cpp:439-489).
+// cudnnConvolutionBackwardData's and cudnnConvolutionBackwardFilter's roles go to the orion kernels
+// (reference src/scheduler/utils_sched.cpp:439-489); the bias gradient and the layers the kernels do
+// not cover (3-channel stem, grouped convolutions) stay with the stock implementation.
 std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_override(
     const at::Tensor& grad_output, const at::Tensor& input, const at::Tensor& weight, at::OptionalIntArrayRef bias_sizes,
     at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, at::IntArrayRef output_padding,
     int64_t groups, std::array<bool, 3> output_mask) {
-    const bool ok = g_overrides.load(std::memory_order_relaxed) && output_mask[0] && input.dim() == 4 && weight.dim() == 4 &&
-                    !transposed && groups == 1 && dtype_code(input) >= 0 && input.scalar_type() == weight.scalar_type() &&
-                    grad_output.scalar_type() == input.scalar_type() && stride.size() == 2 && padding.size() == 2 &&
-                    dilation.size() == 2 && input.numel() > 0 && is_nhwc(weight) && weight.size(0) % (input.scalar_type() == at::kFloat ? 4 : 8) == 0;
-    if (!ok) {
+    const bool base_ok = g_overrides.load(std::memory_order_relaxed) && input.dim() == 4 && weight.dim() == 4 && !transposed &&
+                         groups == 1 && dtype_code(input) >= 0 && input.scalar_type() == weight.scalar_type() &&
+                         grad_output.scalar_type() == input.scalar_type() && stride.size() == 2 && padding.size() == 2 &&
+                         dilation.size() == 2 && input.numel() > 0 && is_nhwc(weight);
+    const int64_t Nb = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3);
+    const int64_t K = weight.size(0), R = weight.size(2), S = weight.size(3);
+    // data gradient: any float32 / bfloat16 layer whose output-channel count fills 16-byte chunks
+    const bool dgrad_ok = base_ok && output_mask[0] && K % (input.scalar_type() == at::kFloat ? 4 : 8) == 0;
+    // filter gradient: float32 layers with channel counts that are multiples of 4 (not the 3-channel stem)
+    const bool wgrad_ok = base_ok && output_mask[1] && input.scalar_type() == at::kFloat && C % 4 == 0 && K % 4 == 0;
+    if (!dgrad_ok && !wgrad_ok) {
         g_fallbacks.fetch_add(1, std::memory_order_relaxed);
         return at::native::convolution_backward(grad_output, input, weight, bias_sizes, stride, padding, dilation, transposed,
                                                 output_padding, groups, output_mask);
     }
     at::Tensor dy = is_nhwc(grad_output) ? grad_output : grad_output.contiguous(at::MemoryFormat::ChannelsLast);
-    const int64_t Nb = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3);
-    const int64_t K = weight.size(0), R = weight.size(2), S = weight.size(3);
-    at::Tensor wt = at::empty({C, K, R, S}, weight.options().memory_format(at::MemoryFormat::ChannelsLast));   // physical [C,R,S,K]
-    check(ob200_filter_transpose(weight.data_ptr(), wt.data_ptr(), (int)K, (int)(R * S), (int)C, (int)weight.element_size(),
-                                 cur_stream()),
-          "ob200_filter_transpose");
-    at::Tensor dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::ChannelsLast));
-    check(ob200_conv2d_dgrad(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), override_dtype_code(input), (int)Nb, (int)H, (int)W, (int)C, (int)K,
-                             (int)R, (int)S, (int)stride[0], (int)stride[1], (int)padding[0], (int)padding[1], (int)dilation[0],
-                             (int)dilation[1], quota(), cur_stream()),
-          "ob200_conv2d_dgrad");
-    at::Tensor dw, db;
-    if (output_mask[1] || output_mask[2]) {
+    at::Tensor x = is_nhwc(input) ? input : input.contiguous(at::MemoryFormat::ChannelsLast);
+    at::Tensor dx, dw, db;
+    if (dgrad_ok) {
+        at::Tensor wt = at::empty({C, K, R, S}, weight.options().memory_format(at::MemoryFormat::ChannelsLast));   // physical [C,R,S,K]
+        check(ob200_filter_transpose(weight.data_ptr(), wt.data_ptr(), (int)K, (int)(R * S), (int)C, (int)weight.element_size(),
+                                     cur_stream()),
+              "ob200_filter_transpose");
+        dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::ChannelsLast));
+        check(ob200_conv2d_dgrad(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), override_dtype_code(input), (int)Nb, (int)H, (int)W,
+                                 (int)C, (int)K, (int)R, (int)S, (int)stride[0], (int)stride[1], (int)padding[0], (int)padding[1],
+                                 (int)dilation[0], (int)dilation[1], quota(), cur_stream()),
+              "ob200_conv2d_dgrad");
+    }
+    if (wgrad_ok) {
+        dw = at::empty(weight.sizes(), weight.options().memory_format(at::MemoryFormat::ChannelsLast));   // physical [K,R,S,C]
+        check(ob200_conv2d_wgrad(x.data_ptr(), dy.data_ptr(), dw.data_ptr<float>(), override_dtype_code(input), (int)Nb, (int)H, (int)W,
+                                 (int)C, (int)K, (int)R, (int)S, (int)stride[0], (int)stride[1], (int)padding[0], (int)padding[1],
+                                 (int)dilation[0], (int)dilation[1], quota(), cur_stream()),
+              "ob200_conv2d_wgrad");
+    }
+    // whatever the kernels above do not cover comes from the stock implementation
+    const bool need_dx = output_mask[0] && !dgrad_ok, need_dw = output_mask[1] && !wgrad_ok, need_db = output_mask[2];
+    if (need_dx || need_dw || need_db) {
         auto rest = at::native::convolution_backward(dy, input, weight, bias_sizes, stride, padding, dilation, transposed,
-                                                     output_padding, groups, {false, output_mask[1], output_mask[2]});
-        dw = std::get<1>(rest);
-        db = std::get<2>(rest);
+                                                     output_padding, groups, {need_dx, need_dw, need_db});
+        if (need_dx) dx = std::get<0>(rest);
+        if (need_dw) dw = std::get<1>(rest);
+        if (need_db) db = std::get<2>(rest);
     }
     return std::make_tuple(dx, dw, db);
 }

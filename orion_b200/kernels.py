@@ -36,6 +36,8 @@ def lib():
         L.ob200_bn_backward_f32.argtypes = [c_void_p] * 9 + [c_ll, c_int, c_int, c_void_p]
         L.ob200_relu_backward_f32.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_void_p]
         L.ob200_sgd_momentum_f32.argtypes = [c_void_p] * 3 + [c_ll, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]
+        L.ob200_conv2d_wgrad.argtypes = [c_void_p] * 3 + [c_int] * 14 + [c_int, c_void_p]
+        L.ob200_conv2d_wgrad.restype = c_int
         L.ob200_layernorm.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_float, c_int, c_int, c_void_p]
         L.ob200_softmax.argtypes = [c_void_p] * 2 + [c_ll, c_int, c_float, c_int, c_int, c_void_p]
         L.ob200_bias_gelu.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_int, c_int, c_void_p]
@@ -268,3 +270,16 @@ def bias_gelu(x, bias=None, num_ctas=None):
 def adamw_(p, g, m, v, step, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, num_ctas=None):
     _check(lib().ob200_adamw_f32(_ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), lr, betas[0], betas[1], eps, weight_decay, step,
                                  num_ctas or sm_count(), _stream()), "ob200_adamw_f32")
+
+
+def conv2d_wgrad_nhwc(x, dy, filter_rs, stride=(1, 1), padding=(0, 0), dilation=(1, 1), num_ctas=None, tf32=False):
+    """x: [N, H, W, C], dy: [N, P, Q, K] (float32) -> dw [K, R, S, C]."""
+    assert x.is_contiguous() and dy.is_contiguous() and x.dtype == torch.float32 and dy.dtype == torch.float32
+    Nb, H, W, C = x.shape
+    K = dy.shape[3]
+    R, S = filter_rs
+    dw = torch.empty((K, R, S, C), device=x.device, dtype=torch.float32)
+    _check(lib().ob200_conv2d_wgrad(_ptr(x), _ptr(dy), _ptr(dw), 2 if tf32 else 0, Nb, H, W, C, K, R, S, stride[0], stride[1],
+                                    padding[0], padding[1], dilation[0], dilation[1], num_ctas or sm_count(), _stream()),
+           "ob200_conv2d_wgrad")
+    return dw

@@ -94,3 +94,27 @@ def test_relu_backward_and_sgd(K):
         opt.step()
         K.sgd_momentum_(p, gstep, m, 0.1, 0.9, 1e-4, first_step=(step == 0))
     assert (p - ref_p.detach()).abs().max().item() < 1e-5
+
+
+def _wgrad_ref(x, dy, rs, stride, pad, dil):
+    """cudnnConvolutionBackwardFilter by definition: the gradient of conv2d with respect to its weight."""
+    xd = x.detach().double().cpu().permute(0, 3, 1, 2)
+    dyd = dy.detach().double().cpu().permute(0, 3, 1, 2)
+    k, c = dy.shape[3], x.shape[3]
+    dw = torch.nn.grad.conv2d_weight(xd, (k, c, rs[0], rs[1]), dyd, stride=stride, padding=pad, dilation=dil)
+    return dw.permute(0, 2, 3, 1).contiguous()
+
+
+@pytest.mark.parametrize("shape", [
+    (2, 8, 8, 32, 128, 1, 1, 0), (4, 56, 56, 64, 64, 3, 1, 1), (4, 56, 56, 64, 256, 1, 1, 0), (4, 28, 28, 128, 128, 3, 2, 1),
+    (4, 14, 14, 256, 1024, 1, 1, 0), (4, 7, 7, 512, 512, 3, 1, 1), (2, 11, 9, 24, 40, 3, 2, 1), (3, 10, 10, 200, 136, 3, 1, 1),
+])
+def test_conv_wgrad_fp32(K, shape):
+    Nb, H, W, C, Ko, R, stride, pad = shape
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - R) // stride + 1
+    x = torch.randn(Nb, H, W, C, device="cuda")
+    dy = torch.randn(Nb, P, Q, Ko, device="cuda") / (Nb * P * Q) ** 0.5
+    dw = K.conv2d_wgrad_nhwc(x, dy, (R, R), (stride, stride), (pad, pad))
+    assert K.read_status() == 0
+    assert O.rel_err(dw, _wgrad_ref(x, dy, (R, R), stride, pad, 1)) < TOL
