@@ -21,6 +21,9 @@ What differs from the reference script, on purpose:
     (`ORION_PREPARE=0` leaves the model untouched: its convolutions and batch norms
     still reach the orion kernels through the dispatcher overrides);
   * each request reads its result back to the host (`ORION_READBACK=0` disables).
+
+`run_client` holds the loop; `imagenet_loop` only says how to build the model and what one
+request does, and so do the language-model clients in transformer_trainer.py.
 """
 import json
 import os
@@ -86,14 +89,16 @@ def _sleep_times(rps, uniform, num_iters, input_file):
     return [0.0] * num_iters
 
 
-def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_data, local_rank, barriers, client_barrier, tid,
-                  input_file=""):
+def run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchsize, build):
+    """The request loop shared by every client kind.  `build(device)` creates the model on the
+    current CUDA stream and returns `step(batch_idx)`, which issues one request / training
+    iteration (including the host-to-device copy of its inputs) and returns a device tensor
+    that is read back to the host after the request completed."""
+    import contextlib
     seed_everything(42)
     backend_lib = capture_library()
     sleep_times = _sleep_times(rps, uniform, num_iters, input_file)
-    reference_data = os.environ.get("ORION_CLIENT_REFERENCE_DATA", "0") == "1"
     readback = os.environ.get("ORION_READBACK", "1") == "1"
-    resident = os.environ.get("ORION_RESIDENT_INPUTS", "0") == "1"
     out_dir = os.environ.get("ORION_OUT_DIR", ".")
 
     barriers[0].wait()   # the scheduler has run setup(): streams exist, this thread is registered
@@ -109,47 +114,24 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
         quota = int(os.environ.get("ORION_BE_SM_QUOTA", "0")) if train else 0
         if quota > 0:
             torch_ops.set_sm_quota(quota)
+        if train and os.environ.get("ORION_DISABLE_OVERRIDES", "0") == "1":
+            torch_ops.set_overrides(False)   # training client on the stock cuDNN / ATen kernels (still captured and scheduled)
         if train and os.environ.get("ORION_TRAIN_TF32", "0") == "1":
             torch.ops.orion.set_tf32(1)   # training convolutions in one TF32 pass, like stock cuDNN's default
-        import contextlib
-        model = models.__dict__[model_name](num_classes=1000)
-        model = model.to(local_rank).to(memory_format=torch.channels_last)
-        if train:
-            model.train()
-            momentum = 0.0 if reference_data else 0.9
-            lr = 0.05 if (model_name == "mobilenet_v2" and not reference_data) else 0.1
-            optimizer = torch.optim.SGD(model.parameters(), lr=lr, momentum=momentum)
-            criterion = torch.nn.CrossEntropyLoss().to(local_rank)
-        else:
-            model.eval()
-            if os.environ.get("ORION_PREPARE", "1") == "1":
-                model = torch_ops.prepare_inference(model)
-        if not dummy_data:
-            raise NotImplementedError("only synthetic data is available (dummy_data=true)")
-        loader = DummyDataLoader(batchsize, reference_data)
-        data, target = next(loader)
-        gpu_data = data.to(local_rank, non_blocking=True).contiguous(memory_format=torch.channels_last)
-        gpu_target = target.to(local_rank, non_blocking=True)
+        with torch_ops.TRACE_LOCK:
+            step = build(torch.device("cuda", torch.cuda.current_device()))
         result = None
-
         next_startup = time.time()
         open_loop = rps > 0 or input_file != ""
         while batch_idx < num_iters:
             if train:
                 start_iter = time.time()
-                if not resident:
-                    gpu_data = data.to(local_rank, non_blocking=True).contiguous(memory_format=torch.channels_last)
-                    gpu_target = target.to(local_rank, non_blocking=True)
-                optimizer.zero_grad()
                 # iteration 0 overlaps with other clients preparing their models (see TRACE_LOCK)
                 with (torch_ops.TRACE_LOCK if batch_idx == 0 else contextlib.nullcontext()):
-                    output = model(gpu_data)
-                    loss = criterion(output, gpu_target)
-                loss.backward()
-                optimizer.step()
+                    result = step(batch_idx)
                 backend_lib.block(batch_idx)
-                if readback:
-                    result = float(loss.detach())
+                if readback and result is not None:
+                    result = float(result.detach())
                 timings.append(time.time() - start_iter)
                 batch_idx += 1
                 if batch_idx == 1 or batch_idx == 10:
@@ -165,13 +147,11 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
                         if wait > 2e-4:
                             time.sleep(wait - 1e-4)
                         continue
-                    if not resident:
-                        gpu_data = data.to(local_rank, non_blocking=True).contiguous(memory_format=torch.channels_last)
                     with (torch_ops.TRACE_LOCK if batch_idx == 0 else contextlib.nullcontext()):
-                        output = model(gpu_data)
+                        result = step(batch_idx)
                     backend_lib.block(batch_idx)
-                    if readback:
-                        result = output.cpu()   # a plain device-to-host copy: no extra kernel in the op stream
+                    if readback and result is not None:
+                        result = result.cpu()   # a plain device-to-host copy: no extra kernel in the op stream
                     timings.append(time.time() - next_startup)
                     if batch_idx >= 10 and open_loop:
                         next_startup += sleep_times[batch_idx]
@@ -201,3 +181,47 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "client_%d.json" % tid), "w") as f:
         json.dump(data_out, f)
+
+
+def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_data, local_rank, barriers, client_barrier, tid,
+                  input_file=""):
+    if not dummy_data:
+        raise NotImplementedError("only synthetic data is available (dummy_data=true)")
+    reference_data = os.environ.get("ORION_CLIENT_REFERENCE_DATA", "0") == "1"
+    resident = os.environ.get("ORION_RESIDENT_INPUTS", "0") == "1"
+
+    def build(device):
+        from orion_b200 import torch_ops
+        model = models.__dict__[model_name](num_classes=1000)
+        model = model.to(device).to(memory_format=torch.channels_last)
+        loader = DummyDataLoader(batchsize, reference_data)
+        data, target = next(loader)
+        state = {"x": data.to(device, non_blocking=True), "t": target.to(device, non_blocking=True)}
+        if train:
+            model.train()
+            momentum = 0.0 if reference_data else 0.9
+            lr = 0.05 if (model_name == "mobilenet_v2" and not reference_data) else 0.1
+            optimizer = torch.optim.SGD(model.parameters(), lr=lr, momentum=momentum)
+            criterion = torch.nn.CrossEntropyLoss().to(device)
+
+            def step(batch_idx):
+                if not resident:
+                    state["x"] = data.to(device, non_blocking=True)
+                    state["t"] = target.to(device, non_blocking=True)
+                optimizer.zero_grad()
+                loss = criterion(model(state["x"]), state["t"])
+                loss.backward()
+                optimizer.step()
+                return loss
+            return step
+        model.eval()
+        if os.environ.get("ORION_PREPARE", "1") == "1":
+            model = torch_ops.prepare_inference(model)
+
+        def step(batch_idx):
+            if not resident:
+                state["x"] = data.to(device, non_blocking=True)
+            return model(state["x"])
+        return step
+
+    run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchsize, build)

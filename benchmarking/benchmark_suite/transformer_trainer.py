@@ -1,0 +1,176 @@
+"""Language-model clients: `bert_loop` (BERT-base question answering, reference
+benchmarking/benchmark_suite/bert_trainer_mock.py:49-234) and `transformer_loop` (language-model
+training, reference benchmarking/benchmark_suite/transformer_trainer.py:43-200), with the
+reference's argument lists.  The request loop is `run_client` of train_imagenet.py.
+
+Models are defined here (the reference imports NVIDIA's example repositories, which are not part
+of it): BERT-base = 12 layers, hidden 768, 12 heads, FFN 3072, vocabulary 30522 padded to 30528,
+sequence 384; the training "transformer" client is the benchmark configuration's decoder-only LM
+(16 layers, d_model 1024, 16 heads, FFN 4096, vocabulary 32000, sequence 512) — the reference's
+Transformer-XL is not reproduced.  Everything is bfloat16 with synthetic token ids.
+
+Inference runs on the orion kernels (tcgen05 GEMM and batched GEMM, LayerNorm, softmax, GELU);
+training uses stock PyTorch modules, whose cuBLASLt / flash-attention / elementwise launches are
+captured and scheduled like any other op.
+"""
+import math
+import os
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .train_imagenet import run_client
+
+BERT = dict(layers=12, hidden=768, heads=12, ffn=3072, vocab=30528, max_pos=512, seq=384)
+LM = dict(layers=16, hidden=1024, heads=16, ffn=4096, vocab=32000, seq=512)
+
+
+class BertLayer(nn.Module):
+    def __init__(self, h, heads, ffn):
+        super().__init__()
+        self.heads = heads
+        self.qkv = nn.Linear(h, 3 * h)
+        self.out = nn.Linear(h, h)
+        self.ln1 = nn.LayerNorm(h, eps=1e-12)
+        self.fc1 = nn.Linear(h, ffn)
+        self.fc2 = nn.Linear(ffn, h)
+        self.ln2 = nn.LayerNorm(h, eps=1e-12)
+
+    def forward(self, x, causal=False):
+        b, s, h = x.shape
+        q, k, v = self.qkv(x).view(b, s, 3, self.heads, h // self.heads).permute(2, 0, 3, 1, 4)
+        ctx = F.scaled_dot_product_attention(q, k, v, is_causal=causal).transpose(1, 2).reshape(b, s, h)
+        x = self.ln1(x + self.out(ctx))
+        return self.ln2(x + self.fc2(F.gelu(self.fc1(x))))
+
+    def forward_orion(self, x):
+        """Same math on the orion kernels (inference): x [B, S, H] bfloat16."""
+        ops = torch.ops.orion
+        b, s, h = x.shape
+        d = h // self.heads
+        flat = x.reshape(b * s, h)
+        qkv = ops.linear(flat, self.qkv.weight, self.qkv.bias.float(), False).view(b, s, 3, self.heads, d)
+        q = qkv[:, :, 0].permute(0, 2, 1, 3).reshape(b * self.heads, s, d).contiguous()
+        k = qkv[:, :, 1].permute(0, 2, 1, 3).reshape(b * self.heads, s, d).contiguous()
+        vt = qkv[:, :, 2].permute(0, 2, 3, 1).reshape(b * self.heads, d, s).contiguous()
+        probs = ops.softmax(ops.linear_batched(q, k), 1.0 / math.sqrt(d))
+        ctx = ops.linear_batched(probs, vt).view(b, self.heads, s, d).permute(0, 2, 1, 3).reshape(b * s, h).contiguous()
+        attn = ops.linear(ctx, self.out.weight, self.out.bias.float(), False)
+        y = ops.layernorm(flat + attn, self.ln1.weight.float(), self.ln1.bias.float(), self.ln1.eps)
+        hid = ops.bias_gelu(ops.linear(y, self.fc1.weight, None, False), self.fc1.bias.float())
+        out = ops.linear(hid, self.fc2.weight, self.fc2.bias.float(), False)
+        return ops.layernorm(y + out, self.ln2.weight.float(), self.ln2.bias.float(), self.ln2.eps).view(b, s, h)
+
+
+class BertQA(nn.Module):
+    def __init__(self, cfg=BERT):
+        super().__init__()
+        h = cfg["hidden"]
+        self.word = nn.Embedding(cfg["vocab"], h)
+        self.pos = nn.Embedding(cfg["max_pos"], h)
+        self.typ = nn.Embedding(2, h)
+        self.ln = nn.LayerNorm(h, eps=1e-12)
+        self.layers = nn.ModuleList([BertLayer(h, cfg["heads"], cfg["ffn"]) for _ in range(cfg["layers"])])
+        self.qa = nn.Linear(h, 2)
+
+    def embed(self, ids):
+        pos = torch.arange(ids.shape[1], device=ids.device)
+        return self.ln(self.word(ids) + self.pos(pos)[None] + self.typ.weight[0])
+
+    def forward(self, ids, orion=False):
+        x = self.embed(ids)
+        for layer in self.layers:
+            x = layer.forward_orion(x) if orion else layer(x)
+        return self.qa(x)   # [B, S, 2]: start / end logits
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg=LM):
+        super().__init__()
+        h = cfg["hidden"]
+        self.word = nn.Embedding(cfg["vocab"], h)
+        self.pos = nn.Embedding(cfg["seq"], h)
+        self.layers = nn.ModuleList([BertLayer(h, cfg["heads"], cfg["ffn"]) for _ in range(cfg["layers"])])
+        self.ln = nn.LayerNorm(h)
+        self.head = nn.Linear(h, cfg["vocab"], bias=False)
+
+    def forward(self, ids):
+        pos = torch.arange(ids.shape[1], device=ids.device)
+        x = self.word(ids) + self.pos(pos)[None]
+        for layer in self.layers:
+            x = layer(x, causal=True)
+        return self.head(self.ln(x))
+
+
+def _pinned(t):
+    return t.pin_memory() if torch.cuda.is_available() else t
+
+
+def bert_loop(batchsize, train, num_iters, rps, uniform, dummy_data, local_rank, barriers, client_barrier, tid, input_file=""):
+    seq, vocab = BERT["seq"], 30522
+    resident = os.environ.get("ORION_RESIDENT_INPUTS", "0") == "1"
+
+    def build(device):
+        model = BertQA().to(device).to(torch.bfloat16)
+        ids = _pinned(torch.randint(0, vocab, (batchsize, seq)))
+        labels = _pinned(torch.randint(0, seq, (2, batchsize)))
+        state = {"ids": ids.to(device, non_blocking=True), "lab": labels.to(device, non_blocking=True)}
+        if train:
+            model.train()
+            opt = torch.optim.AdamW(model.parameters(), lr=3e-5)
+
+            def step(batch_idx):
+                if not resident:
+                    state["ids"] = ids.to(device, non_blocking=True)
+                    state["lab"] = labels.to(device, non_blocking=True)
+                opt.zero_grad()
+                logits = model(state["ids"]).float()
+                loss = F.cross_entropy(logits[:, :, 0], state["lab"][0]) + F.cross_entropy(logits[:, :, 1], state["lab"][1])
+                loss.backward()
+                opt.step()
+                return loss
+            return step
+        model.eval()
+        use_orion = os.environ.get("ORION_PREPARE", "1") == "1"
+
+        def step(batch_idx):
+            if not resident:
+                state["ids"] = ids.to(device, non_blocking=True)
+            return model(state["ids"], orion=use_orion)
+        return step
+
+    run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchsize, build)
+
+
+def transformer_loop(batchsize, train, num_iters, rps, uniform, dummy_data, local_rank, barriers, client_barrier, tid, input_file=""):
+    seq, vocab = LM["seq"], LM["vocab"]
+    resident = os.environ.get("ORION_RESIDENT_INPUTS", "0") == "1"
+
+    def build(device):
+        model = DecoderLM().to(device).to(torch.bfloat16)
+        tokens = _pinned(torch.randint(0, vocab, (batchsize, seq + 1)))
+        state = {"tok": tokens.to(device, non_blocking=True)}
+        if train:
+            model.train()
+            opt = torch.optim.AdamW(model.parameters(), lr=3e-4)
+
+            def step(batch_idx):
+                if not resident:
+                    state["tok"] = tokens.to(device, non_blocking=True)
+                opt.zero_grad()
+                logits = model(state["tok"][:, :-1])
+                loss = F.cross_entropy(logits.float().view(-1, vocab), state["tok"][:, 1:].reshape(-1))
+                loss.backward()
+                opt.step()
+                return loss
+            return step
+        model.eval()
+
+        def step(batch_idx):
+            if not resident:
+                state["tok"] = tokens.to(device, non_blocking=True)
+            return model(state["tok"][:, :-1])[:, -1]
+        return step
+
+    run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchsize, build)

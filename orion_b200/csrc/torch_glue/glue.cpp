@@ -41,6 +41,12 @@ int ob200_sm_count(void);
 int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
 int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream);
+int ob200_layernorm(const void* x, void* y, const float* gamma, const float* beta, float* mean_out, float* rstd_out, long long rows,
+                    int D, float eps, int dtype, int num_ctas, void* stream);
+int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, int dtype, int num_ctas, void* stream);
+int ob200_bias_gelu(const void* x, void* y, const float* bias, long long rows, int D, int dtype, int num_ctas, void* stream);
+int ob200_linear_batched(const void* x, const void* w, void* y, int dtype, int batch, int M, int N, int K, long long stride_x,
+                         long long stride_w, long long stride_y, int num_ctas, void* stream);
 int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
 int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
@@ -303,6 +309,47 @@ at::Tensor add_act_op(const at::Tensor& a, const at::Tensor& b, bool relu) {
     return y;
 }
 
+at::Tensor layernorm_op(const at::Tensor& x, const c10::optional<at::Tensor>& gamma, const c10::optional<at::Tensor>& beta, double eps) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dtype_code(x) >= 0, "orion::layernorm: contiguous float32/bfloat16 CUDA tensor expected");
+    const int64_t D = x.size(-1);
+    at::Tensor y = at::empty_like(x);
+    check(ob200_layernorm(x.data_ptr(), y.data_ptr(), fptr(gamma), fptr(beta), nullptr, nullptr, x.numel() / D, (int)D, (float)eps,
+                          dtype_code(x), quota(), cur_stream()),
+          "ob200_layernorm");
+    return y;
+}
+
+at::Tensor softmax_op(const at::Tensor& x, double scale) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dtype_code(x) >= 0, "orion::softmax: contiguous float32/bfloat16 CUDA tensor expected");
+    const int64_t D = x.size(-1);
+    at::Tensor y = at::empty_like(x);
+    check(ob200_softmax(x.data_ptr(), y.data_ptr(), x.numel() / D, (int)D, (float)scale, dtype_code(x), quota(), cur_stream()),
+          "ob200_softmax");
+    return y;
+}
+
+at::Tensor bias_gelu_op(const at::Tensor& x, const c10::optional<at::Tensor>& bias) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dtype_code(x) >= 0, "orion::bias_gelu: contiguous float32/bfloat16 CUDA tensor expected");
+    const int64_t D = x.size(-1);
+    at::Tensor y = at::empty_like(x);
+    check(ob200_bias_gelu(x.data_ptr(), y.data_ptr(), fptr(bias), x.numel() / D, (int)D, dtype_code(x), quota(), cur_stream()),
+          "ob200_bias_gelu");
+    return y;
+}
+
+// x: [B, M, K], w: [B, N, K] -> [B, M, N]
+at::Tensor linear_batched_op(const at::Tensor& x, const at::Tensor& w) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 3 && w.dim() == 3 && x.is_contiguous() && w.is_contiguous() && dtype_code(x) >= 0 &&
+                    x.scalar_type() == w.scalar_type() && x.size(0) == w.size(0) && x.size(2) == w.size(2),
+                "orion::linear_batched: contiguous [B,M,K] x [B,N,K] float32/bfloat16 expected");
+    const int64_t B = x.size(0), M = x.size(1), K = x.size(2), N = w.size(1);
+    at::Tensor y = at::empty({B, M, N}, x.options());
+    check(ob200_linear_batched(x.data_ptr(), w.data_ptr(), y.data_ptr(), dtype_code(x), (int)B, (int)M, (int)N, (int)K, M * K, N * K,
+                               M * N, quota(), cur_stream()),
+          "ob200_linear_batched");
+    return y;
+}
+
 int64_t set_sm_quota(int64_t n) {
     int old = tls_quota;
     tls_quota = (int)n;
@@ -321,6 +368,10 @@ TORCH_LIBRARY(orion, m) {
     m.def("maxpool(Tensor x, int k, int stride, int pad) -> Tensor");
     m.def("avgpool(Tensor x) -> Tensor");
     m.def("add_act(Tensor a, Tensor b, bool relu) -> Tensor");
+    m.def("layernorm(Tensor x, Tensor? gamma, Tensor? beta, float eps) -> Tensor");
+    m.def("softmax(Tensor x, float scale) -> Tensor");
+    m.def("bias_gelu(Tensor x, Tensor? bias) -> Tensor");
+    m.def("linear_batched(Tensor x, Tensor w) -> Tensor");
     m.def("set_sm_quota(int n) -> int", &set_sm_quota);
     m.def("set_overrides(int on) -> int", &set_overrides);
     m.def("set_tf32(int on) -> int", &set_tf32);
@@ -334,6 +385,10 @@ TORCH_LIBRARY_IMPL(orion, CUDA, m) {
     m.impl("maxpool", &maxpool_op);
     m.impl("avgpool", &avgpool_op);
     m.impl("add_act", &add_act_op);
+    m.impl("layernorm", &layernorm_op);
+    m.impl("softmax", &softmax_op);
+    m.impl("bias_gelu", &bias_gelu_op);
+    m.impl("linear_batched", &linear_batched_op);
 }
 
 TORCH_LIBRARY_IMPL(aten, CUDA, m) {

@@ -20,6 +20,9 @@ CLIENTS = {
     "resnet101_hp": dict(arch="resnet101", batchsize=4, train=False),
     "mobilenet_v2_hp": dict(arch="mobilenet_v2", batchsize=4, train=False),
     "mobilenet_v2_be": dict(arch="mobilenet_v2", batchsize=64, train=True),
+    "bert_hp": dict(arch="bert", batchsize=8, train=False),
+    "bert_be": dict(arch="bert", batchsize=8, train=True),
+    "transformer_be": dict(arch="transformer", batchsize=16, train=True),
 }
 
 
@@ -34,15 +37,19 @@ def _child_env(extra=None, preload=True):
 
 
 def client_args(arch, batchsize, train, rps=0, uniform=False):
-    return {"model_name": arch, "batchsize": batchsize, "rps": rps, "uniform": uniform, "dummy_data": True, "train": train}
+    args = {"batchsize": batchsize, "rps": rps, "uniform": uniform, "dummy_data": True, "train": train}
+    if arch not in ("bert", "transformer"):
+        args["model_name"] = arch
+    return args
 
 
 def run_unscheduled(arch, batchsize, train, iters):
     """Body of a profiling child: one client loop without a scheduler."""
     from benchmarking.benchmark_suite.train_imagenet import imagenet_loop
+    from benchmarking.benchmark_suite.transformer_trainer import bert_loop, transformer_loop
+    loop = {"bert": bert_loop, "transformer": transformer_loop}.get(arch, imagenet_loop)
     barrier = threading.Barrier(1)
-    imagenet_loop(num_iters=iters, local_rank=0, barriers=[barrier], client_barrier=barrier, tid=0,
-                  **client_args(arch, batchsize, train))
+    loop(num_iters=iters, local_rank=0, barriers=[barrier], client_barrier=barrier, tid=0, **client_args(arch, batchsize, train))
 
 
 def profile_client(name, out_dir, iters=12, device=0, timeout=600, extra_env=None):

@@ -72,3 +72,23 @@ def test_training_step_runs_on_overridden_forward_convolutions(ops):
     assert abs(ours[0] - stock[0]) / abs(stock[0]) < 1e-4          # same weights, same data: forward parity
     for a, b in zip(ours[1:], stock[1:]):
         assert abs(a - b) / abs(b) < 5e-2                           # later steps only have to stay close
+
+
+def test_bert_layer_stack_on_orion_kernels_matches_cpu_fp32(ops):
+    """BERT-base layers (hidden 768, 12 heads, FFN 3072, sequence 384) on the tcgen05 GEMM / batched GEMM, LayerNorm,
+    softmax and GELU kernels against float32 CPU math on the same bfloat16 weights; tolerance bf16 relative 2e-2."""
+    from benchmarking.benchmark_suite.transformer_trainer import BertQA
+    torch.manual_seed(11)
+    cfg = dict(layers=3, hidden=768, heads=12, ffn=3072, vocab=30528, max_pos=512, seq=384)
+    model = BertQA(cfg).to(torch.bfloat16).eval()
+    ids = torch.randint(0, 30522, (2, 384))
+    with torch.no_grad():
+        want = model.float()(ids)                      # float32 math on bf16-rounded weights
+        model = model.to(torch.bfloat16).cuda()
+        before = int(torch.ops.orion.own_launches())
+        got = model(ids.cuda(), orion=True)
+        after = int(torch.ops.orion.own_launches())
+    from orion_b200 import kernels
+    assert kernels.read_status() == 0
+    assert after - before == 3 * 10                    # per layer: 4 GEMMs, 2 batched GEMMs, softmax, GELU, 2 LayerNorms
+    assert _rel(got.float(), want) < 2e-2

@@ -105,3 +105,33 @@ def test_profile_shorter_than_the_op_stream_keeps_running(built, tmp_path):
     p = _profile(tmp_path, "p", [(1, 10, 1000)] * 3)
     r = _run({"clients": [{"profile": p, "num_kernels": 3, "iters": 13, "train": False, "ops": [0] * 5}]}, timeout=180)
     assert r["done"] == [13]
+
+
+def test_recorded_run_replays_identically_through_policy_core_and_oracles(built, tmp_path):
+    """ORION_RECORD_SCRIPT: the live scheduler writes its measured phase as an arrival script.  The same
+    script must give one decision log whether it is replayed by the product's policy core, by the Python
+    restatement, or (where it was compiled) by the reference scheduler itself."""
+    import hashlib
+    from oracle import policy_oracle
+    be = _profile(tmp_path, "be", [(1, 40, 9000), (0, 200, 5000), (-1, 30, 3000)] * 8)
+    hp = _profile(tmp_path, "hp", [(1, 60, 8000), (0, 20, 2000)] * 5)
+    script = tmp_path / "recorded.script"
+    r = _run({"clients": [{"profile": be, "num_kernels": 24, "iters": 100000, "train": True, "ops": [1] + [0] * 24},
+                          {"profile": hp, "num_kernels": 10, "iters": 40, "train": False, "ops": [1] + [0] * 10}],
+              "depth": 20000}, env_extra={"ORION_RECORD_SCRIPT": str(script)})
+    assert r["done"][1] == 40 and script.exists()
+    text = script.read_text()
+    assert text.startswith("orion_script 1") and "nclients 2" in text
+    log = tmp_path / "product.log"
+    out = subprocess.run([built["orion_replay"], str(script), "--log", str(log)], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    product = log.read_bytes()
+    assert product.count(b"\nS ") > 100
+    assert policy_oracle.run_script(str(script)).encode() == product
+    ref = os.path.join(ROOT, "oracle", "_ref", "ref_replay")
+    if os.path.exists(ref):
+        ref_log = tmp_path / "ref.log"
+        out = subprocess.run([ref, str(script), os.path.join(ROOT, "oracle", "_ref"), str(ref_log)], capture_output=True, text=True,
+                             timeout=300)
+        assert out.returncode == 0, out.stderr
+        assert hashlib.sha256(ref_log.read_bytes()).hexdigest() == hashlib.sha256(product).hexdigest()
