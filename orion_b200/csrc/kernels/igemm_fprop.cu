@@ -103,13 +103,15 @@ __device__ __forceinline__ void st_chunk(uint8_t* hi, uint8_t*, uint32_t off, co
     *reinterpret_cast<uint4*>(hi + off) = v;
 }
 
-// In place: TF32-rounded high parts; second buffer: exact remainders.
+// The tensor core reads a float32 operand as TF32 by ignoring the low 13 mantissa bits, so the raw
+// value already serves as the high part; only the exact remainder x - trunc(x) is written (second buffer).
 __device__ __forceinline__ void split_chunk(uint8_t* hi, uint8_t* lo) {
     const float4 v = *reinterpret_cast<const float4*>(hi);
-    float4 h, l;
-    h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
-    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-    *reinterpret_cast<float4*>(hi) = h;
+    float4 l;
+    l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+    l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+    l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+    l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
     *reinterpret_cast<float4*>(lo) = l;
 }
 
