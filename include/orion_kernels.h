@@ -133,6 +133,12 @@ int ob200_read_status(void);
 void ob200_set_debug_buffer(long long* dev_buf);
 /* SM count of the current device.  No counterpart in the reference. */
 int ob200_sm_count(void);
+/* Copies [pixels, C] to [pixels, Cpad] (Cpad > C) with zeros in the added channels; elem_bytes 2 or 4.
+ * Lets a 3-channel stem convolution (torchvision resnet / mobilenet conv1, which the reference hands to
+ * cudnnConvolutionForward, src/cuda_capture/intercept_cudnn.cpp:17) use 16-byte operand chunks.
+ * No counterpart in the reference. */
+int ob200_pad_channels(const void* src, void* dst, long long pixels, int C, int Cpad, int elem_bytes, int num_ctas,
+                       void* stream);
 
 #ifdef __cplusplus
 }

@@ -186,3 +186,41 @@ extern "C" int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, 
     avgpool_nhwc_f32_kernel<<<elt_grid((long long)Nb * C, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, HW, C);
     return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- channel padding
+// Copies [pixels, C] to [pixels, Cpad] (Cpad > C), zero in the added channels, so that a
+// channel count that is not a multiple of a 16-byte chunk (the 3-channel image of a stem
+// convolution) can take the vectorised operand path of the implicit-GEMM kernel.
+namespace ob200 {
+template <typename T>
+__global__ void pad_channels_kernel(const T* __restrict__ src, T* __restrict__ dst, long long pixels, int C, int Cpad) {
+    const long long total = pixels * Cpad;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long px = i / Cpad;
+        const int c = (int)(i - px * Cpad);
+        dst[i] = c < C ? src[px * C + c] : T(0);
+    }
+}
+// float32, 3 -> 4 channels: one 16-byte store per pixel.
+__global__ void pad_channels_3to4_f32_kernel(const float* __restrict__ src, float4* __restrict__ dst, long long pixels) {
+    for (long long px = (long long)blockIdx.x * blockDim.x + threadIdx.x; px < pixels; px += (long long)gridDim.x * blockDim.x) {
+        const float* s = src + px * 3;
+        dst[px] = make_float4(__ldg(s), __ldg(s + 1), __ldg(s + 2), 0.f);
+    }
+}
+}  // namespace ob200
+
+extern "C" int ob200_pad_channels(const void* src, void* dst, long long pixels, int C, int Cpad, int elem_bytes, int num_ctas,
+                                  void* stream) {
+    if (pixels <= 0) return 0;
+    if (C <= 0 || Cpad <= C || num_ctas <= 0 || (elem_bytes != 2 && elem_bytes != 4)) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (elem_bytes == 4 && C == 3 && Cpad == 4 && (uintptr_t)dst % 16 == 0)
+        ob200::pad_channels_3to4_f32_kernel<<<elt_grid(pixels, num_ctas), ELT_THREADS, 0, s>>>((const float*)src, (float4*)dst, pixels);
+    else if (elem_bytes == 4)
+        ob200::pad_channels_kernel<float><<<elt_grid(pixels * Cpad, num_ctas), ELT_THREADS, 0, s>>>((const float*)src, (float*)dst, pixels, C, Cpad);
+    else
+        ob200::pad_channels_kernel<unsigned short><<<elt_grid(pixels * Cpad, num_ctas), ELT_THREADS, 0, s>>>(
+            (const unsigned short*)src, (unsigned short*)dst, pixels, C, Cpad);
+    return (int)cudaGetLastError();
+}

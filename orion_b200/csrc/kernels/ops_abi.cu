@@ -63,7 +63,9 @@ extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, i
     int bn = 128;
     const int rem = Kout % 128;
     if (Kout <= 64 || (rem > 0 && rem <= 64 && Kout < 256)) bn = 64;
-    if ((long long)tiles_m * ((Kout + 127) / 128) < num_ctas && Kout >= 128) bn = 64;   // more tiles for small problems
+    // Narrow tiles only while wide ones would leave more than half of the CTAs idle: a wide tile
+    // re-reads and re-splits the activation operand half as often, which outweighs a partial wave.
+    if ((long long)tiles_m * ((Kout + 127) / 128) * 2 <= num_ctas && Kout >= 128) bn = 64;
     const int tiles = tiles_m * ((Kout + bn - 1) / bn);
     int splits = 1;
     if (tiles * 2 <= num_ctas && kblocks >= 8) {

@@ -38,6 +38,7 @@ int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, int W, int C
                            void* stream);
 int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream);
 int ob200_sm_count(void);
+int ob200_pad_channels(const void* src, void* dst, long long pixels, int C, int Cpad, int elem_bytes, int num_ctas, void* stream);
 int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
 int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream);
@@ -101,6 +102,22 @@ const float* fptr(const c10::optional<at::Tensor>& t) {
 // x, w: logical NCHW / KCRS tensors in channels-last memory (physical NHWC / KRSC).
 at::Tensor conv_core(const at::Tensor& x, const at::Tensor& w, const float* scale, const float* shift, const at::Tensor* residual,
                      int act, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int dtype) {
+    // Channel counts that do not fill 16-byte chunks (a 3-channel image) are padded with zero
+    // channels so the convolution takes the kernel's vectorised operand path.  Prepared models
+    // carry a filter that is already padded; only the activation is padded per call then.
+    const int64_t epc = 16 / x.element_size();
+    if (x.size(1) % epc != 0 || w.size(1) != x.size(1)) {
+        const int64_t Cp = (std::max(x.size(1), w.size(1)) + epc - 1) / epc * epc;
+        auto pad = [&](const at::Tensor& t) {
+            if (t.size(1) == Cp) return t;
+            at::Tensor o = at::empty({t.size(0), Cp, t.size(2), t.size(3)}, t.options().memory_format(at::MemoryFormat::ChannelsLast));
+            check(ob200_pad_channels(t.data_ptr(), o.data_ptr(), t.size(0) * t.size(2) * t.size(3), (int)t.size(1), (int)Cp,
+                                     (int)t.element_size(), quota(), cur_stream()),
+                  "ob200_pad_channels");
+            return o;
+        };
+        return conv_core(pad(x), pad(w), scale, shift, residual, act, stride, padding, dilation, dtype);
+    }
     const int64_t Nb = x.size(0), C = x.size(1), H = x.size(2), W = x.size(3);
     const int64_t K = w.size(0), R = w.size(2), S = w.size(3);
     const int64_t P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) / stride[0] + 1;

@@ -41,6 +41,9 @@ def replay(layers, batch, iters, warm, dtype="float32", flush_mb=160):
         w = (torch.randn(k, r, r, c, device=dev) * (1.0 / (c * r * r) ** 0.5)).to(tdtype)
         ho = (h + 2 * p - r) // s + 1
         flops += 2.0 * batch * ho * ho * k * c * r * r
+        epc = 16 // x.element_size()
+        if c % epc:                              # filters are padded once, ahead of time
+            w = torch.nn.functional.pad(w, (0, epc - c % epc)).contiguous()
         work.append((x, w, (s, s), (p, p)))
     flush = torch.empty(flush_mb * 1024 * 1024, dtype=torch.uint8, device=dev) if flush_mb else None
     stream = torch.cuda.current_stream()
@@ -51,6 +54,8 @@ def replay(layers, batch, iters, warm, dtype="float32", flush_mb=160):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for (x, w, s, p) in work:
+            if x.shape[-1] != w.shape[-1]:      # 3-channel stem: the image is padded per call, as the torch op does
+                x = K.pad_channels(x, w.shape[-1])
             K.conv2d_nhwc(x, w, s, p, tf32=tf32)
         e1.record(stream)
         e1.synchronize()

@@ -53,6 +53,8 @@ def lib():
                      "ob200_binary_f32", "ob200_maxpool_nhwc_f32", "ob200_avgpool_nhwc_f32", "ob200_read_status",
                      "ob200_sm_count"):
             getattr(L, name).restype = c_int
+        L.ob200_pad_channels.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
+        L.ob200_pad_channels.restype = c_int
         _lib = L
     return _lib
 
@@ -113,6 +115,15 @@ def conv2d_nhwc(x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None
             counters = torch.zeros(tiles, device=x.device, dtype=torch.int32)
         _check(lib().ob200_conv2d_fprop_ex(*args, bn, splits, _ptr(scratch), _ptr(counters), n, _stream()),
                "ob200_conv2d_fprop_ex")
+    return y
+
+
+def pad_channels(x, c_pad, num_ctas=None):
+    """[..., C] contiguous -> [..., c_pad] with zeros in the added channels."""
+    assert x.is_cuda and x.is_contiguous() and c_pad > x.shape[-1]
+    y = torch.empty(x.shape[:-1] + (c_pad,), device=x.device, dtype=x.dtype)
+    _check(lib().ob200_pad_channels(_ptr(x), _ptr(y), x.numel() // x.shape[-1], x.shape[-1], c_pad, x.element_size(),
+                                    num_ctas or sm_count(), _stream()), "ob200_pad_channels")
     return y
 
 

@@ -52,6 +52,11 @@ class FusedConv(nn.Module):
         super().__init__()
         assert conv.groups == 1 and conv.padding_mode == "zeros"
         w = conv.weight.detach()
+        # a channel count that does not fill 16-byte chunks (the 3-channel stem) is zero-padded once here;
+        # the op pads the activation to match on every call
+        epc = 16 // w.element_size()
+        if w.shape[1] % epc:
+            w = torch.nn.functional.pad(w, (0, 0, 0, 0, 0, epc - w.shape[1] % epc))
         self.register_buffer("weight", w.contiguous(memory_format=torch.channels_last))
         k = w.shape[0]
         if bn is not None:

@@ -53,6 +53,21 @@ def test_conv_fp32_ragged_shapes(K, shape):
     assert _conv(K, *shape) < FP32_TOL
 
 
+@pytest.mark.parametrize("dtype,c,cp", [(torch.float32, 3, 4), (torch.float32, 5, 8), (torch.bfloat16, 3, 8)])
+def test_pad_channels_and_padded_stem_convolution(K, dtype, c, cp):
+    """Zero channels change nothing: the padded stem equals the oracle's convolution of the unpadded one."""
+    x = torch.randn(2, 30, 30, c, device="cuda", dtype=dtype)
+    xp = K.pad_channels(x, cp)
+    assert xp.shape == (2, 30, 30, cp)
+    assert torch.equal(xp[..., :c], x) and torch.count_nonzero(xp[..., c:]) == 0
+    w = (torch.randn(64, 7, 7, c, device="cuda") / (c * 49) ** 0.5).to(dtype)
+    wp = K.pad_channels(w, cp)
+    y = K.conv2d_nhwc(xp, wp, (2, 2), (3, 3))
+    assert K.read_status() == 0
+    want = O.conv2d_nhwc(x, w, (2, 2), (3, 3), (1, 1))
+    assert O.rel_err(y, want) < (FP32_TOL if dtype == torch.float32 else BF16_TOL)
+
+
 def test_conv_dilation_and_empty_batch(K):
     assert _conv(K, 2, 16, 16, 32, 32, 3, 1, 2, dil=2) < FP32_TOL
     x = torch.empty(0, 8, 8, 16, device="cuda")
