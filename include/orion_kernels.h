@@ -131,6 +131,10 @@ int ob200_read_status(void);
  * waiting: [0] epilogue, [1] MMA on operands, [2] MMA on a free accumulator, [3] splitter,
  * [4] producer, [5] whole kernel. */
 void ob200_set_debug_buffer(long long* dev_buf);
+/* Number of implicit-GEMM launches of this process whose operands were fed by TMA tensor maps (the others
+ * gathered with 16-byte asynchronous copies: strided data gradients, filter gradients, channel counts below
+ * one k-block or k-blocks that straddle filter taps).  No counterpart in the reference. */
+long long ob200_tma_launch_count(void);
 /* SM count of the current device.  No counterpart in the reference. */
 int ob200_sm_count(void);
 /* Copies [pixels, C] to [pixels, Cpad] (Cpad > C) with zeros in the added channels; elem_bytes 2 or 4.

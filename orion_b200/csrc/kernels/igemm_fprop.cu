@@ -32,9 +32,13 @@
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the status
 // word, releases TMEM and returns.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+
+#include <atomic>
 
 #include "igemm_params.h"
 #include "sm100_primitives.cuh"
@@ -226,7 +230,7 @@ __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volat
 }
 
 template <typename T, int BN, int PASSES>
-__global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmParams p) {
+__global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_constant__ IgemmParams p) {
     using C = Cfg<T, BN, PASSES>;
     using Chunk = typename ChunkOf<T>::type;
     extern __shared__ uint8_t smem_raw[];
@@ -240,7 +244,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
 
     if (tid == 0) {
         for (int s = 0; s < C::STAGES; s++) {
-            mbar_init(&ctl->raw_full[s], PROD_WARPS * 32);   // every producer thread, when its copies have landed
+            // every producer thread, when its copies have landed; or the one TMA-issuing thread plus the byte count
+            mbar_init(&ctl->raw_full[s], p.use_tma ? 1 : PROD_WARPS * 32);
             mbar_init(&ctl->full[s], SPLIT_WARPS);           // one elected lane per splitter warp
             mbar_init(&ctl->empty[s], 1);      // tcgen05.commit
         }
@@ -518,6 +523,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const IgemmPar
             const T* __restrict__ Wt = W0 + (long long)bidx * p.batch_stride_w;
             const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
             const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
+            if (p.use_tma) {
+                // Both operand tiles of a k-block arrive by one TMA copy each, issued by a single thread:
+                // 128 im2col rows of the activation (zero outside the image, walking pixels in GEMM row
+                // order from the tile's first pixel) and BN filter rows, both landing in the 128-byte
+                // swizzled layout the MMA descriptors expect.
+                if (pt == 0) {
+                    const long long m0 = (long long)tm * BM;
+                    const int pq = p.OH * p.OW;
+                    const int n_img = (int)(m0 / pq);
+                    const int rem = (int)(m0 - (long long)n_img * pq);
+                    const int op = rem / p.OW, oq = rem - op * p.OW;
+                    const int cw = oq * p.bmul_w + p.tma_base_w, ch = op * p.bmul_h + p.tma_base_h;
+                    const int cn = bidx * p.Nb + n_img;
+                    for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+                        const int s = it % C::STAGES;
+                        const int r = kb / p.kblocks_per_r;
+                        const int kin = (kb - r * p.kblocks_per_r) * C::BK;
+                        const int ts = kin / p.C, tc = kin - ts * p.C;
+                        const int off_h = p.step_h >= 0 ? r * p.step_h : (p.R - 1 - r) * -p.step_h;
+                        const int off_w = p.step_w >= 0 ? ts * p.step_w : (p.S - 1 - ts) * -p.step_w;
+                        if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                            if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
+                            dead = true;
+                            break;
+                        }
+                        const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
+                        const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                        mbar_arrive_expect_tx(&ctl->raw_full[s], C::A_BYTES + C::B_BYTES);
+                        tma_load_im2col_4d(a_dst, p.tmap_a, &ctl->raw_full[s], tc, cw, ch, cn, (uint16_t)off_w, (uint16_t)off_h);
+                        tma_load_tile_4d(b_dst, p.tmap_b, &ctl->raw_full[s], kin, r, tn * BN, bidx);
+                    }
+                } else {
+                    break;   // the other producer threads have nothing to do
+                }
+                continue;
+            }
             if (p.mode == 1) {
                 // Filter gradient (float32 data).  A k-block is 32 consecutive output pixels.  Both operands
                 // have the pixel index as their slow dimension in memory, so they are transposed on the way
@@ -746,9 +787,106 @@ static cudaError_t launch_cfg(const IgemmParams& p, int num_ctas, cudaStream_t s
 
 }  // namespace ob200
 
+namespace ob200 {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+using EncodeIm2colFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const int*, const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct TmaApi {
+    EncodeTiledFn tiled = nullptr;
+    EncodeIm2colFn im2col = nullptr;
+    bool ok = false;
+};
+
+// The two driver entry points, looked up once through the runtime (no link against the driver library).
+static const TmaApi& tma_api() {
+    static const TmaApi api = [] {
+        TmaApi a;
+        const char* off = getenv("ORION_NO_TMA");
+        if (off && off[0] == '1') return a;
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess && f &&
+            q == cudaDriverEntryPointSuccess)
+            a.tiled = reinterpret_cast<EncodeTiledFn>(f);
+        f = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &f, cudaEnableDefault, &q) == cudaSuccess && f &&
+            q == cudaDriverEntryPointSuccess)
+            a.im2col = reinterpret_cast<EncodeIm2colFn>(f);
+        a.ok = a.tiled && a.im2col;
+        return a;
+    }();
+    return api;
+}
+
+// Decides whether this launch can feed both operands by TMA and, if so, encodes the two tensor maps.
+// Needs unit-divisor gathers (forward, stride-1 data gradient, GEMM), channels that fill whole 16-byte
+// chunks, and k-blocks that never straddle two filter taps (1x1 filters, or C a multiple of the k-block).
+static bool setup_tma(IgemmParams& p, int bn) {
+    static_assert(sizeof(CUtensorMap) == sizeof(p.tmap_a), "tensor map size");
+    p.use_tma = 0;
+    const TmaApi& api = tma_api();
+    if (!api.ok || p.mode != 0 || p.div_h != 1 || p.div_w != 1) return false;
+    const int elem = p.dtype == 1 ? 2 : 4;
+    const int bk = 128 / elem;
+    if (p.C < bk || (p.C * elem) % 16) return false;
+    if (p.R * p.S != 1 && p.C % bk != 0) return false;
+    if (p.bmul_h < 1 || p.bmul_h > 8 || p.bmul_w < 1 || p.bmul_w > 8) return false;
+    if (((uintptr_t)p.x | (uintptr_t)p.w) % 16) return false;
+    const int batch = p.batch > 1 ? p.batch : 1;
+    if (batch > 1 && (p.batch_stride_x != (long long)p.Nb * p.IH * p.IW * p.C || (p.batch_stride_w * elem) % 16)) return false;
+    const int base_h = p.badd_h + (p.step_h < 0 ? (p.R - 1) * p.step_h : 0);
+    const int base_w = p.badd_w + (p.step_w < 0 ? (p.S - 1) * p.step_w : 0);
+    const int span_h = (p.R - 1) * (p.step_h < 0 ? -p.step_h : p.step_h);
+    const int span_w = (p.S - 1) * (p.step_w < 0 ? -p.step_w : p.step_w);
+    // Base pixels run from the lower corner to (extent - 1 + upper corner): exactly OH x OW of them.
+    int lower[2] = {base_w, base_h};
+    int upper[2] = {base_w + (p.OW - 1) * p.bmul_w + 1 - p.IW, base_h + (p.OH - 1) * p.bmul_h + 1 - p.IH};
+    for (int i = 0; i < 2; i++)
+        if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return false;
+    if (span_h > 127 || span_w > 127) return false;
+    const CUtensorMapDataType dt = p.dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)p.C, (cuuint64_t)p.IW, (cuuint64_t)p.IH, (cuuint64_t)p.Nb * batch};
+        cuuint64_t strides[3] = {(cuuint64_t)p.C * elem, (cuuint64_t)p.IW * p.C * elem, (cuuint64_t)p.IH * p.IW * p.C * elem};
+        cuuint32_t steps[4] = {1, (cuuint32_t)p.bmul_w, (cuuint32_t)p.bmul_h, 1};
+        if (api.im2col(reinterpret_cast<CUtensorMap*>(p.tmap_a), dt, 4, const_cast<void*>(p.x), dims, strides, lower, upper,
+                       (cuuint32_t)bk, (cuuint32_t)BM, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    {
+        const cuuint64_t sc = (cuuint64_t)p.S * p.C;
+        cuuint64_t dims[4] = {sc, (cuuint64_t)p.R, (cuuint64_t)p.Kout, (cuuint64_t)batch};
+        cuuint64_t strides[3] = {sc * elem, sc * p.R * elem,
+                                 (batch > 1 ? (cuuint64_t)p.batch_stride_w : sc * p.R * p.Kout) * elem};
+        cuuint32_t box[4] = {(cuuint32_t)bk, 1, (cuuint32_t)bn, 1};
+        cuuint32_t steps[4] = {1, 1, 1, 1};
+        if (api.tiled(reinterpret_cast<CUtensorMap*>(p.tmap_b), dt, 4, const_cast<void*>(p.w), dims, strides, box, steps,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    p.tma_base_h = base_h;
+    p.tma_base_w = base_w;
+    p.use_tma = 1;
+    return true;
+}
+
+}  // namespace ob200
+
+static std::atomic<long long> g_tma_launches{0};
+
+extern "C" long long ob200_tma_launch_count(void) { return g_tma_launches.load(std::memory_order_relaxed); }
+
 extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_ctas, void* stream) {
     using namespace ob200;
     IgemmParams p = *params;
+    if (setup_tma(p, bn)) g_tma_launches.fetch_add(1, std::memory_order_relaxed);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (p.dtype == 0) {
         return (int)(bn == 64 ? launch_cfg<float, 64, 3>(p, num_ctas, s) : launch_cfg<float, 128, 3>(p, num_ctas, s));

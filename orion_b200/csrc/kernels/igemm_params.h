@@ -5,6 +5,12 @@
 extern "C" {
 #endif
 
+#ifdef __cplusplus
+#define OB200_ALIGN64 alignas(64)
+#else
+#define OB200_ALIGN64 _Alignas(64)
+#endif
+
 typedef struct IgemmParams {
     const void* x;          /* activations, NHWC [Nb, H, W, C] */
     const void* w;          /* filters, KRSC [Kout, R, S, C] */
@@ -43,6 +49,14 @@ typedef struct IgemmParams {
     int mode;
     int ctiles;             /* filter gradient: channel blocks per tap, ceil(C / BN) */
     int bmul_h, bmul_w, badd_h, badd_w, step_h, step_w, div_h, div_w;
+    /* Filled by ob200_igemm_launch.  use_tma = 1: both operands arrive by TMA, the activation through an
+     * im2col tensor map over [Nb, IH, IW, C] whose traversal starts at pixel (oh*bmul_h + tma_base_h,
+     * ow*bmul_w + tma_base_w) and whose per-tap offsets are non-negative, the filter through a tiled map
+     * over [batch, Kout, R, S*C].  0: the producer warps gather with 16-byte asynchronous copies. */
+    int use_tma;
+    int tma_base_h, tma_base_w;
+    OB200_ALIGN64 unsigned char tmap_a[128];
+    OB200_ALIGN64 unsigned char tmap_b[128];
 } IgemmParams;
 
 /* Forward convolution: rows are output pixels (P x Q), the source is the input image. */

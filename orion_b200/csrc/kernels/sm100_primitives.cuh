@@ -54,6 +54,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// One arrival that also announces `bytes` of asynchronous (TMA) transfers to come; the phase
+// completes when the arrival count and the byte count are both met.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// TMA loads (cp.async.bulk.tensor), completion signalled on `bar` by byte count.  `tmap` points to a
+// CUtensorMap in kernel-parameter space.  The innermost coordinate times the element size must be a
+// multiple of 16 bytes.
+//
+// im2col, NHWC rank 4: copies `pixelsPerColumn` pixels x `channelsPerPixel` channels starting at channel
+// c of base pixel (w, h, n) (input-image coordinates; the base pixel must lie inside the map's bounding
+// box), walking base pixels along W, then H, then N in the map's traversal strides; every pixel is read
+// at (w + off_w, h + off_h), zero outside the image.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* tmap, uint64_t* bar, int c, int w, int h, int n,
+                                                   uint16_t off_w, uint16_t off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+        : "memory");
+}
+// Tiled, rank 4: copies the map's box starting at (c0, c1, c2, c3); out-of-range elements read as zero.
+__device__ __forceinline__ void tma_load_tile_4d(uint32_t dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

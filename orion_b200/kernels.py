@@ -53,6 +53,8 @@ def lib():
                      "ob200_binary_f32", "ob200_maxpool_nhwc_f32", "ob200_avgpool_nhwc_f32", "ob200_read_status",
                      "ob200_sm_count"):
             getattr(L, name).restype = c_int
+        L.ob200_tma_launch_count.argtypes = []
+        L.ob200_tma_launch_count.restype = c_ll
         L.ob200_pad_channels.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
         L.ob200_pad_channels.restype = c_int
         _lib = L
@@ -78,6 +80,11 @@ def _dtype_code(t):
     if t.dtype == torch.bfloat16:
         return 1
     raise TypeError("orion_b200 kernels take float32 or bfloat16, got %s" % t.dtype)
+
+
+def tma_launch_count():
+    """Implicit-GEMM launches so far whose operands were fed by TMA."""
+    return lib().ob200_tma_launch_count()
 
 
 def sm_count():

@@ -68,6 +68,20 @@ def test_pad_channels_and_padded_stem_convolution(K, dtype, c, cp):
     assert O.rel_err(y, want) < (FP32_TOL if dtype == torch.float32 else BF16_TOL)
 
 
+def test_tma_feeds_the_eligible_shapes(K):
+    """Forward convolutions with whole k-blocks per tap and GEMMs take the TMA path; small channel counts gather."""
+    n0 = K.tma_launch_count()
+    assert _conv(K, 2, 14, 14, 64, 96, 3, 1, 1) < FP32_TOL          # 3x3, C multiple of 32
+    assert _conv(K, 2, 15, 13, 96, 40, 3, 2, 1) < FP32_TOL          # strided, ragged image
+    assert _conv(K, 3, 9, 9, 44, 24, 1, 2, 0) < FP32_TOL            # 1x1 strided, channel tail inside a k-block
+    assert _conv(K, 2, 12, 12, 32, 32, 3, 1, 2, dil=2) < FP32_TOL   # dilated
+    assert _conv(K, 2, 8, 8, 128, 64, 3, 1, 1, dtype=torch.bfloat16) < BF16_TOL
+    assert K.tma_launch_count() - n0 == 5
+    assert _conv(K, 2, 10, 10, 16, 32, 3, 1, 1) < FP32_TOL          # C below one k-block: gathered
+    assert _conv(K, 2, 10, 10, 48, 32, 3, 1, 1) < FP32_TOL          # k-blocks straddle taps: gathered
+    assert K.tma_launch_count() - n0 == 5
+
+
 def test_conv_dilation_and_empty_batch(K):
     assert _conv(K, 2, 16, 16, 32, 32, 3, 1, 2, dil=2) < FP32_TOL
     x = torch.empty(0, 8, 8, 16, device="cuda")
