@@ -221,6 +221,16 @@ __device__ __forceinline__ void store_out(const IgemmParams& p, const EpiCoef& c
     }
 }
 
+// Row of y that GEMM row m is stored at.
+__device__ __forceinline__ long long out_row(const IgemmParams& p, long long m) {
+    if (!p.out_map) return m;
+    const int pq = p.OH * p.OW;
+    const int n_img = (int)(m / pq);
+    const int rem = (int)(m - (long long)n_img * pq);
+    const int i = rem / p.OW, j = rem - i * p.OW;
+    return ((long long)n_img * p.out_H + i * p.out_mul_h + p.out_add_h) * p.out_W + j * p.out_mul_w + p.out_add_w;
+}
+
 // mbar_wait that also adds the cycles spent waiting to `acc` (role-level wait breakdown for tuning).
 __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long& acc) {
     const long long t0 = clock64();   // the first try_wait may already suspend the thread for a while
@@ -360,7 +370,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     for (int i = 0; i < 8; i++) {
                         const int rr = i * 4 + sub;
                         const long long m = tile_row0 + rr;
-                        if (m < p.M) store_out<T>(p, coef, *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc), m, n, y_off);
+                        if (m < p.M) store_out<T>(p, coef, *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc), out_row(p, m), n, y_off);
                     }
                 }
                 __syncwarp();
@@ -388,7 +398,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                                 float4* part = reinterpret_cast<float4*>(p.scratch + ((long long)tile * BM + warp * 32 + rr) * BN + cb * 32 + cc);
                                 const float4 v = __ldcg(part);
                                 *part = make_float4(0.f, 0.f, 0.f, 0.f);   // leave the scratch zeroed for the next launch
-                                store_out<T>(p, coef, v, m, n, y_off);
+                                store_out<T>(p, coef, v, out_row(p, m), n, y_off);
                             }
                         }
                     }
@@ -552,7 +562,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                         const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
                         mbar_arrive_expect_tx(&ctl->raw_full[s], C::A_BYTES + C::B_BYTES);
                         tma_load_im2col_4d(a_dst, p.tmap_a, &ctl->raw_full[s], tc, cw, ch, cn, (uint16_t)off_w, (uint16_t)off_h);
-                        tma_load_tile_4d(b_dst, p.tmap_b, &ctl->raw_full[s], kin, r, tn * BN, bidx);
+                        tma_load_tile_5d(b_dst, p.tmap_b, &ctl->raw_full[s], tc, ts, r, tn * BN, bidx);
                     }
                 } else {
                     break;   // the other producer threads have nothing to do
@@ -860,13 +870,17 @@ static bool setup_tma(IgemmParams& p, int bn) {
             return false;
     }
     {
-        const cuuint64_t sc = (cuuint64_t)p.S * p.C;
-        cuuint64_t dims[4] = {sc, (cuuint64_t)p.R, (cuuint64_t)p.Kout, (cuuint64_t)batch};
-        cuuint64_t strides[3] = {sc * elem, sc * p.R * elem,
-                                 (batch > 1 ? (cuuint64_t)p.batch_stride_w : sc * p.R * p.Kout) * elem};
-        cuuint32_t box[4] = {(cuuint32_t)bk, 1, (cuuint32_t)bn, 1};
-        cuuint32_t steps[4] = {1, 1, 1, 1};
-        if (api.tiled(reinterpret_cast<CUtensorMap*>(p.tmap_b), dt, 4, const_cast<void*>(p.w), dims, strides, box, steps,
+        // Filter as [batch, Kout, R, S, C]; a tap subset changes the base address and the tap strides.
+        const bool subset = p.w_R > 0;
+        const cuuint64_t wR = subset ? p.w_R : p.R, wS = subset ? p.w_S : p.S;
+        const cuuint64_t rstep = subset ? p.w_rstep : 1, sstep = subset ? p.w_sstep : 1;
+        const char* base = reinterpret_cast<const char*>(p.w) + (subset ? ((size_t)p.w_r0 * wS + p.w_s0) * p.C * elem : 0);
+        cuuint64_t dims[5] = {(cuuint64_t)p.C, (cuuint64_t)p.S, (cuuint64_t)p.R, (cuuint64_t)p.Kout, (cuuint64_t)batch};
+        cuuint64_t strides[4] = {sstep * p.C * elem, rstep * wS * p.C * elem, wR * wS * p.C * elem,
+                                 (batch > 1 ? (cuuint64_t)p.batch_stride_w : wR * wS * p.C * p.Kout) * elem};
+        cuuint32_t box[5] = {(cuuint32_t)bk, 1, 1, (cuuint32_t)bn, 1};
+        cuuint32_t steps[5] = {1, 1, 1, 1, 1};
+        if (api.tiled(reinterpret_cast<CUtensorMap*>(p.tmap_b), dt, 5, const_cast<char*>(base), dims, strides, box, steps,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return false;
@@ -887,6 +901,7 @@ extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_cta
     using namespace ob200;
     IgemmParams p = *params;
     if (setup_tma(p, bn)) g_tma_launches.fetch_add(1, std::memory_order_relaxed);
+    else if (p.require_tma || p.w_R > 0) return -4;   // tap subsets exist only on the TMA path
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (p.dtype == 0) {
         return (int)(bn == 64 ? launch_cfg<float, 64, 3>(p, num_ctas, s) : launch_cfg<float, 128, 3>(p, num_ctas, s));

@@ -49,10 +49,19 @@ typedef struct IgemmParams {
     int mode;
     int ctiles;             /* filter gradient: channel blocks per tap, ceil(C / BN) */
     int bmul_h, bmul_w, badd_h, badd_w, step_h, step_w, div_h, div_w;
+    /* Tap subset (TMA-fed launches only): the filter in memory has w_R x w_S taps and the launch iterates
+     * R x S of them, tap (t, u) being filter tap (w_r0 + w_rstep*t, w_s0 + w_sstep*u).  w_R = 0: the launch
+     * iterates the whole filter.  One parity class of a strided data gradient uses this. */
+    int w_R, w_S, w_r0, w_s0, w_rstep, w_sstep;
+    /* Output row map: out_map = 0 stores GEMM row m at row m of y; 1 stores row m = (n*OH + i)*OW + j at
+     * pixel (n, i*out_mul_h + out_add_h, j*out_mul_w + out_add_w) of an [Nb, out_H, out_W, Kout] tensor. */
+    int out_map, out_H, out_W, out_mul_h, out_mul_w, out_add_h, out_add_w;
+    /* require_tma = 1: ob200_igemm_launch returns -4 instead of falling back to the gathering producers. */
+    int require_tma;
     /* Filled by ob200_igemm_launch.  use_tma = 1: both operands arrive by TMA, the activation through an
      * im2col tensor map over [Nb, IH, IW, C] whose traversal starts at pixel (oh*bmul_h + tma_base_h,
      * ow*bmul_w + tma_base_w) and whose per-tap offsets are non-negative, the filter through a tiled map
-     * over [batch, Kout, R, S*C].  0: the producer warps gather with 16-byte asynchronous copies. */
+     * over [batch, Kout, R, S, C].  0: the producer warps gather with 16-byte asynchronous copies. */
     int use_tma;
     int tma_base_h, tma_base_w;
     OB200_ALIGN64 unsigned char tmap_a[128];

@@ -155,6 +155,78 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
 // Data gradient of the convolution: dx[n,h,w,c] = sum_{r,s,k} dy[n,(h+pad-r*dil)/stride,(w+pad-s*dil)/stride,k] * w[k,r,s,c]
 // over the taps whose division is exact.  wt is the filter re-laid out as [C, R, S, Kout]
 // (ob200_filter_transpose).  Same kernel as the forward pass, with the gather geometry of
+// Strided data gradient as one dense problem per parity class of the input pixel.  Input pixel
+// h = a + stride*i receives only from taps r = r0 + stride*t with r0 = (a + pad) mod stride, and reads
+// dy row i + (a + pad - r0)/stride - t: a unit-stride gather over that class's pixels and taps, with
+// no multiplications by structural zeros (a stride-2 gradient spends a quarter of the dense work).
+// Classes without taps (1x1 filters) keep the zeros of the initial clear.  Returns -4 when a class
+// cannot be fed by TMA (the caller then runs the single dense launch).
+static int dgrad_by_parity_class(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout,
+                                 int R, int S, int stride_h, int stride_w, int pad_h, int pad_w, int P, int Q, int num_ctas,
+                                 void* stream, int dev) {
+    const int elem = dtype == 1 ? 2 : 4;
+    const int bk = 128 / elem;
+    if (Kout % bk != 0) return -4;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (R < stride_h || S < stride_w)
+        if (cudaMemsetAsync(dx, 0, (size_t)Nb * H * W * C * elem, st) != cudaSuccess) return -1;
+    for (int a = 0; a < stride_h && a < H; a++) {
+        for (int b = 0; b < stride_w && b < W; b++) {
+            const int Hc = (H - a + stride_h - 1) / stride_h, Wc = (W - b + stride_w - 1) / stride_w;
+            const int r0 = (a + pad_h) % stride_h, s0 = (b + pad_w) % stride_w;
+            const int Rc = r0 < R ? (R - r0 + stride_h - 1) / stride_h : 0;
+            const int Sc = s0 < S ? (S - s0 + stride_w - 1) / stride_w : 0;
+            if (Rc == 0 || Sc == 0) {
+                if (!(R < stride_h || S < stride_w)) return -1;   // unreachable: an empty class implies the clear above
+                continue;
+            }
+            const long long M = (long long)Nb * Hc * Wc;
+            int bn = 128, splits = 1;
+            ob200_plan_conv(dtype, M, C, Rc, Sc, Kout, num_ctas, &bn, &splits);
+            IgemmParams p;
+            memset(&p, 0, sizeof p);
+            p.x = dy; p.w = wt; p.y = dx;
+            p.dtype = dtype;
+            p.Nb = Nb; p.H = H; p.W = W; p.P = P; p.Q = Q; p.R = Rc; p.S = Sc;
+            p.C = Kout; p.Kout = C;
+            p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = p.dil_w = 1;
+            p.M = (int)M;
+            p.kblocks_per_r = (Sc * Kout + bk - 1) / bk;
+            p.num_kblocks = Rc * p.kblocks_per_r;
+            p.tiles_m = (int)((M + 127) / 128);
+            p.tiles_n = (C + bn - 1) / bn;
+            if (splits > p.num_kblocks) splits = p.num_kblocks;
+            p.status = status_word(dev);
+            p.debug = g_debug;
+            if (splits > 1) {
+                const long long tiles = (long long)p.tiles_m * p.tiles_n;
+                Scratch* sc = scratch_for(dev, st);
+                if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
+                    splits = 1;
+                } else {
+                    p.scratch = sc->partial;
+                    p.counters = sc->counters;
+                }
+            }
+            p.splits = splits;
+            p.OH = Hc; p.OW = Wc; p.IH = P; p.IW = Q;
+            p.bmul_h = p.bmul_w = 1;
+            p.badd_h = (a + pad_h - r0) / stride_h; p.badd_w = (b + pad_w - s0) / stride_w;
+            p.step_h = p.step_w = -1;
+            p.div_h = p.div_w = 1;
+            p.w_R = R; p.w_S = S; p.w_r0 = r0; p.w_s0 = s0; p.w_rstep = stride_h; p.w_sstep = stride_w;
+            p.out_map = 1; p.out_H = H; p.out_W = W;
+            p.out_mul_h = stride_h; p.out_mul_w = stride_w; p.out_add_h = a; p.out_add_w = b;
+            p.require_tma = 1;
+            const long long units = (long long)p.tiles_m * p.tiles_n * splits;
+            const int grid = units < num_ctas ? (int)units : num_ctas;
+            const int rc = ob200_igemm_launch(&p, bn, grid, stream);
+            if (rc != 0) return rc;
+        }
+    }
+    return 0;
+}
+
 // igemm_set_dgrad: GEMM rows are input pixels, the reduction runs over (r, s, k).
 extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R,
                                   int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas,
@@ -172,6 +244,11 @@ extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int 
     if (M > 0x7fffffffLL) return -1;
     int dev = 0;
     cudaGetDevice(&dev);
+    if ((stride_h > 1 || stride_w > 1) && dil_h == 1 && dil_w == 1) {
+        const int rc = dgrad_by_parity_class(dy, wt, dx, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w, P, Q,
+                                             num_ctas, stream, dev);
+        if (rc != -4) return rc;
+    }
     int bn = 128, splits = 1;
     ob200_plan_conv(dtype, M, C, R, S, Kout, num_ctas, &bn, &splits);
     IgemmParams p;

@@ -33,6 +33,9 @@ def _dgrad_ref(dy, w, hw, stride, pad, dil):
     (4, 56, 56, 64, 64, 3, 1, 1), (4, 56, 56, 64, 256, 1, 1, 0), (4, 56, 56, 128, 128, 3, 2, 1), (4, 56, 56, 256, 512, 1, 2, 0),
     (4, 14, 14, 256, 256, 3, 1, 1), (4, 7, 7, 512, 512, 3, 1, 1), (2, 11, 9, 24, 40, 3, 2, 1), (2, 12, 12, 16, 20, 5, 1, 2),
     (1, 224, 224, 3, 64, 7, 2, 3), (2, 16, 16, 32, 32, 3, 1, 2),
+    # strided gradients split by parity class: odd image sizes, stride 3, 5x5 taps, 2x2 filter with stride 2, 1x1 with pad
+    (2, 15, 13, 32, 64, 3, 2, 1), (2, 14, 14, 32, 32, 3, 3, 1), (2, 12, 12, 16, 64, 5, 2, 2), (2, 8, 8, 48, 32, 2, 2, 0),
+    (2, 9, 9, 40, 96, 1, 2, 1), (3, 7, 7, 64, 32, 3, 2, 0),
 ])
 def test_conv_dgrad_fp32(K, shape):
     Nb, H, W, C, Ko, R, stride, pad = shape
@@ -44,6 +47,19 @@ def test_conv_dgrad_fp32(K, shape):
     dx = K.conv2d_dgrad_nhwc(dy, w, (H, W), (stride, stride), (pad, pad), (dil, dil))
     assert K.read_status() == 0
     assert O.rel_err(dx, _dgrad_ref(dy, w, (H, W), stride, pad, dil)) < TOL
+
+
+def test_strided_dgrad_runs_one_tma_launch_per_parity_class(K):
+    dy = torch.randn(2, 14, 14, 64, device="cuda")
+    w = torch.randn(64, 3, 3, 32, device="cuda") / 24.0
+    n0 = K.tma_launch_count()
+    dx = K.conv2d_dgrad_nhwc(dy, w, (28, 28), (2, 2), (1, 1))
+    assert K.tma_launch_count() - n0 == 4
+    assert O.rel_err(dx, _dgrad_ref(dy, w, (28, 28), 2, 1, 1)) < TOL
+    dyb, wb = dy.bfloat16(), w.bfloat16()
+    dxb = K.conv2d_dgrad_nhwc(dyb, wb, (28, 28), (2, 2), (1, 1))
+    assert O.rel_err(dxb, _dgrad_ref(dyb, wb, (28, 28), 2, 1, 1)) < 2e-2
+    assert K.read_status() == 0
 
 
 def test_conv_dgrad_bf16_and_filter_transpose(K):
