@@ -414,7 +414,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMA issue
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(sizeof(T) == 4 ? 2 : 1, BM, BN);
+            // A TMA-fed filter gradient keeps both operands the way they lie in memory (pixel-major, i.e.
+            // MN-major for this GEMM); everything else stages K-major rows.
+            const bool mn_major = p.mode == 1 && p.use_tma;
+            const uint32_t idesc = umma_idesc(sizeof(T) == 4 ? 2 : 1, BM, BN) | (mn_major ? (UMMA_IDESC_A_MN | UMMA_IDESC_B_MN) : 0u);
+            const uint64_t kstep = mn_major ? (1024 >> 4) : (32 >> 4);   // descriptor address advance per k-step of 8 (16 for bf16)
             uint32_t it = 0;
             int local = 0;
             bool dead = false;
@@ -442,23 +446,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     tc_fence_after_sync();
                     const uint32_t base = smem_u32(smem + s * C::STAGE_BYTES);
                     if (C::kSplit) {
-                        const uint64_t a_hi = umma_desc_sw128(base);
-                        const uint64_t a_lo = umma_desc_sw128(base + C::A_BYTES);
-                        const uint64_t b_hi = umma_desc_sw128(base + 2 * C::A_BYTES);
-                        const uint64_t b_lo = umma_desc_sw128(base + 2 * C::A_BYTES + C::B_BYTES);
+                        const uint64_t a_hi = mn_major ? umma_desc_mn(p.mn_desc_bits, base) : umma_desc_sw128(base);
+                        const uint64_t a_lo = mn_major ? umma_desc_mn(p.mn_desc_bits, base + C::A_BYTES) : umma_desc_sw128(base + C::A_BYTES);
+                        const uint64_t b_hi = mn_major ? umma_desc_mn(p.mn_desc_bits, base + 2 * C::A_BYTES) : umma_desc_sw128(base + 2 * C::A_BYTES);
+                        const uint64_t b_lo = mn_major ? umma_desc_mn(p.mn_desc_bits, base + 2 * C::A_BYTES + C::B_BYTES)
+                                                       : umma_desc_sw128(base + 2 * C::A_BYTES + C::B_BYTES);
 #pragma unroll
                         for (int ks = 0; ks < 4; ks++) {
-                            const uint64_t o = (uint64_t)(ks * 2);   // 32 bytes per k-step, in 16-byte units
+                            const uint64_t o = (uint64_t)ks * kstep;
                             umma_tf32(d, a_lo + o, b_hi + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
                             umma_tf32(d, a_hi + o, b_lo + o, idesc, 1u);
                             umma_tf32(d, a_hi + o, b_hi + o, idesc, 1u);
                         }
                     } else {
-                        const uint64_t a = umma_desc_sw128(base);
-                        const uint64_t b = umma_desc_sw128(base + C::A_BYTES);
+                        const uint64_t a = mn_major ? umma_desc_mn(p.mn_desc_bits, base) : umma_desc_sw128(base);
+                        const uint64_t b = mn_major ? umma_desc_mn(p.mn_desc_bits, base + C::A_BYTES) : umma_desc_sw128(base + C::A_BYTES);
 #pragma unroll
                         for (int ks = 0; ks < 4; ks++) {
-                            const uint64_t o = (uint64_t)(ks * 2);
+                            const uint64_t o = (uint64_t)ks * kstep;
                             if (sizeof(T) == 4) umma_tf32(d, a + o, b + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
                             else umma_f16(d, a + o, b + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
                         }
@@ -533,6 +538,44 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             const T* __restrict__ Wt = W0 + (long long)bidx * p.batch_stride_w;
             const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
             const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
+            if (p.use_tma && p.mode == 1) {
+                // Filter gradient fed by TMA (float32).  A k-block is 32 consecutive output pixels; both operands
+                // stay pixel-major: four boxes of 32 pixels x 32 output channels of dy, and BN/32 im2col boxes of
+                // 32 pixels x 32 input channels of the layer input at this tile's tap.
+                if (pt == 0 && sizeof(T) == 4) {
+                    const int tap = tn / p.ctiles, cblk = tn - tap * p.ctiles;
+                    const int fr = tap / p.S, fs = tap - fr * p.S;
+                    const int k0 = tm * BM, c0 = cblk * BN;
+                    const int pq = p.P * p.Q;
+                    int nb_boxes = 0;
+                    for (int g = 0; g < BN / 32; g++) nb_boxes += (c0 + 32 * g < p.C) ? 1 : 0;
+                    for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+                        const int s = it % C::STAGES;
+                        const long long m0 = (long long)kb * 32;
+                        const int n_img = (int)(m0 / pq);
+                        const int rem = (int)(m0 - (long long)n_img * pq);
+                        const int op = rem / p.Q, oq = rem - op * p.Q;
+                        if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                            if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
+                            dead = true;
+                            break;
+                        }
+                        const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
+                        const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                        mbar_arrive_expect_tx(&ctl->raw_full[s], C::A_BYTES + nb_boxes * 4096);
+#pragma unroll
+                        for (int g = 0; g < BM / 32; g++) tma_load_tile_2d(a_dst + g * 4096, p.tmap_a, &ctl->raw_full[s], k0 + 32 * g, (int)m0);
+#pragma unroll
+                        for (int g = 0; g < BN / 32; g++)
+                            if (c0 + 32 * g < p.C)   // columns past C are never stored
+                                tma_load_im2col_4d(b_dst + g * 4096, p.tmap_b, &ctl->raw_full[s], c0 + 32 * g, oq * p.stride_w - p.pad_w,
+                                                   op * p.stride_h - p.pad_h, n_img, (uint16_t)(fs * p.dil_w), (uint16_t)(fr * p.dil_h));
+                    }
+                } else {
+                    break;
+                }
+                continue;
+            }
             if (p.use_tma) {
                 // Both operand tiles of a k-block arrive by one TMA copy each, issued by a single thread:
                 // 128 im2col rows of the activation (zero outside the image, walking pixels in GEMM row
@@ -840,7 +883,46 @@ static bool setup_tma(IgemmParams& p, int bn) {
     static_assert(sizeof(CUtensorMap) == sizeof(p.tmap_a), "tensor map size");
     p.use_tma = 0;
     const TmaApi& api = tma_api();
-    if (!api.ok || p.mode != 0 || p.div_h != 1 || p.div_w != 1) return false;
+    if (!api.ok) return false;
+    if (p.mode == 1) {
+        // Filter gradient: dy as a plain [pixels, Kout] matrix in boxes of 32 x 32, the layer input through an
+        // im2col map that walks 32 output pixels per box.
+        if (p.dtype == 1 || p.C < 32 || (p.C & 3) || (p.Kout & 3) || ((uintptr_t)p.x | (uintptr_t)p.w) % 16) return false;
+        if (p.stride_h > 8 || p.stride_w > 8) return false;
+        int lower[2] = {-p.pad_w, -p.pad_h};
+        int upper[2] = {-p.pad_w + (p.Q - 1) * p.stride_w + 1 - p.W, -p.pad_h + (p.P - 1) * p.stride_h + 1 - p.H};
+        for (int i = 0; i < 2; i++)
+            if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return false;
+        if ((p.R - 1) * p.dil_h > 127 || (p.S - 1) * p.dil_w > 127) return false;
+        const CUtensorMapSwizzle wg_swz = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+        {
+            cuuint64_t dims[2] = {(cuuint64_t)p.Kout, (cuuint64_t)p.M};
+            cuuint64_t strides[1] = {(cuuint64_t)p.Kout * 4};
+            cuuint32_t box[2] = {32, 32};
+            cuuint32_t steps[2] = {1, 1};
+            if (api.tiled(reinterpret_cast<CUtensorMap*>(p.tmap_a), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(p.x), dims,
+                          strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, wg_swz,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return false;
+        }
+        {
+            cuuint64_t dims[4] = {(cuuint64_t)p.C, (cuuint64_t)p.W, (cuuint64_t)p.H, (cuuint64_t)p.Nb};
+            cuuint64_t strides[3] = {(cuuint64_t)p.C * 4, (cuuint64_t)p.W * p.C * 4, (cuuint64_t)p.H * p.W * p.C * 4};
+            cuuint32_t steps[4] = {1, (cuuint32_t)p.stride_w, (cuuint32_t)p.stride_h, 1};
+            if (api.im2col(reinterpret_cast<CUtensorMap*>(p.tmap_b), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(p.w), dims,
+                           strides, lower, upper, 32, 32, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, wg_swz,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return false;
+        }
+        // Operand descriptor above the address: float32 MN-major operands use the 128-byte swizzle with
+        // 32-byte atoms (layout type 1; the pattern repeats every four 128-byte rows), groups of four
+        // reduction indices 512 bytes apart (stride byte offset), the next 32 M/N indices 4096 bytes on
+        // (leading byte offset) -- what the boxes of 32 pixels x 128 bytes written by TMA look like.
+        p.mn_desc_bits = ((4096ull >> 4) << 16) | ((512ull >> 4) << 32) | (1ull << 46) | (1ull << 61);
+        p.use_tma = 1;
+        return true;
+    }
+    if (p.mode != 0 || p.div_h != 1 || p.div_w != 1) return false;
     const int elem = p.dtype == 1 ? 2 : 4;
     const int bk = 128 / elem;
     if (p.C < bk || (p.C * elem) % 16) return false;

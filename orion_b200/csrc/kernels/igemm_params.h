@@ -64,6 +64,7 @@ typedef struct IgemmParams {
      * over [batch, Kout, R, S, C].  0: the producer warps gather with 16-byte asynchronous copies. */
     int use_tma;
     int tma_base_h, tma_base_w;
+    unsigned long long mn_desc_bits;   /* filter gradient on TMA: the operand descriptors' bits above the address */
     OB200_ALIGN64 unsigned char tmap_a[128];
     OB200_ALIGN64 unsigned char tmap_b[128];
 } IgemmParams;

@@ -83,6 +83,11 @@ __device__ __forceinline__ void tma_load_tile_4d(uint32_t dst, const void* tmap,
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_tile_2d(uint32_t dst, const void* tmap, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_tile_5d(uint32_t dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
     asm volatile(
         "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
@@ -129,6 +134,14 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;               // SWIZZLE_128B
     return d;
 }
+
+// Descriptor of an MN-major operand tile (the reduction index is the slow one in memory): `upper_bits`
+// (leading / stride byte offsets, version, layout type) come from the host, the address is added here.
+__device__ __forceinline__ uint64_t umma_desc_mn(uint64_t upper_bits, uint32_t smem_addr) {
+    return upper_bits | (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+}
+// Bits of the instruction descriptor that declare operand A / B as MN-major instead of K-major.
+constexpr uint32_t UMMA_IDESC_A_MN = 1u << 15, UMMA_IDESC_B_MN = 1u << 16;
 
 // Instruction descriptor for kind::f16 / kind::tf32, dense, fp32 accumulate, both
 // operands K-major.  fmt: 0 = f16, 1 = bf16, 2 = tf32.

@@ -112,6 +112,24 @@ def test_relu_backward_and_sgd(K):
     assert (p - ref_p.detach()).abs().max().item() < 1e-5
 
 
+def test_wgrad_takes_the_tma_path_when_channels_allow(K):
+    """Pixel-major operands by TMA (MN-major tensor-core operands); fewer than 32 input channels gather and transpose."""
+    x = torch.randn(2, 12, 12, 64, device="cuda")
+    dy = torch.randn(2, 12, 12, 96, device="cuda") / 17.0
+    n0 = K.tma_launch_count()
+    dw = K.conv2d_wgrad_nhwc(x, dy, (3, 3), (1, 1), (1, 1))
+    assert K.tma_launch_count() - n0 == 1
+    assert O.rel_err(dw, _wgrad_ref(x, dy, (3, 3), 1, 1, 1)) < TOL
+    dw = K.conv2d_wgrad_nhwc(x, dy, (3, 3), (1, 1), (1, 1), tf32=True)
+    assert O.rel_err(dw, _wgrad_ref(x, dy, (3, 3), 1, 1, 1)) < 5e-3
+    x16 = torch.randn(2, 12, 12, 16, device="cuda")
+    n0 = K.tma_launch_count()
+    dw = K.conv2d_wgrad_nhwc(x16, dy, (3, 3), (1, 1), (1, 1))
+    assert K.tma_launch_count() == n0
+    assert O.rel_err(dw, _wgrad_ref(x16, dy, (3, 3), 1, 1, 1)) < TOL
+    assert K.read_status() == 0
+
+
 def _wgrad_ref(x, dy, rs, stride, pad, dil):
     """cudnnConvolutionBackwardFilter by definition: the gradient of conv2d with respect to its weight."""
     xd = x.detach().double().cpu().permute(0, 3, 1, 2)
