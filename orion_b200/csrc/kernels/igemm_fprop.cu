@@ -46,11 +46,12 @@
 namespace ob200 {
 
 constexpr int BM = 128;
-constexpr int EPI_WARPS = 4;
+constexpr int EPI_WARPS = 4;      // warps 0-3; TMA-fed launches add warps 9-12 as a second epilogue group
 constexpr int MMA_WARP = 4;
-constexpr int SPLIT_WARPS = 4;
-constexpr int PROD_WARPS = 8;
-constexpr int NTHREADS = (EPI_WARPS + 1 + SPLIT_WARPS + PROD_WARPS) * 32;   // 544
+constexpr int SPLIT_WARPS = 4;    // warps 5-8; TMA-fed launches add warps 13-16 as a second splitter group
+constexpr int PROD_WARPS = 8;     // warps 9-16 when the operands are gathered with cp.async
+constexpr int TMA_WARP = 17;      // one lane issues the TMA copies of TMA-fed launches
+constexpr int NTHREADS = 18 * 32;
 
 template <typename T, int BN, int PASSES>
 struct Cfg {
@@ -61,7 +62,7 @@ struct Cfg {
     static constexpr int B_BYTES = BN * 128;
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (kSplit ? 2 : 1);
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
-    static constexpr int EPI_BYTES = EPI_WARPS * 32 * 36 * 4;   // per-warp transpose tiles of the epilogue
+    static constexpr int EPI_BYTES = 2 * EPI_WARPS * 32 * 20 * 4;   // per-warp transpose tiles of the epilogue (EPI_LD floats per row)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 512 /*barriers*/;
     static constexpr int TMEM_COLS = 2 * BN;
 };
@@ -138,7 +139,7 @@ __device__ __forceinline__ void set_elem(uint4& v, int i, __nv_bfloat16 x) {
     *w |= bits;
 }
 
-constexpr int EPI_LD = 36;   // floats per staged accumulator row: 16-byte aligned, conflict-free both ways
+constexpr int EPI_LD = 20;   // floats per staged 16-column accumulator row: 16-byte aligned, conflict-free writes
 
 struct EpiCoef {
     float4 scale, shift;
@@ -231,12 +232,97 @@ __device__ __forceinline__ long long out_row(const IgemmParams& p, long long m) 
     return ((long long)n_img * p.out_H + i * p.out_mul_h + p.out_add_h) * p.out_W + j * p.out_mul_w + p.out_add_w;
 }
 
+// Epilogue of one 32-row x 16-column accumulator chunk held one row per lane in v: the per-warp shared-memory
+// tile turns it so that four consecutive lanes own 16 consecutive output channels of one row (full 64-byte
+// segments per row, eight rows per warp instruction), then scale/shift, residual, activation and store.
+template <typename T>
+__device__ __forceinline__ void epilogue_chunk(const IgemmParams& p, float* stage, const float (&v)[16], int lane,
+                                               long long tile_row0, int n_chunk, long long y_off) {
+    const int sub = lane >> 2, cc = (lane & 3) * 4;
+#pragma unroll
+    for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    __syncwarp();
+    const int n = n_chunk + cc;
+    const EpiCoef coef = load_coef<T>(p, n);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int rr = i * 8 + sub;
+        const long long m = tile_row0 + rr;
+        if (m < p.M) store_out<T>(p, coef, *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc), out_row(p, m), n, y_off);
+    }
+    __syncwarp();
+}
+
 // mbar_wait that also adds the cycles spent waiting to `acc` (role-level wait breakdown for tuning).
 __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long& acc) {
     const long long t0 = clock64();   // the first try_wait may already suspend the thread for a while
     const bool ok = mbar_wait(bar, parity, abort_flag);
     acc += clock64() - t0;
     return ok;
+}
+
+// One piece of work of a CTA: k-blocks [kb_begin, kb_end) of output tile `tile`.  nseg is the number of
+// pieces the tile is computed in (1: this piece is the whole tile and stores directly); pieces of a cut
+// tile accumulate in scratch slot `slot`.
+struct Seg {
+    int tile, kb_begin, kb_end, nseg, slot;
+    int first_cta, my_slab;   // stream-K: first CTA with a piece of this tile; slab this piece is written to
+};
+
+// Walks the work of this CTA; every warp role of the CTA runs an identical copy.  Split-K mode hands out
+// (tile, split) units round-robin; stream-K mode gives CTA b the range [b*W/G, (b+1)*W/G) of the W = tiles *
+// num_kblocks k-blocks laid end to end (position x belongs to CTA ceil((x+1)*G/W) - 1).
+struct WorkIter {
+    int nk, splits, G, units, u;
+    long long W, pos, hi;
+    bool sk;
+    __device__ __forceinline__ WorkIter(const IgemmParams& p, int tiles) {
+        nk = p.num_kblocks;
+        splits = p.splits;
+        G = gridDim.x;
+        sk = p.stream_k != 0;
+        units = tiles * p.splits;
+        u = blockIdx.x;
+        W = (long long)tiles * nk;
+        pos = W * blockIdx.x / G;
+        hi = W * (blockIdx.x + 1) / G;
+    }
+    __device__ __forceinline__ int cta_of(long long x) const { return (int)(((x + 1) * G + W - 1) / W) - 1; }
+    // Slab holding CTA c's piece of `tile`: the first slab if c's range begins inside the tile, else the second.
+    __device__ __forceinline__ int slab_of(int c, int tile) const { return 2 * c + (W * c / G >= (long long)tile * nk ? 0 : 1); }
+    __device__ __forceinline__ bool next(Seg& s) {
+        if (sk) {
+            if (pos >= hi) return false;
+            s.tile = (int)(pos / nk);
+            s.kb_begin = (int)(pos - (long long)s.tile * nk);
+            const long long left = hi - pos;
+            const int len = left < (long long)(nk - s.kb_begin) ? (int)left : nk - s.kb_begin;
+            s.kb_end = s.kb_begin + len;
+            const int first = cta_of((long long)s.tile * nk), last = cta_of((long long)s.tile * nk + nk - 1);
+            s.nseg = last - first + 1;
+            s.slot = first + 1;
+            s.first_cta = first;
+            s.my_slab = 2 * (int)blockIdx.x + (pos == W * blockIdx.x / G ? 0 : 1);
+            pos += len;
+            return true;
+        }
+        if (u >= units) return false;
+        s.tile = u / splits;
+        const int split = u - s.tile * splits;
+        s.kb_begin = (int)((long long)nk * split / splits);
+        s.kb_end = (int)((long long)nk * (split + 1) / splits);
+        s.nseg = splits;
+        s.slot = s.tile;
+        s.first_cta = s.my_slab = 0;
+        u += G;
+        return true;
+    }
+};
+
+// Adds four partial sums to scratch with one 16-byte reduction.
+__device__ __forceinline__ void red_add_v4(float* dst, const float4& v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
 template <typename T, int BN, int PASSES>
@@ -256,12 +342,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         for (int s = 0; s < C::STAGES; s++) {
             // every producer thread, when its copies have landed; or the one TMA-issuing thread plus the byte count
             mbar_init(&ctl->raw_full[s], p.use_tma ? 1 : PROD_WARPS * 32);
-            mbar_init(&ctl->full[s], SPLIT_WARPS);           // one elected lane per splitter warp
+            mbar_init(&ctl->full[s], p.use_tma ? 2 * SPLIT_WARPS : SPLIT_WARPS);   // one elected lane per splitter warp
             mbar_init(&ctl->empty[s], 1);      // tcgen05.commit
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&ctl->tmem_full[b], 1);           // tcgen05.commit
-            mbar_init(&ctl->tmem_empty[b], EPI_WARPS);  // one elected lane per epilogue warp
+            mbar_init(&ctl->tmem_empty[b], p.use_tma ? 2 * EPI_WARPS : EPI_WARPS);  // one elected lane per epilogue warp
         }
         ctl->abort_flag = 0;
         ctl->last_flag = 0;
@@ -279,16 +365,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
 
     const int tiles_per_problem = p.tiles_m * p.tiles_n;
     const int tiles = tiles_per_problem * (p.batch > 1 ? p.batch : 1);
-    const int units = tiles * p.splits;
     const int SC = p.S * p.C;
     long long waited = 0;
     const long long t_start = clock64();
+    // Roles of warps 9-17 depend on how the operands arrive: gathered by eight producer warps, or copied by
+    // TMA, which frees those warps for a second epilogue group and a second splitter group.
+    const bool tma_roles = p.use_tma != 0;
+    const int epi_groups = tma_roles ? 2 : 1;
+    const int epi_id = warp < EPI_WARPS ? warp : (tma_roles && warp >= 9 && warp < 13) ? EPI_WARPS + warp - 9 : -1;
+    const int split_id = (warp > MMA_WARP && warp <= MMA_WARP + SPLIT_WARPS) ? warp - MMA_WARP - 1
+                         : (tma_roles && warp >= 13 && warp < 17)            ? SPLIT_WARPS + warp - 13
+                                                                             : -1;
 
-    if (warp < EPI_WARPS) {
+    if (epi_id >= 0) {
         // ------------------------------------------------------------ epilogue
+        // Warp (epi_id % 4 == warp % 4) reads TMEM lanes (accumulator rows) 32*(warp % 4) .. +31; with two
+        // groups of four warps, group g takes columns [g*BN/2, (g+1)*BN/2).
+        const int q = warp & 3;
+        const int grp = epi_id >> 2;
+        const int col_lo = grp * (BN / epi_groups), col_hi = col_lo + BN / epi_groups;
+        const int epi_threads = 128 * epi_groups;
+        float* stage = epi_stage + epi_id * (32 * EPI_LD);
+        const int sub = lane >> 2;          // row within a group of eight
+        const int cc = (lane & 3) * 4;      // first of this lane's four channels within a 16-channel chunk
+        const uint32_t tmem_rows = tmem_base + ((uint32_t)(q * 32) << 16);
         int local = 0;
-        for (int u = blockIdx.x; u < units; u += gridDim.x, local++) {
-            const int tile = u / p.splits;
+        WorkIter work(p, tiles);
+        Seg seg;
+        for (; work.next(seg); local++) {
+            const int tile = seg.tile;
             const int bidx = tile / tiles_per_problem;
             const int tloc = tile - bidx * tiles_per_problem;
             const int tm = tloc / p.tiles_n, tn = tloc % p.tiles_n;
@@ -299,112 +404,154 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 break;
             }
             tc_fence_after_sync();
-            // Accumulator rows sit one per lane; a per-warp shared-memory tile turns them so that
-            // eight consecutive lanes own 32 consecutive output channels of one row, which makes
-            // every global access below a full 128-byte line.
-            float* stage = epi_stage + warp * (32 * EPI_LD);
-            const int sub = lane >> 3;          // row within a group of four
-            const int cc = (lane & 7) * 4;      // first of this lane's four channels within the 32-channel chunk
-            const long long tile_row0 = (long long)tm * BM + warp * 32;
+            const long long tile_row0 = (long long)tm * BM + q * 32;
             if (p.mode == 1) {
                 // Filter gradient: accumulator row = output channel k, columns = channels c of tap (r, s).
                 // The result lands in dw[k][r][s][c]; partial sums of different pixel ranges are added atomically.
                 const int tap = tn / p.ctiles, cblk = tn - tap * p.ctiles;
                 float* dw = reinterpret_cast<float*>(p.y);
 #pragma unroll 1
-                for (int cb = 0; cb < BN / 32; cb++) {
+                for (int c32 = col_lo; c32 < col_hi; c32 += 32) {
                     uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * BN + cb * 32, r);
+                    tmem_ld_32x32(tmem_rows + ab * BN + c32, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) =
-                            make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                    __syncwarp();
-                    const int c = cblk * BN + cb * 32 + cc;
+                    for (int h = 0; h < 2; h++) {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int rr = i * 4 + sub;
-                        const long long k = tile_row0 + rr;
-                        if (k < p.Kout && c < p.C) {
-                            const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc);
-                            float* dst = dw + ((long long)k * p.R * p.S + tap) * p.C + c;
-                            if (p.splits > 1) {
-                                atomicAdd(dst + 0, v.x); atomicAdd(dst + 1, v.y); atomicAdd(dst + 2, v.z); atomicAdd(dst + 3, v.w);
-                            } else {
-                                *reinterpret_cast<float4*>(dst) = v;
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) = make_float4(
+                                __uint_as_float(r[16 * h + j]), __uint_as_float(r[16 * h + j + 1]), __uint_as_float(r[16 * h + j + 2]),
+                                __uint_as_float(r[16 * h + j + 3]));
+                        __syncwarp();
+                        const int c = cblk * BN + c32 + 16 * h + cc;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int rr = i * 8 + sub;
+                            const long long k = tile_row0 + rr;
+                            if (k < p.Kout && c < p.C) {
+                                const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc);
+                                float* dst = dw + ((long long)k * p.R * p.S + tap) * p.C + c;
+                                if (p.splits > 1) red_add_v4(dst, v);
+                                else *reinterpret_cast<float4*>(dst) = v;
                             }
                         }
+                        __syncwarp();
                     }
-                    __syncwarp();
                 }
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->tmem_empty[ab]);
                 continue;
             }
+            if (p.stream_k && seg.nseg > 1) {
+                // Stream-K piece of a cut tile.  The partial accumulator goes to this piece's slab, laid out
+                // [4-column group][row] so that the lanes (rows) of a warp write consecutive 16 bytes.
+                constexpr int SLAB_F4 = BM * BN / 4;
+                float4* slabs = reinterpret_cast<float4*>(p.slabs);
+                float4* mine = slabs + (long long)seg.my_slab * SLAB_F4;
+                const int row = q * 32 + lane;
 #pragma unroll 1
-            for (int cb = 0; cb < BN / 32; cb++) {
+                for (int c32 = col_lo; c32 < col_hi; c32 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_rows + ab * BN + c32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        mine[(c32 / 4 + j) * BM + row] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->tmem_empty[ab]);   // the accumulator is out of TMEM
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+                if (tid == 0) {
+                    int prev = atomicAdd(p.counters + seg.slot, 1);
+                    ctl->last_flag = (prev == seg.nseg - 1);
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
+                if (ctl->last_flag) {
+                    // Last piece to arrive: every slab of the tile is published.  Sum them in CTA order.
+                    __threadfence();
+#pragma unroll 1
+                    for (int c16 = col_lo; c16 < col_hi; c16 += 16) {
+                        float acc[16];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) acc[j] = 0.f;
+                        for (int c = seg.first_cta; c < seg.first_cta + seg.nseg; c++) {
+                            const float4* src = slabs + (long long)work.slab_of(c, tile) * SLAB_F4;
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float4 v = __ldcg(src + (c16 / 4 + j) * BM + row);
+                                acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
+                            }
+                        }
+                        epilogue_chunk<T>(p, stage, acc, lane, tile_row0, tn * BN + c16, y_off);
+                    }
+                    if (tid == 0) p.counters[seg.slot] = 0;
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");   // last_flag is rewritten by the next piece
+                continue;
+            }
+#pragma unroll 1
+            for (int c32 = col_lo; c32 < col_hi; c32 += 32) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + ab * BN + cb * 32, r);
+                tmem_ld_32x32(tmem_rows + ab * BN + c32, r);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) =
-                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                __syncwarp();
-                const int n = tn * BN + cb * 32 + cc;
-                if (p.splits > 1) {
+                for (int h = 0; h < 2; h++) {
+                    float v16[16];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int rr = i * 4 + sub;
-                        if (tile_row0 + rr < p.M) {
-                            const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc);
-                            float* part = p.scratch + ((long long)tile * BM + warp * 32 + rr) * BN + cb * 32 + cc;
-                            atomicAdd(part + 0, v.x); atomicAdd(part + 1, v.y); atomicAdd(part + 2, v.z); atomicAdd(part + 3, v.w);
-                        }
+                    for (int j = 0; j < 16; j++) v16[j] = __uint_as_float(r[16 * h + j]);
+                    if (seg.nseg == 1) {
+                        epilogue_chunk<T>(p, stage, v16, lane, tile_row0, tn * BN + c32 + 16 * h, y_off);
+                        continue;
                     }
-                } else {
-                    const EpiCoef coef = load_coef<T>(p, n);
+                    // split-K: add this unit's partial tile to the tile's zero-initialised scratch
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int rr = i * 4 + sub;
-                        const long long m = tile_row0 + rr;
-                        if (m < p.M) store_out<T>(p, coef, *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc), out_row(p, m), n, y_off);
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) = make_float4(v16[j], v16[j + 1], v16[j + 2], v16[j + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int rr = i * 8 + sub;
+                        if (tile_row0 + rr < p.M)
+                            red_add_v4(p.scratch + ((long long)seg.slot * BM + q * 32 + rr) * BN + c32 + 16 * h + cc,
+                                       *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc));
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
-            if (p.splits > 1) {
-                // The unit that arrives last on the tile's counter applies the epilogue to the sums.
+            if (seg.nseg > 1) {
+                // The piece that arrives last on the tile's counter applies the epilogue to the sums.
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
                 if (tid == 0) {
-                    int prev = atomicAdd(p.counters + tile, 1);
-                    ctl->last_flag = (prev == p.splits - 1);
+                    int prev = atomicAdd(p.counters + seg.slot, 1);
+                    ctl->last_flag = (prev == seg.nseg - 1);
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
                 if (ctl->last_flag) {
                     __threadfence();
 #pragma unroll 1
-                    for (int cb = 0; cb < BN / 32; cb++) {
-                        const int n = tn * BN + cb * 32 + cc;
+                    for (int c16 = col_lo; c16 < col_hi; c16 += 16) {
+                        const int n = tn * BN + c16 + cc;
                         const EpiCoef coef = load_coef<T>(p, n);
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            const int rr = i * 4 + sub;
+                        for (int i = 0; i < 4; i++) {
+                            const int rr = i * 8 + sub;
                             const long long m = tile_row0 + rr;
                             if (m < p.M) {
-                                float4* part = reinterpret_cast<float4*>(p.scratch + ((long long)tile * BM + warp * 32 + rr) * BN + cb * 32 + cc);
+                                float4* part = reinterpret_cast<float4*>(p.scratch + ((long long)seg.slot * BM + q * 32 + rr) * BN + c16 + cc);
                                 const float4 v = __ldcg(part);
                                 *part = make_float4(0.f, 0.f, 0.f, 0.f);   // leave the scratch zeroed for the next launch
                                 store_out<T>(p, coef, v, out_row(p, m), n, y_off);
                             }
                         }
                     }
-                    if (tid == 0) p.counters[tile] = 0;
+                    if (tid == 0) p.counters[seg.slot] = 0;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is rewritten by the next unit
+                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");   // last_flag is rewritten by the next unit
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -423,10 +570,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             int local = 0;
             bool dead = false;
             long long waited2 = 0;
-            for (int u = blockIdx.x; u < units && !dead; u += gridDim.x, local++) {
-                const int split = u % p.splits;
-                const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
-                const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
+            WorkIter work(p, tiles);
+            Seg seg;
+            for (; !dead && work.next(seg); local++) {
+                const int kb_begin = seg.kb_begin, kb_end = seg.kb_end;
                 const int ab = local & 1;
                 if (!timed_wait(&ctl->tmem_empty[ab], ((local >> 1) & 1) ^ 1, abort_flag, waited2)) {
                     if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_EMPTY); }
@@ -474,19 +621,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             }
             if (p.debug && blockIdx.x == 0) { p.debug[1] = waited; p.debug[2] = waited2; }
         }
-    } else if (warp < MMA_WARP + 1 + SPLIT_WARPS) {
+    } else if (split_id >= 0) {
         // ------------------------------------------------------------ splitters (fp32 only)
-        // Turn the raw fp32 operand rows the producers copied into shared memory into the
-        // TF32-rounded high parts (in place) and the exact remainders (second buffer).
+        // Write, for every raw fp32 operand value the producers or TMA put into shared memory, the exact
+        // remainder x - tf32(x) into the second buffer.  The work is elementwise, so the 16-byte chunks of the
+        // two tiles are simply dealt out to the splitter threads in address order.
         if (C::kSplit) {
-            const int st_id = (warp - (MMA_WARP + 1)) * 32 + lane;   // 0..127
-            const int row = st_id;                                    // operand row
+            const int st_id = split_id * 32 + lane;
+            const int st_threads = (tma_roles ? 2 * SPLIT_WARPS : SPLIT_WARPS) * 32;
             uint32_t it = 0;
             bool dead = false;
-            for (int u = blockIdx.x; u < units && !dead; u += gridDim.x) {
-                const int split = u % p.splits;
-                const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
-                const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
+            WorkIter work(p, tiles);
+            Seg seg;
+            while (!dead && work.next(seg)) {
+                const int kb_begin = seg.kb_begin, kb_end = seg.kb_end;
                 for (int kb = kb_begin; kb < kb_end; kb++, it++) {
                     const int s = it % C::STAGES;
                     if (!timed_wait(&ctl->raw_full[s], (it / C::STAGES) & 1, abort_flag, waited)) {
@@ -499,12 +647,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     uint8_t* a_lo = st + C::A_BYTES;
                     uint8_t* b_hi = st + 2 * C::A_BYTES;
                     uint8_t* b_lo = b_hi + C::B_BYTES;
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint32_t off = sw128_offset((uint32_t)row, (uint32_t)j);
-                        split_chunk(a_hi + off, a_lo + off);
-                        if (row < BN) split_chunk(b_hi + off, b_lo + off);
-                    }
+#pragma unroll 4
+                    for (int i = st_id; i < C::A_BYTES / 16; i += st_threads) split_chunk(a_hi + i * 16, a_lo + i * 16);
+#pragma unroll 4
+                    for (int i = st_id; i < C::B_BYTES / 16; i += st_threads) split_chunk(b_hi + i * 16, b_lo + i * 16);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&ctl->full[s]);
@@ -512,13 +658,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             }
             if (p.debug && blockIdx.x == 0 && st_id == 0) p.debug[3] = waited;
         }
-    } else {
+    } else if (warp == TMA_WARP ? tma_roles : (!tma_roles && warp >= 9)) {
         // ------------------------------------------------------------ producers
-        // Asynchronous 16-byte copies (zero-filled outside the image) straight into the swizzled
+        // TMA-fed launches: one lane of the TMA warp issues the copies.  Otherwise warps 9-16 gather with
+        // asynchronous 16-byte copies (zero-filled outside the image) straight into the swizzled
         // stage buffers, several stages ahead of the MMA.  Eight consecutive threads copy the
         // eight 16-byte chunks of one operand row, so a warp instruction reads four full 128-byte
         // lines; each thread serves rows (t/8), (t/8)+16, ... of the tile with its fixed chunk t%8.
-        const int pt = (warp - (MMA_WARP + 1 + SPLIT_WARPS)) * 32 + lane;   // 0..255
+        const int pt = tma_roles ? lane : (warp - 9) * 32 + lane;   // gather: 0..255; TMA: lane 0 issues
         const T* __restrict__ X0 = reinterpret_cast<const T*>(p.x);
         const T* __restrict__ W0 = reinterpret_cast<const T*>(p.w);
         const bool vec = (p.C % C::EPC) == 0;
@@ -529,15 +676,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         const uint32_t sw_off = (uint32_t)row0 * 128u + (uint32_t)((chunk ^ (row0 & 7)) << 4);
         uint32_t it = 0;
         bool dead = false;
-        for (int u = blockIdx.x; u < units && !dead; u += gridDim.x) {
-            const int tile = u / p.splits, split = u % p.splits;
+        WorkIter work(p, tiles);
+        Seg seg;
+        while (!dead && work.next(seg)) {
+            const int tile = seg.tile;
             const int bidx = tile / tiles_per_problem;
             const int tloc = tile - bidx * tiles_per_problem;
             const int tm = tloc / p.tiles_n, tn = tloc % p.tiles_n;
             const T* __restrict__ X = X0 + (long long)bidx * p.batch_stride_x;
             const T* __restrict__ Wt = W0 + (long long)bidx * p.batch_stride_w;
-            const int kb_begin = (int)((long long)p.num_kblocks * split / p.splits);
-            const int kb_end = (int)((long long)p.num_kblocks * (split + 1) / p.splits);
+            const int kb_begin = seg.kb_begin, kb_end = seg.kb_end;
             if (p.use_tma && p.mode == 1) {
                 // Filter gradient fed by TMA (float32).  A k-block is 32 consecutive output pixels; both operands
                 // stay pixel-major: four boxes of 32 pixels x 32 output channels of dy, and BN/32 im2col boxes of
@@ -810,7 +958,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
     }
 
     if (p.debug && blockIdx.x == 0) {
-        if (warp == MMA_WARP + 1 + SPLIT_WARPS && lane == 0) p.debug[4] = waited;   // producer warp 0
+        if (warp == (tma_roles ? TMA_WARP : 9) && lane == 0) p.debug[4] = waited;   // TMA issuer / producer warp 0
         if (tid == 0) p.debug[5] = clock64() - t_start;
     }
     // ---------------------------------------------------------------- teardown

@@ -31,6 +31,14 @@ typedef struct IgemmParams {
     int num_kblocks;        /* R * kblocks_per_r */
     int tiles_m, tiles_n;
     int splits;             /* split-K factor, <= num_kblocks */
+    /* stream_k = 1 (mode 0 only): the k-blocks of all tiles, laid end to end, are cut into one equal contiguous
+     * range per CTA, so a CTA may finish a tile another one began.  Each piece of a cut tile is written to its
+     * own slab of `slabs` (two slabs of 128 x BN floats per CTA, contents arbitrary on entry and exit); the piece
+     * that arrives last on the tile's counter (index: first CTA that starts inside the tile; zero on entry and
+     * exit) adds the slabs in CTA order -- the sum does not depend on arrival order -- and applies the epilogue.
+     * splits is ignored. */
+    int stream_k;
+    float* slabs;
     /* Gather geometry (filled by igemm_set_fprop / igemm_set_dgrad).  GEMM row m = (n*OH + oh)*OW + ow;
      * for tap (r, s) the source pixel of tensor x [Nb, IH, IW, C] is
      *   ih = (oh*bmul_h + badd_h + r*step_h) / div_h   (valid only if the division is exact), same for w. */

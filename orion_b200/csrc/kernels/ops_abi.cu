@@ -13,10 +13,12 @@
 namespace {
 
 struct Scratch {
-    float* partial = nullptr;
-    int* counters = nullptr;
-    size_t partial_bytes = 0;
+    float* partial = nullptr;    // split-K sums: zero between launches
+    int* counters = nullptr;     // arrival counters: zero between launches
+    float* slabs = nullptr;      // stream-K partial tiles: two per CTA, contents arbitrary between launches
+    size_t partial_bytes = 0, slab_bytes = 0;
 };
+constexpr size_t kSlabBytes = 40u << 20;                // two 128 x 128 float slabs for up to 320 CTAs
 constexpr int kMaxTilesSplit = 4096;                    // counters per stream
 constexpr size_t kScratchBytes = 32u << 20;             // split-K partial sums per stream
 
@@ -47,7 +49,9 @@ Scratch* scratch_for(int dev, cudaStream_t s) {
     Scratch sc;
     if (cudaMalloc(&sc.partial, kScratchBytes) != cudaSuccess) return nullptr;
     if (cudaMalloc(&sc.counters, kMaxTilesSplit * sizeof(int)) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&sc.slabs, kSlabBytes) != cudaSuccess) return nullptr;
     sc.partial_bytes = kScratchBytes;
+    sc.slab_bytes = kSlabBytes;
     cudaMemsetAsync(sc.partial, 0, kScratchBytes, s);
     cudaMemsetAsync(sc.counters, 0, kMaxTilesSplit * sizeof(int), s);
     g_scratch[key] = sc;
@@ -79,10 +83,37 @@ extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, i
     return 0;
 }
 
-extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, const float* scale, const float* shift,
-                                     const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R,
-                                     int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn,
-                                     int splits, float* scratch, int* counters, int num_ctas, void* stream) {
+namespace {
+
+// Tile width when the schedule balances the load by itself (stream-K): wide tiles halve the re-reads of
+// the activation operand; narrow ones only where the output is narrow or its last wide tile would be
+// mostly padding.
+int streamk_bn(int Kout) {
+    const int rem = Kout % 128;
+    return (Kout <= 64 || (rem > 0 && rem <= 64 && Kout < 256)) ? 64 : 128;
+}
+
+// Puts a mode-0 launch on the stream-K schedule if the stream's scratch has a slot per CTA; returns the grid.
+// At least four k-blocks per CTA, so tiny problems use fewer CTAs instead of paying a reduction per k-block.
+int schedule_stream_k(IgemmParams& p, int bn, int num_ctas, int dev, cudaStream_t stream) {
+    const long long work = (long long)p.tiles_m * p.tiles_n * p.num_kblocks;
+    long long grid = work / 4;
+    if (grid > num_ctas) grid = num_ctas;
+    if (grid < 1) grid = 1;
+    Scratch* sc = grid > 1 ? scratch_for(dev, stream) : nullptr;
+    if (grid > 1 && (!sc || grid > kMaxTilesSplit || (size_t)grid * 2 * 128 * bn * sizeof(float) > sc->slab_bytes)) return 0;
+    p.stream_k = 1;
+    p.splits = 1;
+    if (sc) {
+        p.slabs = sc->slabs;
+        p.counters = sc->counters;
+    }
+    return (int)grid;
+}
+
+int fprop_impl(const void* x, const void* w, void* y, const float* scale, const float* shift, const void* residual, int relu,
+               int dtype, int Nb, int H, int W, int C, int Kout, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w,
+               int dil_h, int dil_w, int bn, int splits, bool stream_k, float* scratch, int* counters, int num_ctas, void* stream) {
     if (dtype < 0 || dtype > 2) return -1;
     if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || Kout <= 0 || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
         dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0)
@@ -115,6 +146,10 @@ extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, cons
     igemm_set_fprop(&p);
     p.status = status_word(dev);
     p.debug = g_debug;
+    if (stream_k) {
+        const int grid = schedule_stream_k(p, bn, num_ctas, dev, (cudaStream_t)stream);
+        if (grid > 0) return ob200_igemm_launch(&p, bn, grid, stream);
+    }
     if (splits > 1) {
         if (!scratch || !counters) return -1;
         p.scratch = scratch;
@@ -125,6 +160,16 @@ extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, cons
     return ob200_igemm_launch(&p, bn, grid, stream);
 }
 
+}  // namespace
+
+extern "C" int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, const float* scale, const float* shift,
+                                     const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R,
+                                     int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn,
+                                     int splits, float* scratch, int* counters, int num_ctas, void* stream) {
+    return fprop_impl(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w, dil_h,
+                      dil_w, bn, splits, false, scratch, counters, num_ctas, stream);
+}
+
 extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const float* scale, const float* shift,
                                   const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                                   int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas,
@@ -132,24 +177,10 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
     if (Nb <= 0 || H <= 0 || W <= 0) return Nb == 0 ? 0 : -1;
     const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / (stride_h > 0 ? stride_h : 1) + 1;
     const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / (stride_w > 0 ? stride_w : 1) + 1;
-    int bn = 128, splits = 1;
-    ob200_plan_conv(dtype, (long long)Nb * P * Q, Kout, R, S, C, num_ctas, &bn, &splits);
-    float* scratch = nullptr;
-    int* counters = nullptr;
-    if (splits > 1) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        const long long tiles = (long long)(((long long)Nb * P * Q + 127) / 128) * ((Kout + bn - 1) / bn);
-        Scratch* sc = scratch_for(dev, (cudaStream_t)stream);
-        if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
-            splits = 1;
-        } else {
-            scratch = sc->partial;
-            counters = sc->counters;
-        }
-    }
-    return ob200_conv2d_fprop_ex(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h,
-                                 pad_w, dil_h, dil_w, bn, splits, scratch, counters, num_ctas, stream);
+    // Stream-K schedule with the tile width it prefers; without scratch for it, one unit per tile.
+    const int bn = streamk_bn(Kout);
+    return fprop_impl(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w, dil_h,
+                      dil_w, bn, 1, true, nullptr, nullptr, num_ctas, stream);
 }
 
 // Data gradient of the convolution: dx[n,h,w,c] = sum_{r,s,k} dy[n,(h+pad-r*dil)/stride,(w+pad-s*dil)/stride,k] * w[k,r,s,c]
@@ -181,8 +212,7 @@ static int dgrad_by_parity_class(const void* dy, const void* wt, void* dx, int d
                 continue;
             }
             const long long M = (long long)Nb * Hc * Wc;
-            int bn = 128, splits = 1;
-            ob200_plan_conv(dtype, M, C, Rc, Sc, Kout, num_ctas, &bn, &splits);
+            const int bn = streamk_bn(C);
             IgemmParams p;
             memset(&p, 0, sizeof p);
             p.x = dy; p.w = wt; p.y = dx;
@@ -195,20 +225,9 @@ static int dgrad_by_parity_class(const void* dy, const void* wt, void* dx, int d
             p.num_kblocks = Rc * p.kblocks_per_r;
             p.tiles_m = (int)((M + 127) / 128);
             p.tiles_n = (C + bn - 1) / bn;
-            if (splits > p.num_kblocks) splits = p.num_kblocks;
             p.status = status_word(dev);
             p.debug = g_debug;
-            if (splits > 1) {
-                const long long tiles = (long long)p.tiles_m * p.tiles_n;
-                Scratch* sc = scratch_for(dev, st);
-                if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
-                    splits = 1;
-                } else {
-                    p.scratch = sc->partial;
-                    p.counters = sc->counters;
-                }
-            }
-            p.splits = splits;
+            p.splits = 1;
             p.OH = Hc; p.OW = Wc; p.IH = P; p.IW = Q;
             p.bmul_h = p.bmul_w = 1;
             p.badd_h = (a + pad_h - r0) / stride_h; p.badd_w = (b + pad_w - s0) / stride_w;
@@ -218,8 +237,11 @@ static int dgrad_by_parity_class(const void* dy, const void* wt, void* dx, int d
             p.out_map = 1; p.out_H = H; p.out_W = W;
             p.out_mul_h = stride_h; p.out_mul_w = stride_w; p.out_add_h = a; p.out_add_w = b;
             p.require_tma = 1;
-            const long long units = (long long)p.tiles_m * p.tiles_n * splits;
-            const int grid = units < num_ctas ? (int)units : num_ctas;
+            int grid = schedule_stream_k(p, bn, num_ctas, dev, st);
+            if (grid <= 0) {
+                const long long units = (long long)p.tiles_m * p.tiles_n;
+                grid = units < num_ctas ? (int)units : num_ctas;
+            }
             const int rc = ob200_igemm_launch(&p, bn, grid, stream);
             if (rc != 0) return rc;
         }
@@ -249,8 +271,7 @@ extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int 
                                              num_ctas, stream, dev);
         if (rc != -4) return rc;
     }
-    int bn = 128, splits = 1;
-    ob200_plan_conv(dtype, M, C, R, S, Kout, num_ctas, &bn, &splits);
+    const int bn = streamk_bn(C);
     IgemmParams p;
     memset(&p, 0, sizeof p);
     p.x = dy; p.w = wt; p.y = dx;
@@ -265,23 +286,15 @@ extern "C" int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int 
     p.num_kblocks = R * p.kblocks_per_r;
     p.tiles_m = (int)((M + 127) / 128);
     p.tiles_n = (C + bn - 1) / bn;
-    if (splits > p.num_kblocks) splits = p.num_kblocks;
     p.status = status_word(dev);
     p.debug = g_debug;
-    if (splits > 1) {
-        const long long tiles = (long long)p.tiles_m * p.tiles_n;
-        Scratch* sc = scratch_for(dev, (cudaStream_t)stream);
-        if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
-            splits = 1;
-        } else {
-            p.scratch = sc->partial;
-            p.counters = sc->counters;
-        }
-    }
-    p.splits = splits;
+    p.splits = 1;
     igemm_set_dgrad(&p, H, W, P, Q);
-    const long long units = (long long)p.tiles_m * p.tiles_n * splits;
-    const int grid = units < num_ctas ? (int)units : num_ctas;
+    int grid = schedule_stream_k(p, bn, num_ctas, dev, (cudaStream_t)stream);
+    if (grid <= 0) {
+        const long long units = (long long)p.tiles_m * p.tiles_n;
+        grid = units < num_ctas ? (int)units : num_ctas;
+    }
     return ob200_igemm_launch(&p, bn, grid, stream);
 }
 

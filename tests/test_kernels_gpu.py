@@ -119,6 +119,22 @@ def test_conv_result_does_not_depend_on_the_sm_quota(K):
     assert K.read_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(4, 28, 28, 128, 128, 3, 1, 1), (4, 7, 7, 512, 512, 3, 1, 1), (8, 14, 14, 256, 1024, 1, 1, 0),
+                                   (2, 9, 11, 24, 40, 3, 1, 1), (4, 56, 56, 64, 64, 1, 1, 0)])
+def test_stream_k_schedule_for_any_sm_quota(K, shape):
+    """The default schedule cuts the k-blocks of all tiles into one equal range per CTA; tiles that straddle two
+    CTAs are summed in scratch.  Any quota gives the oracle's result, launch after launch (scratch is left zero)."""
+    Nb, H, W, C, Ko, R, stride, pad = shape
+    x = torch.randn(Nb, H, W, C, device="cuda")
+    w = torch.randn(Ko, R, R, C, device="cuda") / (C * R * R) ** 0.5
+    shift = torch.randn(Ko, device="cuda")
+    want = O.conv2d_nhwc(x, w, (stride, stride), (pad, pad), shift=shift, act=1)
+    for q in (148, 1, 8, 37, 64, 100, 148):
+        y = K.conv2d_nhwc(x, w, (stride, stride), (pad, pad), shift=shift, relu=True, num_ctas=q)
+        assert O.rel_err(y, want) < FP32_TOL, q
+    assert K.read_status() == 0
+
+
 def test_conv_is_linear_at_training_batch_size(K):
     """Size-independent property at the BE batch size (32): conv(a*x1 + x2) = a*conv(x1) + conv(x2)."""
     x1 = torch.randn(32, 56, 56, 64, device="cuda")
