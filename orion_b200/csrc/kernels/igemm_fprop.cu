@@ -64,7 +64,11 @@ struct Cfg {
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
     static constexpr int EPI_BYTES = 2 * EPI_WARPS * 32 * 20 * 4;   // per-warp transpose tiles of the epilogue (EPI_LD floats per row)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 512 /*barriers*/;
-    static constexpr int TMEM_COLS = 2 * BN;
+    // Two accumulators of BN columns; 3xTF32 also keeps, per stage, the two parts of the activation tile
+    // (32 + 32 columns) in tensor memory.  Allocations are powers of two.
+    static constexpr int A_TMEM_COL0 = 2 * BN;
+    static constexpr int TMEM_COLS = kSplit ? 512 : 2 * BN;
+    static_assert(!kSplit || 2 * BN + STAGES * 64 <= 512, "tensor memory budget");
 };
 
 struct SharedCtl {
@@ -598,12 +602,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                         const uint64_t b_hi = mn_major ? umma_desc_mn(p.mn_desc_bits, base + 2 * C::A_BYTES) : umma_desc_sw128(base + 2 * C::A_BYTES);
                         const uint64_t b_lo = mn_major ? umma_desc_mn(p.mn_desc_bits, base + 2 * C::A_BYTES + C::B_BYTES)
                                                        : umma_desc_sw128(base + 2 * C::A_BYTES + C::B_BYTES);
+                        if (p.a_in_tmem) {
+                            const uint32_t ta_hi = tmem_base + C::A_TMEM_COL0 + s * 64, ta_lo = ta_hi + 32;
 #pragma unroll
-                        for (int ks = 0; ks < 4; ks++) {
-                            const uint64_t o = (uint64_t)ks * kstep;
-                            umma_tf32(d, a_lo + o, b_hi + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
-                            umma_tf32(d, a_hi + o, b_lo + o, idesc, 1u);
-                            umma_tf32(d, a_hi + o, b_hi + o, idesc, 1u);
+                            for (int ks = 0; ks < 4; ks++) {
+                                const uint64_t o = (uint64_t)ks * kstep;
+                                umma_tf32_ts(d, ta_lo + ks * 8, b_hi + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
+                                umma_tf32_ts(d, ta_hi + ks * 8, b_lo + o, idesc, 1u);
+                                umma_tf32_ts(d, ta_hi + ks * 8, b_hi + o, idesc, 1u);
+                            }
+                        } else {
+#pragma unroll
+                            for (int ks = 0; ks < 4; ks++) {
+                                const uint64_t o = (uint64_t)ks * kstep;
+                                umma_tf32(d, a_lo + o, b_hi + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
+                                umma_tf32(d, a_hi + o, b_lo + o, idesc, 1u);
+                                umma_tf32(d, a_hi + o, b_hi + o, idesc, 1u);
+                            }
                         }
                     } else {
                         const uint64_t a = mn_major ? umma_desc_mn(p.mn_desc_bits, base) : umma_desc_sw128(base);
@@ -647,8 +662,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     uint8_t* a_lo = st + C::A_BYTES;
                     uint8_t* b_hi = st + 2 * C::A_BYTES;
                     uint8_t* b_lo = b_hi + C::B_BYTES;
+                    if (p.a_in_tmem) {
+                        // Activation tile: this thread owns row (32*(warp%4) + lane) = its tensor-memory lane and
+                        // 16 of the row's 32 values (all 32 with a single splitter group).  Both parts go to tensor
+                        // memory, where the MMA reads its A operand without touching shared memory again.
+                        const int q = warp & 3;
+                        const uint32_t row = (uint32_t)(q * 32 + lane);
+                        const int ngrp = tma_roles ? 2 : 1;
+                        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + C::A_TMEM_COL0 + s * 64;
+                        for (int c0 = (split_id >> 2) * 16; c0 < 32; c0 += 16 * ngrp) {
+                            uint32_t hi[16], lo[16];
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float4 v = *reinterpret_cast<const float4*>(a_hi + sw128_offset(row, (uint32_t)(c0 / 4 + j)));
+                                const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                                for (int k = 0; k < 4; k++) {
+                                    hi[4 * j + k] = __float_as_uint(e[k]);
+                                    lo[4 * j + k] = __float_as_uint(e[k] - __uint_as_float(__float_as_uint(e[k]) & 0xffffe000u));
+                                }
+                            }
+                            tmem_st_32x16(t_row + c0, hi);
+                            tmem_st_32x16(t_row + 32 + c0, lo);
+                        }
+                        tmem_st_wait();
+                        tc_fence_before_sync();
+                    } else {
 #pragma unroll 4
-                    for (int i = st_id; i < C::A_BYTES / 16; i += st_threads) split_chunk(a_hi + i * 16, a_lo + i * 16);
+                        for (int i = st_id; i < C::A_BYTES / 16; i += st_threads) split_chunk(a_hi + i * 16, a_lo + i * 16);
+                    }
 #pragma unroll 4
                     for (int i = st_id; i < C::B_BYTES / 16; i += st_threads) split_chunk(b_hi + i * 16, b_lo + i * 16);
                     fence_proxy_async_smem();
@@ -1130,6 +1172,10 @@ extern "C" long long ob200_tma_launch_count(void) { return g_tma_launches.load(s
 extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_ctas, void* stream) {
     using namespace ob200;
     IgemmParams p = *params;
+    {
+        const char* e = getenv("ORION_A_TMEM");
+        p.a_in_tmem = (p.dtype == 0 && p.mode == 0 && !(e && e[0] == '0')) ? 1 : 0;
+    }
     if (setup_tma(p, bn)) g_tma_launches.fetch_add(1, std::memory_order_relaxed);
     else if (p.require_tma || p.w_R > 0) return -4;   // tap subsets exist only on the TMA path
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -71,6 +71,7 @@ typedef struct IgemmParams {
      * ow*bmul_w + tma_base_w) and whose per-tap offsets are non-negative, the filter through a tiled map
      * over [batch, Kout, R, S, C].  0: the producer warps gather with 16-byte asynchronous copies. */
     int use_tma;
+    int a_in_tmem;     /* 3xTF32, mode 0: the splitters put both parts of the activation tile into tensor memory */
     int tma_base_h, tma_base_w;
     unsigned long long mn_desc_bits;   /* filter gradient on TMA: the operand descriptors' bits above the address */
     OB200_ALIGN64 unsigned char tmap_a[128];

@@ -93,10 +93,28 @@ int streamk_bn(int Kout) {
     return (Kout <= 64 || (rem > 0 && rem <= 64 && Kout < 256)) ? 64 : 128;
 }
 
-// Puts a mode-0 launch on the stream-K schedule if the stream's scratch has a slot per CTA; returns the grid.
-// At least four k-blocks per CTA, so tiny problems use fewer CTAs instead of paying a reduction per k-block.
+// Whether stream-K beats one unit per tile, in units of one k-block of MMA work per CTA: a tile costs its
+// k-blocks plus about four for the epilogue; stream-K gives every CTA an equal share of all k-blocks but
+// pays about twelve for writing and re-reading the two tiles a CTA shares with its neighbours.  It wins
+// where the tiles are deep and the last wave would be partly empty (3x3 layers at moderate batch), and
+// loses on shallow 1x1 layers and where a tile would be cut into many pieces.
+bool stream_k_pays(long long tiles, int num_kblocks, int num_ctas) {
+    const char* force = getenv("ORION_SCHEDULE");   // "streamk" / "tiles": pin the schedule (for measurements)
+    if (force && force[0] == 's') return true;
+    if (force && force[0] == 't') return false;
+    if (tiles * 4 < num_ctas || num_kblocks < 8) return false;
+    const double waves = (double)((tiles + num_ctas - 1) / num_ctas);
+    const double tiles_cost = waves * (num_kblocks + 4);
+    const double sk_cost = (double)tiles * num_kblocks / num_ctas + 4 + 12;
+    return sk_cost < 0.9 * tiles_cost;
+}
+
+// Puts a mode-0 launch on the stream-K schedule if it pays and the stream's scratch has two slabs per CTA;
+// returns the grid, or 0 to keep the caller's schedule.
 int schedule_stream_k(IgemmParams& p, int bn, int num_ctas, int dev, cudaStream_t stream) {
-    const long long work = (long long)p.tiles_m * p.tiles_n * p.num_kblocks;
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    if (!stream_k_pays(tiles, p.num_kblocks, num_ctas)) return 0;
+    const long long work = tiles * p.num_kblocks;
     long long grid = work / 4;
     if (grid > num_ctas) grid = num_ctas;
     if (grid < 1) grid = 1;
@@ -177,10 +195,34 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
     if (Nb <= 0 || H <= 0 || W <= 0) return Nb == 0 ? 0 : -1;
     const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / (stride_h > 0 ? stride_h : 1) + 1;
     const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / (stride_w > 0 ? stride_w : 1) + 1;
-    // Stream-K schedule with the tile width it prefers; without scratch for it, one unit per tile.
-    const int bn = streamk_bn(Kout);
+    const long long M = (long long)Nb * P * Q;
+    {   // stream-K with the tile width it prefers, where it pays
+        const int bn = streamk_bn(Kout);
+        const int bk = dtype == 1 ? 64 : 32;
+        const long long tiles = ((M + 127) / 128) * ((Kout + bn - 1) / bn);
+        if (stream_k_pays(tiles, R * ((S * C + bk - 1) / bk), num_ctas))
+            return fprop_impl(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w,
+                              dil_h, dil_w, bn, 1, true, nullptr, nullptr, num_ctas, stream);
+    }
+    // otherwise one unit per tile, or split-K where the tiles are few
+    int bn = 128, splits = 1;
+    ob200_plan_conv(dtype, M, Kout, R, S, C, num_ctas, &bn, &splits);
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    if (splits > 1) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const long long tiles = ((M + 127) / 128) * ((Kout + bn - 1) / bn);
+        Scratch* sc = scratch_for(dev, (cudaStream_t)stream);
+        if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
+            splits = 1;
+        } else {
+            scratch = sc->partial;
+            counters = sc->counters;
+        }
+    }
     return fprop_impl(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w, dil_h,
-                      dil_w, bn, 1, true, nullptr, nullptr, num_ctas, stream);
+                      dil_w, bn, splits, false, scratch, counters, num_ctas, stream);
 }
 
 // Data gradient of the convolution: dx[n,h,w,c] = sum_{r,s,k} dy[n,(h+pad-r*dil)/stride,(w+pad-s*dil)/stride,k] * w[k,r,s,c]
