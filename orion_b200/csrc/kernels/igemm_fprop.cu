@@ -114,13 +114,18 @@ __device__ __forceinline__ void st_chunk(uint8_t* hi, uint8_t*, uint32_t off, co
 
 // The tensor core reads a float32 operand as TF32 by ignoring the low 13 mantissa bits, so the raw
 // value already serves as the high part; only the exact remainder x - trunc(x) is written (second buffer).
+// The remainder is rounded to TF32 precision here (to nearest), so the tensor core's truncation of it is exact
+// and the split leaves no systematic error: x = trunc_tf32(x) + remainder up to an unbiased 2^-22 relative.
+__device__ __forceinline__ float tf32_remainder(float x) {
+    return tf32_round(x - __uint_as_float(__float_as_uint(x) & 0xffffe000u));
+}
 __device__ __forceinline__ void split_chunk(uint8_t* hi, uint8_t* lo) {
     const float4 v = *reinterpret_cast<const float4*>(hi);
     float4 l;
-    l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-    l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-    l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-    l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+    l.x = tf32_remainder(v.x);
+    l.y = tf32_remainder(v.y);
+    l.z = tf32_remainder(v.z);
+    l.w = tf32_remainder(v.w);
     *reinterpret_cast<float4*>(lo) = l;
 }
 
@@ -678,8 +683,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                                 const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                                 for (int k = 0; k < 4; k++) {
-                                    hi[4 * j + k] = __float_as_uint(e[k]);
-                                    lo[4 * j + k] = __float_as_uint(e[k] - __uint_as_float(__float_as_uint(e[k]) & 0xffffe000u));
+                                    // Round to nearest on this side (it costs nothing here): the remainder is then
+                                    // zero-mean, so the dropped lo*lo product carries no bias even though the filter
+                                    // side splits by truncation.
+                                    const float h = tf32_round(e[k]);
+                                    hi[4 * j + k] = __float_as_uint(h);
+                                    lo[4 * j + k] = __float_as_uint(tf32_round(e[k] - h));
                                 }
                             }
                             tmem_st_32x16(t_row + c0, hi);

@@ -72,9 +72,10 @@ extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, i
     if ((long long)tiles_m * ((Kout + 127) / 128) * 2 <= num_ctas && Kout >= 128) bn = 64;
     const int tiles = tiles_m * ((Kout + bn - 1) / bn);
     int splits = 1;
-    if (tiles * 2 <= num_ctas && kblocks >= 8) {
+    if (tiles * 2 <= num_ctas && kblocks >= 4) {
         splits = num_ctas / tiles;
-        if (splits > kblocks / 4) splits = kblocks / 4;
+        const int min_chain = getenv("ORION_MIN_CHAIN") ? atoi(getenv("ORION_MIN_CHAIN")) : 4;
+        if (splits > kblocks / min_chain) splits = kblocks / min_chain;
         if (splits > 16) splits = 16;
         if (splits < 1) splits = 1;
     }

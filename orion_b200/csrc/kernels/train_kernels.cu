@@ -13,6 +13,7 @@
 // backward 5x4 B (dy and x twice, dx once).
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace ob200 {
 
@@ -41,14 +42,35 @@ __global__ void __launch_bounds__(TR_THREADS) bn_reduce_kernel(const float* __re
         }
         const long long per = (rows + slabs - 1) / slabs;
         const long long r0 = slab * per, r1 = r0 + per < rows ? r0 + per : rows;
-        for (long long r = r0 + threadIdx.y; r < r1; r += ry) {
+        // Four rows per trip, all loads issued before the first use: the kernel is bound by bytes in flight.
+        constexpr int U = 4;
+        long long r = r0 + threadIdx.y;
+        for (; r + (long long)(U - 1) * ry < r1; r += (long long)U * ry) {
+            float4 v[U], x[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) v[u] = __ldcs(reinterpret_cast<const float4*>(a + (r + (long long)u * ry) * C + c));
+            if (mode == 1) {
+#pragma unroll
+                for (int u = 0; u < U; u++) x[u] = __ldcs(reinterpret_cast<const float4*>(b + (r + (long long)u * ry) * C + c));
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                s0.x += v[u].x; s0.y += v[u].y; s0.z += v[u].z; s0.w += v[u].w;
+                if (mode == 0) {
+                    s1.x += v[u].x * v[u].x; s1.y += v[u].y * v[u].y; s1.z += v[u].z * v[u].z; s1.w += v[u].w * v[u].w;
+                } else {
+                    s1.x += v[u].x * (x[u].x - mu.x) * is.x; s1.y += v[u].y * (x[u].y - mu.y) * is.y;
+                    s1.z += v[u].z * (x[u].z - mu.z) * is.z; s1.w += v[u].w * (x[u].w - mu.w) * is.w;
+                }
+            }
+        }
+        for (; r < r1; r += ry) {
             const float4 v = __ldcs(reinterpret_cast<const float4*>(a + r * C + c));
+            s0.x += v.x; s0.y += v.y; s0.z += v.z; s0.w += v.w;
             if (mode == 0) {
-                s0.x += v.x; s0.y += v.y; s0.z += v.z; s0.w += v.w;
                 s1.x += v.x * v.x; s1.y += v.y * v.y; s1.z += v.z * v.z; s1.w += v.w * v.w;
             } else {
                 const float4 x = __ldcs(reinterpret_cast<const float4*>(b + r * C + c));
-                s0.x += v.x; s0.y += v.y; s0.z += v.z; s0.w += v.w;
                 s1.x += v.x * (x.x - mu.x) * is.x; s1.y += v.y * (x.y - mu.y) * is.y;
                 s1.z += v.z * (x.z - mu.z) * is.z; s1.w += v.w * (x.w - mu.w) * is.w;
             }
@@ -93,27 +115,52 @@ __global__ void bn_stats_finish_kernel(const double* __restrict__ sums, float* _
     }
 }
 
-// y = (x - mean) * invstd * gamma + beta
+// y = (x - mean) * invstd * gamma + beta.
+// When the grid stride is a multiple of the channel-quad count every thread stays on one channel quad,
+// so the per-channel coefficients are computed once per thread and the loop is loads, FMAs and stores.
 __global__ void __launch_bounds__(TR_THREADS) bn_apply_kernel(const float4* __restrict__ x, float4* __restrict__ y,
                                                              const float* __restrict__ gamma, const float* __restrict__ beta,
                                                              const float* __restrict__ mean, const float* __restrict__ invstd,
                                                              long long n4, int c4) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-        const int c = (int)(i % c4) * 4;
-        const float4 v = __ldcs(x + i);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    auto coef = [&](int c, float4& a, float4& b) {
         const float4 m = __ldg(reinterpret_cast<const float4*>(mean + c));
         const float4 is = __ldg(reinterpret_cast<const float4*>(invstd + c));
-        float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 g = make_float4(1.f, 1.f, 1.f, 1.f), be = make_float4(0.f, 0.f, 0.f, 0.f);
         if (gamma) g = __ldg(reinterpret_cast<const float4*>(gamma + c));
-        if (beta) b = __ldg(reinterpret_cast<const float4*>(beta + c));
-        float4 o;
-        o.x = (v.x - m.x) * is.x * g.x + b.x; o.y = (v.y - m.y) * is.y * g.y + b.y;
-        o.z = (v.z - m.z) * is.z * g.z + b.z; o.w = (v.w - m.w) * is.w * g.w + b.w;
-        y[i] = o;
+        if (beta) be = __ldg(reinterpret_cast<const float4*>(beta + c));
+        a = make_float4(is.x * g.x, is.y * g.y, is.z * g.z, is.w * g.w);
+        b = make_float4(be.x - m.x * a.x, be.y - m.y * a.y, be.z - m.z * a.z, be.w - m.w * a.w);
+    };
+    if (stride % c4 == 0) {
+        if (i >= n4) return;
+        float4 a, b;
+        coef((int)(i % c4) * 4, a, b);
+        for (; i + 3 * stride < n4; i += 4 * stride) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = __ldcs(x + i + u * stride);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                y[i + u * stride] = make_float4(fmaf(v[u].x, a.x, b.x), fmaf(v[u].y, a.y, b.y), fmaf(v[u].z, a.z, b.z), fmaf(v[u].w, a.w, b.w));
+        }
+        for (; i < n4; i += stride) {
+            const float4 v = __ldcs(x + i);
+            y[i] = make_float4(fmaf(v.x, a.x, b.x), fmaf(v.y, a.y, b.y), fmaf(v.z, a.z, b.z), fmaf(v.w, a.w, b.w));
+        }
+        return;
+    }
+    for (; i < n4; i += stride) {
+        float4 a, b;
+        coef((int)(i % c4) * 4, a, b);
+        const float4 v = __ldcs(x + i);
+        y[i] = make_float4(fmaf(v.x, a.x, b.x), fmaf(v.y, a.y, b.y), fmaf(v.z, a.z, b.z), fmaf(v.w, a.w, b.w));
     }
 }
 
-// dx = gamma * invstd * (dy - sum_dy/M - xhat * sum_dy_xhat/M);  dgamma = sum_dy_xhat, dbeta = sum_dy
+// dx = gamma * invstd * (dy - sum_dy/M - xhat * sum_dy_xhat/M) = a*dy + b*x + c per channel;
+// dgamma = sum_dy_xhat, dbeta = sum_dy.  Same fixed-channel fast path as bn_apply_kernel.
 __global__ void __launch_bounds__(TR_THREADS) bn_backward_apply_kernel(const float4* __restrict__ dy, const float4* __restrict__ x,
                                                                       float4* __restrict__ dx, const float* __restrict__ gamma,
                                                                       const float* __restrict__ mean,
@@ -123,25 +170,52 @@ __global__ void __launch_bounds__(TR_THREADS) bn_backward_apply_kernel(const flo
                                                                       long long rows) {
     const int C = c4 * 4;
     const float inv_rows = 1.0f / (float)rows;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-        const int c = (int)(i % c4) * 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    auto coef = [&](int c, bool publish, float4& a, float4& b, float4& k) {
         const float4 g = gamma ? __ldg(reinterpret_cast<const float4*>(gamma + c)) : make_float4(1.f, 1.f, 1.f, 1.f);
         const float4 m = __ldg(reinterpret_cast<const float4*>(mean + c));
         const float4 is = __ldg(reinterpret_cast<const float4*>(invstd + c));
         const float sd[4] = {(float)sums[c], (float)sums[c + 1], (float)sums[c + 2], (float)sums[c + 3]};
         const float sx[4] = {(float)sums[C + c], (float)sums[C + c + 1], (float)sums[C + c + 2], (float)sums[C + c + 3]};
-        const float4 d = __ldcs(dy + i);
-        const float4 v = __ldcs(x + i);
-        float4 o;
-        o.x = g.x * is.x * (d.x - sd[0] * inv_rows - (v.x - m.x) * is.x * sx[0] * inv_rows);
-        o.y = g.y * is.y * (d.y - sd[1] * inv_rows - (v.y - m.y) * is.y * sx[1] * inv_rows);
-        o.z = g.z * is.z * (d.z - sd[2] * inv_rows - (v.z - m.z) * is.z * sx[2] * inv_rows);
-        o.w = g.w * is.w * (d.w - sd[3] * inv_rows - (v.w - m.w) * is.w * sx[3] * inv_rows);
-        dx[i] = o;
-        if (i < c4) {   // the first row's threads also publish the parameter gradients
+        const float gg[4] = {g.x, g.y, g.z, g.w}, mm[4] = {m.x, m.y, m.z, m.w}, ii[4] = {is.x, is.y, is.z, is.w};
+        float aa[4], bb[4], kk[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            aa[e] = gg[e] * ii[e];
+            bb[e] = -aa[e] * ii[e] * sx[e] * inv_rows;
+            kk[e] = -aa[e] * sd[e] * inv_rows - bb[e] * mm[e];
+        }
+        a = make_float4(aa[0], aa[1], aa[2], aa[3]);
+        b = make_float4(bb[0], bb[1], bb[2], bb[3]);
+        k = make_float4(kk[0], kk[1], kk[2], kk[3]);
+        if (publish) {   // the first row's threads also publish the parameter gradients
             if (dbeta) { dbeta[c] = sd[0]; dbeta[c + 1] = sd[1]; dbeta[c + 2] = sd[2]; dbeta[c + 3] = sd[3]; }
             if (dgamma) { dgamma[c] = sx[0]; dgamma[c + 1] = sx[1]; dgamma[c + 2] = sx[2]; dgamma[c + 3] = sx[3]; }
         }
+    };
+    auto apply = [](const float4& d, const float4& v, const float4& a, const float4& b, const float4& k) {
+        return make_float4(fmaf(a.x, d.x, fmaf(b.x, v.x, k.x)), fmaf(a.y, d.y, fmaf(b.y, v.y, k.y)), fmaf(a.z, d.z, fmaf(b.z, v.z, k.z)),
+                           fmaf(a.w, d.w, fmaf(b.w, v.w, k.w)));
+    };
+    if (stride % c4 == 0) {
+        if (i >= n4) return;
+        float4 a, b, k;
+        coef((int)(i % c4) * 4, i < c4, a, b, k);
+        for (; i + stride < n4; i += 2 * stride) {
+            float4 d[2], v[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) { d[u] = __ldcs(dy + i + u * stride); v[u] = __ldcs(x + i + u * stride); }
+#pragma unroll
+            for (int u = 0; u < 2; u++) dx[i + u * stride] = apply(d[u], v[u], a, b, k);
+        }
+        for (; i < n4; i += stride) dx[i] = apply(__ldcs(dy + i), __ldcs(x + i), a, b, k);
+        return;
+    }
+    for (; i < n4; i += stride) {
+        float4 a, b, k;
+        coef((int)(i % c4) * 4, i < c4, a, b, k);
+        dx[i] = apply(__ldcs(dy + i), __ldcs(x + i), a, b, k);
     }
 }
 
@@ -190,11 +264,23 @@ __global__ void __launch_bounds__(TR_THREADS) sgd_momentum_kernel(float* __restr
     }
 }
 
+// Grid for the per-channel elementwise kernels: like grid_for, rounded down so that the grid stride (grid *
+// TR_THREADS float4 elements) is a multiple of the channel-quad count whenever that costs little.
+static inline int grid_for_channels(long long items, int num_ctas, int per_sm, int c4);
+
 static inline int grid_for(long long items, int num_ctas, int per_sm) {
     long long want = (items + TR_THREADS - 1) / TR_THREADS;
     long long cap = (long long)num_ctas * per_sm;
     if (want < 1) want = 1;
     return (int)(want < cap ? want : cap);
+}
+
+static inline int grid_for_channels(long long items, int num_ctas, int per_sm, int c4) {
+    int g = grid_for(items, num_ctas, per_sm);
+    int need = 1;   // smallest grid multiple that makes grid * TR_THREADS divisible by c4
+    while (((long long)need * TR_THREADS) % c4 != 0 && need < 4096) need++;
+    if (need > 1 && g >= need && need <= 64) g -= g % need;
+    return g;
 }
 
 static cudaError_t launch_reduce(const float* a, const float* b, const float* mean, const float* invstd, double* out, long long rows,
@@ -205,7 +291,8 @@ static cudaError_t launch_reduce(const float* a, const float* b, const float* me
     while (pow2 * 2 <= ry) pow2 *= 2;
     ry = pow2;
     const int c_groups = (C / 4 + cq - 1) / cq;
-    long long slabs = (long long)num_ctas * 2 / c_groups;
+    static const int slab_factor = getenv("ORION_BN_SLABS") ? atoi(getenv("ORION_BN_SLABS")) : 2;
+    long long slabs = (long long)num_ctas * slab_factor / c_groups;
     if (slabs < 1) slabs = 1;
     if (slabs > (rows + ry - 1) / ry) slabs = (rows + ry - 1) / ry;
     if (slabs < 1) slabs = 1;
@@ -232,7 +319,7 @@ extern "C" int ob200_bn_train_forward_f32(const float* x, float* y, const float*
     bn_stats_finish_kernel<<<(C + 127) / 128, 128, 0, s>>>(sums, save_mean, save_invstd, running_mean, running_var, rows, C, eps,
                                                            momentum);
     const long long n4 = rows * C / 4;
-    bn_apply_kernel<<<grid_for(n4, num_ctas, 4), TR_THREADS, 0, s>>>((const float4*)x, (float4*)y, gamma, beta, save_mean, save_invstd,
+    bn_apply_kernel<<<grid_for_channels(n4, num_ctas, 6, C / 4), TR_THREADS, 0, s>>>((const float4*)x, (float4*)y, gamma, beta, save_mean, save_invstd,
                                                                     n4, C / 4);
     return (int)cudaGetLastError();
 }
@@ -248,7 +335,7 @@ extern "C" int ob200_bn_backward_f32(const float* dy, const float* x, float* dx,
     cudaError_t e = launch_reduce(dy, x, save_mean, save_invstd, sums, rows, C, 1, num_ctas, s);
     if (e != cudaSuccess) return (int)e;
     const long long n4 = rows * C / 4;
-    bn_backward_apply_kernel<<<grid_for(n4, num_ctas, 4), TR_THREADS, 0, s>>>((const float4*)dy, (const float4*)x, (float4*)dx, gamma,
+    bn_backward_apply_kernel<<<grid_for_channels(n4, num_ctas, 6, C / 4), TR_THREADS, 0, s>>>((const float4*)dy, (const float4*)x, (float4*)dx, gamma,
                                                                              save_mean, save_invstd, sums, dgamma, dbeta, n4, C / 4,
                                                                              rows);
     return (int)cudaGetLastError();
