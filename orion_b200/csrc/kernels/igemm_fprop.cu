@@ -53,22 +53,34 @@ constexpr int PROD_WARPS = 8;     // warps 9-16 when the operands are gathered w
 constexpr int TMA_WARP = 17;      // one lane issues the TMA copies of TMA-fed launches
 constexpr int NTHREADS = 18 * 32;
 
-template <typename T, int BN, int PASSES>
+// ATMEM: 3xTF32 with both parts of the activation tile in tensor memory (forward / data gradient / GEMM).
+template <typename T, int BN, int PASSES, bool ATMEM>
 struct Cfg {
     static constexpr bool kSplit = sizeof(T) == 4 && PASSES == 3;   // 3xTF32; PASSES == 1 is plain TF32
+    static_assert(!ATMEM || kSplit, "tensor-memory activation parts exist only for 3xTF32");
     static constexpr int BK = 128 / sizeof(T);                // elements per 128-byte row
     static constexpr int EPC = 16 / sizeof(T);                // elements per 16-byte chunk
     static constexpr int A_BYTES = BM * 128;
     static constexpr int B_BYTES = BN * 128;
-    static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (kSplit ? 2 : 1);
-    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+    // Stage: [A raw][A remainder][B raw][B remainder] (3xTF32 from shared memory), [A raw][B raw][B remainder]
+    // (activation parts in tensor memory), or [A][B] (one pass).
+    static constexpr int STAGE_BYTES = ATMEM ? A_BYTES + 2 * B_BYTES : (A_BYTES + B_BYTES) * (kSplit ? 2 : 1);
+    static constexpr int B_OFF = (kSplit && !ATMEM) ? 2 * A_BYTES : A_BYTES;
+#ifndef OB200_STAGE_CAP
+#define OB200_STAGE_CAP 8
+#endif
+    static constexpr int BY_SMEM0 = (192 * 1024) / STAGE_BYTES;
+    static constexpr int BY_SMEM = BY_SMEM0 > OB200_STAGE_CAP ? OB200_STAGE_CAP : BY_SMEM0;
+    static constexpr int BY_TMEM = ATMEM ? (512 - 2 * BN) / 64 : 8;      // 64 tensor-memory columns per stage
+    static constexpr int STAGES = BY_SMEM < BY_TMEM ? (BY_SMEM > 8 ? 8 : BY_SMEM) : (BY_TMEM > 8 ? 8 : BY_TMEM);
+    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
     static constexpr int EPI_BYTES = 2 * EPI_WARPS * 32 * 20 * 4;   // per-warp transpose tiles of the epilogue (EPI_LD floats per row)
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 512 /*barriers*/;
-    // Two accumulators of BN columns; 3xTF32 also keeps, per stage, the two parts of the activation tile
-    // (32 + 32 columns) in tensor memory.  Allocations are powers of two.
+    static constexpr int SMEM_BYTES = RING_BYTES + EPI_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+    // Two accumulators of BN columns; ATMEM adds, per stage, the two parts of the activation tile (32 + 32 columns).
+    // Allocations are powers of two.
     static constexpr int A_TMEM_COL0 = 2 * BN;
-    static constexpr int TMEM_COLS = kSplit ? 512 : 2 * BN;
-    static_assert(!kSplit || 2 * BN + STAGES * 64 <= 512, "tensor memory budget");
+    static constexpr int TMEM_COLS = ATMEM ? 512 : 2 * BN;
+    static_assert(!ATMEM || 2 * BN + STAGES * 64 <= 512, "tensor memory budget");
 };
 
 struct SharedCtl {
@@ -271,6 +283,15 @@ __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volat
     return ok;
 }
 
+// Position in the ring of operand stages: stage index and the parity of the number of completed laps.
+struct RingPos {
+    int s = 0;
+    uint32_t ph = 0;
+    __device__ __forceinline__ void advance(int stages) {
+        if (++s == stages) { s = 0; ph ^= 1u; }
+    }
+};
+
 // One piece of work of a CTA: k-blocks [kb_begin, kb_end) of output tile `tile`.  nseg is the number of
 // pieces the tile is computed in (1: this piece is the whole tile and stores directly); pieces of a cut
 // tile accumulate in scratch slot `slot`.
@@ -334,21 +355,24 @@ __device__ __forceinline__ void red_add_v4(float* dst, const float4& v) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-template <typename T, int BN, int PASSES>
+template <typename T, int BN, int PASSES, bool ATMEM>
 __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_constant__ IgemmParams p) {
-    using C = Cfg<T, BN, PASSES>;
+    using C = Cfg<T, BN, PASSES, ATMEM>;
     using Chunk = typename ChunkOf<T>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    float* epi_stage = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);
-    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + C::STAGES * C::STAGE_BYTES + C::EPI_BYTES);
+    float* epi_stage = reinterpret_cast<float*>(smem + C::RING_BYTES);
+    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + C::RING_BYTES + C::EPI_BYTES);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    constexpr int stages = C::STAGES;
+    constexpr int stage_bytes = C::STAGE_BYTES;
+    constexpr int b_off = C::B_OFF;
 
     if (tid == 0) {
-        for (int s = 0; s < C::STAGES; s++) {
+        for (int s = 0; s < stages; s++) {
             // every producer thread, when its copies have landed; or the one TMA-issuing thread plus the byte count
             mbar_init(&ctl->raw_full[s], p.use_tma ? 1 : PROD_WARPS * 32);
             mbar_init(&ctl->full[s], p.use_tma ? 2 * SPLIT_WARPS : SPLIT_WARPS);   // one elected lane per splitter warp
@@ -575,7 +599,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             const bool mn_major = p.mode == 1 && p.use_tma;
             const uint32_t idesc = umma_idesc(sizeof(T) == 4 ? 2 : 1, BM, BN) | (mn_major ? (UMMA_IDESC_A_MN | UMMA_IDESC_B_MN) : 0u);
             const uint64_t kstep = mn_major ? (1024 >> 4) : (32 >> 4);   // descriptor address advance per k-step of 8 (16 for bf16)
-            uint32_t it = 0;
+            RingPos ring;
             int local = 0;
             bool dead = false;
             long long waited2 = 0;
@@ -590,24 +614,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 }
                 tc_fence_after_sync();
                 const uint32_t d = tmem_base + ab * BN;
-                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                    const int s = it % C::STAGES;
+                for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
+                    const int s = ring.s;
                     // fp32: operands are ready when the splitters are done; bf16: when the copies have landed
-                    if (!timed_wait(C::kSplit ? &ctl->full[s] : &ctl->raw_full[s], (it / C::STAGES) & 1, abort_flag, waited)) {
+                    if (!timed_wait(C::kSplit ? &ctl->full[s] : &ctl->raw_full[s], ring.ph, abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_FULL); }
                         dead = true;
                         break;
                     }
                     if (!C::kSplit) fence_proxy_async_smem();   // cp.async wrote through the generic proxy
                     tc_fence_after_sync();
-                    const uint32_t base = smem_u32(smem + s * C::STAGE_BYTES);
+                    const uint32_t base = smem_u32(smem + s * stage_bytes);
                     if (C::kSplit) {
                         const uint64_t a_hi = mn_major ? umma_desc_mn(p.mn_desc_bits, base) : umma_desc_sw128(base);
                         const uint64_t a_lo = mn_major ? umma_desc_mn(p.mn_desc_bits, base + C::A_BYTES) : umma_desc_sw128(base + C::A_BYTES);
-                        const uint64_t b_hi = mn_major ? umma_desc_mn(p.mn_desc_bits, base + 2 * C::A_BYTES) : umma_desc_sw128(base + 2 * C::A_BYTES);
-                        const uint64_t b_lo = mn_major ? umma_desc_mn(p.mn_desc_bits, base + 2 * C::A_BYTES + C::B_BYTES)
-                                                       : umma_desc_sw128(base + 2 * C::A_BYTES + C::B_BYTES);
-                        if (p.a_in_tmem) {
+                        const uint64_t b_hi = mn_major ? umma_desc_mn(p.mn_desc_bits, base + b_off) : umma_desc_sw128(base + b_off);
+                        const uint64_t b_lo = mn_major ? umma_desc_mn(p.mn_desc_bits, base + b_off + C::B_BYTES)
+                                                       : umma_desc_sw128(base + b_off + C::B_BYTES);
+                        if (ATMEM) {
                             const uint32_t ta_hi = tmem_base + C::A_TMEM_COL0 + s * 64, ta_lo = ta_hi + 32;
 #pragma unroll
                             for (int ks = 0; ks < 4; ks++) {
@@ -649,25 +673,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         if (C::kSplit) {
             const int st_id = split_id * 32 + lane;
             const int st_threads = (tma_roles ? 2 * SPLIT_WARPS : SPLIT_WARPS) * 32;
-            uint32_t it = 0;
+            RingPos ring;
             bool dead = false;
             WorkIter work(p, tiles);
             Seg seg;
             while (!dead && work.next(seg)) {
                 const int kb_begin = seg.kb_begin, kb_end = seg.kb_end;
-                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                    const int s = it % C::STAGES;
-                    if (!timed_wait(&ctl->raw_full[s], (it / C::STAGES) & 1, abort_flag, waited)) {
+                for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
+                    const int s = ring.s;
+                    if (!timed_wait(&ctl->raw_full[s], ring.ph, abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_FULL); }
                         dead = true;
                         break;
                     }
-                    uint8_t* st = smem + s * C::STAGE_BYTES;
+                    uint8_t* st = smem + s * stage_bytes;
                     uint8_t* a_hi = st;
                     uint8_t* a_lo = st + C::A_BYTES;
-                    uint8_t* b_hi = st + 2 * C::A_BYTES;
+                    uint8_t* b_hi = st + b_off;
                     uint8_t* b_lo = b_hi + C::B_BYTES;
-                    if (p.a_in_tmem) {
+                    if (ATMEM) {
                         // Activation tile: this thread owns row (32*(warp%4) + lane) = its tensor-memory lane and
                         // 16 of the row's 32 values (all 32 with a single splitter group).  Both parts go to tensor
                         // memory, where the MMA reads its A operand without touching shared memory again.
@@ -725,7 +749,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         const int row0 = pt >> 3;               // 0..31; this thread serves rows row0 + 32*i
         // (row & 7) == (row0 & 7) for all of them, so the swizzled chunk position is a per-thread constant
         const uint32_t sw_off = (uint32_t)row0 * 128u + (uint32_t)((chunk ^ (row0 & 7)) << 4);
-        uint32_t it = 0;
+        RingPos ring;
         bool dead = false;
         WorkIter work(p, tiles);
         Seg seg;
@@ -748,19 +772,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     const int pq = p.P * p.Q;
                     int nb_boxes = 0;
                     for (int g = 0; g < BN / 32; g++) nb_boxes += (c0 + 32 * g < p.C) ? 1 : 0;
-                    for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                        const int s = it % C::STAGES;
+                    for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
+                        const int s = ring.s;
                         const long long m0 = (long long)kb * 32;
                         const int n_img = (int)(m0 / pq);
                         const int rem = (int)(m0 - (long long)n_img * pq);
                         const int op = rem / p.Q, oq = rem - op * p.Q;
-                        if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                        if (!timed_wait(&ctl->empty[s], (ring.ph ^ 1u), abort_flag, waited)) {
                             if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                             dead = true;
                             break;
                         }
-                        const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
-                        const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                        const uint32_t a_dst = smem_u32(smem + s * stage_bytes);
+                        const uint32_t b_dst = a_dst + b_off;
                         mbar_arrive_expect_tx(&ctl->raw_full[s], C::A_BYTES + nb_boxes * 4096);
 #pragma unroll
                         for (int g = 0; g < BM / 32; g++) tma_load_tile_2d(a_dst + g * 4096, p.tmap_a, &ctl->raw_full[s], k0 + 32 * g, (int)m0);
@@ -788,20 +812,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     const int op = rem / p.OW, oq = rem - op * p.OW;
                     const int cw = oq * p.bmul_w + p.tma_base_w, ch = op * p.bmul_h + p.tma_base_h;
                     const int cn = bidx * p.Nb + n_img;
-                    for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                        const int s = it % C::STAGES;
+                    for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
+                        const int s = ring.s;
                         const int r = kb / p.kblocks_per_r;
                         const int kin = (kb - r * p.kblocks_per_r) * C::BK;
                         const int ts = kin / p.C, tc = kin - ts * p.C;
                         const int off_h = p.step_h >= 0 ? r * p.step_h : (p.R - 1 - r) * -p.step_h;
                         const int off_w = p.step_w >= 0 ? ts * p.step_w : (p.S - 1 - ts) * -p.step_w;
-                        if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                        if (!timed_wait(&ctl->empty[s], (ring.ph ^ 1u), abort_flag, waited)) {
                             if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                             dead = true;
                             break;
                         }
-                        const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
-                        const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                        const uint32_t a_dst = smem_u32(smem + s * stage_bytes);
+                        const uint32_t b_dst = a_dst + b_off;
                         mbar_arrive_expect_tx(&ctl->raw_full[s], C::A_BYTES + C::B_BYTES);
                         tma_load_im2col_4d(a_dst, p.tmap_a, &ctl->raw_full[s], tc, cw, ch, cn, (uint16_t)off_w, (uint16_t)off_h);
                         tma_load_tile_5d(b_dst, p.tmap_b, &ctl->raw_full[s], tc, ts, r, tn * BN, bidx);
@@ -825,8 +849,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     const int prow = pt >> 3, cg = pt & 7;
                     const float* __restrict__ DY = reinterpret_cast<const float*>(X);
                     const float* __restrict__ IN = reinterpret_cast<const float*>(Wt);
-                    for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                        const int s = it % C::STAGES;
+                    for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
+                        const int s = ring.s;
                         const long long m = (long long)kb * 32 + prow;
                         const bool m_ok = m < p.M;
                         const float* xsrc = nullptr;
@@ -850,13 +874,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                             const int c = c0 + (cg + 8 * i) * 4;
                             bv[i] = (xsrc != nullptr && c < p.C) ? __ldg(reinterpret_cast<const float4*>(xsrc + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
                         }
-                        if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                        if (!timed_wait(&ctl->empty[s], (ring.ph ^ 1u), abort_flag, waited)) {
                             if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                             dead = true;
                             break;
                         }
-                        uint8_t* a_dst = smem + s * C::STAGE_BYTES;
-                        uint8_t* b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                        uint8_t* a_dst = smem + s * stage_bytes;
+                        uint8_t* b_dst = a_dst + b_off;
                         const uint32_t col_chunk = (uint32_t)prow >> 2, col_word = ((uint32_t)prow & 3u) * 4u;
 #pragma unroll
                         for (int i = 0; i < BM / 32; i++) {
@@ -908,8 +932,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     const int kout = tn * BN + i * 32 + row0;
                     wrow[i] = kout < p.Kout ? Wt + (long long)kout * p.R * SC : nullptr;
                 }
-                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                    const int s = it % C::STAGES;
+                for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
+                    const int s = ring.s;
                     const int r = kb / p.kblocks_per_r;
                     const int kk = (kb - r * p.kblocks_per_r) * C::BK + chunk * C::EPC;
                     const bool k_ok = kk < SC;
@@ -917,13 +941,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     const int dh = r * p.step_h, dw = ts * p.step_w;
                     const long long xoff = ((long long)dh * p.IW + dw) * p.C + tc;   // same for every row of the tile
                     const long long woff = (long long)r * SC + kk;
-                    if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                    if (!timed_wait(&ctl->empty[s], (ring.ph ^ 1u), abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                         dead = true;
                         break;
                     }
-                    const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES) + sw_off;
-                    const uint32_t b_dst = a_dst + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                    const uint32_t a_dst = smem_u32(smem + s * stage_bytes) + sw_off;
+                    const uint32_t b_dst = a_dst + b_off;
                     if (unit) {
 #pragma unroll
                         for (int i = 0; i < RPT; i++) {
@@ -966,8 +990,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 }
                 const int kout = tn * BN + row;
                 const bool b_ok = worker && row < BN && kout < p.Kout;
-                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
-                    const int s = it % C::STAGES;
+                for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
+                    const int s = ring.s;
                     const int r = kb / p.kblocks_per_r;
                     const int kk0 = (kb - r * p.kblocks_per_r) * C::BK;
                     const int hn = h_base + r * p.step_h;
@@ -975,14 +999,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     const bool h_ok = m_ok && hn >= 0 && h * p.div_h == hn && h < p.IH;
                     const T* xrow = X + ((long long)n_img * p.IH + (h_ok ? h : 0)) * p.IW * p.C;
                     const T* wrow = Wt + ((long long)(b_ok ? kout : 0) * p.R + r) * SC;
-                    if (!timed_wait(&ctl->empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, waited)) {
+                    if (!timed_wait(&ctl->empty[s], (ring.ph ^ 1u), abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                         dead = true;
                         break;
                     }
-                    uint8_t* st = smem + s * C::STAGE_BYTES;
+                    uint8_t* st = smem + s * stage_bytes;
                     uint8_t* a_dst = st;
-                    uint8_t* b_dst = st + (C::kSplit ? 2 : 1) * C::A_BYTES;
+                    uint8_t* b_dst = st + b_off;
                     int ts = kk0 / p.C, tc = kk0 - ts * p.C;
 #pragma unroll 1
                     for (int j = 0; j < (worker ? 8 : 0); j++) {
@@ -1022,18 +1046,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
     }
 }
 
-template <typename T, int BN, int PASSES>
+template <typename T, int BN, int PASSES, bool ATMEM = false>
 static cudaError_t launch_cfg(const IgemmParams& p, int num_ctas, cudaStream_t stream) {
-    using C = Cfg<T, BN, PASSES>;
+    using C = Cfg<T, BN, PASSES, ATMEM>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_fprop_kernel<T, BN, PASSES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(igemm_fprop_kernel<T, BN, PASSES, ATMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    igemm_fprop_kernel<T, BN, PASSES><<<num_ctas, NTHREADS, C::SMEM_BYTES, stream>>>(p);
+    igemm_fprop_kernel<T, BN, PASSES, ATMEM><<<num_ctas, NTHREADS, C::SMEM_BYTES, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -1189,6 +1213,7 @@ extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_cta
     else if (p.require_tma || p.w_R > 0) return -4;   // tap subsets exist only on the TMA path
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (p.dtype == 0) {
+        if (p.a_in_tmem) return (int)(bn == 64 ? launch_cfg<float, 64, 3, true>(p, num_ctas, s) : launch_cfg<float, 128, 3, true>(p, num_ctas, s));
         return (int)(bn == 64 ? launch_cfg<float, 64, 3>(p, num_ctas, s) : launch_cfg<float, 128, 3>(p, num_ctas, s));
     } else if (p.dtype == 1) {
         return (int)(bn == 64 ? launch_cfg<__nv_bfloat16, 64, 1>(p, num_ctas, s) : launch_cfg<__nv_bfloat16, 128, 1>(p, num_ctas, s));
