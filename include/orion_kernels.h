@@ -131,6 +131,13 @@ int ob200_read_status(void);
  * waiting: [0] epilogue, [1] MMA on operands, [2] MMA on a free accumulator, [3] splitter,
  * [4] producer, [5] whole kernel. */
 void ob200_set_debug_buffer(long long* dev_buf);
+/* Depthwise convolution (groups = C, channel multiplier 1), NHWC float32, C a multiple of 4, with the same
+ * fused epilogue as ob200_conv2d_fprop (scale, shift, relu 0/1/2 = none/ReLU/ReLU6).  w_tap_major = 0: filter
+ * [C][R][S] as torch holds a [C,1,R,S] weight; 1: [R][S][C].  Stands in for the grouped cudnnConvolutionForward
+ * calls of MobileNetV2 that the reference replays (src/scheduler/utils_sched.cpp:284-296). */
+int ob200_depthwise_conv2d_f32(const float* x, const float* w, float* y, const float* scale, const float* shift, int relu, int Nb,
+                               int H, int W, int C, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
+                               int dil_w, int w_tap_major, int num_ctas, void* stream);
 /* Number of implicit-GEMM launches of this process whose operands were fed by TMA tensor maps (the others
  * gathered with 16-byte asynchronous copies: strided data gradients, filter gradients, channel counts below
  * one k-block or k-blocks that straddle filter taps).  No counterpart in the reference. */

@@ -14,12 +14,12 @@ import torch
 import torch.nn.functional as F
 
 
-def conv2d_nhwc(x, w, stride, padding, dilation=(1, 1), scale=None, shift=None, residual=None, act=0):
+def conv2d_nhwc(x, w, stride, padding, dilation=(1, 1), scale=None, shift=None, residual=None, act=0, groups=1):
     """cudnnConvolutionForward as the reference calls it (utils_sched.cpp:284-296), for NHWC x / KRSC w,
     followed by the optional per-channel affine, residual add and activation of the fused epilogue."""
     xd = x.detach().double().cpu().permute(0, 3, 1, 2)
     wd = w.detach().double().cpu().permute(0, 3, 1, 2)
-    y = F.conv2d(xd, wd, stride=stride, padding=padding, dilation=dilation).permute(0, 2, 3, 1)
+    y = F.conv2d(xd, wd, stride=stride, padding=padding, dilation=dilation, groups=groups).permute(0, 2, 3, 1)
     if scale is not None:
         y = y * scale.detach().double().cpu()
     if shift is not None:

@@ -224,3 +224,84 @@ extern "C" int ob200_pad_channels(const void* src, void* dst, long long pixels, 
             (const unsigned short*)src, (unsigned short*)dst, pixels, C, Cpad);
     return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- depthwise convolution
+// y[n,p,q,c] = act( scale[c] * sum_{r,s} x[n, p*sh - ph + r*dh, q*sw - pw + s*dw, c] * w[c][r][s] + shift[c] ),
+// NHWC float32, channel multiplier 1 (groups = C): the depthwise layers of MobileNetV2, which the reference
+// hands to cudnnConvolutionForward like any other convolution (src/scheduler/utils_sched.cpp:284-296).
+// One thread per output pixel and channel quad; a warp covers 32 consecutive channel quads, so every tap is a
+// coalesced 512-byte read and neighbouring pixels re-read it from L1/L2.  HBM-bound: 8 B per element.
+// w_tap_major = 1: filter stored [R][S][C] (one float4 per tap), 0: [C][R][S] as torch holds it.
+namespace ob200 {
+__global__ void __launch_bounds__(ELT_THREADS) depthwise_conv_nhwc_f32_kernel(
+    const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, const float* __restrict__ scale,
+    const float* __restrict__ shift, int relu, int Nb, int H, int W, int C, int R, int S, int P, int Q, int stride_h, int stride_w,
+    int pad_h, int pad_w, int dil_h, int dil_w, int w_tap_major) {
+    const int c4 = C / 4;
+    const long long total = (long long)Nb * P * Q * c4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int cq = (int)(i % c4);
+        long long pix = i / c4;
+        const int q = (int)(pix % Q);
+        pix /= Q;
+        const int p = (int)(pix % P);
+        const int n = (int)(pix / P);
+        const int c = cq * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int h0 = p * stride_h - pad_h, w0 = q * stride_w - pad_w;
+        for (int r = 0; r < R; r++) {
+            const int h = h0 + r * dil_h;
+            if ((unsigned)h >= (unsigned)H) continue;
+            for (int s = 0; s < S; s++) {
+                const int ww = w0 + s * dil_w;
+                if ((unsigned)ww >= (unsigned)W) continue;
+                const float4 v = __ldg(reinterpret_cast<const float4*>(x + (((long long)n * H + h) * W + ww) * C + c));
+                float4 f;
+                if (w_tap_major) {
+                    f = __ldg(reinterpret_cast<const float4*>(w + ((long long)r * S + s) * C + c));
+                } else {
+                    const int t = r * S + s, rs = R * S;
+                    f = make_float4(__ldg(w + (long long)c * rs + t), __ldg(w + (long long)(c + 1) * rs + t),
+                                    __ldg(w + (long long)(c + 2) * rs + t), __ldg(w + (long long)(c + 3) * rs + t));
+                }
+                acc.x = fmaf(v.x, f.x, acc.x); acc.y = fmaf(v.y, f.y, acc.y);
+                acc.z = fmaf(v.z, f.z, acc.z); acc.w = fmaf(v.w, f.w, acc.w);
+            }
+        }
+        if (scale) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(scale + c));
+            acc.x *= g.x; acc.y *= g.y; acc.z *= g.z; acc.w *= g.w;
+        }
+        if (shift) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(shift + c));
+            acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+        }
+        if (relu) {
+            acc.x = fmaxf(acc.x, 0.f); acc.y = fmaxf(acc.y, 0.f); acc.z = fmaxf(acc.z, 0.f); acc.w = fmaxf(acc.w, 0.f);
+            if (relu == 2) { acc.x = fminf(acc.x, 6.f); acc.y = fminf(acc.y, 6.f); acc.z = fminf(acc.z, 6.f); acc.w = fminf(acc.w, 6.f); }
+        }
+        reinterpret_cast<float4*>(y)[i] = acc;
+    }
+}
+}  // namespace ob200
+
+extern "C" int ob200_depthwise_conv2d_f32(const float* x, const float* w, float* y, const float* scale, const float* shift, int relu,
+                                          int Nb, int H, int W, int C, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w,
+                                          int dil_h, int dil_w, int w_tap_major, int num_ctas, void* stream) {
+    if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || (C & 3) || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || dil_h <= 0 ||
+        dil_w <= 0 || pad_h < 0 || pad_w < 0 || num_ctas <= 0 || relu < 0 || relu > 2)
+        return -1;
+    if (Nb == 0) return 0;
+    const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / stride_h + 1;
+    const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / stride_w + 1;
+    if (P <= 0 || Q <= 0) return -1;
+    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)shift) % 16 || (w_tap_major && (uintptr_t)w % 16)) return -2;
+    const long long total = (long long)Nb * P * Q * (C / 4);
+    // up to eight CTAs of 256 threads per granted SM: the kernel lives on loads in flight
+    long long want = (total + ELT_THREADS - 1) / ELT_THREADS, cap = (long long)num_ctas * 8;
+    const int grid = (int)(want < cap ? want : cap);
+    ob200::depthwise_conv_nhwc_f32_kernel<<<grid, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, R, S,
+                                                                                         P, Q, stride_h, stride_w, pad_h, pad_w, dil_h,
+                                                                                         dil_w, w_tap_major);
+    return (int)cudaGetLastError();
+}

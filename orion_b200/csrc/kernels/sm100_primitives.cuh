@@ -42,13 +42,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds (or until the
+// phase completes) instead of returning at once, so a waiting warp does not eat the issue slots of working ones.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait; also gives up early when another role of the CTA raised `abort_flag`.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = clock64();
     while (true) {
-        for (int i = 0; i < 64; i++)
-            if (mbar_try_wait(bar, parity)) return true;
+        for (int i = 0; i < 16; i++)
+            if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > OB200_WAIT_CYCLES) return false;
     }

@@ -38,6 +38,9 @@ int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, int W, int C
                            void* stream);
 int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream);
 int ob200_sm_count(void);
+int ob200_depthwise_conv2d_f32(const float* x, const float* w, float* y, const float* scale, const float* shift, int relu, int Nb,
+                               int H, int W, int C, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
+                               int dil_w, int w_tap_major, int num_ctas, void* stream);
 int ob200_pad_channels(const void* src, void* dst, long long pixels, int C, int Cpad, int elem_bytes, int num_ctas, void* stream);
 int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
@@ -132,10 +135,33 @@ at::Tensor conv_core(const at::Tensor& x, const at::Tensor& w, const float* scal
     return y;
 }
 
+// Depthwise convolution (groups = C, multiplier 1), float32 NHWC.  w: [C, R, S] or, tap_major, [R, S, C].
+at::Tensor depthwise_core(const at::Tensor& x, const at::Tensor& w, int64_t R, int64_t S, bool tap_major, const float* scale,
+                          const float* shift, int act, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation) {
+    const int64_t Nb = x.size(0), C = x.size(1), H = x.size(2), W = x.size(3);
+    const int64_t P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) / stride[0] + 1;
+    const int64_t Q = (W + 2 * padding[1] - dilation[1] * (S - 1) - 1) / stride[1] + 1;
+    at::Tensor y = at::empty({Nb, C, P, Q}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
+    check(ob200_depthwise_conv2d_f32(x.data_ptr<float>(), w.data_ptr<float>(), y.data_ptr<float>(), scale, shift, act, (int)Nb, (int)H,
+                                     (int)W, (int)C, (int)R, (int)S, (int)stride[0], (int)stride[1], (int)padding[0],
+                                     (int)padding[1], (int)dilation[0], (int)dilation[1], tap_major ? 1 : 0, quota(), cur_stream()),
+          "ob200_depthwise_conv2d_f32");
+    return y;
+}
+
 // ------------------------------------------------------------------ aten overrides
 at::Tensor convolution_override(const at::Tensor& input, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
                                 at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed,
                                 at::IntArrayRef output_padding, int64_t groups) {
+    // depthwise, channel multiplier 1: a [C,1,R,S] weight is [C][R][S] in memory in either memory format
+    const bool depthwise = g_overrides.load(std::memory_order_relaxed) && input.dim() == 4 && weight.dim() == 4 && !transposed &&
+                           groups > 1 && groups == input.size(1) && weight.size(0) == groups && weight.size(1) == 1 &&
+                           input.scalar_type() == at::kFloat && weight.scalar_type() == at::kFloat && groups % 4 == 0 &&
+                           stride.size() == 2 && padding.size() == 2 && dilation.size() == 2 && input.numel() > 0 && is_nhwc(input) &&
+                           (!bias.has_value() || !bias->defined() || bias->scalar_type() == at::kFloat) &&
+                           (weight.is_contiguous() || weight.is_contiguous(at::MemoryFormat::ChannelsLast));
+    if (depthwise)
+        return depthwise_core(input, weight, weight.size(2), weight.size(3), false, nullptr, fptr(bias), 0, stride, padding, dilation);
     const bool ok = g_overrides.load(std::memory_order_relaxed) && input.dim() == 4 && weight.dim() == 4 && !transposed &&
                     groups == 1 && dtype_code(input) >= 0 && input.scalar_type() == weight.scalar_type() && stride.size() == 2 &&
                     padding.size() == 2 && dilation.size() == 2 && input.numel() > 0 &&
@@ -284,6 +310,17 @@ at::Tensor conv_bn_act(const at::Tensor& x, const at::Tensor& w, const c10::opti
     return conv_core(xin, w, fptr(scale), fptr(shift), res, (int)act, stride, padding, dilation, dtype_code(xin));
 }
 
+// Prepared models: depthwise convolution + folded batch-norm + activation, filter stored [R, S, C].
+at::Tensor depthwise_bn_act(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& scale,
+                            const c10::optional<at::Tensor>& shift, int64_t act, at::IntArrayRef stride, at::IntArrayRef padding,
+                            at::IntArrayRef dilation) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kFloat && w.dim() == 3 && w.scalar_type() == at::kFloat &&
+                    w.is_contiguous() && w.size(2) == x.size(1) && x.size(1) % 4 == 0,
+                "orion::depthwise_bn_act: float32 NCHW-shaped input and an [R, S, C] filter expected");
+    at::Tensor xin = is_nhwc(x) ? x : x.contiguous(at::MemoryFormat::ChannelsLast);
+    return depthwise_core(xin, w, w.size(0), w.size(1), true, fptr(scale), fptr(shift), (int)act, stride, padding, dilation);
+}
+
 at::Tensor linear_op(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias, bool relu) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.is_contiguous() && w.is_contiguous() && dtype_code(x) >= 0 &&
                     x.scalar_type() == w.scalar_type() && x.size(1) == w.size(1),
@@ -381,6 +418,7 @@ int64_t fallbacks() { return g_fallbacks.load(); }
 
 TORCH_LIBRARY(orion, m) {
     m.def("conv_bn_act(Tensor x, Tensor w, Tensor? scale, Tensor? shift, Tensor? residual, int act, int[] stride, int[] padding, int[] dilation) -> Tensor");
+    m.def("depthwise_bn_act(Tensor x, Tensor w, Tensor? scale, Tensor? shift, int act, int[] stride, int[] padding, int[] dilation) -> Tensor");
     m.def("linear(Tensor x, Tensor w, Tensor? bias, bool relu) -> Tensor");
     m.def("maxpool(Tensor x, int k, int stride, int pad) -> Tensor");
     m.def("avgpool(Tensor x) -> Tensor");
@@ -398,6 +436,7 @@ TORCH_LIBRARY(orion, m) {
 
 TORCH_LIBRARY_IMPL(orion, CUDA, m) {
     m.impl("conv_bn_act", &conv_bn_act);
+    m.impl("depthwise_bn_act", &depthwise_bn_act);
     m.impl("linear", &linear_op);
     m.impl("maxpool", &maxpool_op);
     m.impl("avgpool", &avgpool_op);

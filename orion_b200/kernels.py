@@ -53,6 +53,8 @@ def lib():
                      "ob200_binary_f32", "ob200_maxpool_nhwc_f32", "ob200_avgpool_nhwc_f32", "ob200_read_status",
                      "ob200_sm_count"):
             getattr(L, name).restype = c_int
+        L.ob200_depthwise_conv2d_f32.argtypes = [c_void_p] * 5 + [c_int] * 14 + [c_int, c_void_p]
+        L.ob200_depthwise_conv2d_f32.restype = c_int
         L.ob200_tma_launch_count.argtypes = []
         L.ob200_tma_launch_count.restype = c_ll
         L.ob200_pad_channels.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
@@ -122,6 +124,21 @@ def conv2d_nhwc(x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None
             counters = torch.zeros(tiles, device=x.device, dtype=torch.int32)
         _check(lib().ob200_conv2d_fprop_ex(*args, bn, splits, _ptr(scratch), _ptr(counters), n, _stream()),
                "ob200_conv2d_fprop_ex")
+    return y
+
+
+def depthwise_conv2d_nhwc(x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, shift=None, relu=0, tap_major=False,
+                          num_ctas=None):
+    """x: [N, H, W, C] float32, w: [C, R, S] (or [R, S, C] with tap_major) -> [N, P, Q, C]."""
+    assert x.is_cuda and x.is_contiguous() and w.is_contiguous() and x.dtype == torch.float32 and w.dtype == torch.float32
+    Nb, H, W, C = x.shape
+    R, S = (w.shape[0], w.shape[1]) if tap_major else (w.shape[1], w.shape[2])
+    P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) // stride[0] + 1
+    Q = (W + 2 * padding[1] - dilation[1] * (S - 1) - 1) // stride[1] + 1
+    y = torch.empty((Nb, P, Q, C), device=x.device, dtype=x.dtype)
+    _check(lib().ob200_depthwise_conv2d_f32(_ptr(x), _ptr(w), _ptr(y), _ptr(scale), _ptr(shift), int(relu), Nb, H, W, C, R, S,
+                                            stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1], int(tap_major),
+                                            num_ctas or sm_count(), _stream()), "ob200_depthwise_conv2d_f32")
     return y
 
 

@@ -50,15 +50,20 @@ class FusedConv(nn.Module):
 
     def __init__(self, conv, bn=None, act=0):
         super().__init__()
-        assert conv.groups == 1 and conv.padding_mode == "zeros"
+        assert conv.padding_mode == "zeros"
         w = conv.weight.detach()
+        self.depthwise = conv.groups > 1
+        if self.depthwise:
+            # groups = C, multiplier 1 (MobileNetV2): the filter is kept tap-major, [R, S, C]
+            assert conv.groups == conv.in_channels == conv.out_channels and w.dtype == torch.float32 and conv.groups % 4 == 0
+            w = w[:, 0].permute(1, 2, 0).contiguous()
         # a channel count that does not fill 16-byte chunks (the 3-channel stem) is zero-padded once here;
         # the op pads the activation to match on every call
         epc = 16 // w.element_size()
-        if w.shape[1] % epc:
+        if not self.depthwise and w.shape[1] % epc:
             w = torch.nn.functional.pad(w, (0, 0, 0, 0, 0, epc - w.shape[1] % epc))
-        self.register_buffer("weight", w.contiguous(memory_format=torch.channels_last))
-        k = w.shape[0]
+        self.register_buffer("weight", w if self.depthwise else w.contiguous(memory_format=torch.channels_last))
+        k = conv.out_channels
         if bn is not None:
             inv = torch.rsqrt(bn.running_var.detach().double() + bn.eps)
             g = bn.weight.detach().double() if bn.weight is not None else torch.ones(k, dtype=torch.float64, device=w.device)
@@ -79,6 +84,10 @@ class FusedConv(nn.Module):
         self.stride, self.padding, self.dilation = list(conv.stride), list(conv.padding), list(conv.dilation)
 
     def forward(self, x, residual=None):
+        if self.depthwise:
+            assert residual is None
+            return torch.ops.orion.depthwise_bn_act(x, self.weight, self.scale, self.shift, self.act, self.stride, self.padding,
+                                                    self.dilation)
         return torch.ops.orion.conv_bn_act(x, self.weight, self.scale, self.shift, residual, self.act, self.stride,
                                            self.padding, self.dilation)
 
@@ -156,7 +165,9 @@ def prepare_inference(model):
         if node.op != "call_module":
             continue
         m = mods.get(node.target)
-        if isinstance(m, nn.Conv2d) and m.groups == 1 and m.padding_mode == "zeros" and isinstance(m.padding, tuple):
+        depthwise = isinstance(m, nn.Conv2d) and m.groups > 1 and m.groups == m.in_channels == m.out_channels and \
+            m.groups % 4 == 0 and m.weight.dtype == torch.float32
+        if isinstance(m, nn.Conv2d) and (m.groups == 1 or depthwise) and m.padding_mode == "zeros" and isinstance(m.padding, tuple):
             bn_node, bn = None, None
             users = list(node.users)
             if len(users) == 1 and users[0].op == "call_module" and isinstance(mods.get(users[0].target), nn.BatchNorm2d):
@@ -172,7 +183,7 @@ def prepare_inference(model):
                 elif u.op == "call_function" and u.target in (operator.add, operator.iadd, torch.add) and len(u.args) == 2 \
                         and not u.kwargs and all(isinstance(x, fx.Node) for x in u.args):
                     other = u.args[1] if u.args[0] is last else u.args[0]
-                    if other is not last:
+                    if other is not last and not depthwise:
                         add_node, res = u, other
                         uu = list(u.users)
                         if len(uu) == 1 and _act_of(uu[0], mods):

@@ -82,6 +82,21 @@ def test_tma_feeds_the_eligible_shapes(K):
     assert K.tma_launch_count() - n0 == 5
 
 
+@pytest.mark.parametrize("shape", [(4, 112, 112, 32, 3, 1, 1), (4, 112, 112, 96, 3, 2, 1), (2, 14, 14, 576, 3, 1, 1),
+                                   (2, 7, 7, 960, 3, 1, 1), (3, 9, 11, 24, 5, 2, 2), (1, 6, 6, 8, 3, 1, 0)])
+@pytest.mark.parametrize("tap_major", [False, True])
+def test_depthwise_convolution(K, shape, tap_major):
+    """MobileNetV2's depthwise layers (groups = C): both filter layouts, fused scale/shift and ReLU6."""
+    Nb, H, W, C, R, stride, pad = shape
+    x = torch.randn(Nb, H, W, C, device="cuda")
+    w = torch.randn(C, R, R, device="cuda") / R
+    scale, shift = torch.rand(C, device="cuda") + 0.5, torch.randn(C, device="cuda")
+    wk = w.permute(1, 2, 0).contiguous() if tap_major else w
+    y = K.depthwise_conv2d_nhwc(x, wk, (stride, stride), (pad, pad), scale=scale, shift=shift, relu=2, tap_major=tap_major)
+    want = O.conv2d_nhwc(x, w.unsqueeze(-1), (stride, stride), (pad, pad), scale=scale, shift=shift, act=2, groups=C)
+    assert O.rel_err(y, want) < FP32_TOL
+
+
 def test_conv_dilation_and_empty_batch(K):
     assert _conv(K, 2, 16, 16, 32, 32, 3, 1, 2, dil=2) < FP32_TOL
     x = torch.empty(0, 8, 8, 16, device="cuda")
