@@ -34,6 +34,10 @@ sys.path.insert(0, ROOT)
 METRIC = "HP p99 latency (x solo) + BE train samples/s, co-located on one B200"
 HP_RPS = 80
 RESNET50_FWD_FLOP_B1 = 32.71e9 / 4   # conv + fc, 2*MAC, per image
+# DRAM bytes per launch of the roofline replay (53 ResNet-50 convolutions, batch 32): 1354.2 MB read + 296.3 MB
+# written over the 53 launches in one ncu pass of `python -m orion_b200.kernel_replay --batch 32 --iters 1 --warm 1`;
+# the algorithmic bytes (activations + filters + outputs) are 54.5 MB per launch, most outputs stay in L2.
+ROOFLINE_TRAFFIC_BYTES_PER_LAUNCH = 31.14e6
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -297,8 +301,11 @@ def main():
         "gpu_launches": int(sum(g["launches"] for g in gathered)),
         "scheduler": gathered[0]["sched"],
         "roofline": {"bound": "tensor", "achieved": roof["achieved_tflops"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": roof["achieved_tflops"] / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "igemm_fprop_kernel<float> (3xTF32), all 53 ResNet-50 convolutions at batch 32",
+                     "frac": roof["achieved_tflops"] / peaks["bf16_tflops"], "traffic": ROOFLINE_TRAFFIC_BYTES_PER_LAUNCH,
+                     "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, ncu, averaged over the same "
+                                     "53 launches; profiles/igemm_fprop_f32_resnet50_b32.md)",
+                     "peak_source": peaks["source"],
+                     "kernel": "igemm_fprop_kernel<float> (3xTF32, TMA-fed, A operand in TMEM), all 53 ResNet-50 convolutions at batch 32",
                      "avg_launch_us": roof["avg_launch_us"], "launches_timed": roof["launches"],
                      "note": "peak is the bf16 dense figure; fp32 runs three TF32 MMAs per product"},
         "cpu_baseline": base,

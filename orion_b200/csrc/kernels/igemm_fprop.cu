@@ -266,7 +266,9 @@ __device__ __forceinline__ void epilogue_chunk(const IgemmParams& p, float* stag
     __syncwarp();
     const int n = n_chunk + cc;
     const EpiCoef coef = load_coef<T>(p, n);
-#pragma unroll
+    // Not unrolled on purpose: the epilogue runs once per tile, and keeping its code small keeps the instruction
+    // cache for the roles that loop per k-block.
+#pragma unroll 1
     for (int i = 0; i < 4; i++) {
         const int rr = i * 8 + sub;
         const long long m = tile_row0 + rr;
