@@ -50,8 +50,13 @@ int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y, const floa
                                int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn, int splits,
                                int num_ctas, void* stream);
 
-/* The choice ob200_conv2d_fprop makes for a problem size. */
+/* Tile width and split-K factor of the one-unit-per-tile / split-K schedule for a problem size (host logic only). */
 int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out);
+/* The schedule ob200_conv2d_fprop picks (host logic only): stream_k_out = 1 means the k-blocks of all tiles are cut
+ * into one equal range per CTA (then splits_out = 1); otherwise the ob200_plan_conv choice.  No counterpart in the
+ * reference (cuDNN picks its own algorithm behind cudnnConvolutionForward). */
+int ob200_plan_schedule(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out,
+                        int* stream_k_out);
 
 /* Data gradient of the convolution, dx [Nb,H,W,C] from dy [Nb,P,Q,Kout] and the re-laid-out filter
  * wt [C,R,S,Kout] (ob200_filter_transpose).  Takes the place of cudnnConvolutionBackwardData

@@ -130,6 +130,28 @@ int schedule_stream_k(IgemmParams& p, int bn, int num_ctas, int dev, cudaStream_
     return (int)grid;
 }
 
+}  // namespace
+
+// The schedule ob200_conv2d_fprop picks for a problem (host logic only, no launch): tile width, split-K factor
+// and whether the stream-K schedule is used (then splits = 1 and the tile width is the wide-tile preference).
+extern "C" int ob200_plan_schedule(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out,
+                                   int* stream_k_out) {
+    if (M <= 0 || Kout <= 0 || R <= 0 || S <= 0 || C <= 0 || num_ctas <= 0 || !bn_out || !splits_out || !stream_k_out) return -1;
+    const int bk = dtype == 1 ? 64 : 32;
+    const int bn = streamk_bn(Kout);
+    const long long tiles = ((M + 127) / 128) * ((Kout + bn - 1) / bn);
+    if (stream_k_pays(tiles, R * ((S * C + bk - 1) / bk), num_ctas)) {
+        *bn_out = bn;
+        *splits_out = 1;
+        *stream_k_out = 1;
+        return 0;
+    }
+    *stream_k_out = 0;
+    return ob200_plan_conv(dtype, M, Kout, R, S, C, num_ctas, bn_out, splits_out);
+}
+
+namespace {
+
 int fprop_impl(const void* x, const void* w, void* y, const float* scale, const float* shift, const void* residual, int relu,
                int dtype, int Nb, int H, int W, int C, int Kout, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w,
                int dil_h, int dil_w, int bn, int splits, bool stream_k, float* scratch, int* counters, int num_ctas, void* stream) {
