@@ -266,6 +266,32 @@ __device__ __forceinline__ void epilogue_chunk(const IgemmParams& p, float* stag
     __syncwarp();
     const int n = n_chunk + cc;
     const EpiCoef coef = load_coef<T>(p, n);
+    if (sizeof(T) == 4 && !p.out_map && (p.Kout & 3) == 0 && n + 3 < p.Kout) {
+        // Common case (float32, whole 16-byte groups, rows stored in place): everything that does not depend on the
+        // row is decided here, the loop is a shared-memory read, four FMAs, the activation and one 16-byte store.
+        float* ycol = reinterpret_cast<float*>(p.y) + y_off + n;
+        const float* rcol = p.residual ? reinterpret_cast<const float*>(p.residual) + y_off + n : nullptr;
+        const float lo = p.relu ? 0.f : -INFINITY, hi = p.relu == 2 ? 6.f : INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int rr = i * 8 + sub;
+            const long long m = tile_row0 + rr;
+            if (m < p.M) {
+                const float4 a = *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc);
+                float4 x = make_float4(fmaf(a.x, coef.scale.x, coef.shift.x), fmaf(a.y, coef.scale.y, coef.shift.y),
+                                       fmaf(a.z, coef.scale.z, coef.shift.z), fmaf(a.w, coef.scale.w, coef.shift.w));
+                if (rcol) {
+                    const float4 q = __ldg(reinterpret_cast<const float4*>(rcol + m * p.Kout));
+                    x.x += q.x; x.y += q.y; x.z += q.z; x.w += q.w;
+                }
+                x.x = fminf(fmaxf(x.x, lo), hi); x.y = fminf(fmaxf(x.y, lo), hi);
+                x.z = fminf(fmaxf(x.z, lo), hi); x.w = fminf(fmaxf(x.w, lo), hi);
+                *reinterpret_cast<float4*>(ycol + m * p.Kout) = x;
+            }
+        }
+        __syncwarp();
+        return;
+    }
     // Not unrolled on purpose: the epilogue runs once per tile, and keeping its code small keeps the instruction
     // cache for the roles that loop per k-block.
 #pragma unroll 1
