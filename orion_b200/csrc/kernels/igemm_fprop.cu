@@ -414,14 +414,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         ctl->last_flag = 0;
         fence_barrier_init();
     }
-    if (warp == MMA_WARP) {
-        tmem_alloc(&ctl->tmem_base, C::TMEM_COLS);
-        tmem_relinquish();
+    if (warp == TMA_WARP && lane == 0 && p.use_tma) {
+        prefetch_tensormap(p.tmap_a);   // hide the descriptor fetch behind the rest of the set-up
+        prefetch_tensormap(p.tmap_b);
     }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = ctl->tmem_base;
+    __syncthreads();   // barriers are initialised: the TMA warp may start copying
+    uint32_t tmem_base = 0;
+    if (warp != TMA_WARP) {
+        // Everyone but the TMA warp needs the tensor-memory base; the allocation overlaps the first copies.
+        if (warp == MMA_WARP) {
+            tmem_alloc(&ctl->tmem_base, C::TMEM_COLS);
+            tmem_relinquish();
+        }
+        tc_fence_before_sync();
+        asm volatile("bar.sync 2, %0;" ::"r"(TMA_WARP * 32) : "memory");
+        tc_fence_after_sync();
+        tmem_base = ctl->tmem_base;
+    }
     volatile int* abort_flag = &ctl->abort_flag;
 
     const int tiles_per_problem = p.tiles_m * p.tiles_n;
@@ -1233,6 +1242,7 @@ extern "C" long long ob200_tma_launch_count(void) { return g_tma_launches.load(s
 extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_ctas, void* stream) {
     using namespace ob200;
     IgemmParams p = *params;
+    if (bn != 64 && bn != 128 && !(bn == 256 && p.dtype != 0)) return -1;
     {
         const char* e = getenv("ORION_A_TMEM");
         p.a_in_tmem = (p.dtype == 0 && p.mode == 0 && !(e && e[0] == '0')) ? 1 : 0;
@@ -1244,8 +1254,11 @@ extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_cta
         if (p.a_in_tmem) return (int)(bn == 64 ? launch_cfg<float, 64, 3, true>(p, num_ctas, s) : launch_cfg<float, 128, 3, true>(p, num_ctas, s));
         return (int)(bn == 64 ? launch_cfg<float, 64, 3>(p, num_ctas, s) : launch_cfg<float, 128, 3>(p, num_ctas, s));
     } else if (p.dtype == 1) {
+        // 128 x 256 tiles (single-pass modes only: 3xTF32 needs the tensor-memory columns for the activation parts)
+        if (bn == 256) return p.mode == 0 ? (int)launch_cfg<__nv_bfloat16, 256, 1>(p, num_ctas, s) : -1;
         return (int)(bn == 64 ? launch_cfg<__nv_bfloat16, 64, 1>(p, num_ctas, s) : launch_cfg<__nv_bfloat16, 128, 1>(p, num_ctas, s));
     } else if (p.dtype == 2) {   // float32 data, one TF32 pass (the precision cuDNN uses by default on tensor cores)
+        if (bn == 256) return p.mode == 0 ? (int)launch_cfg<float, 256, 1>(p, num_ctas, s) : -1;
         return (int)(bn == 64 ? launch_cfg<float, 64, 1>(p, num_ctas, s) : launch_cfg<float, 128, 1>(p, num_ctas, s));
     }
     return -1;

@@ -94,6 +94,15 @@ int streamk_bn(int Kout) {
     return (Kout <= 64 || (rem > 0 && rem <= 64 && Kout < 256)) ? 64 : 128;
 }
 
+// Single-pass modes (bf16, one TF32 pass) are bound by L2->SM operand traffic at 128 x 128; a 128 x 256 tile moves a
+// quarter less per FLOP.  Taken when the output is wide enough and the wide tiles still fill the granted SMs.
+bool wide_tiles_pay(int dtype, long long M, int Kout, int num_ctas) {
+    if (dtype == 0 || Kout < 256 || (Kout % 256 != 0 && Kout % 256 <= 128)) return false;
+    const char* e = getenv("ORION_WIDE_TILES");
+    if (e && e[0] == '0') return false;
+    return ((M + 127) / 128) * ((Kout + 255) / 256) >= num_ctas;
+}
+
 // Whether stream-K beats one unit per tile, in units of one k-block of MMA work per CTA: a tile costs its
 // k-blocks plus about four for the epilogue; stream-K gives every CTA an equal share of all k-blocks but
 // pays about twelve for writing and re-reading the two tiles a CTA shares with its neighbours.  It wins
@@ -179,7 +188,7 @@ int fprop_impl(const void* x, const void* w, void* y, const float* scale, const 
     const int bk = 128 / elem;
     p.kblocks_per_r = (S * C + bk - 1) / bk;
     p.num_kblocks = R * p.kblocks_per_r;
-    if (bn != 64 && bn != 128) return -1;
+    if (bn != 64 && bn != 128 && !(bn == 256 && dtype != 0)) return -1;
     p.tiles_m = (int)((M + 127) / 128);
     p.tiles_n = (Kout + bn - 1) / bn;
     if (splits < 1 || splits > p.num_kblocks) return -1;
@@ -219,6 +228,9 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
     const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / (stride_h > 0 ? stride_h : 1) + 1;
     const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / (stride_w > 0 ? stride_w : 1) + 1;
     const long long M = (long long)Nb * P * Q;
+    if (wide_tiles_pay(dtype, M, Kout, num_ctas))
+        return fprop_impl(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w, dil_h,
+                          dil_w, 256, 1, true, nullptr, nullptr, num_ctas, stream);
     {   // stream-K with the tile width it prefers, where it pays
         const int bn = streamk_bn(Kout);
         const int bk = dtype == 1 ? 64 : 32;
@@ -445,7 +457,7 @@ extern "C" int ob200_linear_batched(const void* x, const void* w, void* y, int d
     const int bk = 128 / elem;
     p.kblocks_per_r = (K + bk - 1) / bk;
     p.num_kblocks = p.kblocks_per_r;
-    const int bn = N <= 64 ? 64 : 128;
+    const int bn = N <= 64 ? 64 : wide_tiles_pay(dtype, (long long)M * batch, N, num_ctas) ? 256 : 128;
     p.tiles_m = (M + 127) / 128;
     p.tiles_n = (N + bn - 1) / bn;
     p.splits = 1;

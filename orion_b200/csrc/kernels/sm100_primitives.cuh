@@ -96,6 +96,10 @@ __device__ __forceinline__ void tma_load_tile_4d(uint32_t dst, const void* tmap,
         : "memory");
 }
 
+// Brings a tensor map (in kernel-parameter space) into the descriptor cache ahead of its first use.
+__device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
 __device__ __forceinline__ void tma_load_tile_2d(uint32_t dst, const void* tmap, uint64_t* bar, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
                  "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)

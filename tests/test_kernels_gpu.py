@@ -97,6 +97,29 @@ def test_depthwise_convolution(K, shape, tap_major):
     assert O.rel_err(y, want) < FP32_TOL
 
 
+def test_wide_tiles_in_single_pass_modes(K):
+    """128 x 256 tiles (bf16 and single-pass TF32 only): explicit, and picked by the planner for wide outputs."""
+    x = torch.randn(8, 28, 28, 128, device="cuda")
+    w = torch.randn(512, 3, 3, 128, device="cuda") / 34.0
+    shift = torch.randn(512, device="cuda")
+    want = O.conv2d_nhwc(x, w, (1, 1), (1, 1), shift=shift, act=1)
+    assert O.rel_err(K.conv2d_nhwc(x, w, (1, 1), (1, 1), shift=shift, relu=True, tf32=True, bn=256, splits=1), want) < 5e-3
+    assert O.rel_err(K.conv2d_nhwc(x, w, (1, 1), (1, 1), shift=shift, relu=True, tf32=True), want) < 5e-3
+    xb, wb = x.bfloat16(), w.bfloat16()
+    wantb = O.conv2d_nhwc(xb, wb, (1, 1), (1, 1), shift=shift, act=1)
+    assert O.rel_err(K.conv2d_nhwc(xb, wb, (1, 1), (1, 1), shift=shift, relu=True, bn=256, splits=1), wantb) < BF16_TOL
+    assert O.rel_err(K.conv2d_nhwc(xb, wb, (1, 1), (1, 1), shift=shift, relu=True), wantb) < BF16_TOL
+    # ragged: 300 output channels (256 + 44) and an M tail
+    w2 = torch.randn(300, 1, 1, 128, device="cuda").bfloat16()
+    x2 = torch.randn(3, 13, 11, 128, device="cuda").bfloat16()
+    assert O.rel_err(K.conv2d_nhwc(x2, w2, bn=256, splits=1), O.conv2d_nhwc(x2, w2, (1, 1), (0, 0))) < BF16_TOL
+    a, b = torch.randn(4096, 1024, device="cuda").bfloat16(), torch.randn(2048, 1024, device="cuda").bfloat16()
+    assert O.rel_err(K.linear(a, b), O.linear(a, b)) < BF16_TOL      # planner takes the wide tile here
+    with pytest.raises(RuntimeError):
+        K.conv2d_nhwc(x, w, (1, 1), (1, 1), bn=256, splits=1)          # 3xTF32 has no room for it in tensor memory
+    assert K.read_status() == 0
+
+
 def test_conv_dilation_and_empty_batch(K):
     assert _conv(K, 2, 16, 16, 32, 32, 3, 1, 2, dil=2) < FP32_TOL
     x = torch.empty(0, 8, 8, 16, device="cuda")
