@@ -1243,10 +1243,11 @@ extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_cta
     using namespace ob200;
     IgemmParams p = *params;
     if (bn != 64 && bn != 128 && !(bn == 256 && p.dtype != 0)) return -1;
-    {
+    static const bool a_tmem_off = [] {   // ORION_A_TMEM=0: activation parts through shared memory (for measurements)
         const char* e = getenv("ORION_A_TMEM");
-        p.a_in_tmem = (p.dtype == 0 && p.mode == 0 && !(e && e[0] == '0')) ? 1 : 0;
-    }
+        return e && e[0] == '0';
+    }();
+    p.a_in_tmem = (p.dtype == 0 && p.mode == 0 && !a_tmem_off) ? 1 : 0;
     if (setup_tma(p, bn)) g_tma_launches.fetch_add(1, std::memory_order_relaxed);
     else if (p.require_tma || p.w_R > 0) return -4;   // tap subsets exist only on the TMA path
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -29,9 +29,16 @@ std::unordered_map<int, int*> g_status;                 // per device
 long long* g_debug = nullptr;   // optional role-wait counters, see ob200_set_debug_buffer
 
 int* status_word(int dev) {
+    thread_local int cached_dev = -1;
+    thread_local int* cached = nullptr;
+    if (dev == cached_dev && cached) return cached;
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_status.find(dev);
-    if (it != g_status.end()) return it->second;
+    if (it != g_status.end()) {
+        cached_dev = dev;
+        cached = it->second;
+        return cached;
+    }
     int* p = nullptr;
     if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
     cudaMemset(p, 0, sizeof(int));
@@ -42,10 +49,17 @@ int* status_word(int dev) {
 // Split-K scratch is private to a stream: two clients that run split-K convolutions
 // at the same time on different streams must not share partial sums.
 Scratch* scratch_for(int dev, cudaStream_t s) {
-    std::lock_guard<std::mutex> lk(g_mu);
     uint64_t key = ((uint64_t)dev << 56) ^ (uint64_t)(uintptr_t)s;
+    thread_local uint64_t cached_key = ~0ull;
+    thread_local Scratch* cached = nullptr;
+    if (key == cached_key && cached) return cached;   // entries are never erased; unordered_map nodes do not move
+    std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_scratch.find(key);
-    if (it != g_scratch.end()) return &it->second;
+    if (it != g_scratch.end()) {
+        cached_key = key;
+        cached = &it->second;
+        return cached;
+    }
     Scratch sc;
     if (cudaMalloc(&sc.partial, kScratchBytes) != cudaSuccess) return nullptr;
     if (cudaMalloc(&sc.counters, kMaxTilesSplit * sizeof(int)) != cudaSuccess) return nullptr;
@@ -74,8 +88,7 @@ extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, i
     int splits = 1;
     if (tiles * 2 <= num_ctas && kblocks >= 4) {
         splits = num_ctas / tiles;
-        const int min_chain = getenv("ORION_MIN_CHAIN") ? atoi(getenv("ORION_MIN_CHAIN")) : 4;
-        if (splits > kblocks / min_chain) splits = kblocks / min_chain;
+        if (splits > kblocks / 4) splits = kblocks / 4;   // chains of at least four k-blocks
         if (splits > 16) splits = 16;
         if (splits < 1) splits = 1;
     }
@@ -98,8 +111,11 @@ int streamk_bn(int Kout) {
 // quarter less per FLOP.  Taken when the output is wide enough and the wide tiles still fill the granted SMs.
 bool wide_tiles_pay(int dtype, long long M, int Kout, int num_ctas) {
     if (dtype == 0 || Kout < 256 || (Kout % 256 != 0 && Kout % 256 <= 128)) return false;
-    const char* e = getenv("ORION_WIDE_TILES");
-    if (e && e[0] == '0') return false;
+    static const bool off = [] {
+        const char* e = getenv("ORION_WIDE_TILES");
+        return e && e[0] == '0';
+    }();
+    if (off) return false;
     return ((M + 127) / 128) * ((Kout + 255) / 256) >= num_ctas;
 }
 
@@ -109,9 +125,12 @@ bool wide_tiles_pay(int dtype, long long M, int Kout, int num_ctas) {
 // where the tiles are deep and the last wave would be partly empty (3x3 layers at moderate batch), and
 // loses on shallow 1x1 layers and where a tile would be cut into many pieces.
 bool stream_k_pays(long long tiles, int num_kblocks, int num_ctas) {
-    const char* force = getenv("ORION_SCHEDULE");   // "streamk" / "tiles": pin the schedule (for measurements)
-    if (force && force[0] == 's') return true;
-    if (force && force[0] == 't') return false;
+    static const char force = [] {   // ORION_SCHEDULE=streamk / tiles pins the schedule (for measurements); read once
+        const char* e = getenv("ORION_SCHEDULE");
+        return e ? e[0] : '\0';
+    }();
+    if (force == 's') return true;
+    if (force == 't') return false;
     if (tiles * 4 < num_ctas || num_kblocks < 8) return false;
     const double waves = (double)((tiles + num_ctas - 1) / num_ctas);
     const double tiles_cost = waves * (num_kblocks + 4);
