@@ -285,6 +285,73 @@ __global__ void __launch_bounds__(ELT_THREADS) depthwise_conv_nhwc_f32_kernel(
 }
 }  // namespace ob200
 
+// 3x3 depthwise, stride 1 or 2, dilation 1: each thread produces four consecutive output pixels of one row for
+// its channel quad, so the 3 x (3 + 3*STRIDE) input vectors it loads are shared by the four outputs (6.75 loads per
+// output at stride 1 against 18 in the generic kernel, filter taps included) and the filter is read once.
+namespace ob200 {
+template <int STRIDE>
+__global__ void __launch_bounds__(ELT_THREADS) depthwise3x3_nhwc_f32_kernel(
+    const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, const float* __restrict__ scale,
+    const float* __restrict__ shift, int relu, int Nb, int H, int W, int C, int P, int Q, int pad_h, int pad_w, int w_tap_major) {
+    constexpr int TW = 4, NCOL = (TW - 1) * STRIDE + 3;
+    const int c4 = C / 4, qb_n = (Q + TW - 1) / TW;
+    const long long total = (long long)Nb * P * qb_n * c4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int cq = (int)(i % c4);
+        long long rest = i / c4;
+        const int qb = (int)(rest % qb_n);
+        rest /= qb_n;
+        const int p = (int)(rest % P);
+        const int n = (int)(rest / P);
+        const int c = cq * 4;
+        float4 f[9];
+#pragma unroll
+        for (int t = 0; t < 9; t++) {
+            if (w_tap_major) f[t] = __ldg(reinterpret_cast<const float4*>(w + (long long)t * C + c));
+            else f[t] = make_float4(__ldg(w + (long long)c * 9 + t), __ldg(w + (long long)(c + 1) * 9 + t), __ldg(w + (long long)(c + 2) * 9 + t),
+                                    __ldg(w + (long long)(c + 3) * 9 + t));
+        }
+        float4 acc[TW];
+#pragma unroll
+        for (int t = 0; t < TW; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int q0 = qb * TW;
+        const int w0 = q0 * STRIDE - pad_w;
+#pragma unroll
+        for (int r = 0; r < 3; r++) {
+            const int h = p * STRIDE - pad_h + r;
+            if ((unsigned)h >= (unsigned)H) continue;
+            const float* xrow = x + (((long long)n * H + h) * W) * C + c;
+            float4 v[NCOL];
+#pragma unroll
+            for (int j = 0; j < NCOL; j++) {
+                const int ww = w0 + j;
+                v[j] = (unsigned)ww < (unsigned)W ? __ldg(reinterpret_cast<const float4*>(xrow + (long long)ww * C)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int t = 0; t < TW; t++) {
+#pragma unroll
+                for (int s2 = 0; s2 < 3; s2++) {
+                    const float4 a = v[t * STRIDE + s2], b = f[r * 3 + s2];
+                    acc[t].x = fmaf(a.x, b.x, acc[t].x); acc[t].y = fmaf(a.y, b.y, acc[t].y);
+                    acc[t].z = fmaf(a.z, b.z, acc[t].z); acc[t].w = fmaf(a.w, b.w, acc[t].w);
+                }
+            }
+        }
+        float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (scale) g = __ldg(reinterpret_cast<const float4*>(scale + c));
+        if (shift) b = __ldg(reinterpret_cast<const float4*>(shift + c));
+        const float lo = relu ? 0.f : -INFINITY, hi = relu == 2 ? 6.f : INFINITY;
+#pragma unroll
+        for (int t = 0; t < TW; t++) {
+            if (q0 + t >= Q) break;
+            float4 o = make_float4(fmaf(acc[t].x, g.x, b.x), fmaf(acc[t].y, g.y, b.y), fmaf(acc[t].z, g.z, b.z), fmaf(acc[t].w, g.w, b.w));
+            o.x = fminf(fmaxf(o.x, lo), hi); o.y = fminf(fmaxf(o.y, lo), hi); o.z = fminf(fmaxf(o.z, lo), hi); o.w = fminf(fmaxf(o.w, lo), hi);
+            *reinterpret_cast<float4*>(y + ((((long long)n * P + p) * Q + q0 + t) * C + c)) = o;
+        }
+    }
+}
+}  // namespace ob200
+
 extern "C" int ob200_depthwise_conv2d_f32(const float* x, const float* w, float* y, const float* scale, const float* shift, int relu,
                                           int Nb, int H, int W, int C, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w,
                                           int dil_h, int dil_w, int w_tap_major, int num_ctas, void* stream) {
@@ -296,6 +363,18 @@ extern "C" int ob200_depthwise_conv2d_f32(const float* x, const float* w, float*
     const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / stride_w + 1;
     if (P <= 0 || Q <= 0) return -1;
     if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)shift) % 16 || (w_tap_major && (uintptr_t)w % 16)) return -2;
+    if (R == 3 && S == 3 && dil_h == 1 && dil_w == 1 && stride_h == stride_w && (stride_h == 1 || stride_h == 2)) {
+        const long long total4 = (long long)Nb * P * ((Q + 3) / 4) * (C / 4);
+        long long want4 = (total4 + ELT_THREADS - 1) / ELT_THREADS, cap4 = (long long)num_ctas * 4;
+        const int grid4 = (int)(want4 < cap4 ? want4 : cap4);
+        if (stride_h == 1)
+            ob200::depthwise3x3_nhwc_f32_kernel<1><<<grid4, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, P,
+                                                                                                Q, pad_h, pad_w, w_tap_major);
+        else
+            ob200::depthwise3x3_nhwc_f32_kernel<2><<<grid4, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, P,
+                                                                                                Q, pad_h, pad_w, w_tap_major);
+        return (int)cudaGetLastError();
+    }
     const long long total = (long long)Nb * P * Q * (C / 4);
     // up to eight CTAs of 256 threads per granted SM: the kernel lives on loads in flight
     long long want = (total + ELT_THREADS - 1) / ELT_THREADS, cap = (long long)num_ctas * 8;

@@ -50,6 +50,21 @@ struct VecIO<__nv_bfloat16> {
     }
 };
 
+// N (4 or 8) consecutive per-column coefficients as 16-byte loads; `fill` where the vector is absent.
+template <int N>
+__device__ __forceinline__ void load_cols(const float* __restrict__ p, int i, float fill, float (&o)[8]) {
+    if (!p) {
+#pragma unroll
+        for (int e = 0; e < N; e++) o[e] = fill;
+        return;
+    }
+#pragma unroll
+    for (int e = 0; e < N; e += 4) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(p + i + e));
+        o[e] = q.x; o[e + 1] = q.y; o[e + 2] = q.z; o[e + 3] = q.w;
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
@@ -59,6 +74,108 @@ __device__ __forceinline__ float warp_max(float x) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
     return x;
+}
+
+// Rows that fit a warp's registers (D <= 32 lanes x CH chunks of 16 bytes) are read once: every lane issues all
+// its 16-byte loads up front, the statistics and the result come from registers.  One global read and one write
+// per element, and CH independent loads in flight per lane.
+template <typename T, int CH>
+__global__ void __launch_bounds__(ROW_THREADS) layernorm_regs_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                    float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                    long long rows, int D, float eps) {
+    constexpr int N = VecIO<T>::N;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
+        const T* xr = x + row * D;
+        float v[CH][8];
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            const int i = (c * 32 + lane) * N;
+            if (i < D) VecIO<T>::load(xr + i, v[c]);
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; c++)
+            if ((c * 32 + lane) * N < D) {
+#pragma unroll
+                for (int e = 0; e < N; e++) s += v[c][e];
+            }
+        const float mean = warp_sum(s) / (float)D;
+        float q = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; c++)
+            if ((c * 32 + lane) * N < D) {
+#pragma unroll
+                for (int e = 0; e < N; e++) q += (v[c][e] - mean) * (v[c][e] - mean);
+            }
+        const float rstd = rsqrtf(warp_sum(q) / (float)D + eps);
+        T* yr = y + row * D;
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            const int i = (c * 32 + lane) * N;
+            if (i < D) {
+                float g[8], b[8];
+                load_cols<N>(gamma, i, 1.f, g);
+                load_cols<N>(beta, i, 0.f, b);
+#pragma unroll
+                for (int e = 0; e < N; e++) v[c][e] = fmaf((v[c][e] - mean) * rstd, g[e], b[e]);
+                VecIO<T>::store(yr + i, v[c]);
+            }
+        }
+        if (lane == 0) {
+            if (mean_out) mean_out[row] = mean;
+            if (rstd_out) rstd_out[row] = rstd;
+        }
+    }
+}
+
+template <typename T, int CH>
+__global__ void __launch_bounds__(ROW_THREADS) softmax_regs_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int D,
+                                                                  float scale) {
+    constexpr int N = VecIO<T>::N;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
+        const T* xr = x + row * D;
+        float v[CH][8];
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            const int i = (c * 32 + lane) * N;
+            if (i < D) VecIO<T>::load(xr + i, v[c]);
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < CH; c++)
+            if ((c * 32 + lane) * N < D) {
+#pragma unroll
+                for (int e = 0; e < N; e++) {
+                    v[c][e] *= scale;
+                    m = fmaxf(m, v[c][e]);
+                }
+            }
+        m = warp_max(m);
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; c++)
+            if ((c * 32 + lane) * N < D) {
+#pragma unroll
+                for (int e = 0; e < N; e++) {
+                    v[c][e] = __expf(v[c][e] - m);
+                    s += v[c][e];
+                }
+            }
+        const float inv = 1.0f / warp_sum(s);
+        T* yr = y + row * D;
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            const int i = (c * 32 + lane) * N;
+            if (i < D) {
+#pragma unroll
+                for (int e = 0; e < N; e++) v[c][e] *= inv;
+                VecIO<T>::store(yr + i, v[c]);
+            }
+        }
+    }
 }
 
 // y = (x - mean) / sqrt(var + eps) * gamma + beta over the last dimension D (D % VecIO<T>::N == 0).
@@ -142,7 +259,26 @@ template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) bias_gelu_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ bias,
                                                                long long n_vec, int D) {
     constexpr int N = VecIO<T>::N;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n_vec; i += 4 * stride) {   // four independent 16-byte loads in flight per thread
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; u++) VecIO<T>::load(x + (i + u * stride) * N, v[u]);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int col = (int)(((i + u * stride) * N) % D);
+            float b[8];
+            load_cols<N>(bias, col, 0.f, b);
+#pragma unroll
+            for (int e = 0; e < N; e++) {
+                const float a = v[u][e] + b[e];
+                v[u][e] = 0.5f * a * (1.0f + erff(a * 0.70710678118654752f));
+            }
+            VecIO<T>::store(y + (i + u * stride) * N, v[u]);
+        }
+    }
+    for (; i < n_vec; i += stride) {
         float v[8];
         VecIO<T>::load(x + i * N, v);
         const int col = (int)((i * N) % D);
@@ -174,7 +310,7 @@ __global__ void __launch_bounds__(ROW_THREADS) adamw_kernel(float* __restrict__ 
 
 static inline int row_grid(long long rows, int num_ctas) {
     long long want = (rows + 7) / 8;
-    long long cap = (long long)num_ctas * 4;
+    long long cap = (long long)num_ctas * 8;   // eight CTAs of eight warps per granted SM: rows in flight hide the latency
     if (want < 1) want = 1;
     return (int)(want < cap ? want : cap);
 }
@@ -192,14 +328,24 @@ extern "C" int ob200_layernorm(const void* x, void* y, const float* gamma, const
                                long long rows, int D, float eps, int dtype, int num_ctas, void* stream) {
     if (rows <= 0) return 0;
     if ((dtype != 0 && dtype != 1) || num_ctas <= 0) return -1;
-    if (!vec_ok(x, y, D, dtype)) return -2;
+    if (!vec_ok(x, y, D, dtype) || (((uintptr_t)gamma | (uintptr_t)beta) % 16) != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == 0)
-        layernorm_kernel<float><<<row_grid(rows, num_ctas), ROW_THREADS, 0, s>>>((const float*)x, (float*)y, gamma, beta, mean_out, rstd_out,
-                                                                                 rows, D, eps);
-    else
-        layernorm_kernel<__nv_bfloat16><<<row_grid(rows, num_ctas), ROW_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, gamma,
-                                                                                        beta, mean_out, rstd_out, rows, D, eps);
+    const int grid = row_grid(rows, num_ctas);
+    const int chunks = (D / (dtype == 1 ? 8 : 4) + 31) / 32;   // 16-byte chunks per lane
+#define OB200_LN(T, CH) layernorm_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, gamma, beta, mean_out, rstd_out, rows, D, eps)
+    if (dtype == 0) {
+        if (chunks <= 2) OB200_LN(float, 2);
+        else if (chunks <= 4) OB200_LN(float, 4);
+        else if (chunks <= 8) OB200_LN(float, 8);
+        else layernorm_kernel<float><<<grid, ROW_THREADS, 0, s>>>((const float*)x, (float*)y, gamma, beta, mean_out, rstd_out, rows, D, eps);
+    } else {
+        if (chunks <= 2) OB200_LN(__nv_bfloat16, 2);
+        else if (chunks <= 4) OB200_LN(__nv_bfloat16, 4);
+        else if (chunks <= 8) OB200_LN(__nv_bfloat16, 8);
+        else layernorm_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, gamma, beta, mean_out,
+                                                                        rstd_out, rows, D, eps);
+    }
+#undef OB200_LN
     return (int)cudaGetLastError();
 }
 
@@ -208,21 +354,31 @@ extern "C" int ob200_softmax(const void* x, void* y, long long rows, int D, floa
     if ((dtype != 0 && dtype != 1) || num_ctas <= 0) return -1;
     if (!vec_ok(x, y, D, dtype)) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == 0)
-        softmax_kernel<float><<<row_grid(rows, num_ctas), ROW_THREADS, 0, s>>>((const float*)x, (float*)y, rows, D, scale);
-    else
-        softmax_kernel<__nv_bfloat16><<<row_grid(rows, num_ctas), ROW_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, D,
-                                                                                      scale);
+    const int grid = row_grid(rows, num_ctas);
+    const int chunks = (D / (dtype == 1 ? 8 : 4) + 31) / 32;
+#define OB200_SM(T, CH) softmax_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, rows, D, scale)
+    if (dtype == 0) {
+        if (chunks <= 2) OB200_SM(float, 2);
+        else if (chunks <= 4) OB200_SM(float, 4);
+        else if (chunks <= 8) OB200_SM(float, 8);
+        else softmax_kernel<float><<<grid, ROW_THREADS, 0, s>>>((const float*)x, (float*)y, rows, D, scale);
+    } else {
+        if (chunks <= 2) OB200_SM(__nv_bfloat16, 2);
+        else if (chunks <= 4) OB200_SM(__nv_bfloat16, 4);
+        else if (chunks <= 8) OB200_SM(__nv_bfloat16, 8);
+        else softmax_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, D, scale);
+    }
+#undef OB200_SM
     return (int)cudaGetLastError();
 }
 
 extern "C" int ob200_bias_gelu(const void* x, void* y, const float* bias, long long rows, int D, int dtype, int num_ctas, void* stream) {
     if (rows <= 0) return 0;
     if ((dtype != 0 && dtype != 1) || num_ctas <= 0) return -1;
-    if (!vec_ok(x, y, D, dtype)) return -2;
+    if (!vec_ok(x, y, D, dtype) || ((uintptr_t)bias % 16) != 0) return -2;
     const int n = dtype == 1 ? 8 : 4;
     const long long n_vec = rows * D / n;
-    long long want = (n_vec + ROW_THREADS - 1) / ROW_THREADS, cap = (long long)num_ctas * 4;
+    long long want = (n_vec + ROW_THREADS - 1) / ROW_THREADS, cap = (long long)num_ctas * 6;
     const int grid = (int)(want < cap ? want : cap);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == 0)

@@ -1,0 +1,96 @@
+"""Times the HBM-bound kernels (batch norm, elementwise, pooling, depthwise convolution, LayerNorm,
+softmax, GELU, optimizer steps) at the sizes the benchmark configurations use, one launch each per
+iteration, with CUDA events on the launching stream and the L2 flushed before every launch.
+
+    python -m orion_b200.eltwise_replay [--iters 5] [--warm 2]
+
+Prints one JSON line per kernel: algorithmic bytes (what the op has to read and write once),
+microseconds per launch and achieved GB/s.  The algorithmic byte counts are the ones the kernels are
+judged against: 8 B per element for an in/out elementwise op, 12 B for training batch norm forward
+(read for the statistics, read and write for the normalisation), 20 B for its backward, and so on.
+"""
+import argparse
+import json
+
+import torch
+
+from orion_b200 import kernels as K
+
+
+def cases():
+    dev = torch.device("cuda", torch.cuda.current_device())
+    f32 = dict(device=dev, dtype=torch.float32)
+    out = []
+
+    def add(name, nbytes, fn):
+        out.append((name, nbytes, fn))
+
+    # ResNet-50 training, batch 32: the 56x56x256 activation (102.8 MB) and the 28x28x512 one (51.4 MB)
+    for (n, h, c) in ((32, 56, 256), (32, 28, 512)):
+        x = torch.randn(n, h, h, c, **f32)
+        dy = torch.randn_like(x)
+        g, b = torch.rand(c, **f32) + 0.5, torch.randn(c, **f32)
+        rm, rv = torch.zeros(c, **f32), torch.ones(c, **f32)
+        _, sm, si = K.bn_train_forward(x, g, b, rm, rv, 1e-5, 0.1)
+        e = x.numel()
+        tag = "%dx%dx%dx%d" % (n, h, h, c)
+        add("bn_train_forward " + tag, 12 * e, lambda x=x, g=g, b=b, rm=rm, rv=rv: K.bn_train_forward(x, g, b, rm, rv, 1e-5, 0.1))
+        add("bn_backward " + tag, 20 * e, lambda dy=dy, x=x, g=g, sm=sm, si=si: K.bn_backward(dy, x, g, sm, si))
+        add("bn_inference+relu " + tag, 8 * e, lambda x=x, g=g, b=b, rm=rm, rv=rv: K.bn_inference(x, g, b, rm, rv, 1e-5, relu=True))
+        add("add+relu " + tag, 12 * e, lambda x=x, dy=dy: K.binary(x, dy, 2))
+        add("relu_backward " + tag, 12 * e, lambda x=x, dy=dy: K.relu_backward(dy, x))
+    x = torch.randn(32, 112, 112, 64, **f32)
+    add("maxpool 3x3/2 32x112x112x64", 4 * (x.numel() + x.numel() // 4), lambda x=x: K.maxpool_nhwc(x, 3, 2, 1))
+    x = torch.randn(256, 7, 7, 2048, **f32)
+    add("avgpool 256x7x7x2048", 4 * (x.numel() + 256 * 2048), lambda x=x: K.avgpool_nhwc(x))
+    # MobileNetV2 batch 64: depthwise 3x3 on 112x112x96 (stride 2) and 56x56x144 (stride 1), fused scale/shift/ReLU6
+    for (n, h, c, s) in ((64, 112, 96, 2), (64, 56, 144, 1)):
+        x = torch.randn(n, h, h, c, **f32)
+        w = torch.randn(3, 3, c, **f32)
+        sc, sh = torch.rand(c, **f32) + 0.5, torch.randn(c, **f32)
+        ho = (h + 2 - 3) // s + 1
+        add("depthwise 3x3/%d %dx%dx%dx%d" % (s, n, h, h, c), 4 * (x.numel() + n * ho * ho * c),
+            lambda x=x, w=w, sc=sc, sh=sh, s=s: K.depthwise_conv2d_nhwc(x, w, (s, s), (1, 1), scale=sc, shift=sh, relu=2, tap_major=True))
+    # BERT-base batch 8 x 384 (bf16) and the decoder LM batch 16 x 512
+    x = torch.randn(64 * 384, 768, device=dev).bfloat16()
+    g, b = torch.ones(768, **f32), torch.zeros(768, **f32)
+    add("layernorm bf16 24576x768", 4 * x.numel(), lambda x=x, g=g, b=b: K.layernorm(x, g, b))
+    x = torch.randn(8 * 12 * 8 * 384, 384, device=dev).bfloat16()
+    add("softmax bf16 294912x384", 4 * x.numel(), lambda x=x: K.softmax(x, 0.125))
+    x = torch.randn(32 * 384, 3072, device=dev).bfloat16()
+    bias = torch.randn(3072, **f32)
+    add("bias+gelu bf16 12288x3072", 4 * x.numel(), lambda x=x, bias=bias: K.bias_gelu(x, bias))
+    # optimizer steps over 25.6 M parameters (ResNet-50)
+    p_, g_, m_, v_ = (torch.randn(25_600_000, **f32) for _ in range(4))
+    v_.abs_()
+    add("sgd_momentum 25.6M", 20 * p_.numel(), lambda: K.sgd_momentum_(p_, g_, m_, 0.1, 0.9))
+    add("adamw 25.6M", 28 * p_.numel(), lambda: K.adamw_(p_, g_, m_, v_, 10, 1e-3))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warm", type=int, default=2)
+    a = ap.parse_args()
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for name, nbytes, fn in cases():
+        total = 0.0
+        for it in range(a.warm + a.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            if it >= a.warm:
+                total += e0.elapsed_time(e1)
+        us = total * 1e3 / a.iters
+        print(json.dumps({"kernel": name, "algorithmic_MB": round(nbytes / 1e6, 1), "us": round(us, 1),
+                          "GBps": round(nbytes / us / 1e3, 1)}), flush=True)
+    if K.read_status() != 0:
+        raise RuntimeError("a kernel reported a timed-out wait")
+
+
+if __name__ == "__main__":
+    main()
