@@ -25,23 +25,42 @@ __global__ void __launch_bounds__(ELT_THREADS) bn_inference_f32_kernel(const flo
                                                                      const float* __restrict__ mean,
                                                                      const float* __restrict__ var, float eps,
                                                                      long long n4, int c4, int relu) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-        const int c = (int)(i % c4) * 4;
-        const float4 v = __ldcs(x + i);
+    // y = a * x + b per channel.  When the grid stride is a multiple of the channel-quad count a thread stays on one
+    // channel quad: the coefficients (and their square roots) are computed once, the loop keeps four loads in flight.
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    auto coef = [&](int c, float4& a, float4& b) {
         const float4 m = __ldg(reinterpret_cast<const float4*>(mean + c));
         const float4 s2 = __ldg(reinterpret_cast<const float4*>(var + c));
-        float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 g = make_float4(1.f, 1.f, 1.f, 1.f), be = make_float4(0.f, 0.f, 0.f, 0.f);
         if (gamma) g = __ldg(reinterpret_cast<const float4*>(gamma + c));
-        if (beta) b = __ldg(reinterpret_cast<const float4*>(beta + c));
-        float4 o;
-        o.x = (v.x - m.x) * (1.0f / sqrtf(s2.x + eps)) * g.x + b.x;
-        o.y = (v.y - m.y) * (1.0f / sqrtf(s2.y + eps)) * g.y + b.y;
-        o.z = (v.z - m.z) * (1.0f / sqrtf(s2.z + eps)) * g.z + b.z;
-        o.w = (v.w - m.w) * (1.0f / sqrtf(s2.w + eps)) * g.w + b.w;
-        if (relu) {
-            o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f);
+        if (beta) be = __ldg(reinterpret_cast<const float4*>(beta + c));
+        a = make_float4(g.x / sqrtf(s2.x + eps), g.y / sqrtf(s2.y + eps), g.z / sqrtf(s2.z + eps), g.w / sqrtf(s2.w + eps));
+        b = make_float4(be.x - m.x * a.x, be.y - m.y * a.y, be.z - m.z * a.z, be.w - m.w * a.w);
+    };
+    const float lo = relu ? 0.f : -INFINITY;
+    auto apply = [&](const float4& v, const float4& a, const float4& b) {
+        return make_float4(fmaxf(fmaf(v.x, a.x, b.x), lo), fmaxf(fmaf(v.y, a.y, b.y), lo), fmaxf(fmaf(v.z, a.z, b.z), lo),
+                           fmaxf(fmaf(v.w, a.w, b.w), lo));
+    };
+    if (stride % c4 == 0) {
+        if (i >= n4) return;
+        float4 a, b;
+        coef((int)(i % c4) * 4, a, b);
+        for (; i + 3 * stride < n4; i += 4 * stride) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = __ldcs(x + i + u * stride);
+#pragma unroll
+            for (int u = 0; u < 4; u++) y[i + u * stride] = apply(v[u], a, b);
         }
-        y[i] = o;
+        for (; i < n4; i += stride) y[i] = apply(__ldcs(x + i), a, b);
+        return;
+    }
+    for (; i < n4; i += stride) {
+        float4 a, b;
+        coef((int)(i % c4) * 4, a, b);
+        y[i] = apply(__ldcs(x + i), a, b);
     }
 }
 
@@ -146,7 +165,11 @@ extern "C" int ob200_bn_inference_f32(const float* x, float* y, const float* gam
     const bool aligned = ((uintptr_t)x | (uintptr_t)y | (uintptr_t)mean | (uintptr_t)var | (uintptr_t)gamma | (uintptr_t)beta) % 16 == 0;
     if ((C & 3) == 0 && aligned) {
         long long n4 = n_elems / 4;
-        bn_inference_f32_kernel<<<elt_grid(n4, num_ctas), ELT_THREADS, 0, s>>>((const float4*)x, (float4*)y, gamma, beta, mean, var,
+        int grid = elt_grid(n4, num_ctas);
+        int need = 1;   // smallest grid multiple that makes grid * ELT_THREADS a multiple of the channel-quad count
+        while (((long long)need * ELT_THREADS) % (C / 4) != 0 && need < 64) need++;
+        if (need > 1 && need < 64 && grid >= need) grid -= grid % need;
+        bn_inference_f32_kernel<<<grid, ELT_THREADS, 0, s>>>((const float4*)x, (float4*)y, gamma, beta, mean, var,
                                                                               eps, n4, C / 4, relu);
     } else {
         bn_inference_f32_scalar_kernel<<<elt_grid(n_elems, num_ctas), ELT_THREADS, 0, s>>>(x, y, gamma, beta, mean, var, eps,

@@ -6,7 +6,7 @@ iteration, with CUDA events on the launching stream and the L2 flushed before ev
 
 Prints one JSON line per kernel: algorithmic bytes (what the op has to read and write once),
 microseconds per launch and achieved GB/s.  The algorithmic byte counts are the ones the kernels are
-judged against: 8 B per element for an in/out elementwise op, 12 B for training batch norm forward
+measured against: 8 B per element for an in/out elementwise op, 12 B for training batch norm forward
 (read for the statistics, read and write for the normalisation), 20 B for its backward, and so on.
 """
 import argparse
