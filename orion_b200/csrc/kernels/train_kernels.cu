@@ -42,8 +42,8 @@ __global__ void __launch_bounds__(TR_THREADS) bn_reduce_kernel(const float* __re
         }
         const long long per = (rows + slabs - 1) / slabs;
         const long long r0 = slab * per, r1 = r0 + per < rows ? r0 + per : rows;
-        // Four rows per trip, all loads issued before the first use: the kernel is bound by bytes in flight.
-        constexpr int U = 4;
+        // Eight rows per trip, all loads issued before the first use: the kernel is bound by bytes in flight.
+        constexpr int U = 8;
         long long r = r0 + threadIdx.y;
         for (; r + (long long)(U - 1) * ry < r1; r += (long long)U * ry) {
             float4 v[U], x[U];
