@@ -478,7 +478,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             if (p.mode == 1) {
                 // Filter gradient: accumulator row = output channel k, columns = channels c of tap (r, s).
                 // The result lands in dw[k][r][s][c]; partial sums of different pixel ranges are added atomically.
-                const int tap = tn / p.ctiles, cblk = tn - tap * p.ctiles;
+                const bool multi = p.wg_tpt > 1;
+                const int tap0 = multi ? tn * p.wg_tpt : tn / p.ctiles;
+                const int cbase = multi ? 0 : (tn - tap0 * p.ctiles) * BN;
+                const int taps = p.R * p.S;
                 float* dw = reinterpret_cast<float*>(p.y);
 #pragma unroll 1
                 for (int c32 = col_lo; c32 < col_hi; c32 += 32) {
@@ -493,12 +496,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                                 __uint_as_float(r[16 * h + j]), __uint_as_float(r[16 * h + j + 1]), __uint_as_float(r[16 * h + j + 2]),
                                 __uint_as_float(r[16 * h + j + 3]));
                         __syncwarp();
-                        const int c = cblk * BN + c32 + 16 * h + cc;
+                        const int ncol = c32 + 16 * h + cc;   // column of the tile -> (tap, channel)
+                        const int tap = multi ? tap0 + ncol / p.wg_cr : tap0;
+                        const int c = multi ? ncol % p.wg_cr : cbase + ncol;
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
                             const int rr = i * 8 + sub;
                             const long long k = tile_row0 + rr;
-                            if (k < p.Kout && c < p.C) {
+                            if (k < p.Kout && c < p.C && tap < taps) {
                                 const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc);
                                 float* dst = dw + ((long long)k * p.R * p.S + tap) * p.C + c;
                                 if (p.splits > 1) red_add_v4(dst, v);
@@ -803,12 +808,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 // stay pixel-major: four boxes of 32 pixels x 32 output channels of dy, and BN/32 im2col boxes of
                 // 32 pixels x 32 input channels of the layer input at this tile's tap.
                 if (pt == 0 && sizeof(T) == 4) {
-                    const int tap = tn / p.ctiles, cblk = tn - tap * p.ctiles;
-                    const int fr = tap / p.S, fs = tap - fr * p.S;
-                    const int k0 = tm * BM, c0 = cblk * BN;
+                    const bool multi = p.wg_tpt > 1;
+                    const int tap0 = multi ? tn * p.wg_tpt : tn / p.ctiles;
+                    const int cbase = multi ? 0 : (tn - tap0 * p.ctiles) * BN;
+                    const int taps = p.R * p.S;
+                    const int k0 = tm * BM;
                     const int pq = p.P * p.Q;
-                    int nb_boxes = 0;
-                    for (int g = 0; g < BN / 32; g++) nb_boxes += (c0 + 32 * g < p.C) ? 1 : 0;
+                    // box g holds 32 columns of the tile: one tap's channels [bc[g], bc[g] + 32); -1: nothing to load
+                    // (tap offsets are worked out here, once per tile: the loop below is the copy-issuing thread's
+                    // critical path)
+                    int bc[BN / 32], nb_boxes = 0;
+                    uint16_t boff_w[BN / 32], boff_h[BN / 32];
+#pragma unroll
+                    for (int g = 0; g < BN / 32; g++) {
+                        const int btap = multi ? tap0 + (32 * g) / p.wg_cr : tap0;
+                        bc[g] = multi ? (32 * g) % p.wg_cr : cbase + 32 * g;
+                        const int fr = btap / p.S, fs = btap - fr * p.S;
+                        boff_w[g] = (uint16_t)(fs * p.dil_w);
+                        boff_h[g] = (uint16_t)(fr * p.dil_h);
+                        if (bc[g] >= p.C || btap >= taps) bc[g] = -1;
+                        else nb_boxes++;
+                    }
                     for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
                         const int s = ring.s;
                         const long long m0 = (long long)kb * 32;
@@ -827,9 +847,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                         for (int g = 0; g < BM / 32; g++) tma_load_tile_2d(a_dst + g * 4096, p.tmap_a, &ctl->raw_full[s], k0 + 32 * g, (int)m0);
 #pragma unroll
                         for (int g = 0; g < BN / 32; g++)
-                            if (c0 + 32 * g < p.C)   // columns past C are never stored
-                                tma_load_im2col_4d(b_dst + g * 4096, p.tmap_b, &ctl->raw_full[s], c0 + 32 * g, oq * p.stride_w - p.pad_w,
-                                                   op * p.stride_h - p.pad_h, n_img, (uint16_t)(fs * p.dil_w), (uint16_t)(fr * p.dil_h));
+                            if (bc[g] >= 0)   // columns past C or past the last tap are never stored
+                                tma_load_im2col_4d(b_dst + g * 4096, p.tmap_b, &ctl->raw_full[s], bc[g], oq * p.stride_w - p.pad_w,
+                                                   op * p.stride_h - p.pad_h, n_img, boff_w[g], boff_h[g]);
                     }
                 } else {
                     break;

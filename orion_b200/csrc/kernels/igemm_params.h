@@ -56,6 +56,10 @@ typedef struct IgemmParams {
      * (tap, channel block). */
     int mode;
     int ctiles;             /* filter gradient: channel blocks per tap, ceil(C / BN) */
+    /* Filter gradient with few input channels (TMA-fed only): a tile's BN columns cover wg_tpt consecutive taps of
+     * wg_cr columns each (wg_cr = C rounded up to 32), so dy is read once per wg_tpt taps.  wg_tpt <= 1: one tap
+     * (and one channel block) per tile. */
+    int wg_tpt, wg_cr;
     int bmul_h, bmul_w, badd_h, badd_w, step_h, step_w, div_h, div_w;
     /* Tap subset (TMA-fed launches only): the filter in memory has w_R x w_S taps and the launch iterates
      * R x S of them, tap (t, u) being filter tap (w_r0 + w_rstep*t, w_s0 + w_sstep*u).  w_R = 0: the launch

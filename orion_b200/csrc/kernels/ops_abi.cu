@@ -423,10 +423,20 @@ extern "C" int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int 
     p.Nb = Nb; p.H = H; p.W = W; p.C = C; p.Kout = Kout; p.R = R; p.S = S; p.P = P; p.Q = Q;
     p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
     p.M = (int)Mpix;
-    const int bn = C > 64 ? 128 : 64;
+    // Few input channels and several taps: a 128-column tile covers 128 / roundup(C, 32) consecutive taps, so dy is
+    // read once per group of taps (TMA-fed launches only; `multi_tap` falls back below if TMA is not available).
+    const bool multi_tap = C >= 32 && C <= 64 && R * S > 1;
+    const int bn = (C > 64 || multi_tap) ? 128 : 64;
     p.ctiles = (C + bn - 1) / bn;
     p.tiles_m = (Kout + 127) / 128;
     p.tiles_n = R * S * p.ctiles;
+    if (multi_tap) {
+        p.wg_cr = (C + 31) / 32 * 32;
+        p.wg_tpt = 128 / p.wg_cr;
+        p.ctiles = 1;
+        p.tiles_n = (R * S + p.wg_tpt - 1) / p.wg_tpt;
+        p.require_tma = 1;
+    }
     p.kblocks_per_r = (int)((Mpix + 31) / 32);
     p.num_kblocks = p.kblocks_per_r;
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
@@ -444,7 +454,22 @@ extern "C" int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int 
     }
     const long long units = tiles * p.splits;
     const int grid = units < num_ctas ? (int)units : num_ctas;
-    return ob200_igemm_launch(&p, bn, grid, stream);
+    const int rc = ob200_igemm_launch(&p, bn, grid, stream);
+    if (rc == -4 && multi_tap) {   // no TMA for this problem: one tap per 64-column tile through the gathering producers
+        p.wg_tpt = p.wg_cr = p.require_tma = 0;
+        p.ctiles = 1;
+        p.tiles_n = R * S;
+        const long long tiles1 = (long long)p.tiles_m * p.tiles_n;
+        long long sp = (2LL * num_ctas + tiles1 - 1) / tiles1;
+        if (sp > p.num_kblocks / 2) sp = p.num_kblocks / 2;
+        if (sp > 64) sp = 64;
+        if (sp < 1) sp = 1;
+        p.splits = (int)sp;
+        if (p.splits > 1 && cudaMemsetAsync(dw, 0, dw_bytes, s) != cudaSuccess) return -1;
+        const long long units1 = tiles1 * p.splits;
+        return ob200_igemm_launch(&p, 64, units1 < num_ctas ? (int)units1 : num_ctas, stream);
+    }
+    return rc;
 }
 
 // y[M, N] = x[M, K] . w[N, K]^T (+ bias) (+ ReLU): a 1x1 convolution over M "pixels".

@@ -142,6 +142,8 @@ def _wgrad_ref(x, dy, rs, stride, pad, dil):
 @pytest.mark.parametrize("shape", [
     (2, 8, 8, 32, 128, 1, 1, 0), (4, 56, 56, 64, 64, 3, 1, 1), (4, 56, 56, 64, 256, 1, 1, 0), (4, 28, 28, 128, 128, 3, 2, 1),
     (4, 14, 14, 256, 1024, 1, 1, 0), (4, 7, 7, 512, 512, 3, 1, 1), (2, 11, 9, 24, 40, 3, 2, 1), (3, 10, 10, 200, 136, 3, 1, 1),
+    # few input channels: one tile covers several taps (4 taps of 32 channels, 2 taps of 48 -> 64, 5x5 = 25 taps, stride 2)
+    (3, 12, 12, 32, 96, 3, 1, 1), (2, 13, 13, 48, 200, 5, 1, 2), (2, 16, 16, 64, 64, 3, 2, 1), (2, 9, 9, 36, 20, 2, 1, 0),
 ])
 def test_conv_wgrad_fp32(K, shape):
     Nb, H, W, C, Ko, R, stride, pad = shape
