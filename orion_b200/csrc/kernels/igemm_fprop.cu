@@ -869,13 +869,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     const int op = rem / p.OW, oq = rem - op * p.OW;
                     const int cw = oq * p.bmul_w + p.tma_base_w, ch = op * p.bmul_h + p.tma_base_h;
                     const int cn = bidx * p.Nb + n_img;
+                    // Filter row r, tap ts and channel tc of the k-block are carried along instead of divided out
+                    // every time: this loop is the copy-issuing thread's critical path.
+                    int r = kb_begin / p.kblocks_per_r;
+                    int kb_in_r = kb_begin - r * p.kblocks_per_r;
+                    int ts = (kb_in_r * C::BK) / p.C, tc = kb_in_r * C::BK - ts * p.C;
                     for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
                         const int s = ring.s;
-                        const int r = kb / p.kblocks_per_r;
-                        const int kin = (kb - r * p.kblocks_per_r) * C::BK;
-                        const int ts = kin / p.C, tc = kin - ts * p.C;
                         const int off_h = p.step_h >= 0 ? r * p.step_h : (p.R - 1 - r) * -p.step_h;
                         const int off_w = p.step_w >= 0 ? ts * p.step_w : (p.S - 1 - ts) * -p.step_w;
+                        const int cur_r = r, cur_ts = ts, cur_tc = tc;
+                        tc += C::BK;                       // next k-block: whole taps per k-block row (C % BK == 0), or one tap
+                        if (tc >= p.C) { tc -= p.C; ts++; }
+                        if (++kb_in_r == p.kblocks_per_r) { kb_in_r = 0; r++; ts = 0; tc = 0; }
                         if (!timed_wait(&ctl->empty[s], (ring.ph ^ 1u), abort_flag, waited)) {
                             if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                             dead = true;
@@ -884,8 +890,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                         const uint32_t a_dst = smem_u32(smem + s * stage_bytes);
                         const uint32_t b_dst = a_dst + b_off;
                         mbar_arrive_expect_tx(&ctl->raw_full[s], C::A_BYTES + C::B_BYTES);
-                        tma_load_im2col_4d(a_dst, p.tmap_a, &ctl->raw_full[s], tc, cw, ch, cn, (uint16_t)off_w, (uint16_t)off_h);
-                        tma_load_tile_5d(b_dst, p.tmap_b, &ctl->raw_full[s], tc, ts, r, tn * BN, bidx);
+                        tma_load_im2col_4d(a_dst, p.tmap_a, &ctl->raw_full[s], cur_tc, cw, ch, cn, (uint16_t)off_w, (uint16_t)off_h);
+                        tma_load_tile_5d(b_dst, p.tmap_b, &ctl->raw_full[s], cur_tc, cur_ts, cur_r, tn * BN, bidx);
                     }
                 } else {
                     break;   // the other producer threads have nothing to do
