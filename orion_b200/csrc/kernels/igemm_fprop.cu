@@ -829,12 +829,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                         if (bc[g] >= p.C || btap >= taps) bc[g] = -1;
                         else nb_boxes++;
                     }
+                    // first pixel of the k-block as (image, row, column), carried along from k-block to k-block
+                    int n_img, op, oq;
+                    {
+                        const long long mb = (long long)kb_begin * 32;
+                        n_img = (int)(mb / pq);
+                        const int rem = (int)(mb - (long long)n_img * pq);
+                        op = rem / p.Q;
+                        oq = rem - op * p.Q;
+                    }
                     for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
                         const int s = ring.s;
                         const long long m0 = (long long)kb * 32;
-                        const int n_img = (int)(m0 / pq);
-                        const int rem = (int)(m0 - (long long)n_img * pq);
-                        const int op = rem / p.Q, oq = rem - op * p.Q;
+                        const int cur_n = n_img, cur_p = op, cur_q = oq;
+                        oq += 32;
+                        while (oq >= p.Q) {
+                            oq -= p.Q;
+                            if (++op == p.P) { op = 0; n_img++; }
+                        }
                         if (!timed_wait(&ctl->empty[s], (ring.ph ^ 1u), abort_flag, waited)) {
                             if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
                             dead = true;
@@ -848,8 +860,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
 #pragma unroll
                         for (int g = 0; g < BN / 32; g++)
                             if (bc[g] >= 0)   // columns past C or past the last tap are never stored
-                                tma_load_im2col_4d(b_dst + g * 4096, p.tmap_b, &ctl->raw_full[s], bc[g], oq * p.stride_w - p.pad_w,
-                                                   op * p.stride_h - p.pad_h, n_img, boff_w[g], boff_h[g]);
+                                tma_load_im2col_4d(b_dst + g * 4096, p.tmap_b, &ctl->raw_full[s], bc[g], cur_q * p.stride_w - p.pad_w,
+                                                   cur_p * p.stride_h - p.pad_h, cur_n, boff_w[g], boff_h[g]);
                     }
                 } else {
                     break;
