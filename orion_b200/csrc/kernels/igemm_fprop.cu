@@ -403,7 +403,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         for (int s = 0; s < stages; s++) {
             // every producer thread, when its copies have landed; or the one TMA-issuing thread plus the byte count
             mbar_init(&ctl->raw_full[s], p.use_tma ? 1 : PROD_WARPS * 32);
-            mbar_init(&ctl->full[s], p.use_tma ? 2 * SPLIT_WARPS : SPLIT_WARPS);   // one elected lane per splitter warp
+            // one elected lane per splitter warp that works on the k-block (one group of four, or both groups)
+            mbar_init(&ctl->full[s], (p.use_tma && !ATMEM) ? 2 * SPLIT_WARPS : SPLIT_WARPS);
             mbar_init(&ctl->empty[s], 1);      // tcgen05.commit
         }
         for (int b = 0; b < 2; b++) {
@@ -713,8 +714,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         // remainder x - tf32(x) into the second buffer.  The work is elementwise, so the 16-byte chunks of the
         // two tiles are simply dealt out to the splitter threads in address order.
         if (C::kSplit) {
-            const int st_id = split_id * 32 + lane;
-            const int st_threads = (tma_roles ? 2 * SPLIT_WARPS : SPLIT_WARPS) * 32;
+            // With two splitter groups (TMA-fed launches) the groups take alternate k-blocks: splitting one k-block is
+            // a chain of latencies (barrier wake-up, shared-memory reads, tcgen05.st and its wait, fence, arrive), so
+            // two k-blocks in flight double the rate where sharing one k-block between the groups did not.
+            // (Only where the activation parts go to tensor memory; the shared-memory variant is bound by the traffic
+            // itself, there both groups share every k-block.)
+            const bool alternate = ATMEM && tma_roles;
+            const int st_id = alternate ? (split_id & 3) * 32 + lane : split_id * 32 + lane;
+            const int st_threads = (tma_roles && !alternate ? 2 * SPLIT_WARPS : SPLIT_WARPS) * 32;
+            const int grp = alternate ? split_id >> 2 : 0, ngrp = alternate ? 2 : 1;
+            int turn = 0;
             RingPos ring;
             bool dead = false;
             WorkIter work(p, tiles);
@@ -723,6 +732,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 const int kb_begin = seg.kb_begin, kb_end = seg.kb_end;
                 for (int kb = kb_begin; kb < kb_end; kb++, ring.advance(stages)) {
                     const int s = ring.s;
+                    const bool mine = turn == grp;
+                    if (++turn == ngrp) turn = 0;
+                    if (!mine) continue;
                     if (!timed_wait(&ctl->raw_full[s], ring.ph, abort_flag, waited)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_FULL); }
                         dead = true;
@@ -734,14 +746,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                     uint8_t* b_hi = st + b_off;
                     uint8_t* b_lo = b_hi + C::B_BYTES;
                     if (ATMEM) {
-                        // Activation tile: this thread owns row (32*(warp%4) + lane) = its tensor-memory lane and
-                        // 16 of the row's 32 values (all 32 with a single splitter group).  Both parts go to tensor
-                        // memory, where the MMA reads its A operand without touching shared memory again.
+                        // Activation tile: this thread owns row (32*(warp%4) + lane) = its tensor-memory lane.  Both
+                        // parts of the row's 32 values go to tensor memory, where the MMA reads its A operand without
+                        // touching shared memory again.
                         const int q = warp & 3;
                         const uint32_t row = (uint32_t)(q * 32 + lane);
-                        const int ngrp = tma_roles ? 2 : 1;
                         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + C::A_TMEM_COL0 + s * 64;
-                        for (int c0 = (split_id >> 2) * 16; c0 < 32; c0 += 16 * ngrp) {
+#pragma unroll
+                        for (int c0 = 0; c0 < 32; c0 += 16) {
                             uint32_t hi[16], lo[16];
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
