@@ -130,6 +130,47 @@ __global__ void __launch_bounds__(ELT_THREADS) maxpool_nhwc_f32_kernel(const flo
     }
 }
 
+// 3x3 / stride 2 max-pool (the ResNet stem): a thread produces four consecutive output pixels of one row for
+// its channel quad, sharing the nine input columns they need (27 loads for four outputs instead of 36).
+__global__ void __launch_bounds__(ELT_THREADS) maxpool3x3s2_nhwc_f32_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                                          int Nb, int H, int W, int C, int P, int Q, int pad) {
+    const int c4 = C >> 2, qb_n = (Q + 3) / 4;
+    const long long total = (long long)Nb * P * qb_n * c4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % c4) * 4;
+        long long t = i / c4;
+        const int qb = (int)(t % qb_n); t /= qb_n;
+        const int p = (int)(t % P);
+        const int n = (int)(t / P);
+        const float4 lowest = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        float4 m[4] = {lowest, lowest, lowest, lowest};
+        const int w0 = qb * 8 - pad;
+#pragma unroll
+        for (int r = 0; r < 3; r++) {
+            const int h = p * 2 - pad + r;
+            if ((unsigned)h >= (unsigned)H) continue;
+            const float* xrow = x + (((long long)n * H + h) * W) * C + c;
+            float4 v[9];
+#pragma unroll
+            for (int j = 0; j < 9; j++) {
+                const int w = w0 + j;
+                v[j] = (unsigned)w < (unsigned)W ? __ldg(reinterpret_cast<const float4*>(xrow + (long long)w * C)) : lowest;
+            }
+#pragma unroll
+            for (int o = 0; o < 4; o++) {
+#pragma unroll
+                for (int s2 = 0; s2 < 3; s2++) {
+                    const float4 a = v[2 * o + s2];
+                    m[o].x = fmaxf(m[o].x, a.x); m[o].y = fmaxf(m[o].y, a.y); m[o].z = fmaxf(m[o].z, a.z); m[o].w = fmaxf(m[o].w, a.w);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 0; o < 4; o++)
+            if (qb * 4 + o < Q) *reinterpret_cast<float4*>(y + (((long long)n * P + p) * Q + qb * 4 + o) * C + c) = m[o];
+    }
+}
+
 // Global average pool NHWC [Nb, HW, C] -> [Nb, C]; one thread per (image, channel),
 // consecutive threads read consecutive channels so every row read is coalesced.
 __global__ void __launch_bounds__(ELT_THREADS) avgpool_nhwc_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int Nb,
@@ -197,6 +238,11 @@ extern "C" int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, i
     if (Nb <= 0) return 0;
     if ((C & 3) || k <= 0 || stride <= 0 || num_ctas <= 0) return -1;
     const int P = (H + 2 * pad - k) / stride + 1, Q = (W + 2 * pad - k) / stride + 1;
+    if (k == 3 && stride == 2) {
+        const long long total4 = (long long)Nb * P * ((Q + 3) / 4) * (C / 4);
+        maxpool3x3s2_nhwc_f32_kernel<<<elt_grid(total4, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, H, W, C, P, Q, pad);
+        return (int)cudaGetLastError();
+    }
     long long total = (long long)Nb * P * Q * (C / 4);
     maxpool_nhwc_f32_kernel<<<elt_grid(total, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, H, W, C, P, Q, k, stride,
                                                                                                pad);

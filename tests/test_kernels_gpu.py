@@ -227,6 +227,9 @@ def test_elementwise_and_pooling(K):
     assert torch.equal(K.binary(odd, odd, mode=2), torch.relu(odd + odd))          # tail that is not a multiple of 4
     x = torch.randn(4, 112, 112, 64, device="cuda")
     assert torch.equal(K.maxpool_nhwc(x, 3, 2, 1).double().cpu(), O.maxpool_nhwc(x, 3, 2, 1))
+    for shp, (k, st, pd) in (((2, 15, 13, 8), (3, 2, 1)), ((3, 9, 10, 12), (3, 2, 0)), ((2, 11, 11, 16), (2, 2, 0)), ((1, 8, 8, 4), (3, 1, 1))):
+        xr = torch.randn(*shp, device="cuda")      # ragged widths (output tails of the four-pixel groups) and the generic kernel
+        assert torch.equal(K.maxpool_nhwc(xr, k, st, pd).double().cpu(), O.maxpool_nhwc(xr, k, st, pd))
     z = torch.randn(4, 7, 7, 2048, device="cuda")
     assert O.rel_err(K.avgpool_nhwc(z), O.avgpool_nhwc(z)) < 1e-6
 
