@@ -5,27 +5,38 @@ training client co-located on each GPU under the orion scheduler.
 
 Workload (N=1): HP ResNet-50 inference, fp32, batch 4, N(0,1) 3x224x224 inputs, Poisson
 arrivals at 80 requests/s; BE ResNet-50 training, batch 32, SGD(momentum 0.9, lr 0.1),
-labels uniform in [0,1000); random init; synthetic data.  A step is one HP request;
-K = --steps measured HP requests after the launch protocol's 10 warm-up requests.
+labels uniform in [0,1000); random init; synthetic data.
+
+A step is a block of 100 HP requests.  Every run (HP alone, co-located with host buffers,
+co-located with resident inputs) issues the launch protocol's 10 warm-up requests, then
+W untimed blocks, then exactly K timed blocks; the same seeded arrival sequence is used
+alone and co-located.  The default K = 20 gives 2000 measured Poisson requests per run.
 
 Printed JSON (one line, rank 0):
-  value      BE training samples/s while co-located, inputs resident in HBM
+  value      BE training samples/s inside the window of the K timed blocks, inputs resident in HBM
   e2e        the same through host buffers: every HP request copies its pinned batch to
              the device and its logits back, every BE iteration copies its batch and
              reads the loss back
-  hp         HP p50/p99 latency co-located and solo, and the p99 ratio (target <= 1.15)
-  be         BE samples/s solo and the co-located fraction (target >= 0.70)
+  hp         HP p50/p99 latency co-located and alone over the timed requests, the p99 ratio
+             (target <= 1.15) and a paired-bootstrap 95 % interval of that ratio
+  be         BE samples/s alone and the co-located fraction (target >= 0.70)
   roofline   the implicit-GEMM convolution kernel, timed here with CUDA events
-  cpu_baseline  the same workload in eager PyTorch on the host cores (bounded sample)
-With N > 1 (torchrun) every rank runs an independent replica on its own GPU; nothing is
-exchanged on the data path; `value` sums the ranks and the latency ratio is the worst rank.
+  roofline_hbm  the HBM-bound kernels of the BE training step (batch norm, add+ReLU, ReLU
+             backward, pooling, SGD), timed the same way
+  cpu_baseline  the same workload in eager PyTorch on the host cores (bounded sample), and the
+             reference scheduler replaying the arrival script recorded from this run's
+             co-located phase next to the product's policy core (same decision log or not)
+With N > 1 (torchrun) every rank runs an independent replica on its own GPU and its own
+cores; nothing is exchanged on the data path; `value` sums the ranks and the latency ratio is
+the worst rank (every rank's figures are listed under `ranks`).
 """
 import argparse
 import json
 import os
+import shutil
 import subprocess
 import sys
-import threading
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -33,11 +44,15 @@ sys.path.insert(0, ROOT)
 
 METRIC = "HP p99 latency (x solo) + BE train samples/s, co-located on one B200"
 HP_RPS = 80
-RESNET50_FWD_FLOP_B1 = 32.71e9 / 4   # conv + fc, 2*MAC, per image
+STEP_REQUESTS = 100
 # DRAM bytes per launch of the roofline replay (53 ResNet-50 convolutions, batch 32): 1354.2 MB read + 296.3 MB
 # written over the 53 launches in one ncu pass of `python -m orion_b200.kernel_replay --batch 32 --iters 1 --warm 1`;
 # the algorithmic bytes (activations + filters + outputs) are 54.5 MB per launch, most outputs stay in L2.
 ROOFLINE_TRAFFIC_BYTES_PER_LAUNCH = 31.14e6
+# DRAM bytes of one ob200_bn_backward_f32 call on 32x56x56x256 (statistics pass 205.9 MB + apply pass 251.3 MB,
+# one ncu pass of `python -m orion_b200.eltwise_replay --iters 1 --warm 0`); algorithmic 513.8 MB (20 B per element:
+# the apply pass finds part of dy and x still in L2).
+HBM_TRAFFIC_BN_BACKWARD = 457.2e6
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -105,9 +120,46 @@ def kernel_roofline(batch, iters, warm):
     return kernel_replay.replay(kernel_replay.conv_layers_resnet50(), batch, iters, warm)
 
 
-def cpu_baseline(sample_hp=12, sample_be=2):
+def hbm_roofline(peaks, iters=5, warm=3):
+    """The HBM-bound kernels of the BE ResNet-50 training step at its two dominant activation sizes, one C-ABI call
+    each per iteration with CUDA events around it and L2 flushed before (orion_b200/eltwise_replay.py)."""
+    from orion_b200 import eltwise_replay
+    rows = eltwise_replay.replay(iters, warm, only=("bn_", "add+relu", "relu_backward", "maxpool", "sgd_momentum"))
+    total_bytes = sum(r["algorithmic_bytes"] for r in rows)
+    total_us = sum(r["us"] for r in rows)
+    dom = next((r for r in rows if r["kernel"].startswith("bn_backward 32x56x56x256")), rows[0])
+    return {"bound": "hbm", "achieved": dom["GBps"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": dom["GBps"] / peaks["hbm_gbs"],
+            "traffic": HBM_TRAFFIC_BN_BACKWARD, "peak_source": peaks["source"],
+            "kernel": "ob200_bn_backward_f32 (bn_reduce_kernel + bn_backward_apply_kernel), 32x56x56x256 fp32: the largest "
+                      "HBM-bound entry of the BE training step; algorithmic 20 B per element",
+            "set_achieved": total_bytes / total_us / 1e3, "set_frac": total_bytes / total_us / 1e3 / peaks["hbm_gbs"],
+            "set": [{"kernel": r["kernel"], "GBps": round(r["GBps"], 1), "us": round(r["us"], 1)} for r in rows]}
+
+
+def policy_replay(script, repeat=1):
+    """Decisions/s of the reference scheduler (oracle/_ref, its own sources compiled unmodified) and of this
+    repository's policy core on one arrival script, one core each, and whether their decision logs agree."""
+    out = {"script": os.path.basename(script)}
+    ref = os.path.join(ROOT, "oracle", "_ref", "ref_replay")
+    try:
+        if os.path.exists(ref):
+            r = subprocess.run([ref, script, os.path.join(ROOT, "oracle", "_ref"), "-"], capture_output=True, text=True, timeout=240)
+            out["reference"] = json.loads(r.stdout.strip().splitlines()[-1])
+        own = os.path.join(ROOT, "orion_b200", "bin", "orion_replay")
+        if os.path.exists(own):
+            r = subprocess.run([own, script, "--repeat", str(repeat)], capture_output=True, text=True, timeout=240)
+            out["orion_b200"] = json.loads(r.stdout.strip().splitlines()[-1])
+        if "reference" in out and "orion_b200" in out:
+            out["same_log"] = out["reference"]["log_fnv1a"] == out["orion_b200"]["log_fnv1a"]
+    except (OSError, ValueError, subprocess.SubprocessError, IndexError) as e:
+        out["error"] = repr(e)[:200]
+    return out
+
+
+def cpu_baseline(sample_hp=12, sample_be=2, recorded_script=None):
     """Eager PyTorch on the host cores: the reference's numeric path for this workload
-    (reference benchmarking/benchmark_suite/train_imagenet.py:111-116), on a bounded sample."""
+    (reference benchmarking/benchmark_suite/train_imagenet.py:111-116), on a bounded sample; plus the reference
+    scheduler's decisions on an arrival script (this run's recorded one when given)."""
     import numpy as np
     import torch
     from torchvision import models
@@ -138,31 +190,30 @@ def cpu_baseline(sample_hp=12, sample_be=2):
         crit(be(xb), yb).backward()
         opt.step()
     be_sps = 32 * sample_be / (time.perf_counter() - t0)
+    script = recorded_script or os.path.join(ROOT, "tests", "golden", "pair_open.script")
     return {"value": be_sps, "unit": "samples/s", "cores": threads, "kind": "port",
             "sample": "eager PyTorch fp32 on host cores, run one after the other: %d ResNet-50 b32 SGD steps (value) and %d "
                       "ResNet-50 b4 forwards" % (sample_be, sample_hp),
-            "hp_p50_ms": float(np.percentile(lat, 50)) * 1e3, "hp_p99_ms": float(np.percentile(lat, 99)) * 1e3}
+            "hp_p50_ms": float(np.percentile(lat, 50)) * 1e3, "hp_p99_ms": float(np.percentile(lat, 99)) * 1e3,
+            "policy": dict(policy_replay(script, repeat=1 if recorded_script else 3),
+                           trace="recorded from this run's co-located phase" if recorded_script else "committed synthetic script")}
 
 
-def reference_policy_rate():
-    """Decisions/s of the reference scheduler (oracle/_ref, its own sources compiled unmodified)
-    and of this repository's policy core on the same arrival script, one core each."""
-    script = os.path.join(ROOT, "tests", "golden", "pair_open.script")
-    out = {}
-    ref = os.path.join(ROOT, "oracle", "_ref", "ref_replay")
-    try:
-        if os.path.exists(ref):
-            r = subprocess.run([ref, script, os.path.join(ROOT, "oracle", "_ref"), "-"], capture_output=True, text=True, timeout=120)
-            out["reference"] = json.loads(r.stdout.strip().splitlines()[-1])
-        own = os.path.join(ROOT, "orion_b200", "bin", "orion_replay")
-        if os.path.exists(own):
-            r = subprocess.run([own, script, "--repeat", "3"], capture_output=True, text=True, timeout=120)
-            out["orion_b200"] = json.loads(r.stdout.strip().splitlines()[-1])
-        if "reference" in out and "orion_b200" in out:
-            out["same_log"] = out["reference"]["log_fnv1a"] == out["orion_b200"]["log_fnv1a"]
-    except (OSError, ValueError, subprocess.SubprocessError, IndexError):
-        pass
-    return out
+def paired_bootstrap_p99_ratio(coloc, solo, n_boot=1000, seed=7):
+    """95 % interval of p99(co-located) / p99(alone).  Both runs see the same arrival sequence, so request i of one
+    corresponds to request i of the other: indices are resampled, and both percentiles are taken over the same
+    resampled requests."""
+    import numpy as np
+    n = min(len(coloc), len(solo))
+    if n < 50:
+        return None
+    a, b = np.asarray(coloc[:n]), np.asarray(solo[:n])
+    rng = np.random.default_rng(seed)
+    ratios = []
+    for _ in range(n_boot):
+        idx = rng.integers(0, n, n)
+        ratios.append(np.percentile(a[idx], 99) / np.percentile(b[idx], 99))
+    return [float(np.percentile(ratios, 2.5)), float(np.percentile(ratios, 97.5))]
 
 
 # ----------------------------------------------------------------------------- the product arm
@@ -176,39 +227,65 @@ def physical_gpu(local_rank):
     return ids[local_rank] if local_rank < len(ids) else str(local_rank)
 
 
-def run_replica(gpu, steps, out_dir, be_quota):
+def rank_cores(local_rank, local_world):
+    """Disjoint slice of the cores this process may run on, one slice per replica of the node (the scheduler thread
+    and the HP client spin; the BE client and its autograd thread are busy most of the time): each replica's child
+    processes run inside its slice and pin their spinning threads to distinct cores of it."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+    except AttributeError:
+        return None
+    per = len(cores) // max(1, local_world)
+    if per < 3:
+        return None
+    return cores[local_rank * per:(local_rank + 1) * per]
+
+
+def be_rate_in_window(be_client, t0, t1):
+    """BE samples/s from the iterations that completed inside [t0, t1] (the window of the timed HP requests)."""
+    ends = [t for t in be_client.get("iteration_end_times", []) if t0 <= t <= t1]
+    if len(ends) < 2:
+        return be_client.get("samples_per_s", 0.0), len(ends)
+    return (len(ends) - 1) * be_client["batchsize"] / (ends[-1] - ends[0]), len(ends)
+
+
+def run_replica(gpu, steps, warm_steps, out_dir, be_quota):
     from orion_b200 import experiments as E
-    env = {"CUDA_VISIBLE_DEVICES": gpu}
+    env = {"CUDA_VISIBLE_DEVICES": gpu, "ORION_PIN_THREADS": os.environ.get("ORION_PIN_THREADS", "2"),
+           "ORION_EXTRA_WARMUP_REQUESTS": warm_steps * STEP_REQUESTS}
     if be_quota > 0:
         env["ORION_BE_SM_QUOTA"] = be_quota
     hp_prof = E.profile_client("resnet50_hp", os.path.join(out_dir, "profiles"), extra_env=env)
     be_prof = E.profile_client("resnet50_be", os.path.join(out_dir, "profiles"), extra_env=env)
-    n_hp = steps + 10
+    n_hp = 10 + (warm_steps + steps) * STEP_REQUESTS
     hp_solo = E.run_launch_jobs([E.client_entry("resnet50_hp", hp_prof, n_hp, rps=HP_RPS)], os.path.join(out_dir, "hp_solo"),
                                 extra_env=env)
-    be_solo = E.run_launch_jobs([E.client_entry("resnet50_be", be_prof, 90)], os.path.join(out_dir, "be_solo"), extra_env=env)
+    be_solo = E.run_launch_jobs([E.client_entry("resnet50_be", be_prof, 130)], os.path.join(out_dir, "be_solo"), extra_env=env)
     # DUR_THRESHOLD the way the reference derived its 160 us: 2.5 % of the HP solo latency
     # (reference benchmarking/benchmark_suite/utility_scripts/compute_average.py:42-44).
     depth = int(os.environ.get("ORION_DUR_THRESHOLD_NS", 0)) or int(0.025 * hp_solo["clients"][0]["p50_latency"] * 1e6)
     pair = [E.client_entry("resnet50_be", be_prof, 1000000), E.client_entry("resnet50_hp", hp_prof, n_hp, rps=HP_RPS)]
     e2e = E.run_launch_jobs(pair, os.path.join(out_dir, "coloc_e2e"), depth=depth, extra_env=env)
     env_res = dict(env)
-    env_res.update({"ORION_RESIDENT_INPUTS": 1, "ORION_READBACK": 0})
+    script = os.path.join(out_dir, "coloc_resident", "recorded.script")
+    env_res.update({"ORION_RESIDENT_INPUTS": 1, "ORION_READBACK": 0, "ORION_RECORD_SCRIPT": script, "ORION_RECORD_MAX_ITERS": 400})
     res = E.run_launch_jobs(pair, os.path.join(out_dir, "coloc_resident"), depth=depth, extra_env=env_res)
     return {"hp_solo": hp_solo, "be_solo": be_solo, "e2e": e2e, "resident": res, "depth": depth,
-            "profile_rows": {"hp": hp_prof[3], "be": be_prof[3]}}
+            "profile_rows": {"hp": hp_prof[3], "be": be_prof[3]}, "script": script if os.path.exists(script) else None}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1500)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20, help="timed blocks of %d HP requests" % STEP_REQUESTS)
+    ap.add_argument("--warmup", type=int, default=3, help="untimed blocks after the protocol's 10 warm-up requests")
     ap.add_argument("--impl", type=str, default="orion_b200")
+    ap.add_argument("--keep", action="store_true", help="keep the per-run files (client and scheduler JSON, profiles, logs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
 
     if args.impl == "reference":
         if rank != 0:
@@ -221,7 +298,7 @@ def main():
                                        "(the reference's numeric path), run one after the other"},
                 "cpu_baseline": base, "hp": {"p50_ms": base["hp_p50_ms"], "p99_ms": base["hp_p99_ms"]},
                 "e2e": {"value": base["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                "policy_decisions_per_s": reference_policy_rate()}
+                "policy_decisions_per_s": base["policy"]}
         print(json.dumps(line))
         return 0
 
@@ -236,66 +313,84 @@ def main():
     from orion_b200 import build
     build.build_all()
 
-    steps = max(args.steps, 20)
+    steps, warm_steps = max(args.steps, 1), max(args.warmup, 0)
     be_quota = int(os.environ.get("ORION_BE_SM_QUOTA", "0"))
-    out_dir = os.path.join(ROOT, "gpurun_out", "bench", "rank%d" % rank)
+    base_dir = os.environ.get("ORION_BENCH_DIR") or tempfile.mkdtemp(prefix="orion_bench_")
+    out_dir = os.path.join(base_dir, "rank%d" % rank)
     gpu = physical_gpu(local_rank)
     sampler = ClockSampler(gpu)
+    all_cores = None
+    mine = rank_cores(local_rank, local_world)
+    if mine:   # child processes inherit the mask; the CPU baseline below gets every core back
+        all_cores = os.sched_getaffinity(0)
+        os.sched_setaffinity(0, mine)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler.start()
     t0 = time.time()
-    rep = run_replica(gpu, steps, out_dir, be_quota)
+    rep = run_replica(gpu, steps, warm_steps, out_dir, be_quota)
     torch.cuda.synchronize()
     wall = time.time() - t0
     clocks = sampler.stop()
+    if all_cores:
+        os.sched_setaffinity(0, all_cores)
 
-    def pick(run):
-        be, hp = run["clients"][0], run["clients"][1]
-        return be, hp
-
-    be_e2e, hp_e2e = pick(rep["e2e"])
-    be_res, hp_res = pick(rep["resident"])
+    be_e2e, hp_e2e = rep["e2e"]["clients"]
+    be_res, hp_res = rep["resident"]["clients"]
     hp_solo = rep["hp_solo"]["clients"][0]
     be_solo = rep["be_solo"]["clients"][0]
-    local = {"be_sps": be_res["samples_per_s"], "be_sps_e2e": be_e2e["samples_per_s"], "be_solo_sps": be_solo["samples_per_s"],
+    be_sps, be_iters = be_rate_in_window(be_res, hp_res["measure_start_time"], hp_res["measure_end_time"])
+    be_sps_e2e, _ = be_rate_in_window(be_e2e, hp_e2e["measure_start_time"], hp_e2e["measure_end_time"])
+    local = {"be_sps": be_sps, "be_sps_e2e": be_sps_e2e, "be_solo_sps": be_solo["samples_per_s"], "be_iterations_timed": be_iters,
              "hp_p99": hp_e2e["p99_latency"], "hp_p50": hp_e2e["p50_latency"], "hp_solo_p99": hp_solo["p99_latency"],
              "hp_solo_p50": hp_solo["p50_latency"], "hp_p99_resident": hp_res["p99_latency"],
-             "coloc_time": hp_res["total_time"], "launches": rep["resident"]["scheduler"].get("own_launches", 0),
-             "sched": rep["resident"]["scheduler"]["stats"], "wall": wall}
+             "hp_requests": hp_e2e["measured_requests"],
+             "p99_ratio_ci95": paired_bootstrap_p99_ratio(hp_e2e["latencies_ms"], hp_solo["latencies_ms"]),
+             "p99_ratio_resident_ci95": paired_bootstrap_p99_ratio(hp_res["latencies_ms"], hp_solo["latencies_ms"]),
+             "timed_s": hp_res["measure_end_time"] - hp_res["measure_start_time"],
+             "launches": rep["resident"]["scheduler"].get("own_launches", 0),
+             "sched": rep["resident"]["scheduler"]["stats"], "wall": wall, "cores": mine}
     if world > 1:
         gathered = [None] * world
         dist.all_gather_object(gathered, local)
     else:
         gathered = [local]
     if rank != 0:
+        if not args.keep and not os.environ.get("ORION_BENCH_DIR"):
+            shutil.rmtree(base_dir, ignore_errors=True)
         return 0
 
-    roof = kernel_roofline(batch=32, iters=5, warm=3)
     peaks = read_peaks()
-    base = cpu_baseline()
+    roof = kernel_roofline(batch=32, iters=5, warm=3)
+    roof_hbm = hbm_roofline(peaks)
+    base = cpu_baseline(recorded_script=rep["script"])
     worst = max(gathered, key=lambda g: g["hp_p99"] / g["hp_solo_p99"])
     value = sum(g["be_sps"] for g in gathered)
     e2e_value = sum(g["be_sps_e2e"] for g in gathered)
-    step_time = max(g["coloc_time"] for g in gathered)
+    step_time = max(g["timed_s"] for g in gathered)
+    solo_sum = sum(g["be_solo_sps"] for g in gathered)
     line = {
-        "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
+        "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": steps, "warmup": warm_steps,
         "ms_per_step": step_time * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "configs[1]: HP ResNet-50 inference fp32 b4 Poisson %d req/s x %d requests + BE ResNet-50 training "
-                               "b32 SGD(0.9, 0.1), one pair per GPU" % (HP_RPS, steps),
-                   "step": "one HP request (the BE client trains concurrently until the HP client is done)",
-                   "protocol_warmup_requests": 10, "algo": "orion", "dur_threshold_ns": rep["depth"],
-                   "be_sm_quota": be_quota or None, "profile_rows": rep["profile_rows"],
-                   "l2": "roofline replay rotates through >126 MB between iterations; co-location inputs exceed L2 per BE step"},
-        "hp": {"p99_ms": worst["hp_p99"], "p50_ms": worst["hp_p50"], "solo_p99_ms": worst["hp_solo_p99"],
-               "solo_p50_ms": worst["hp_solo_p50"], "p99_x_solo": worst["hp_p99"] / worst["hp_solo_p99"],
-               "p99_ms_resident": worst["hp_p99_resident"], "target_x_solo": 1.15},
-        "be": {"samples_per_s": value, "solo_samples_per_s": sum(g["be_solo_sps"] for g in gathered),
-               "fraction_of_solo": value / max(1e-9, sum(g["be_solo_sps"] for g in gathered)), "target_fraction": 0.70},
-        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": 4 * 3 * 224 * 224 * 4,
-                "d2h_bytes_per_step": 4 * 1000 * 4,
+        "config": {"workload": "configs[1]: HP ResNet-50 inference fp32 b4 Poisson %d req/s + BE ResNet-50 training "
+                               "b32 SGD(0.9, 0.1), one pair per GPU" % HP_RPS,
+                   "step": "a block of %d HP requests (the BE client trains concurrently until the HP client is done)" % STEP_REQUESTS,
+                   "hp_requests_timed": steps * STEP_REQUESTS, "hp_requests_untimed": 10 + warm_steps * STEP_REQUESTS,
+                   "algo": "orion", "dur_threshold_ns": rep["depth"], "sm_quota_in_grants": os.environ.get("ORION_SM_QUOTA", "1") != "0",
+                   "be_green_context_sms": be_quota or None, "profile_rows": rep["profile_rows"],
+                   "l2": "roofline replays flush L2 (160 MB rewritten) between iterations; co-location inputs exceed L2 per BE step"},
+        "hp": {"requests": worst["hp_requests"], "p99_ms": worst["hp_p99"], "p50_ms": worst["hp_p50"],
+               "solo_p99_ms": worst["hp_solo_p99"], "solo_p50_ms": worst["hp_solo_p50"],
+               "p99_x_solo": worst["hp_p99"] / worst["hp_solo_p99"], "p99_x_solo_ci95": worst["p99_ratio_ci95"],
+               "p99_ms_resident": worst["hp_p99_resident"], "p99_x_solo_resident": worst["hp_p99_resident"] / worst["hp_solo_p99"],
+               "p99_x_solo_resident_ci95": worst["p99_ratio_resident_ci95"], "target_x_solo": 1.15},
+        "be": {"samples_per_s": value, "solo_samples_per_s": solo_sum, "fraction_of_solo": value / max(1e-9, solo_sum),
+               "fraction_of_solo_e2e": e2e_value / max(1e-9, solo_sum), "iterations_timed": sum(g["be_iterations_timed"] for g in gathered),
+               "target_fraction": 0.70},
+        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": STEP_REQUESTS * 4 * 3 * 224 * 224 * 4,
+                "d2h_bytes_per_step": STEP_REQUESTS * 4 * 1000 * 4,
                 "be_h2d_bytes_per_iteration": 32 * 3 * 224 * 224 * 4 + 32 * 8, "be_d2h_bytes_per_iteration": 4,
                 "hp_p99_x_solo": worst["hp_p99"] / worst["hp_solo_p99"]},
         "gpu_launches": int(sum(g["launches"] for g in gathered)),
@@ -308,11 +403,18 @@ def main():
                      "kernel": "igemm_fprop_kernel<float> (3xTF32, TMA-fed, A operand in TMEM), all 53 ResNet-50 convolutions at batch 32",
                      "avg_launch_us": roof["avg_launch_us"], "launches_timed": roof["launches"],
                      "note": "peak is the bf16 dense figure; fp32 runs three TF32 MMAs per product"},
+        "roofline_hbm": roof_hbm,
         "cpu_baseline": base,
         "clocks": clocks,
         "wall_s": wall,
     }
+    if world > 1:
+        line["ranks"] = [{"hp_p99_x_solo": g["hp_p99"] / g["hp_solo_p99"], "hp_p99_x_solo_ci95": g["p99_ratio_ci95"],
+                          "be_fraction_of_solo": g["be_sps"] / max(1e-9, g["be_solo_sps"]), "be_samples_per_s": g["be_sps"],
+                          "cores": g["cores"]} for g in gathered]
     print(json.dumps(line))
+    if not args.keep and not os.environ.get("ORION_BENCH_DIR"):
+        shutil.rmtree(base_dir, ignore_errors=True)
     return 0
 
 

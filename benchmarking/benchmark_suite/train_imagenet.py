@@ -100,12 +100,16 @@ def run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchs
     sleep_times = _sleep_times(rps, uniform, num_iters, input_file)
     readback = os.environ.get("ORION_READBACK", "1") == "1"
     out_dir = os.environ.get("ORION_OUT_DIR", ".")
+    # Requests left out of the latency statistics: the protocol's ten warm-up requests plus any further
+    # untimed ones the experiment asks for (ORION_EXTRA_WARMUP_REQUESTS).
+    skip = 10 + max(0, int(os.environ.get("ORION_EXTRA_WARMUP_REQUESTS", "0")))
 
     barriers[0].wait()   # the scheduler has run setup(): streams exist, this thread is registered
 
     stream_ptr = backend_lib.orion_capture_client_stream(tid)
     stream = torch.cuda.ExternalStream(stream_ptr) if stream_ptr else torch.cuda.current_stream()
     timings = []
+    end_times = []   # wall-clock time at which each request / iteration completed
     start = time.time()
     batch_idx = 0
     with torch.cuda.stream(stream):
@@ -132,7 +136,8 @@ def run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchs
                 backend_lib.block(batch_idx)
                 if readback and result is not None:
                     result = float(result.detach())
-                timings.append(time.time() - start_iter)
+                end_times.append(time.time())
+                timings.append(end_times[-1] - start_iter)
                 batch_idx += 1
                 if batch_idx == 1 or batch_idx == 10:
                     barriers[0].wait()
@@ -152,7 +157,8 @@ def run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchs
                     backend_lib.block(batch_idx)
                     if readback and result is not None:
                         result = result.cpu()   # a plain device-to-host copy: no extra kernel in the op stream
-                    timings.append(time.time() - next_startup)
+                    end_times.append(time.time())
+                    timings.append(end_times[-1] - next_startup)
                     if batch_idx >= 10 and open_loop:
                         next_startup += sleep_times[batch_idx]
                     else:
@@ -168,16 +174,21 @@ def run_client(tid, train, num_iters, rps, uniform, barriers, input_file, batchs
 
     barriers[0].wait()
     total_time = time.time() - start
-    measured = sorted(timings[10:])
+    measured = sorted(timings[skip:])
     data_out = {"throughput": (batch_idx - 10) / total_time if total_time > 0 else 0.0, "iterations": batch_idx,
                 "batchsize": batchsize, "total_time": total_time}
     if not train and measured:
-        data_out.update({"p50_latency": float(np.percentile(measured, 50)) * 1000,
+        # the measured window opens when the last untimed request completed
+        data_out.update({"measured_requests": len(measured), "measure_start_time": end_times[skip - 1],
+                         "measure_end_time": end_times[-1],
+                         "latencies_ms": [round(t * 1000, 4) for t in timings[skip:]],
+                         "p50_latency": float(np.percentile(measured, 50)) * 1000,
                          "p95_latency": float(np.percentile(measured, 95)) * 1000,
                          "p99_latency": float(np.percentile(measured, 99)) * 1000,
                          "mean_latency": float(np.mean(measured)) * 1000})
-    elif train and measured:
+    elif train and timings[10:]:
         data_out["samples_per_s"] = data_out["throughput"] * batchsize
+        data_out["iteration_end_times"] = end_times
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "client_%d.json" % tid), "w") as f:
         json.dump(data_out, f)

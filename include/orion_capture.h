@@ -7,7 +7,9 @@
  * intercept_cudnn.cpp, intercept_cublas.cpp, utils_interc.cpp).
  *
  * Interposed: cudaLaunchKernel, cudaLaunchKernelExC, cudaMemcpy, cudaMemcpyAsync,
- * cudaMemset, cudaMemsetAsync, cudaMalloc, cudaFree; cublasSgemm_v2,
+ * cudaMemset, cudaMemsetAsync, cudaMalloc, cudaFree, cudaMallocAsync, cudaFreeAsync,
+ * cudaMallocManaged (passed through), cudaGraphLaunch (refused with cudaErrorNotSupported
+ * when a scheduled client calls it); cublasSgemm_v2,
  * cublasSgemmStridedBatched, cublasGemmEx, cublasGemmStridedBatchedEx,
  * cublasLtMatmul; cudnnBackendExecute, cudnnConvolutionForward,
  * cudnnConvolutionBackwardData, cudnnConvolutionBackwardFilter,
@@ -40,6 +42,16 @@ void* orion_capture_client_stream(int idx);          /* cudaStream_t of client i
 int orion_capture_register_thread(int idx);          /* register the calling thread as a helper thread of client idx */
 unsigned long long orion_capture_count(int type);    /* scheduled calls of a record type (-1: passed-through calls) */
 unsigned long long orion_capture_seen(int type);     /* all intercepted calls of a record type */
+
+/* SM quota of grants.  The reference stores the SM need of the high-priority op it released
+ * (reference src/scheduler/scheduler_eval.cpp:317) and never reads it; here a best-effort grant carries
+ * "device SMs minus that need" as its quota, and a kernel whose library declared it elastic (any grid
+ * width gives the same result) is launched with at most quota x ctas_per_sm blocks. */
+int orion_capture_mark_elastic(const void* func, int ctas_per_sm);   /* func: the handle passed to cudaLaunchKernel */
+int orion_capture_quota_hint(void);                  /* quota the calling client would be granted now (0: whole device) */
+int orion_capture_last_quota(void);                  /* quota carried by the calling thread's latest grant */
+unsigned orion_capture_clamp_grid(const void* func, unsigned grid_x, int num_ctas);   /* grid width under a quota */
+unsigned long long orion_capture_clamped_launches(void);   /* launches cut to their quota so far */
 
 #ifdef __cplusplus
 }

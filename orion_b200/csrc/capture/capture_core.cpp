@@ -48,6 +48,7 @@ namespace orion_capture {
 static thread_local int tls_idx = -1;
 static thread_local int tls_epoch = -1;
 static thread_local int tls_tid = 0;
+static thread_local int tls_last_quota = 0;      // SM quota of the calling thread's latest grant
 static thread_local bool tls_in_gate = false;   // a call made while this thread is already inside a gate passes through
 
 static inline int my_tid() {
@@ -63,7 +64,8 @@ static void maybe_pin(int slot, int idx) {
     if (!sh.pin_threads || sh.affinity_set[slot].load(std::memory_order_relaxed)) return;
     cpu_set_t mask;
     CPU_ZERO(&mask);
-    CPU_SET(sh.core_offset + idx, &mask);
+    if (sh.n_cores > 0) CPU_SET(sh.core_list[(1 + idx) % sh.n_cores], &mask);
+    else CPU_SET(sh.core_offset + idx, &mask);
     if (sched_setaffinity(0, sizeof(mask), &mask) != 0) perror("orion: sched_setaffinity");
     sh.affinity_set[slot].store(1, std::memory_order_relaxed);
 }
@@ -94,6 +96,35 @@ int client_index_of_stream(void* stream) {
     for (int i = 0; i < sh.num_clients; i++)
         if (sh.client_stream[i] == stream) return i;
     return -1;
+}
+
+// Elastic kernels: a small open-addressing table of device-function pointers, written rarely
+// (once per kernel, the first time its library launches it) and read on every granted launch.
+static constexpr int kElasticSlots = 256;
+static std::atomic<uintptr_t> g_elastic_func[kElasticSlots];
+static std::atomic<int> g_elastic_factor[kElasticSlots];
+
+static inline unsigned elastic_hash(uintptr_t f) { return (unsigned)((f >> 4) * 2654435761u) % kElasticSlots; }
+
+static int elastic_factor_of(const void* func) {
+    const uintptr_t f = (uintptr_t)func;
+    unsigned h = elastic_hash(f);
+    for (int probe = 0; probe < kElasticSlots; probe++, h = (h + 1) % kElasticSlots) {
+        uintptr_t cur = g_elastic_func[h].load(std::memory_order_acquire);
+        if (cur == f) return g_elastic_factor[h].load(std::memory_order_acquire);
+        if (cur == 0) return 0;
+    }
+    return 0;
+}
+
+unsigned clamp_grid(const void* func, unsigned grid_x, int num_ctas) {
+    if (num_ctas <= 0) return grid_x;
+    const int factor = elastic_factor_of(func);
+    if (factor <= 0) return grid_x;
+    const unsigned long long cap = (unsigned long long)num_ctas * (unsigned)factor;
+    if (grid_x <= cap) return grid_x;
+    g_shared.clamped_launches.fetch_add(1, std::memory_order_relaxed);
+    return (unsigned)cap;
 }
 
 static inline int64_t mono_ms() {
@@ -128,6 +159,7 @@ bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
             g->seq = 0;
             g->stream = user_stream;
             g->event = nullptr;
+            g->num_ctas = 0;
             g->type = type;
             g->tag = tag;
             tls_in_gate = true;
@@ -183,6 +215,8 @@ bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
     g->type = type;
     g->tag = tag;
     g->event = self_granted ? nullptr : r.grant.event;
+    g->num_ctas = self_granted ? 0 : r.grant.num_ctas;
+    tls_last_quota = g->num_ctas;
     void* granted_stream = self_granted ? sh.client_stream[idx] : r.grant.stream;
     g->stream = is_default_stream(user_stream) ? granted_stream : user_stream;
     return true;
@@ -282,6 +316,45 @@ int orion_capture_register_thread(int idx) {
     }
     return -1;
 }
+
+// A kernel library declares `func` (the host-side handle its launches pass to cudaLaunchKernel) elastic:
+// its result does not depend on gridDim.x, and it keeps `ctas_per_sm` CTAs resident per SM.  Under a grant
+// that carries an SM quota q the launch interposers cut its grid to q * ctas_per_sm CTAs.
+int orion_capture_mark_elastic(const void* func, int ctas_per_sm) {
+    if (!func || ctas_per_sm <= 0) return -1;
+    const uintptr_t f = (uintptr_t)func;
+    unsigned h = elastic_hash(f);
+    for (int probe = 0; probe < kElasticSlots; probe++, h = (h + 1) % kElasticSlots) {
+        uintptr_t cur = g_elastic_func[h].load(std::memory_order_acquire);
+        if (cur == f) {
+            g_elastic_factor[h].store(ctas_per_sm, std::memory_order_release);
+            return 0;
+        }
+        if (cur == 0) {
+            uintptr_t expect = 0;
+            if (g_elastic_func[h].compare_exchange_strong(expect, f, std::memory_order_acq_rel) || expect == f) {
+                g_elastic_factor[h].store(ctas_per_sm, std::memory_order_release);
+                return 0;
+            }
+        }
+    }
+    return -1;   // table full
+}
+
+// SM quota the scheduler would grant the calling client at this moment (0: whole device, or not a client).
+int orion_capture_quota_hint(void) {
+    int idx = client_index_of_thread();
+    if (idx < 0) return 0;
+    return g_shared.quota_hint[idx].load(std::memory_order_relaxed);
+}
+
+// SM quota carried by the latest grant of the calling thread (0: none).
+int orion_capture_last_quota(void) { return tls_last_quota; }
+
+// What the launch interposers would make of a grid of `grid_x` blocks of `func` under an SM quota of `num_ctas`.
+unsigned orion_capture_clamp_grid(const void* func, unsigned grid_x, int num_ctas) { return clamp_grid(func, grid_x, num_ctas); }
+
+unsigned long long orion_capture_clamped_launches(void) { return g_shared.clamped_launches.load(); }
 
 unsigned long long orion_capture_count(int type) {
     if (type < 0) return g_shared.passthrough.load();

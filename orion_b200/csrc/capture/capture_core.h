@@ -19,6 +19,7 @@ struct Gate {
     uint64_t seq;
     void* stream;   // stream to launch on (the caller's, or the client's scheduler stream)
     void* event;    // event to record behind the op
+    int num_ctas;   // SM quota of the grant (0 = no limit)
     int type;
     uint64_t tag;
     const LaunchInfo* launch;
@@ -30,6 +31,11 @@ struct Gate {
 bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag);
 // Records the granted event on the granted stream and retires the record.
 void gate_end(Gate* g);
+
+// Grid width to launch `func` with under a grant of `num_ctas` SMs: kernels registered as elastic (their
+// blocks walk the work with a gridDim.x stride, so any grid width gives the same result) are cut to
+// num_ctas x their CTAs-per-SM factor; every other kernel keeps its grid.
+unsigned clamp_grid(const void* func, unsigned grid_x, int num_ctas);
 
 int client_index_of_thread();
 int client_index_of_stream(void* stream);

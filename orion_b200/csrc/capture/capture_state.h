@@ -10,8 +10,10 @@
 // Protocol for one captured call (the client thread runs steps 1,3,4; the
 // scheduler thread runs step 2):
 //   1. push:    ring[tail % CAP] = {type,...}; tail.store(tail+1, release)
-//   2. grant:   the policy picks the head; the scheduler writes the stream and the
-//               event to record behind the op and publishes granted = head+1
+//   2. grant:   the policy picks the head; the scheduler writes the stream, the
+//               event to record behind the op and the SM quota of the grant (the
+//               number of CTAs a persistent kernel may occupy) and publishes
+//               granted = head+1
 //   3. launch:  the client thread, which has been spinning on `granted`, performs
 //               the real CUDA/cuBLAS/cuDNN call itself on the granted stream and
 //               records the granted event — so launch cost is paid on the client's
@@ -32,7 +34,7 @@
 
 #include <atomic>
 
-#define ORION_CAPTURE_ABI_VERSION 1
+#define ORION_CAPTURE_ABI_VERSION 2
 #define ORION_MAX_CLIENTS 16
 #define ORION_RING_CAP 64
 #define ORION_MAX_THREADS (2 * ORION_MAX_CLIENTS + 1)
@@ -46,6 +48,8 @@ struct orion_record {
 struct alignas(64) orion_grant {
     void* stream;          // cudaStream_t to launch on
     void* event;           // cudaEvent_t to record behind the op (may be null)
+    int num_ctas;          // SM quota of this grant: a kernel whose grid is elastic (see orion_capture_mark_elastic)
+                           // is launched with at most this many CTAs per resident-CTA slot; 0 = no limit
 };
 
 struct alignas(64) orion_ring {
@@ -77,6 +81,13 @@ struct orion_shared {
     std::atomic<uint8_t> affinity_set[ORION_MAX_THREADS];
     int pin_threads;                         // 0: leave affinity alone
     int core_offset;                         // first core for client 0 (reference: 1, or 4 with two clients)
+    int n_cores;                             // > 0: pin inside this list instead (the process's own affinity mask, so
+    int core_list[256];                      //      that replicas with disjoint masks stay disjoint): scheduler thread
+                                             //      on core_list[0], client i on core_list[(1 + i) % n_cores]
+    // SM quota the scheduler would grant client i right now (a hint for planning a launch before it is queued;
+    // the quota that binds is the one in the grant); 0 = the whole device
+    std::atomic<int> quota_hint[ORION_MAX_CLIENTS];
+    std::atomic<uint64_t> clamped_launches;  // kernel launches whose grid was cut to the granted quota
     // statistics
     std::atomic<uint64_t> captured[32];      // per record type
     std::atomic<uint64_t> passthrough;       // intercepted calls from unknown threads

@@ -73,6 +73,7 @@ cudaError_t cudaLaunchKernel(const void* func, dim3 gridDim, dim3 blockDim, void
     Gate g;
     if (!gate_begin(&g, ORION_KERNEL_RECORD, stream, (uint64_t)(uintptr_t)func))
         return real_cudaLaunchKernel(func, gridDim, blockDim, args, sharedMem, stream);
+    gridDim.x = clamp_grid(func, gridDim.x, g.num_ctas);   // persistent kernels take the SM quota of the grant
     LaunchInfo li{func, {gridDim.x, gridDim.y, gridDim.z}, {blockDim.x, blockDim.y, blockDim.z}, sharedMem};
     g.launch = &li;
     cudaError_t e = real_cudaLaunchKernel(func, gridDim, blockDim, args, sharedMem, (cudaStream_t)g.stream);
@@ -88,6 +89,7 @@ cudaError_t cudaLaunchKernelExC(const cudaLaunchConfig_t* config, const void* fu
         return real_cudaLaunchKernelExC(config, func, args);
     cudaLaunchConfig_t cfg = *config;
     cfg.stream = (cudaStream_t)g.stream;
+    cfg.gridDim.x = clamp_grid(func, cfg.gridDim.x, g.num_ctas);
     LaunchInfo li{func, {cfg.gridDim.x, cfg.gridDim.y, cfg.gridDim.z}, {cfg.blockDim.x, cfg.blockDim.y, cfg.blockDim.z},
                   cfg.dynamicSmemBytes};
     g.launch = &li;
@@ -163,6 +165,50 @@ cudaError_t cudaFree(void* devPtr) {
     cudaError_t e = real_cudaFree(devPtr);
     gate_end(&g);
     return e;
+}
+
+// Stream-ordered allocation (torch's cudaMallocAsync allocator backend): queued as the MALLOC / FREE records
+// the reference uses for cudaMalloc / cudaFree (intercept_temp.cpp:145-192, 368-415) and run on the granted stream.
+static cudaError_t (*real_cudaMallocAsync)(void**, size_t, cudaStream_t);
+cudaError_t cudaMallocAsync(void** devPtr, size_t size, cudaStream_t stream) {
+    REAL(cudaMallocAsync);
+    Gate g;
+    if (!gate_begin(&g, ORION_MALLOC_RECORD, stream, 0)) return real_cudaMallocAsync(devPtr, size, stream);
+    cudaError_t e = real_cudaMallocAsync(devPtr, size, (cudaStream_t)g.stream);
+    gate_end(&g);
+    return e;
+}
+
+static cudaError_t (*real_cudaFreeAsync)(void*, cudaStream_t);
+cudaError_t cudaFreeAsync(void* devPtr, cudaStream_t stream) {
+    REAL(cudaFreeAsync);
+    Gate g;
+    if (!gate_begin(&g, ORION_FREE_RECORD, stream, 0)) return real_cudaFreeAsync(devPtr, stream);
+    cudaError_t e = real_cudaFreeAsync(devPtr, (cudaStream_t)g.stream);
+    gate_end(&g);
+    return e;
+}
+
+// Managed allocations pass straight through, as in the reference (intercept_temp.cpp:194-206).
+static cudaError_t (*real_cudaMallocManaged)(void**, size_t, unsigned int);
+cudaError_t cudaMallocManaged(void** devPtr, size_t size, unsigned int flags) {
+    return REAL(cudaMallocManaged)(devPtr, size, flags);
+}
+
+// A captured CUDA graph would put a whole iteration on the device behind one call, past every admission rule,
+// with kernels the profile has no rows for.  A scheduled client that launches one is stopped with a message
+// instead of slipping past the scheduler silently; unscheduled threads launch graphs as usual.
+static cudaError_t (*real_cudaGraphLaunch)(cudaGraphExec_t, cudaStream_t);
+cudaError_t cudaGraphLaunch(cudaGraphExec_t graphExec, cudaStream_t stream) {
+    REAL(cudaGraphLaunch);
+    int idx = client_index_of_thread();
+    if (idx < 0) idx = client_index_of_stream((void*)stream);
+    if (idx >= 0) {
+        fprintf(stderr, "orion: client %d called cudaGraphLaunch; captured graphs cannot be scheduled op by op "
+                        "(run the client without CUDA graphs)\n", idx);
+        return cudaErrorNotSupported;
+    }
+    return real_cudaGraphLaunch(graphExec, stream);
 }
 
 // ------------------------------------------------------------------ cuBLAS

@@ -10,12 +10,21 @@
 //                 residency comes from the occupancy API instead of V100 tables;
 //                 library calls whose launch shape is not visible get the device's
 //                 SM count;
-//   * Duration  = device time of the op in ns, measured with an event pair;
-//   * Profile   = 1 compute-bound / 0 memory-bound / -1 unknown
-//                 (roofline_analysis.py:51-71 decides this from ncu counters; here it is
-//                 decided from what the op is: GEMM / convolution calls and the orion
-//                 implicit-GEMM kernels are compute-bound; batch-norm, elementwise,
-//                 pooling, reduction and copy kernels are memory-bound);
+//   * Duration  = device time of the op in ns, from an event pair recorded around the op on its
+//                 stream.  The pairs of one iteration are read when the iteration ends (block(it)),
+//                 so the stream is never drained between two ops: while the device has work queued
+//                 the pair brackets the kernel alone; when the host is the slower side (small batches)
+//                 it also contains the idle gap until the launch arrives, as a timeline view would
+//                 show for that op.  The cost of an empty pair, measured once, is subtracted;
+//   * Profile   = 1 compute-bound / 0 memory-bound / -1 unknown.  The reference decides this from
+//                 ncu counters: arithmetic intensity against `ai_threshold`, else >= 60 % of the
+//                 compute or DRAM throughput (roofline_analysis.py:51-71).  The orion kernels
+//                 announce their class themselves (orion_capture_annotate): the launcher knows the
+//                 algorithmic FLOP and bytes of the problem and compares their ratio with the
+//                 device's measured peak FLOP/s over measured HBM bytes/s.  Only foreign kernels
+//                 (stock ATen / cuDNN / cuBLAS launches) are classified by what the op is: GEMM /
+//                 convolution calls are compute-bound; batch-norm, elementwise, pooling, reduction
+//                 and copy kernels are memory-bound;
 //   * memory ops are not rows (generate_file.py:50-52); Memory_footprint is 0.
 //
 // Use: ORION_PROFILE_OUT=<file> [ORION_PROFILE_OUT0=<file for iteration 0>]
@@ -41,7 +50,15 @@ struct Row {
     int profile;
     int sm;
     float ns;
+    int pair;       // index of the event pair that brackets the op
 };
+
+struct Annotation {
+    bool set = false;
+    int op_class = -1;
+    double flop = 0, bytes = 0;
+};
+thread_local Annotation tls_note;
 
 struct Recorder {
     bool enabled = false;
@@ -59,7 +76,9 @@ struct Recorder {
     cudaError_t (*func_name)(const char**, const void*) = nullptr;
     cudaError_t (*occupancy)(int*, const void*, int, size_t, unsigned) = nullptr;
     cudaError_t (*dev_attr)(int*, cudaDeviceAttr, int) = nullptr;
-    cudaEvent_t ev_a = nullptr, ev_b = nullptr;
+    std::vector<cudaEvent_t> ev_a, ev_b;   // event pairs, reused by every iteration
+    int pairs_used = 0;
+    float empty_pair_ms = 0.f;
     bool bound = false;
 } R;
 
@@ -84,8 +103,22 @@ bool bind() {
         R.event_create = nullptr;
         return false;
     }
-    R.event_create(&R.ev_a);
-    R.event_create(&R.ev_b);
+    {   // device time of an empty pair (two events back to back on an idle stream)
+        cudaEvent_t a = nullptr, b = nullptr;
+        R.event_create(&a);
+        R.event_create(&b);
+        float best = 1e9f;
+        for (int k = 0; k < 8 && a && b; k++) {
+            R.event_record(a, nullptr);
+            R.event_record(b, nullptr);
+            R.event_sync(b);
+            float ms = 0.f;
+            if (R.event_elapsed(&ms, a, b) == cudaSuccess && ms < best) best = ms;
+        }
+        R.empty_pair_ms = best < 1e8f ? best : 0.f;
+        R.ev_a.push_back(a);
+        R.ev_b.push_back(b);
+    }
     if (R.dev_attr) R.dev_attr(&R.sm_count, cudaDevAttrMultiProcessorCount, 0);
     if (R.sm_count <= 0) R.sm_count = 148;
     return true;
@@ -153,17 +186,22 @@ void profile_begin(Gate* g) {
         R.mu.unlock();
         return;
     }
-    g->prof_start = R.ev_a;
-    R.event_record(R.ev_a, (cudaStream_t)g->stream);
+    if (R.pairs_used == (int)R.ev_a.size()) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        R.event_create(&a);
+        R.event_create(&b);
+        R.ev_a.push_back(a);
+        R.ev_b.push_back(b);
+    }
+    g->prof_start = R.ev_a[R.pairs_used];
+    R.event_record(R.ev_a[R.pairs_used], (cudaStream_t)g->stream);
 }
 
 void profile_end(Gate* g) {
     if (!g->prof_start) return;
-    R.event_record(R.ev_b, (cudaStream_t)g->stream);
-    R.event_sync(R.ev_b);
-    float ms = 0.f;
-    R.event_elapsed(&ms, R.ev_a, R.ev_b);
+    R.event_record(R.ev_b[R.pairs_used], (cudaStream_t)g->stream);
     Row row;
+    row.pair = R.pairs_used++;
     row.name = type_name(g->type);
     row.sm = R.sm_count;
     if (g->launch) {
@@ -184,15 +222,30 @@ void profile_end(Gate* g) {
         else
             row.sm = (int)blocks;
     }
-    row.profile = classify(g->type, row.name);
-    row.ns = ms * 1e6f;
+    if (tls_note.set) row.profile = tls_note.op_class;   // an orion kernel: its launcher announced the class
+    else row.profile = classify(g->type, row.name);
+    tls_note.set = false;
+    row.ns = 0.f;
     R.rows.push_back(row);
     R.mu.unlock();
+}
+
+// Reads the event pairs of the iteration that just ended.
+static void resolve_durations() {
+    for (Row& r : R.rows) {
+        float ms = 0.f;
+        if (R.event_sync(R.ev_b[r.pair]) == cudaSuccess && R.event_elapsed(&ms, R.ev_a[r.pair], R.ev_b[r.pair]) == cudaSuccess) {
+            ms -= R.empty_pair_ms;
+            r.ns = ms > 0.0005f ? ms * 1e6f : 500.f;   // never below half a microsecond
+        }
+    }
+    R.pairs_used = 0;
 }
 
 void profile_mark_iteration(int it) {
     if (!R.enabled) return;
     std::lock_guard<std::mutex> lk(R.mu);
+    if (R.bound && R.event_create) resolve_durations();
     if (it == 0) write_rows(R.out0);
     if (it == R.steady_iter) write_rows(R.out);
     R.rows.clear();
@@ -200,3 +253,13 @@ void profile_mark_iteration(int it) {
 }
 
 }  // namespace orion_capture
+
+// A kernel library announces the class of the launch it is about to make from the calling thread:
+// op_class 1 compute-bound, 0 memory-bound, -1 unknown; flop / bytes are the algorithmic work of the problem.
+extern "C" void orion_capture_annotate(int op_class, double flop, double bytes) {
+    if (!R.enabled) return;
+    tls_note.set = true;
+    tls_note.op_class = op_class;
+    tls_note.flop = flop;
+    tls_note.bytes = bytes;
+}

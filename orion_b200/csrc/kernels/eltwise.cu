@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 #include <float.h>
 #include <stdint.h>
+#include "elastic.h"
 
 namespace ob200 {
 
@@ -210,9 +211,11 @@ extern "C" int ob200_bn_inference_f32(const float* x, float* y, const float* gam
         int need = 1;   // smallest grid multiple that makes grid * ELT_THREADS a multiple of the channel-quad count
         while (((long long)need * ELT_THREADS) % (C / 4) != 0 && need < 64) need++;
         if (need > 1 && need < 64 && grid >= need) grid -= grid % need;
+        OB200_ELASTIC_HBM(bn_inference_f32_kernel, ELT_CTAS_PER_SM);
         bn_inference_f32_kernel<<<grid, ELT_THREADS, 0, s>>>((const float4*)x, (float4*)y, gamma, beta, mean, var,
                                                                               eps, n4, C / 4, relu);
     } else {
+        OB200_HBM_BOUND();
         bn_inference_f32_scalar_kernel<<<elt_grid(n_elems, num_ctas), ELT_THREADS, 0, s>>>(x, y, gamma, beta, mean, var, eps,
                                                                                           n_elems, C, relu);
     }
@@ -226,10 +229,14 @@ extern "C" int ob200_binary_f32(const float* a, const float* b, float* y, long l
     cudaStream_t s = (cudaStream_t)stream;
     const bool aligned = ((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) % 16 == 0;
     long long n4 = aligned ? n_elems / 4 : 0;
-    if (n4 > 0)
+    if (n4 > 0) {
+        OB200_ELASTIC_HBM(binary_f32_kernel, ELT_CTAS_PER_SM);
         binary_f32_kernel<<<elt_grid(n4, num_ctas), ELT_THREADS, 0, s>>>((const float4*)a, (const float4*)b, (float4*)y, n4, mode);
-    if (n4 * 4 < n_elems)
+    }
+    if (n4 * 4 < n_elems) {
+        OB200_HBM_BOUND();
         binary_f32_tail_kernel<<<elt_grid(n_elems - n4 * 4, num_ctas), ELT_THREADS, 0, s>>>(a, b, y, n4 * 4, n_elems, mode);
+    }
     return (int)cudaGetLastError();
 }
 
@@ -240,10 +247,12 @@ extern "C" int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, i
     const int P = (H + 2 * pad - k) / stride + 1, Q = (W + 2 * pad - k) / stride + 1;
     if (k == 3 && stride == 2) {
         const long long total4 = (long long)Nb * P * ((Q + 3) / 4) * (C / 4);
+        OB200_ELASTIC_HBM(maxpool3x3s2_nhwc_f32_kernel, ELT_CTAS_PER_SM);
         maxpool3x3s2_nhwc_f32_kernel<<<elt_grid(total4, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, H, W, C, P, Q, pad);
         return (int)cudaGetLastError();
     }
     long long total = (long long)Nb * P * Q * (C / 4);
+    OB200_ELASTIC_HBM(maxpool_nhwc_f32_kernel, ELT_CTAS_PER_SM);
     maxpool_nhwc_f32_kernel<<<elt_grid(total, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, H, W, C, P, Q, k, stride,
                                                                                                pad);
     return (int)cudaGetLastError();
@@ -252,6 +261,7 @@ extern "C" int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, i
 extern "C" int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream) {
     if (Nb <= 0) return 0;
     if (HW <= 0 || C <= 0 || num_ctas <= 0) return -1;
+    OB200_ELASTIC_HBM(avgpool_nhwc_f32_kernel, ELT_CTAS_PER_SM);
     avgpool_nhwc_f32_kernel<<<elt_grid((long long)Nb * C, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, HW, C);
     return (int)cudaGetLastError();
 }
@@ -284,6 +294,7 @@ extern "C" int ob200_pad_channels(const void* src, void* dst, long long pixels, 
     if (pixels <= 0) return 0;
     if (C <= 0 || Cpad <= C || num_ctas <= 0 || (elem_bytes != 2 && elem_bytes != 4)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
+    OB200_HBM_BOUND();
     if (elem_bytes == 4 && C == 3 && Cpad == 4 && (uintptr_t)dst % 16 == 0)
         ob200::pad_channels_3to4_f32_kernel<<<elt_grid(pixels, num_ctas), ELT_THREADS, 0, s>>>((const float*)src, (float4*)dst, pixels);
     else if (elem_bytes == 4)
@@ -436,6 +447,8 @@ extern "C" int ob200_depthwise_conv2d_f32(const float* x, const float* w, float*
         const long long total4 = (long long)Nb * P * ((Q + 3) / 4) * (C / 4);
         long long want4 = (total4 + ELT_THREADS - 1) / ELT_THREADS, cap4 = (long long)num_ctas * 4;
         const int grid4 = (int)(want4 < cap4 ? want4 : cap4);
+        OB200_ELASTIC_HBM(ob200::depthwise3x3_nhwc_f32_kernel<1>, 4);
+        OB200_ELASTIC_HBM(ob200::depthwise3x3_nhwc_f32_kernel<2>, 4);
         if (stride_h == 1)
             ob200::depthwise3x3_nhwc_f32_kernel<1><<<grid4, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, P,
                                                                                                 Q, pad_h, pad_w, w_tap_major);
@@ -448,6 +461,7 @@ extern "C" int ob200_depthwise_conv2d_f32(const float* x, const float* w, float*
     // up to eight CTAs of 256 threads per granted SM: the kernel lives on loads in flight
     long long want = (total + ELT_THREADS - 1) / ELT_THREADS, cap = (long long)num_ctas * 8;
     const int grid = (int)(want < cap ? want : cap);
+    OB200_ELASTIC_HBM(ob200::depthwise_conv_nhwc_f32_kernel, 8);
     ob200::depthwise_conv_nhwc_f32_kernel<<<grid, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, R, S,
                                                                                          P, Q, stride_h, stride_w, pad_h, pad_w, dil_h,
                                                                                          dil_w, w_tap_major);

@@ -41,6 +41,7 @@
 #include <atomic>
 
 #include "igemm_params.h"
+#include "elastic.h"
 #include "sm100_primitives.cuh"
 
 namespace ob200 {
@@ -1144,6 +1145,8 @@ static cudaError_t launch_cfg(const IgemmParams& p, int num_ctas, cudaStream_t s
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
+    // Every role derives its share of the work from gridDim.x (WorkIter), in all three schedules.
+    OB200_ELASTIC((igemm_fprop_kernel<T, BN, PASSES, ATMEM>), 1);
     igemm_fprop_kernel<T, BN, PASSES, ATMEM><<<num_ctas, NTHREADS, C::SMEM_BYTES, stream>>>(p);
     return cudaGetLastError();
 }
@@ -1300,6 +1303,14 @@ extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_cta
     p.a_in_tmem = (p.dtype == 0 && p.mode == 0 && !a_tmem_off) ? 1 : 0;
     if (setup_tma(p, bn)) g_tma_launches.fetch_add(1, std::memory_order_relaxed);
     else if (p.require_tma || p.w_R > 0) return -4;   // tap subsets exist only on the TMA path
+    {   // class of this launch for the scheduler's profiles: arithmetic intensity of the problem against the device's
+        const double batch = p.batch > 1 ? p.batch : 1;
+        const double elem = p.dtype == 1 ? 2.0 : 4.0;
+        const double flop = 2.0 * p.M * (double)p.Kout * p.C * p.R * p.S * batch;
+        const double bytes = p.mode == 1 ? ((double)p.M * p.Kout + (double)p.Nb * p.H * p.W * p.C) * elem + (double)p.Kout * p.R * p.S * p.C * 4.0
+                                         : ((double)p.Nb * p.IH * p.IW * p.C + (double)p.Kout * p.R * p.S * p.C + (double)p.M * p.Kout) * elem * batch;
+        annotate_launch(flop >= ai_threshold(p.dtype) * bytes ? 1 : 0, flop, bytes);
+    }
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (p.dtype == 0) {
         if (p.a_in_tmem) return (int)(bn == 64 ? launch_cfg<float, 64, 3, true>(p, num_ctas, s) : launch_cfg<float, 128, 3, true>(p, num_ctas, s));

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include "elastic.h"
 
 namespace ob200 {
 
@@ -332,7 +333,11 @@ extern "C" int ob200_layernorm(const void* x, void* y, const float* gamma, const
     cudaStream_t s = (cudaStream_t)stream;
     const int grid = row_grid(rows, num_ctas);
     const int chunks = (D / (dtype == 1 ? 8 : 4) + 31) / 32;   // 16-byte chunks per lane
-#define OB200_LN(T, CH) layernorm_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, gamma, beta, mean_out, rstd_out, rows, D, eps)
+#define OB200_LN(T, CH)                                                                                                             \
+    do {                                                                                                                           \
+        OB200_ELASTIC_HBM((layernorm_regs_kernel<T, CH>), 8);                                                                          \
+        layernorm_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, gamma, beta, mean_out, rstd_out, rows, D, eps); \
+    } while (0)
     if (dtype == 0) {
         if (chunks <= 2) OB200_LN(float, 2);
         else if (chunks <= 4) OB200_LN(float, 4);
@@ -356,7 +361,11 @@ extern "C" int ob200_softmax(const void* x, void* y, long long rows, int D, floa
     cudaStream_t s = (cudaStream_t)stream;
     const int grid = row_grid(rows, num_ctas);
     const int chunks = (D / (dtype == 1 ? 8 : 4) + 31) / 32;
-#define OB200_SM(T, CH) softmax_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, rows, D, scale)
+#define OB200_SM(T, CH)                                                                        \
+    do {                                                                                       \
+        OB200_ELASTIC_HBM((softmax_regs_kernel<T, CH>), 8);                                        \
+        softmax_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, rows, D, scale); \
+    } while (0)
     if (dtype == 0) {
         if (chunks <= 2) OB200_SM(float, 2);
         else if (chunks <= 4) OB200_SM(float, 4);
@@ -381,6 +390,8 @@ extern "C" int ob200_bias_gelu(const void* x, void* y, const float* bias, long l
     long long want = (n_vec + ROW_THREADS - 1) / ROW_THREADS, cap = (long long)num_ctas * 6;
     const int grid = (int)(want < cap ? want : cap);
     cudaStream_t s = (cudaStream_t)stream;
+    OB200_ELASTIC_HBM(bias_gelu_kernel<float>, 6);
+    OB200_ELASTIC_HBM(bias_gelu_kernel<__nv_bfloat16>, 6);
     if (dtype == 0)
         bias_gelu_kernel<float><<<grid, ROW_THREADS, 0, s>>>((const float*)x, (float*)y, bias, n_vec, D);
     else
@@ -395,6 +406,7 @@ extern "C" int ob200_adamw_f32(float* p, const float* g, float* m, float* v, lon
     const float bc1 = 1.0f - powf(beta1, (float)step);
     const float bc2_sqrt = sqrtf(1.0f - powf(beta2, (float)step));
     long long want = (n + ROW_THREADS - 1) / ROW_THREADS, cap = (long long)num_ctas * 4;
+    OB200_ELASTIC_HBM(adamw_kernel, 4);
     adamw_kernel<<<(int)(want < cap ? want : cap), ROW_THREADS, 0, (cudaStream_t)stream>>>(p, g, m, v, n, lr, beta1, beta2, eps,
                                                                                           weight_decay, bc1, bc2_sqrt);
     return (int)cudaGetLastError();

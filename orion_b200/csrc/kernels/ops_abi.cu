@@ -23,7 +23,7 @@ constexpr int kMaxTilesSplit = 4096;                    // counters per stream
 constexpr size_t kScratchBytes = 32u << 20;             // split-K partial sums per stream
 
 std::mutex g_mu;
-std::unordered_map<uint64_t, Scratch> g_scratch;        // key: device << 48 ^ stream
+std::unordered_map<uint64_t, Scratch> g_scratch;        // key: device << 56 ^ stream
 std::unordered_map<int, int*> g_status;                 // per device
 
 long long* g_debug = nullptr;   // optional role-wait counters, see ob200_set_debug_buffer

@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include "elastic.h"
 
 namespace ob200 {
 
@@ -297,6 +298,7 @@ static cudaError_t launch_reduce(const float* a, const float* b, const float* me
     if (slabs > (rows + ry - 1) / ry) slabs = (rows + ry - 1) / ry;
     if (slabs < 1) slabs = 1;
     dim3 block(cq, ry);
+    OB200_HBM_BOUND();
     bn_reduce_kernel<<<(unsigned)(slabs * c_groups), block, (size_t)cq * ry * 8 * sizeof(float), s>>>(a, b, mean, invstd, out, rows,
                                                                                                         C, mode);
     return cudaGetLastError();
@@ -316,9 +318,11 @@ extern "C" int ob200_bn_train_forward_f32(const float* x, float* y, const float*
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e = launch_reduce(x, nullptr, nullptr, nullptr, sums, rows, C, 0, num_ctas, s);
     if (e != cudaSuccess) return (int)e;
+    OB200_HBM_BOUND();
     bn_stats_finish_kernel<<<(C + 127) / 128, 128, 0, s>>>(sums, save_mean, save_invstd, running_mean, running_var, rows, C, eps,
                                                            momentum);
     const long long n4 = rows * C / 4;
+    OB200_ELASTIC_HBM(bn_apply_kernel, 6);
     bn_apply_kernel<<<grid_for_channels(n4, num_ctas, 6, C / 4), TR_THREADS, 0, s>>>((const float4*)x, (float4*)y, gamma, beta, save_mean, save_invstd,
                                                                     n4, C / 4);
     return (int)cudaGetLastError();
@@ -335,6 +339,7 @@ extern "C" int ob200_bn_backward_f32(const float* dy, const float* x, float* dx,
     cudaError_t e = launch_reduce(dy, x, save_mean, save_invstd, sums, rows, C, 1, num_ctas, s);
     if (e != cudaSuccess) return (int)e;
     const long long n4 = rows * C / 4;
+    OB200_ELASTIC_HBM(bn_backward_apply_kernel, 6);
     bn_backward_apply_kernel<<<grid_for_channels(n4, num_ctas, 6, C / 4), TR_THREADS, 0, s>>>((const float4*)dy, (const float4*)x, (float4*)dx, gamma,
                                                                              save_mean, save_invstd, sums, dgamma, dbeta, n4, C / 4,
                                                                              rows);
@@ -347,6 +352,7 @@ extern "C" int ob200_relu_backward_f32(const float* dy, const float* y, float* d
     cudaStream_t s = (cudaStream_t)stream;
     const bool aligned = ((uintptr_t)dy | (uintptr_t)y | (uintptr_t)dx) % 16 == 0;
     const long long n4 = aligned ? n / 4 : 0;
+    OB200_ELASTIC_HBM(relu_backward_kernel, 4);
     if (n4 > 0) relu_backward_kernel<<<grid_for(n4, num_ctas, 4), TR_THREADS, 0, s>>>((const float4*)dy, (const float4*)y, (float4*)dx, n4);
     if (n4 * 4 < n) relu_backward_tail_kernel<<<grid_for(n - n4 * 4, num_ctas, 4), TR_THREADS, 0, s>>>(dy, y, dx, n4 * 4, n);
     return (int)cudaGetLastError();
@@ -356,6 +362,7 @@ extern "C" int ob200_relu_backward_f32(const float* dy, const float* y, float* d
 extern "C" int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream) {
     if (K <= 0 || RS <= 0 || C <= 0) return -1;
     dim3 grid((C + 31) / 32, (K + 31) / 32, RS);
+    OB200_HBM_BOUND();
     if (elem_bytes == 4)
         filter_transpose_kernel<float><<<grid, TR_THREADS, 0, (cudaStream_t)stream>>>((const float*)w, (float*)wt, K, RS, C);
     else if (elem_bytes == 2)
@@ -369,6 +376,7 @@ extern "C" int ob200_sgd_momentum_f32(float* p, const float* g, float* m, long l
                                       int first_step, int num_ctas, void* stream) {
     if (n <= 0) return 0;
     if (num_ctas <= 0) return -1;
+    OB200_ELASTIC_HBM(sgd_momentum_kernel, 4);
     sgd_momentum_kernel<<<grid_for(n, num_ctas, 4), TR_THREADS, 0, (cudaStream_t)stream>>>(p, g, m, n, lr, mu, wd, nesterov, first_step);
     return (int)cudaGetLastError();
 }

@@ -23,6 +23,9 @@
 //   void    iter_done(int client, int iter)   request `iter` complete: publish and unlock
 //   void    stop(int client, bool locked)     ask a best-effort client to stop
 //   bool    stop_ack(int client)        client acknowledged the stop
+//   void    poll_end(bool progressed)   end of one pass of the loop; `progressed` = an op was released or an
+//                                       iteration closed in it.  A hook for the live scheduler (publishing the SM
+//                                       quota, easing off the core when nothing moves); replay environments ignore it.
 //   bool    client_blocked(int client, int iter)
 //                                       live runs only: the client already waits for request
 //                                       `iter` to complete and has nothing queued.  If that
@@ -87,7 +90,14 @@ public:
     std::vector<std::vector<char>> starts_set;
     std::vector<std::vector<float>> client_durations;   // ms per finished request
     int penalty = 0;                            // reef; survives across phases
-    int error = 0;                              // 1 = unsupported record type seen
+    int error = 0;                              // 1 = unsupported record type seen, 2 = more compute ops in one
+                                                // iteration than there are events per client
+    int max_events = INT_MAX;                   // events per client list (the reference creates 30000 and never checks)
+    uint64_t released = 0;                      // ops handed to Env::submit so far
+    int hp_sm_need = 0;                         // SM need of the high-priority op released last: what the reference
+                                                // stores in cur_sms[hp] (scheduler_eval.cpp:317) and never reads.  No
+                                                // decision depends on it; the live scheduler sizes the SM quota of
+                                                // best-effort grants with it.
     PolicyStats stats;
 
     void init(int n, int* kernels, int* iters) {
@@ -123,7 +133,12 @@ private:
             return;
         }
         int slot = event_ids[evid];   // the event pointer is taken before the increment
+        if (slot >= max_events) {
+            error = 2;
+            return;
+        }
         env.submit(idx, type, stream, evid, slot);
+        released++;
         if (!orion_is_memop(type)) {
             event_ids[evid] += 1;
             seen[idx] += 1;
@@ -236,6 +251,8 @@ void PolicyCore::run_phase(Env& env, const PhaseArgs& a) {
     while (true) {
         stats.polls++;
         size = 0;
+        const uint64_t released_before = released;
+        bool closed_iter = false;
         for (int i = 0; i < n; i++) {
             heads[i] = -1;
             if (seen[i] == num_kernels[i]) continue;
@@ -267,6 +284,7 @@ void PolicyCore::run_phase(Env& env, const PhaseArgs& a) {
             if (heads[hp] >= 0) {
                 const OpInfo& op1 = op_info[hp][seen[hp]];
                 int prof = op1.profile;
+                hp_sm_need = op1.sm_used;
                 submit(env, heads[hp], hp, hp, hp);
                 profiles[hp] = prof;
                 stats.hp_submits++;
@@ -337,6 +355,7 @@ void PolicyCore::run_phase(Env& env, const PhaseArgs& a) {
                     if (!env.query(evl, event_ids[evl] - 1)) ready = false;
                 }
                 if (ready) {
+                    closed_iter = true;
                     seen[i] = 0;
                     if (seq) event_ids[0] = 0;
                     event_ids[i] = 0;
@@ -374,6 +393,7 @@ void PolicyCore::run_phase(Env& env, const PhaseArgs& a) {
             }
         }
         if (finished == n) break;
+        env.poll_end(closed_iter || released != released_before);
     }
 }
 

@@ -169,6 +169,7 @@ public:
     }
     bool stop_ack(int i) const { return clients[i].stop_ack; }
     bool client_blocked(int, int) const { return false; }
+    void poll_end(bool) {}
 
 private:
     const std::vector<ScriptOp>& seq_of(const Client& c) const {

@@ -21,6 +21,7 @@
 //     for replay through orion_replay and through the reference scheduler.
 #include <dlfcn.h>
 #include <pthread.h>
+#include <sched.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -34,6 +35,13 @@
 #include "../capture/capture_state.h"
 #include "../policy/policy.hpp"
 #include "green_ctx.hpp"
+
+#if defined(__x86_64__)
+#include <immintrin.h>
+#define ORION_PAUSE() _mm_pause()
+#else
+#define ORION_PAUSE() ((void)0)
+#endif
 
 namespace {
 
@@ -107,6 +115,14 @@ struct LiveEnv {
     std::vector<std::vector<uint64_t>> ev_seq;          // grant sequence behind each event slot
     std::vector<std::vector<int>> ev_owner;             // client whose launch records the slot
     uint64_t join_timeouts = 0;
+    // SM quota of best-effort grants (execution side; no decision depends on it)
+    orion::PolicyCore* core = nullptr;
+    bool quota_on = false;
+    int quota_reserve = 0;    // SMs left free for the high-priority client while it has no request in flight
+    int quota_floor = 8;      // a best-effort grant never goes below this
+    int quota_gran = 8;       // SM-partition granularity of the device
+    uint64_t quota_grants = 0, quota_ctas_sum = 0;
+    uint32_t idle_polls = 0;
     // recording (arrival-script abstraction of the run)
     bool recording = false;
     std::vector<int64_t> last_pop_us;
@@ -122,6 +138,32 @@ struct LiveEnv {
         return r.recs[head % ORION_RING_CAP].type;
     }
     int64_t now_us() { return wall_us(); }
+    // SM quota a best-effort client is granted right now: the device's SMs minus the SM need of the
+    // high-priority op in flight (the value the reference stores at scheduler_eval.cpp:317 and never uses),
+    // or minus a fixed reserve while no high-priority request is in flight; rounded down to the partition
+    // granularity.  0 = no limit (the high-priority client, a single client, or the feature switched off).
+    int quota_for(int i) const {
+        if (!quota_on || n < 2 || i == n - 1 || !core) return 0;
+        const int hp = n - 1;
+        const int max_sms = core->max_sms;
+        const bool hp_in_flight = core->seen[hp] > 0;
+        int need = hp_in_flight ? core->hp_sm_need : quota_reserve;
+        if (need <= 0) return 0;
+        int q = (max_sms - need) / quota_gran * quota_gran;
+        if (q < quota_floor) q = quota_floor;
+        return q >= max_sms ? 0 : q;
+    }
+    void poll_end(bool progressed) {
+        if (quota_on)
+            for (int i = 0; i + 1 < n; i++) sh->quota_hint[i].store(quota_for(i), std::memory_order_relaxed);
+        // Nothing moved for a while: ease off the core in short bursts so that a client thread spinning
+        // on the sibling hardware thread gets the issue slots (a poll is then a fraction of a microsecond late).
+        if (progressed) {
+            idle_polls = 0;
+        } else if (++idle_polls > 64) {
+            for (int k = 0; k < 8; k++) ORION_PAUSE();
+        }
+    }
     void submit(int i, int type, int stream, int evl, int evs) {
         orion_ring& r = sh->rings[i];
         if (recording) {
@@ -133,6 +175,12 @@ struct LiveEnv {
         uint64_t head = r.granted.load(std::memory_order_acquire);
         r.grant.stream = streams[stream];
         r.grant.event = events[evl][evs];
+        const int q = orion_is_memop(type) ? 0 : quota_for(i);
+        r.grant.num_ctas = q;
+        if (q > 0) {
+            quota_grants++;
+            quota_ctas_sum += (uint64_t)q;
+        }
         ev_seq[evl][evs] = head + 1;
         ev_owner[evl][evs] = i;
         // Fails only if the client granted itself a memory operation in the instant
@@ -222,6 +270,17 @@ static orion_shared* find_capture(Scheduler* s) {
 
 static void write_recorded_script(Scheduler* s, const orion::PhaseArgs& a);
 
+// The policy indexes a client's profile with its op counter up to num_kernels - 1 (policy.hpp, as the
+// reference does at scheduler_eval.cpp:306,330): a profile with fewer rows than that, or none, would make
+// it decide on memory past the vector.  The reference has the same hole; here the run ends with a message.
+static void check_profile_rows(const char* where, int client, const char* file, int rows, int num_kernels) {
+    if (rows < 1 || num_kernels < 1 || num_kernels > rows) {
+        fprintf(stderr, "orion: %s: client %d announces %d kernels per iteration but its profile %s has %d rows\n", where, client,
+                num_kernels, file ? file : "(null)", rows);
+        abort();
+    }
+}
+
 extern "C" {
 
 Scheduler* sched_init() { return new Scheduler(); }
@@ -263,6 +322,7 @@ void setup_change(Scheduler* s, int client_id, char* file, int num_kernels) {
         fprintf(stderr, "%s\n", e.what());
         abort();   // the reference asserts on an unreadable profile
     }
+    check_profile_rows("setup_change", client_id, file, (int)s->core.op_info[client_id].size(), num_kernels);
     s->core.max_sms_clients[client_id] = orion::max_sm_used(s->core.op_info[client_id]);
     s->core.num_kernels[client_id] = num_kernels;   // written into the caller's array, like the reference
     s->profile_paths[client_id] = file;
@@ -306,6 +366,27 @@ void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files
     sh->pin_threads = pin ? atoi(pin) : 0;
     const char* off = getenv("ORION_CORE_OFFSET");
     sh->core_offset = off ? atoi(off) : (num_clients == 2 ? 4 : 1);   // reference offsets, utils_interc.cpp:37-41
+    // ORION_PIN_THREADS=2: pin inside the cores this process may run on, so that replicas started with
+    // disjoint affinity masks (one per GPU) never share a core: this scheduler thread takes the first core
+    // of the mask, client i the (1 + i)-th; other threads (autograd workers) float inside the mask.
+    sh->n_cores = 0;
+    if (sh->pin_threads == 2) {
+        cpu_set_t mask;
+        CPU_ZERO(&mask);
+        if (sched_getaffinity(0, sizeof(mask), &mask) == 0) {
+            for (int c = 0; c < CPU_SETSIZE && sh->n_cores < 256; c++)
+                if (CPU_ISSET(c, &mask)) sh->core_list[sh->n_cores++] = c;
+        }
+        if (sh->n_cores >= num_clients + 1) {
+            cpu_set_t one;
+            CPU_ZERO(&one);
+            CPU_SET(sh->core_list[0], &one);
+            if (sched_setaffinity(0, sizeof(one), &one) != 0) perror("orion: sched_setaffinity (scheduler thread)");
+        } else {
+            sh->n_cores = 0;      // too few cores to give every spinning thread its own: leave affinity alone
+            sh->pin_threads = 0;
+        }
+    }
 
     // 2. profiles
     orion::PolicyCore& core = s->core;
@@ -319,11 +400,13 @@ void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files
             fprintf(stderr, "%s\n", e.what());
             abort();
         }
+        check_profile_rows("setup", i, files[i], (int)core.op_info[i].size(), num_kernels[i]);
         core.max_sms_clients.push_back(orion::max_sm_used(core.op_info[i]));
         core.is_train.push_back(train[i]);
         s->profile_paths[i] = files[i];
     }
     core.init(num_clients, num_kernels, num_iters);   // both arrays are borrowed and kept
+    core.max_events = kEventsPerClient;
 
     // max_sms: the reference hard-codes 80 (V100); default to the device's SM count.
     int max_sms = 80;
@@ -363,6 +446,14 @@ void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files
     env.events.assign(num_clients, {});
     env.ev_seq.assign(num_clients, std::vector<uint64_t>(kEventsPerClient, 0));
     env.ev_owner.assign(num_clients, std::vector<int>(kEventsPerClient, -1));
+    env.core = &s->core;
+    {   // SM quota carried by best-effort grants; ORION_SM_QUOTA=0 switches it off
+        const char* q = getenv("ORION_SM_QUOTA");
+        env.quota_on = !(q && q[0] == '0') && num_clients > 1;
+        if (const char* e = getenv("ORION_HP_RESERVE_SMS")) env.quota_reserve = atoi(e);
+        if (const char* e = getenv("ORION_BE_MIN_SMS")) env.quota_floor = atoi(e) > 0 ? atoi(e) : 8;
+        for (int i = 0; i < ORION_MAX_CLIENTS; i++) sh->quota_hint[i].store(0);
+    }
     int lp = 0, hp = 0;
     if (!s->api.fake) s->api.prio_range(&lp, &hp);
     int be_quota = 0;
@@ -423,6 +514,11 @@ void* schedule(Scheduler* s, int num_clients, bool profile_mode, int iter, bool 
     s->core.run_phase(s->env, a);
     s->sh->polling.store(0, std::memory_order_release);
     s->phases_run++;
+    if (s->core.error == 2) {
+        fprintf(stderr, "orion: an iteration has more than %d compute ops, the number of events per client - ABORT\n",
+                kEventsPerClient);
+        abort();
+    }
     if (s->core.error) {
         fprintf(stderr, "UNSUPPORTED OPERATION - ABORT\n");   // utils_sched.cpp:514-516
         abort();
@@ -450,14 +546,17 @@ void orion_sched_shutdown(Scheduler* s) {
     if (s && s->sh) s->sh->active.store(0, std::memory_order_release);
 }
 
-// stats: [polls, hp_submits, be_submits, be_rejects, queries, join_timeouts, max_sms, green_be_sms, forced_iter_ends]
+// stats: [polls, hp_submits, be_submits, be_rejects, queries, join_timeouts, max_sms, green_be_sms, forced_iter_ends,
+//         quota_grants (best-effort grants that carried an SM quota), quota_ctas_sum (sum of those quotas),
+//         clamped_launches (kernel launches the capture library cut to their quota)]
 void orion_sched_stats(Scheduler* s, unsigned long long* out, int n) {
     if (!s || !out) return;
-    unsigned long long v[9] = {s->core.stats.polls,      s->core.stats.hp_submits, s->core.stats.be_submits,
-                               s->core.stats.be_rejects, s->core.stats.queries,    s->env.join_timeouts,
-                               (unsigned long long)s->core.max_sms, (unsigned long long)s->green.be_sms,
-                               s->core.stats.forced_iter_ends};
-    for (int i = 0; i < n && i < 9; i++) out[i] = v[i];
+    unsigned long long v[12] = {s->core.stats.polls,      s->core.stats.hp_submits, s->core.stats.be_submits,
+                                s->core.stats.be_rejects, s->core.stats.queries,    s->env.join_timeouts,
+                                (unsigned long long)s->core.max_sms, (unsigned long long)s->green.be_sms,
+                                s->core.stats.forced_iter_ends, s->env.quota_grants, s->env.quota_ctas_sum,
+                                s->sh ? s->sh->clamped_launches.load() : 0ull};
+    for (int i = 0; i < n && i < 12; i++) out[i] = v[i];
 }
 
 // Latency samples (ms) the scheduler measured for client `idx` (scheduler_eval.cpp:423-426).
@@ -498,6 +597,8 @@ static void write_recorded_script(Scheduler* s, const orion::PhaseArgs& a) {
             }
         }
         int n_iters = (int)iters.size();
+        if (const char* cap = getenv("ORION_RECORD_MAX_ITERS"))   // bound the length of the replay
+            if (atoi(cap) > 0 && n_iters > atoi(cap)) n_iters = atoi(cap);
         if (n_iters < 12) n_iters = 12;
         fprintf(f, "client %d\n  train %d num_iters %d think 0\n  profile %s %d\n", i, s->core.is_train[i] ? 1 : 0, n_iters,
                 s->profile_paths[i].c_str(), s->core.num_kernels[i]);

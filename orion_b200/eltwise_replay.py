@@ -68,28 +68,39 @@ def cases():
     return out
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--iters", type=int, default=5)
-    ap.add_argument("--warm", type=int, default=2)
-    a = ap.parse_args()
+def replay(iters=5, warm=2, only=None):
+    """Times every case (or those whose name starts with one of `only`); returns a list of
+    {"kernel", "algorithmic_bytes", "us", "GBps"}."""
     flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    out = []
     for name, nbytes, fn in cases():
+        if only is not None and not any(name.startswith(o) for o in only):
+            continue
         total = 0.0
-        for it in range(a.warm + a.iters):
+        for it in range(warm + iters):
             flush.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()
             e1.record()
             e1.synchronize()
-            if it >= a.warm:
+            if it >= warm:
                 total += e0.elapsed_time(e1)
-        us = total * 1e3 / a.iters
-        print(json.dumps({"kernel": name, "algorithmic_MB": round(nbytes / 1e6, 1), "us": round(us, 1),
-                          "GBps": round(nbytes / us / 1e3, 1)}), flush=True)
+        us = total * 1e3 / iters
+        out.append({"kernel": name, "algorithmic_bytes": nbytes, "us": us, "GBps": nbytes / us / 1e3})
     if K.read_status() != 0:
         raise RuntimeError("a kernel reported a timed-out wait")
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warm", type=int, default=2)
+    a = ap.parse_args()
+    for r in replay(a.iters, a.warm):
+        print(json.dumps({"kernel": r["kernel"], "algorithmic_MB": round(r["algorithmic_bytes"] / 1e6, 1), "us": round(r["us"], 1),
+                          "GBps": round(r["GBps"], 1)}), flush=True)
 
 
 if __name__ == "__main__":

@@ -124,6 +124,11 @@ def _one(v):
     return v[0] if isinstance(v, (tuple, list)) else v
 
 
+def _square(v):
+    """True if a kernel-size / stride / padding argument is one number or the same number twice."""
+    return not isinstance(v, (tuple, list)) or all(e == v[0] for e in v)
+
+
 def _act_of(node, mods):
     """0 if `node` is not an activation the epilogue can apply, else 1 (ReLU) / 2 (ReLU6)."""
     if node.op == "call_module":
@@ -170,8 +175,9 @@ def prepare_inference(model):
         if isinstance(m, nn.Conv2d) and (m.groups == 1 or depthwise) and m.padding_mode == "zeros" and isinstance(m.padding, tuple):
             bn_node, bn = None, None
             users = list(node.users)
-            if len(users) == 1 and users[0].op == "call_module" and isinstance(mods.get(users[0].target), nn.BatchNorm2d):
-                bn_node, bn = users[0], mods[users[0].target]
+            if len(users) == 1 and users[0].op == "call_module" and isinstance(mods.get(users[0].target), nn.BatchNorm2d) \
+                    and mods[users[0].target].running_mean is not None and mods[users[0].target].running_var is not None:
+                bn_node, bn = users[0], mods[users[0].target]   # a batch norm without running statistics stays unfused
             last = bn_node or node
             act, act_node, res, add_node = 0, None, None, None
             users = list(last.users)
@@ -197,7 +203,8 @@ def prepare_inference(model):
             for dead in (act_node, add_node, bn_node, node):
                 if dead is not None and len(dead.users) == 0:
                     g.erase_node(dead)
-        elif isinstance(m, nn.MaxPool2d) and not m.ceil_mode and _one(m.dilation) == 1 and not m.return_indices:
+        elif isinstance(m, nn.MaxPool2d) and not m.ceil_mode and _one(m.dilation) == 1 and not m.return_indices and \
+                _square(m.kernel_size) and _square(m.stride or m.kernel_size) and _square(m.padding) and _square(m.dilation):
             name = add_module(OrionMaxPool(_one(m.kernel_size), _one(m.stride or m.kernel_size), _one(m.padding)))
             with g.inserting_before(node):
                 new = g.call_module(name, node.args)

@@ -44,10 +44,10 @@ class PyScheduler:
         return self._sched_lib.orion_sched_client_stream(self._scheduler, idx)
 
     def stats(self):
-        out = (ctypes.c_ulonglong * 9)()
-        self._sched_lib.orion_sched_stats(self._scheduler, out, 9)
+        out = (ctypes.c_ulonglong * 12)()
+        self._sched_lib.orion_sched_stats(self._scheduler, out, 12)
         keys = ("polls", "hp_submits", "be_submits", "be_rejects", "queries", "join_timeouts", "max_sms", "green_be_sms",
-                "forced_iter_ends")
+                "forced_iter_ends", "quota_grants", "quota_ctas_sum", "clamped_launches")
         return dict(zip(keys, [int(v) for v in out]))
 
     def durations_ms(self, idx, cap=1 << 20):

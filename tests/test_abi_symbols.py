@@ -32,7 +32,8 @@ def test_reference_entry_points_are_present(built):
     cap = ctypes.CDLL(built["liborion_capture.so"])
     for name in ("block", "stop", "cudaLaunchKernel", "cudaMemcpyAsync", "cudaMalloc", "cublasSgemm_v2",
                  "cublasSgemmStridedBatched", "cudnnConvolutionForward", "cudnnBatchNormalizationForwardInference",
-                 "cudnnBackendExecute", "cublasGemmEx", "cublasLtMatmul", "cudaLaunchKernelExC"):
+                 "cudnnBackendExecute", "cublasGemmEx", "cublasLtMatmul", "cudaLaunchKernelExC", "cudaMallocAsync", "cudaFreeAsync",
+                 "cudaMallocManaged", "cudaGraphLaunch"):
         assert hasattr(cap, name), name
 
 

@@ -22,6 +22,7 @@ DRIVER = textwrap.dedent('''
     barriers = [threading.Barrier(N + 1)]
     done = [0] * N
     wrong = []
+    quotas = [set() for _ in range(N)]
     def client(i):
         c = cfg["clients"][i]
         barriers[0].wait()
@@ -30,6 +31,7 @@ DRIVER = textwrap.dedent('''
             for t in c["ops"]:
                 got = cap.orion_capture_op(t)
                 if got != i: wrong.append((i, got))
+                if t == 0: quotas[i].add(cap.orion_capture_last_quota())
             cap.block(it)
             for t in c.get("after", []):
                 cap.orion_capture_op(t)
@@ -49,15 +51,18 @@ DRIVER = textwrap.dedent('''
     for t in ths: t.join()
     st.join()
     print(json.dumps({"done": done, "wrong": wrong, "stats": ps.stats(), "secs": time.time() - t0,
-                      "hp_samples": len(ps.durations_ms(N - 1))}))
+                      "hp_samples": len(ps.durations_ms(N - 1)), "quotas": [sorted(q) for q in quotas]}))
 ''')
 
 
-def _run(cfg, env_extra=None, timeout=120):
+def _run(cfg, env_extra=None, timeout=120, expect_failure=False):
     env = dict(os.environ, ORION_FAKE_GPU="1", ORION_GATE_TIMEOUT_S="5")
     env.update(env_extra or {})
     out = subprocess.run([sys.executable, "-c", DRIVER % {"root": ROOT}, json.dumps(cfg)], capture_output=True, text=True,
                          timeout=timeout, env=env)
+    if expect_failure:
+        assert out.returncode != 0
+        return out.stderr
     assert out.returncode == 0, out.stderr[-3000:]
     return json.loads(out.stdout.strip().splitlines()[-1])
 
@@ -135,3 +140,61 @@ def test_recorded_run_replays_identically_through_policy_core_and_oracles(built,
                              timeout=300)
         assert out.returncode == 0, out.stderr
         assert hashlib.sha256(ref_log.read_bytes()).hexdigest() == hashlib.sha256(product).hexdigest()
+
+
+def test_more_kernels_announced_than_profile_rows_ends_the_run_with_a_message(built, tmp_path):
+    """The policy indexes the profile with the op counter; a profile shorter than num_kernels (or empty) would be read
+    past its end.  setup() refuses it."""
+    p = _profile(tmp_path, "p", [(1, 10, 1000)] * 3)
+    err = _run({"clients": [{"profile": p, "num_kernels": 5, "iters": 12, "train": False, "ops": [0] * 5}]}, expect_failure=True)
+    assert "announces 5 kernels" in err and "3 rows" in err
+    empty = _profile(tmp_path, "empty", [])
+    err = _run({"clients": [{"profile": empty, "num_kernels": 1, "iters": 12, "train": False, "ops": [0]}]}, expect_failure=True)
+    assert "0 rows" in err
+
+
+def test_more_compute_ops_than_events_in_one_iteration_aborts(built, tmp_path):
+    """30000 events exist per client (reference utils_sched.cpp:150); op 30001 of one iteration must not index past them."""
+    n = 30001
+    p = _profile(tmp_path, "big", [(1, 10, 1000)] * n)
+    err = _run({"clients": [{"profile": p, "num_kernels": n, "iters": 12, "train": False, "ops": [0] * n}]}, expect_failure=True,
+               timeout=300)
+    assert "events per client" in err
+
+
+def test_best_effort_grants_carry_the_sm_quota_left_by_the_high_priority_op(built, tmp_path):
+    """148 SMs; the high-priority ops need 60 and 20 SMs.  A best-effort kernel granted while a high-priority request is in
+    flight gets 148 - need rounded down to the partition granularity of 8 (88 or 128); with no request in flight it gets the
+    whole device minus the configured reserve (148 - 16 -> 128).  The high-priority client's grants carry no quota."""
+    be = _profile(tmp_path, "be", [(1, 40, 9000), (0, 200, 5000), (-1, 30, 3000)] * 10)
+    hp = _profile(tmp_path, "hp", [(1, 60, 8000), (0, 20, 2000)] * 6)
+    cfg = {"clients": [{"profile": be, "num_kernels": 30, "iters": 100000, "train": True, "ops": [1] + [0] * 30},
+                       {"profile": hp, "num_kernels": 12, "iters": 300, "train": False, "ops": [1] + [0] * 12}],
+           "depth": 20000}
+    r = _run(cfg, env_extra={"ORION_MAX_SMS": "148", "ORION_HP_RESERVE_SMS": "16"})
+    assert r["quotas"][1] == [0]
+    assert set(r["quotas"][0]) <= {0, 88, 128} and 128 in r["quotas"][0]
+    assert r["stats"]["quota_grants"] > 0 and r["stats"]["quota_ctas_sum"] >= 88 * r["stats"]["quota_grants"]
+    r = _run(cfg, env_extra={"ORION_MAX_SMS": "148", "ORION_SM_QUOTA": "0"})
+    assert r["quotas"] == [[0], [0]] and r["stats"]["quota_grants"] == 0
+
+
+def test_elastic_kernels_are_cut_to_the_quota_and_others_are_not(built):
+    cap = ctypes_lib(built["liborion_capture.so"])
+    k1, k2 = 0x7f0000001230, 0x7f0000004560
+    assert cap.orion_capture_mark_elastic(k1, 4) == 0
+    assert cap.orion_capture_clamp_grid(k1, 592, 88) == 352      # 88 SMs x 4 resident CTAs
+    assert cap.orion_capture_clamp_grid(k1, 100, 88) == 100      # already narrower
+    assert cap.orion_capture_clamp_grid(k1, 592, 0) == 592       # no quota
+    assert cap.orion_capture_clamp_grid(k2, 592, 88) == 592      # not declared elastic
+    assert cap.orion_capture_mark_elastic(k1, 1) == 0            # re-declaring changes the factor
+    assert cap.orion_capture_clamp_grid(k1, 148, 88) == 88
+
+
+def ctypes_lib(path):
+    import ctypes
+    lib = ctypes.CDLL(path)
+    lib.orion_capture_mark_elastic.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.orion_capture_clamp_grid.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_int]
+    lib.orion_capture_clamp_grid.restype = ctypes.c_uint
+    return lib
