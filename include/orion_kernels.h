@@ -28,8 +28,9 @@ int ob200_conv2d_fprop(const void* x, const void* w, void* y, const float* scale
                        int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
 
 /* Same with the tile width (bn: 64 or 128), the split-K factor and the scratch
- * passed by the caller: scratch = tiles*128*bn floats, counters = tiles ints, both
- * zero on entry (the kernel leaves them zero); unused when splits == 1. */
+ * passed by the caller: scratch = tiles*splits*128*bn floats (one partial tile per split, any
+ * contents), counters = tiles ints, zero on entry (the kernel leaves them zero); unused when
+ * splits == 1.  The partial tiles are added in split order, so the result is reproducible bit for bit. */
 int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, const float* scale, const float* shift, const void* residual,
                           int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S, int stride_h, int stride_w,
                           int pad_h, int pad_w, int dil_h, int dil_w, int bn, int splits, float* scratch, int* counters,
@@ -40,9 +41,9 @@ int ob200_conv2d_fprop_ex(const void* x, const void* w, void* y, const float* sc
  * framework hook where a cudaMalloc would re-enter the allocator, or an embedder that hands out all
  * device memory up front.  The split-K scratch is a fixed 8 MiB (+1 KiB of tile counters) array
  * compiled into the library (held by every GPU that loads it, until exit); the call performs no
- * cudaMalloc / cudaFree and uses no allocating library routine.  Limits: tiles*128*bn floats must fit
+ * cudaMalloc / cudaFree and uses no allocating library routine.  Limits: tiles*splits*128*bn floats must fit
  * in 2 Mi floats and tiles (ceil(M/128)*ceil(Kout/bn)) in 256, else the call returns -3 and launches
- * nothing.  All calls share the array: each call clears the part it uses on `stream` first, and calls
+ * nothing.  All calls share the array: each call clears the tile counters it uses on `stream` first, and calls
  * that overlap on the GPU without an ordering between their streams race on it.  The first call on a
  * device resolves the array's device address (not a stream operation): make it before any capture. */
 int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y, const float* scale, const float* shift,

@@ -11,11 +11,13 @@
 // Cost and limits:
 //   * the array (kScratchFloats floats + kCounterInts ints, 8 MiB + 1 KiB) is part of
 //     the module image, so every GPU that loads the library holds it until exit;
-//   * a problem whose split-K partial sums (tiles * 128 * bn floats) or tile count do
-//     not fit is rejected with OB200_ERR_STATIC_SCRATCH_TOO_SMALL (-3);
-//   * all calls share the one array.  It keeps whatever the previous call left, so the
-//     part a call uses is cleared on the call's stream before its kernel runs; two
-//     calls that overlap on the GPU (different streams, no ordering) race on it;
+//   * a problem whose split-K partial tiles (tiles * splits * 128 * bn floats) or tile
+//     count do not fit is rejected with OB200_ERR_STATIC_SCRATCH_TOO_SMALL (-3);
+//   * all calls share the one array.  It keeps whatever the previous call left: the
+//     partial tiles need no particular start value (every unit overwrites its own),
+//     the tile counters must start at zero and are cleared on the call's stream before
+//     its kernel runs; two calls that overlap on the GPU (different streams, no
+//     ordering) race on the array;
 //   * the first call on each device looks up the array's device address (a set-up step
 //     that is not a stream operation): make that first call before any stream capture.
 #include <cuda_runtime.h>
@@ -26,7 +28,7 @@
 
 namespace {
 
-constexpr size_t kScratchFloats = 2u * 1024 * 1024;   // 8 MiB of split-K partial sums
+constexpr size_t kScratchFloats = 2u * 1024 * 1024;   // 8 MiB of split-K partial tiles
 constexpr int kCounterInts = 256;                     // one arrival counter per output tile
 constexpr int kMaxDevices = 64;
 
@@ -97,7 +99,7 @@ extern "C" int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y,
     igemm_set_fprop(&p);
 
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
-    const unsigned long long need = (unsigned long long)tiles * 128ull * (unsigned long long)bn;
+    const unsigned long long need = (unsigned long long)tiles * (unsigned long long)splits * 128ull * (unsigned long long)bn;
     if (splits > 1 && (tiles > kCounterInts || need > kScratchFloats)) return -3;   // OB200_ERR_STATIC_SCRATCH_TOO_SMALL
 
     StaticScratch* sc = nullptr;
@@ -106,11 +108,11 @@ extern "C" int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y,
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     p.status = nullptr;   // the status word of the other entry points is heap-allocated; this path has none
     if (splits > 1) {
-        // The array still holds the previous call's leftovers: zero exactly the part this call reads.
-        cudaError_t e = cudaMemsetAsync(sc->partial, 0, (size_t)need * sizeof(float), s);
-        if (e == cudaSuccess) e = cudaMemsetAsync(sc->counters, 0, (size_t)tiles * sizeof(int), s);
+        // The array still holds the previous call's leftovers.  Every unit overwrites its own partial tile before
+        // anyone reads it, so only the arrival counters have to start at zero.
+        cudaError_t e = cudaMemsetAsync(sc->counters, 0, (size_t)tiles * sizeof(int), s);
         if (e != cudaSuccess) return (int)e;
-        p.scratch = sc->partial;
+        p.slabs = sc->partial;
         p.counters = sc->counters;
     }
     const long long units = tiles * splits;

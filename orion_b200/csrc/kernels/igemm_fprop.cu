@@ -25,10 +25,10 @@
 // kind::f16 MMA per k-step.
 //
 // Split-K: when `splits > 1` each work unit covers a contiguous range of k-blocks of
-// one tile and adds its partial tile into a zero-initialised fp32 scratch buffer
-// with red.global.add; the unit that arrives last on the tile's counter applies the
-// epilogue from the scratch sums.  (Accumulation order across splits is not fixed;
-// `splits = 1` is bit-reproducible.)
+// one tile and writes its partial tile to a slab of its own; the unit that arrives
+// last on the tile's counter adds the slabs in split order and applies the epilogue,
+// so the result does not depend on which unit finishes first (bit-reproducible for
+// a given schedule, like `splits = 1`).
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the status
 // word, releases TMEM and returns.
@@ -37,6 +37,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <atomic>
 
@@ -349,7 +350,10 @@ struct WorkIter {
     }
     __device__ __forceinline__ int cta_of(long long x) const { return (int)(((x + 1) * G + W - 1) / W) - 1; }
     // Slab holding CTA c's piece of `tile`: the first slab if c's range begins inside the tile, else the second.
-    __device__ __forceinline__ int slab_of(int c, int tile) const { return 2 * c + (W * c / G >= (long long)tile * nk ? 0 : 1); }
+    __device__ __forceinline__ int slab_of(int c, int tile) const {
+        if (!sk) return tile * splits + c;   // split-K: c is the split index
+        return 2 * c + (W * c / G >= (long long)tile * nk ? 0 : 1);
+    }
     __device__ __forceinline__ bool next(Seg& s) {
         if (sk) {
             if (pos >= hi) return false;
@@ -373,7 +377,8 @@ struct WorkIter {
         s.kb_end = (int)((long long)nk * (split + 1) / splits);
         s.nseg = splits;
         s.slot = s.tile;
-        s.first_cta = s.my_slab = 0;
+        s.first_cta = 0;
+        s.my_slab = u;          // split-K: slab tile * splits + split
         u += G;
         return true;
     }
@@ -421,6 +426,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         prefetch_tensormap(p.tmap_b);
     }
     __syncthreads();   // barriers are initialised: the TMA warp may start copying
+    // Everything above touched only this CTA's shared memory and the kernel parameters, so under programmatic
+    // dependent launch it overlaps the tail of the previous kernel of the stream.  From here on global memory is
+    // read (operands, residual, scratch): wait for that kernel to complete.  The next kernel may start its own
+    // set-up as soon as every CTA of this one has got this far.
+    pdl_wait();
+    if (tid == 0) pdl_launch_dependents();
     uint32_t tmem_base = 0;
     if (warp != TMA_WARP) {
         // Everyone but the TMA warp needs the tensor-memory base; the allocation overlaps the first copies.
@@ -461,6 +472,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
         const int sub = lane >> 2;          // row within a group of eight
         const int cc = (lane & 3) * 4;      // first of this lane's four channels within a 16-channel chunk
         const uint32_t tmem_rows = tmem_base + ((uint32_t)(q * 32) << 16);
+        const bool cross = ATMEM && p.cross_acc != 0;
+        // 32 columns of the finished accumulator, one row per lane (main part plus, if kept apart, the cross terms)
+        auto load_acc = [&](uint32_t col, uint32_t (&r)[32]) {
+            tmem_ld_32x32(tmem_rows + col, r);
+            if (ATMEM && cross) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t c[16];
+                    tmem_ld_32x16(tmem_rows + BN + col + 16 * h, c);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) r[16 * h + j] = __float_as_uint(__uint_as_float(r[16 * h + j]) + __uint_as_float(c[j]));
+                }
+            } else {
+                tmem_ld_wait();
+            }
+        };
         int local = 0;
         WorkIter work(p, tiles);
         Seg seg;
@@ -470,8 +498,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             const int tloc = tile - bidx * tiles_per_problem;
             const int tm = tloc / p.tiles_n, tn = tloc % p.tiles_n;
             const long long y_off = (long long)bidx * p.batch_stride_y;
-            const int ab = local & 1;
-            if (!timed_wait(&ctl->tmem_full[ab], (local >> 1) & 1, abort_flag, waited)) {
+            // With the cross-term accumulator there is one output buffer (0) and its barriers flip every tile.
+            const int ab = cross ? 0 : (local & 1);
+            const uint32_t acc_use = cross ? (uint32_t)local : (uint32_t)(local >> 1);
+            if (!timed_wait(&ctl->tmem_full[ab], acc_use & 1u, abort_flag, waited)) {
                 if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_FULL); }
                 break;
             }
@@ -520,9 +550,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 if (lane == 0) mbar_arrive(&ctl->tmem_empty[ab]);
                 continue;
             }
-            if (p.stream_k && seg.nseg > 1) {
-                // Stream-K piece of a cut tile.  The partial accumulator goes to this piece's slab, laid out
-                // [4-column group][row] so that the lanes (rows) of a warp write consecutive 16 bytes.
+            if (seg.nseg > 1) {
+                // Piece of a cut tile (stream-K, or one split of split-K).  The partial accumulator goes to this
+                // piece's slab, laid out [4-column group][row] so that the lanes (rows) of a warp write consecutive 16 bytes.
                 constexpr int SLAB_F4 = BM * BN / 4;
                 float4* slabs = reinterpret_cast<float4*>(p.slabs);
                 float4* mine = slabs + (long long)seg.my_slab * SLAB_F4;
@@ -530,8 +560,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
 #pragma unroll 1
                 for (int c32 = col_lo; c32 < col_hi; c32 += 32) {
                     uint32_t r[32];
-                    tmem_ld_32x32(tmem_rows + ab * BN + c32, r);
-                    tmem_ld_wait();
+                    load_acc((uint32_t)(ab * BN + c32), r);
 #pragma unroll
                     for (int j = 0; j < 8; j++)
                         mine[(c32 / 4 + j) * BM + row] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
@@ -548,7 +577,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 }
                 asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
                 if (ctl->last_flag) {
-                    // Last piece to arrive: every slab of the tile is published.  Sum them in CTA order.
+                    // Last piece to arrive: every slab of the tile is published.  Sum them in CTA (split) order.
                     __threadfence();
 #pragma unroll 1
                     for (int c16 = col_lo; c16 < col_hi; c16 += 16) {
@@ -571,64 +600,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
                 continue;
             }
 #pragma unroll 1
-            for (int c32 = col_lo; c32 < col_hi; c32 += 32) {
+            for (int c32 = col_lo; c32 < col_hi; c32 += 32) {   // whole tile in one piece: straight to the output
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_rows + ab * BN + c32, r);
-                tmem_ld_wait();
+                load_acc((uint32_t)(ab * BN + c32), r);
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     float v16[16];
 #pragma unroll
                     for (int j = 0; j < 16; j++) v16[j] = __uint_as_float(r[16 * h + j]);
-                    if (seg.nseg == 1) {
-                        epilogue_chunk<T>(p, stage, v16, lane, tile_row0, tn * BN + c32 + 16 * h, y_off);
-                        continue;
-                    }
-                    // split-K: add this unit's partial tile to the tile's zero-initialised scratch
-#pragma unroll
-                    for (int j = 0; j < 16; j += 4)
-                        *reinterpret_cast<float4*>(stage + lane * EPI_LD + j) = make_float4(v16[j], v16[j + 1], v16[j + 2], v16[j + 3]);
-                    __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int rr = i * 8 + sub;
-                        if (tile_row0 + rr < p.M)
-                            red_add_v4(p.scratch + ((long long)seg.slot * BM + q * 32 + rr) * BN + c32 + 16 * h + cc,
-                                       *reinterpret_cast<const float4*>(stage + rr * EPI_LD + cc));
-                    }
-                    __syncwarp();
+                    epilogue_chunk<T>(p, stage, v16, lane, tile_row0, tn * BN + c32 + 16 * h, y_off);
                 }
-            }
-            if (seg.nseg > 1) {
-                // The piece that arrives last on the tile's counter applies the epilogue to the sums.
-                __threadfence();
-                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
-                if (tid == 0) {
-                    int prev = atomicAdd(p.counters + seg.slot, 1);
-                    ctl->last_flag = (prev == seg.nseg - 1);
-                }
-                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");
-                if (ctl->last_flag) {
-                    __threadfence();
-#pragma unroll 1
-                    for (int c16 = col_lo; c16 < col_hi; c16 += 16) {
-                        const int n = tn * BN + c16 + cc;
-                        const EpiCoef coef = load_coef<T>(p, n);
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const int rr = i * 8 + sub;
-                            const long long m = tile_row0 + rr;
-                            if (m < p.M) {
-                                float4* part = reinterpret_cast<float4*>(p.scratch + ((long long)seg.slot * BM + q * 32 + rr) * BN + c16 + cc);
-                                const float4 v = __ldcg(part);
-                                *part = make_float4(0.f, 0.f, 0.f, 0.f);   // leave the scratch zeroed for the next launch
-                                store_out<T>(p, coef, v, out_row(p, m), n, y_off);
-                            }
-                        }
-                    }
-                    if (tid == 0) p.counters[seg.slot] = 0;
-                }
-                asm volatile("bar.sync 1, %0;" ::"r"(epi_threads) : "memory");   // last_flag is rewritten by the next unit
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -647,12 +628,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
             int local = 0;
             bool dead = false;
             long long waited2 = 0;
+            const bool cross = ATMEM && p.cross_acc != 0;
             WorkIter work(p, tiles);
             Seg seg;
             for (; !dead && work.next(seg); local++) {
                 const int kb_begin = seg.kb_begin, kb_end = seg.kb_end;
-                const int ab = local & 1;
-                if (!timed_wait(&ctl->tmem_empty[ab], ((local >> 1) & 1) ^ 1, abort_flag, waited2)) {
+                const int ab = cross ? 0 : (local & 1);
+                const uint32_t acc_use = cross ? (uint32_t)local : (uint32_t)(local >> 1);
+                if (!timed_wait(&ctl->tmem_empty[ab], (acc_use & 1u) ^ 1u, abort_flag, waited2)) {
                     if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_EMPTY); }
                     break;
                 }
@@ -680,9 +663,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) igemm_fprop_kernel(const __grid_c
 #pragma unroll
                             for (int ks = 0; ks < 4; ks++) {
                                 const uint64_t o = (uint64_t)ks * kstep;
-                                umma_tf32_ts(d, ta_lo + ks * 8, b_hi + o, idesc, (kb > kb_begin || ks > 0) ? 1u : 0u);
-                                umma_tf32_ts(d, ta_hi + ks * 8, b_lo + o, idesc, 1u);
-                                umma_tf32_ts(d, ta_hi + ks * 8, b_hi + o, idesc, 1u);
+                                const uint32_t first = (kb > kb_begin || ks > 0) ? 1u : 0u;
+                                // cross terms: into the main accumulator, or into one of their own (columns BN..2BN)
+                                const uint32_t dx = cross ? tmem_base + BN : d;
+                                umma_tf32_ts(dx, ta_lo + ks * 8, b_hi + o, idesc, first);
+                                umma_tf32_ts(dx, ta_hi + ks * 8, b_lo + o, idesc, 1u);
+                                umma_tf32_ts(d, ta_hi + ks * 8, b_hi + o, idesc, cross ? first : 1u);
                             }
                         } else {
 #pragma unroll
@@ -1147,8 +1133,22 @@ static cudaError_t launch_cfg(const IgemmParams& p, int num_ctas, cudaStream_t s
     }
     // Every role derives its share of the work from gridDim.x (WorkIter), in all three schedules.
     OB200_ELASTIC((igemm_fprop_kernel<T, BN, PASSES, ATMEM>), 1);
-    igemm_fprop_kernel<T, BN, PASSES, ATMEM><<<num_ctas, NTHREADS, C::SMEM_BYTES, stream>>>(p);
-    return cudaGetLastError();
+    static const bool pdl = [] {   // ORION_PDL=0: plain stream order between consecutive kernels
+        const char* e = getenv("ORION_PDL");
+        return !(e && e[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3((unsigned)num_ctas);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, igemm_fprop_kernel<T, BN, PASSES, ATMEM>, p);
 }
 
 }  // namespace ob200
@@ -1301,6 +1301,21 @@ extern "C" int ob200_igemm_launch(const IgemmParams* params, int bn, int num_cta
         return e && e[0] == '0';
     }();
     p.a_in_tmem = (p.dtype == 0 && p.mode == 0 && !a_tmem_off) ? 1 : 0;
+    {   // Cross-term accumulator where no CTA of a whole-device launch computes more than two pieces (see
+        // IgemmParams::cross_acc); decided from the problem and the device, not from this call's CTA count, so that the
+        // arithmetic does not change with the SM quota.  ORION_CROSS_ACC=0/1 pins it.
+        static const int device_sms = [] {
+            int dev = 0, v = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+            return v;
+        }();
+        static const char force = [] {
+            const char* e = getenv("ORION_CROSS_ACC");
+            return e ? e[0] : '\0';
+        }();
+        const long long units = (long long)p.tiles_m * p.tiles_n * (p.splits > 1 ? p.splits : 1) * (p.batch > 1 ? p.batch : 1);
+        p.cross_acc = (p.a_in_tmem && (force == '1' || (force != '0' && !p.stream_k && units <= 2LL * device_sms))) ? 1 : 0;
+    }
     if (setup_tma(p, bn)) g_tma_launches.fetch_add(1, std::memory_order_relaxed);
     else if (p.require_tma || p.w_R > 0) return -4;   // tap subsets exist only on the TMA path
     {   // class of this launch for the scheduler's profiles: arithmetic intensity of the problem against the device's

@@ -18,8 +18,8 @@ typedef struct IgemmParams {
     const float* scale;     /* optional per-output-channel multiplier */
     const float* shift;     /* optional per-output-channel addend (bias) */
     const void* residual;   /* optional tensor of y's shape added before the ReLU */
-    float* scratch;         /* split-K partial sums, zero on entry, zero on exit */
-    int* counters;          /* split-K arrival counters, one per tile, zero on entry and exit */
+    float* scratch;         /* filter gradient only: unused (its partial sums are added into y) */
+    int* counters;          /* arrival counters of cut tiles (split-K: one per tile; stream-K: see below), zero on entry and exit */
     int* status;            /* optional device word that receives an error code */
     long long* debug;       /* optional: 8 cycle counters written by CTA 0 (role wait times) */
     int relu;               /* 0 none, 1 ReLU, 2 ReLU6 */
@@ -30,7 +30,11 @@ typedef struct IgemmParams {
     int kblocks_per_r;      /* ceil(S*C / BK) */
     int num_kblocks;        /* R * kblocks_per_r */
     int tiles_m, tiles_n;
-    int splits;             /* split-K factor, <= num_kblocks */
+    /* Split-K factor, <= num_kblocks.  splits > 1 (mode 0): unit (tile, split) covers a contiguous range of the
+     * tile's k-blocks and writes its partial accumulator to slab tile*splits + split of `slabs` (128 x BN floats
+     * each, contents arbitrary on entry and exit); the unit that arrives last on the tile's counter adds the
+     * slabs in split order -- the sum does not depend on arrival order -- and applies the epilogue. */
+    int splits;
     /* stream_k = 1 (mode 0 only): the k-blocks of all tiles, laid end to end, are cut into one equal contiguous
      * range per CTA, so a CTA may finish a tile another one began.  Each piece of a cut tile is written to its
      * own slab of `slabs` (two slabs of 128 x BN floats per CTA, contents arbitrary on entry and exit); the piece
@@ -76,6 +80,13 @@ typedef struct IgemmParams {
      * over [batch, Kout, R, S, C].  0: the producer warps gather with 16-byte asynchronous copies. */
     int use_tma;
     int a_in_tmem;     /* 3xTF32, mode 0: the splitters put both parts of the activation tile into tensor memory */
+    /* 3xTF32 with a_in_tmem: the two small cross products (lo*hi, hi*lo) accumulate in a second accumulator and are
+     * added to the main one in the epilogue.  The tensor core adds into its fp32 accumulator by truncation; with the
+     * cross terms elsewhere the large accumulator takes one addition per k-step instead of three, which cuts the
+     * systematic shrinkage of long reductions threefold.  The second accumulator takes the place of the second
+     * output buffer, so the epilogue of a tile no longer overlaps the next tile's MMAs: set by the launcher where a
+     * CTA computes at most two tiles anyway (small batches). */
+    int cross_acc;
     int tma_base_h, tma_base_w;
     unsigned long long mn_desc_bits;   /* filter gradient on TMA: the operand descriptors' bits above the address */
     OB200_ALIGN64 unsigned char tmap_a[128];

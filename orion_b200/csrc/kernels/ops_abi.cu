@@ -13,14 +13,13 @@
 namespace {
 
 struct Scratch {
-    float* partial = nullptr;    // split-K sums: zero between launches
     int* counters = nullptr;     // arrival counters: zero between launches
-    float* slabs = nullptr;      // stream-K partial tiles: two per CTA, contents arbitrary between launches
-    size_t partial_bytes = 0, slab_bytes = 0;
+    float* slabs = nullptr;      // partial tiles of cut tiles (split-K: one per unit; stream-K: two per CTA); contents
+                                 // arbitrary between launches
+    size_t slab_bytes = 0;
 };
-constexpr size_t kSlabBytes = 40u << 20;                // two 128 x 128 float slabs for up to 320 CTAs
+constexpr size_t kSlabBytes = 40u << 20;                // 128 x 128 float slabs for up to 640 pieces
 constexpr int kMaxTilesSplit = 4096;                    // counters per stream
-constexpr size_t kScratchBytes = 32u << 20;             // split-K partial sums per stream
 
 std::mutex g_mu;
 std::unordered_map<uint64_t, Scratch> g_scratch;        // key: device << 56 ^ stream
@@ -61,18 +60,29 @@ Scratch* scratch_for(int dev, cudaStream_t s) {
         return cached;
     }
     Scratch sc;
-    if (cudaMalloc(&sc.partial, kScratchBytes) != cudaSuccess) return nullptr;
     if (cudaMalloc(&sc.counters, kMaxTilesSplit * sizeof(int)) != cudaSuccess) return nullptr;
     if (cudaMalloc(&sc.slabs, kSlabBytes) != cudaSuccess) return nullptr;
-    sc.partial_bytes = kScratchBytes;
     sc.slab_bytes = kSlabBytes;
-    cudaMemsetAsync(sc.partial, 0, kScratchBytes, s);
     cudaMemsetAsync(sc.counters, 0, kMaxTilesSplit * sizeof(int), s);
     g_scratch[key] = sc;
     return &g_scratch[key];
 }
 
 }  // namespace
+
+// Number of SMs the schedule of a problem is planned for.  The plan (tile width, split-K factor, stream-K or not)
+// depends on the device alone, never on the SM quota of the call: the quota only sets how many CTAs walk the
+// planned work units, so a split-K result is bit-identical for every quota (the scheduler may cut a launch to
+// its granted quota at the last moment).
+static int plan_sm_count() {
+    static const int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+            v = 148;
+        return v;
+    }();
+    return n;
+}
 
 extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out) {
     const int bk = dtype == 1 ? 64 : 32;
@@ -142,7 +152,7 @@ bool stream_k_pays(long long tiles, int num_kblocks, int num_ctas) {
 // returns the grid, or 0 to keep the caller's schedule.
 int schedule_stream_k(IgemmParams& p, int bn, int num_ctas, int dev, cudaStream_t stream) {
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
-    if (!stream_k_pays(tiles, p.num_kblocks, num_ctas)) return 0;
+    if (!stream_k_pays(tiles, p.num_kblocks, plan_sm_count())) return 0;
     const long long work = tiles * p.num_kblocks;
     long long grid = work / 4;
     if (grid > num_ctas) grid = num_ctas;
@@ -221,7 +231,7 @@ int fprop_impl(const void* x, const void* w, void* y, const float* scale, const 
     }
     if (splits > 1) {
         if (!scratch || !counters) return -1;
-        p.scratch = scratch;
+        p.slabs = scratch;      // one 128 x bn slab per (tile, split)
         p.counters = counters;
     }
     const int units = p.tiles_m * p.tiles_n * splits;
@@ -244,23 +254,25 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
                                   int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas,
                                   void* stream) {
     if (Nb <= 0 || H <= 0 || W <= 0) return Nb == 0 ? 0 : -1;
+    if (num_ctas <= 0) return -1;
     const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / (stride_h > 0 ? stride_h : 1) + 1;
     const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / (stride_w > 0 ? stride_w : 1) + 1;
     const long long M = (long long)Nb * P * Q;
-    if (wide_tiles_pay(dtype, M, Kout, num_ctas))
+    const int plan_ctas = plan_sm_count();
+    if (wide_tiles_pay(dtype, M, Kout, plan_ctas))
         return fprop_impl(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w, dil_h,
                           dil_w, 256, 1, true, nullptr, nullptr, num_ctas, stream);
     {   // stream-K with the tile width it prefers, where it pays
         const int bn = streamk_bn(Kout);
         const int bk = dtype == 1 ? 64 : 32;
         const long long tiles = ((M + 127) / 128) * ((Kout + bn - 1) / bn);
-        if (stream_k_pays(tiles, R * ((S * C + bk - 1) / bk), num_ctas))
+        if (stream_k_pays(tiles, R * ((S * C + bk - 1) / bk), plan_ctas))
             return fprop_impl(x, w, y, scale, shift, residual, relu, dtype, Nb, H, W, C, Kout, R, S, stride_h, stride_w, pad_h, pad_w,
                               dil_h, dil_w, bn, 1, true, nullptr, nullptr, num_ctas, stream);
     }
     // otherwise one unit per tile, or split-K where the tiles are few
     int bn = 128, splits = 1;
-    ob200_plan_conv(dtype, M, Kout, R, S, C, num_ctas, &bn, &splits);
+    ob200_plan_conv(dtype, M, Kout, R, S, C, plan_ctas, &bn, &splits);
     float* scratch = nullptr;
     int* counters = nullptr;
     if (splits > 1) {
@@ -268,10 +280,10 @@ extern "C" int ob200_conv2d_fprop(const void* x, const void* w, void* y, const f
         cudaGetDevice(&dev);
         const long long tiles = ((M + 127) / 128) * ((Kout + bn - 1) / bn);
         Scratch* sc = scratch_for(dev, (cudaStream_t)stream);
-        if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * 128 * bn * sizeof(float) > sc->partial_bytes) {
+        if (!sc || tiles > kMaxTilesSplit || (size_t)tiles * splits * 128 * bn * sizeof(float) > sc->slab_bytes) {
             splits = 1;
         } else {
-            scratch = sc->partial;
+            scratch = sc->slabs;
             counters = sc->counters;
         }
     }

@@ -44,6 +44,20 @@ static inline int orion_is_memop(int type) {
            type == ORION_FREE_RECORD || type == ORION_MEMSET_RECORD;
 }
 
+/* The reference's record type for an entry point it does not trap but whose role one of its own records plays
+ * (torch 2.x calls cublasGemmEx / cublasLtMatmul where torch 1.12 called cublasSgemm, cudnnBackendExecute where it
+ * called cudnnConvolutionForward, cudaLaunchKernelExC where it called cudaLaunchKernel).  Recorded arrival scripts
+ * carry these numbers so that the reference scheduler, whose replay switch knows only 0..16, can replay them. */
+static inline int orion_reference_type(int type) {
+    switch (type) {
+        case ORION_CUBLAS_GEMMEX_RECORD: case ORION_CUBLASLT_MATMUL_RECORD: return ORION_CUBLAS_SGEMM_RECORD;
+        case ORION_CUBLAS_GEMMEX_STRIDED_RECORD: return ORION_CUBLAS_SGEMM_STRIDED_RECORD;
+        case ORION_CUDNN_BACKEND_EXECUTE_RECORD: return ORION_CUDNN_CONV_RECORD;
+        case ORION_KERNEL_EXC_RECORD: return ORION_KERNEL_RECORD;
+        default: return type;
+    }
+}
+
 /* Types the reference's replay switch aborts on (utils_sched.cpp:514-516). */
 static inline int orion_is_unsupported(int type) {
     return type < 0 || type >= ORION_REC_TYPE_COUNT || type == ORION_CUDNN_CREATE_RECORD ||

@@ -123,6 +123,11 @@ struct LiveEnv {
     int quota_gran = 8;       // SM-partition granularity of the device
     uint64_t quota_grants = 0, quota_ctas_sum = 0;
     uint32_t idle_polls = 0;
+    // An inference client's events are only ever queried for the last compute op of a request (iteration end,
+    // policy.hpp; the update-phase rule needs a training high-priority client).  Its other ops are granted without an
+    // event, so nothing sits between two of its kernels in the stream and a kernel may begin while its predecessor
+    // drains (programmatic dependent launch).  Queries and their answers are unchanged.
+    bool skip_inner_events = true;
     // recording (arrival-script abstraction of the run)
     bool recording = false;
     std::vector<int64_t> last_pop_us;
@@ -174,7 +179,9 @@ struct LiveEnv {
         }
         uint64_t head = r.granted.load(std::memory_order_acquire);
         r.grant.stream = streams[stream];
-        r.grant.event = events[evl][evs];
+        const bool inner_op_of_inference_request = skip_inner_events && core && evl == i && !core->is_train[i] &&
+                                                   (orion_is_memop(type) || core->seen[i] + 1 < core->num_kernels[i]);
+        r.grant.event = inner_op_of_inference_request ? nullptr : events[evl][evs];
         const int q = orion_is_memop(type) ? 0 : quota_for(i);
         r.grant.num_ctas = q;
         if (q > 0) {
@@ -510,6 +517,10 @@ void* schedule(Scheduler* s, int num_clients, bool profile_mode, int iter, bool 
     a.depth = reef_depth;
     a.hp_limit = hp_limit;
     a.update_start = update_start;
+    {
+        const char* e = getenv("ORION_SKIP_INNER_EVENTS");
+        s->env.skip_inner_events = !seq && !(e && e[0] == '0');   // the sequential policy shares one event list
+    }
     s->sh->polling.store(1, std::memory_order_release);
     s->core.run_phase(s->env, a);
     s->sh->polling.store(0, std::memory_order_release);
@@ -608,7 +619,7 @@ static void write_recorded_script(Scheduler* s, const orion::PhaseArgs& a) {
             for (const RecordedOp& o : *pick) {
                 long dur = 0;
                 if (!orion_is_memop(o.type) && row < s->core.op_info[i].size()) dur = (long)(s->core.op_info[i][row++].duration / 1000.0f);
-                fprintf(f, " %d %ld %ld", o.type, (long)(o.gap_us < 0 ? 0 : o.gap_us), dur < 1 ? 1 : dur);
+                fprintf(f, " %d %ld %ld", orion_reference_type(o.type), (long)(o.gap_us < 0 ? 0 : o.gap_us), dur < 1 ? 1 : dur);
             }
         }
         fprintf(f, "\n");

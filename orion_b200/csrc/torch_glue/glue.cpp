@@ -24,6 +24,10 @@
 #include <torch/library.h>
 
 #include <atomic>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
 
 extern "C" {
 int ob200_conv2d_fprop(const void* x, const void* w, void* y, const float* scale, const float* shift, const void* residual, int relu,
@@ -404,6 +408,101 @@ at::Tensor linear_batched_op(const at::Tensor& x, const at::Tensor& w) {
     return y;
 }
 
+// ------------------------------------------------------------------ inference plans
+// A prepared inference model as a flat list of kernel launches over numbered tensor slots, run by ONE
+// call from Python.  The interpreter lock is taken once per request instead of once per layer, so a
+// high-priority client is not held up, between two of its layers, by another client's Python code in the
+// same process (the reference runs every client as a thread of one process, benchmarking/launch_jobs.py:44-148),
+// and the per-layer host cost is the launch and its grant alone.
+struct PlanStep {
+    int kind;   // 0 conv, 1 depthwise, 2 maxpool, 3 global avgpool, 4 linear, 5 add(+relu), 6 flatten, 7 alias
+    int in, res, out;
+    at::Tensor w;
+    c10::optional<at::Tensor> scale, shift;
+    int act;
+    std::vector<int64_t> stride, pad, dil;
+};
+struct Plan {
+    std::vector<PlanStep> steps;
+    int n_slots = 0, out_slot = 0;
+    std::vector<int> last_use;   // per slot: index of the last step that reads it
+};
+std::mutex g_plan_mu;
+std::vector<std::unique_ptr<Plan>> g_plans;
+
+int64_t plan_create(int64_t n_slots, int64_t out_slot) {
+    TORCH_CHECK(n_slots > 0 && out_slot >= 0 && out_slot < n_slots, "orion::plan_create: bad slot numbers");
+    std::lock_guard<std::mutex> lk(g_plan_mu);
+    auto p = std::make_unique<Plan>();
+    p->n_slots = (int)n_slots;
+    p->out_slot = (int)out_slot;
+    p->last_use.assign((size_t)n_slots, -1);
+    g_plans.push_back(std::move(p));
+    return (int64_t)g_plans.size() - 1;
+}
+
+Plan* plan_of(int64_t id) {
+    std::lock_guard<std::mutex> lk(g_plan_mu);
+    TORCH_CHECK(id >= 0 && id < (int64_t)g_plans.size(), "orion: unknown plan ", id);
+    return g_plans[(size_t)id].get();
+}
+
+void plan_add(int64_t id, int64_t kind, int64_t in, int64_t res, int64_t out, const c10::optional<at::Tensor>& w,
+              const c10::optional<at::Tensor>& scale, const c10::optional<at::Tensor>& shift, int64_t act, at::IntArrayRef stride,
+              at::IntArrayRef pad, at::IntArrayRef dil) {
+    Plan* p = plan_of(id);
+    TORCH_CHECK(kind >= 0 && kind <= 7 && in >= 0 && in < p->n_slots && out >= 0 && out < p->n_slots && res < p->n_slots,
+                "orion::plan_add: bad step");
+    PlanStep st;
+    st.kind = (int)kind;
+    st.in = (int)in;
+    st.res = (int)res;
+    st.out = (int)out;
+    if (w.has_value() && w->defined()) st.w = *w;
+    st.scale = scale;
+    st.shift = shift;
+    st.act = (int)act;
+    st.stride = stride.vec();
+    st.pad = pad.vec();
+    st.dil = dil.vec();
+    const int idx = (int)p->steps.size();
+    p->last_use[(size_t)in] = idx;
+    if (res >= 0) p->last_use[(size_t)res] = idx;
+    p->steps.push_back(std::move(st));
+}
+
+at::Tensor plan_run(int64_t id, const at::Tensor& x) {
+    Plan* p = plan_of(id);
+    std::vector<at::Tensor> slot((size_t)p->n_slots);
+    slot[0] = x;
+    const int n = (int)p->steps.size();
+    for (int i = 0; i < n; i++) {
+        const PlanStep& st = p->steps[(size_t)i];
+        const at::Tensor& in = slot[(size_t)st.in];
+        at::Tensor out;
+        switch (st.kind) {
+            case 0: {
+                c10::optional<at::Tensor> res;
+                if (st.res >= 0) res = slot[(size_t)st.res];
+                out = conv_bn_act(in, st.w, st.scale, st.shift, res, st.act, st.stride, st.pad, st.dil);
+                break;
+            }
+            case 1: out = depthwise_bn_act(in, st.w, st.scale, st.shift, st.act, st.stride, st.pad, st.dil); break;
+            case 2: out = maxpool_op(in, st.dil[0], st.stride[0], st.pad[0]); break;   // dil carries the window size
+            case 3: out = avgpool_op(in); break;
+            case 4: out = linear_op(in.dim() == 2 ? in : in.reshape({in.size(0), -1}), st.w, st.shift, st.act != 0); break;
+            case 5: out = add_act_op(in, slot[(size_t)st.res], st.act != 0); break;
+            case 6: out = in.dim() == 2 ? in : in.reshape({in.size(0), -1}); break;
+            default: out = in; break;
+        }
+        slot[(size_t)st.out] = std::move(out);
+        // a slot nobody reads any more gives its memory back to the allocator (the stream keeps the order)
+        if (p->last_use[(size_t)st.in] == i && st.in != p->out_slot && st.in != st.out) slot[(size_t)st.in] = at::Tensor();
+        if (st.res >= 0 && p->last_use[(size_t)st.res] == i && st.res != p->out_slot && st.res != st.out) slot[(size_t)st.res] = at::Tensor();
+    }
+    return slot[(size_t)p->out_slot];
+}
+
 int64_t set_sm_quota(int64_t n) {
     int old = tls_quota;
     tls_quota = (int)n;
@@ -427,6 +526,9 @@ TORCH_LIBRARY(orion, m) {
     m.def("softmax(Tensor x, float scale) -> Tensor");
     m.def("bias_gelu(Tensor x, Tensor? bias) -> Tensor");
     m.def("linear_batched(Tensor x, Tensor w) -> Tensor");
+    m.def("plan_create(int n_slots, int out_slot) -> int", &plan_create);
+    m.def("plan_add(int plan, int kind, int src, int res, int dst, Tensor? w, Tensor? scale, Tensor? shift, int act, int[] stride, int[] pad, int[] dil) -> ()", &plan_add);
+    m.def("plan_run(int plan, Tensor x) -> Tensor");
     m.def("set_sm_quota(int n) -> int", &set_sm_quota);
     m.def("set_overrides(int on) -> int", &set_overrides);
     m.def("set_tf32(int on) -> int", &set_tf32);
@@ -445,6 +547,7 @@ TORCH_LIBRARY_IMPL(orion, CUDA, m) {
     m.impl("softmax", &softmax_op);
     m.impl("bias_gelu", &bias_gelu_op);
     m.impl("linear_batched", &linear_batched_op);
+    m.impl("plan_run", &plan_run);
 }
 
 TORCH_LIBRARY_IMPL(aten, CUDA, m) {

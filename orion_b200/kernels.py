@@ -120,7 +120,7 @@ def conv2d_nhwc(x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None
         scratch = counters = None
         if splits > 1:
             tiles = ((Nb * P * Q + 127) // 128) * ((K + bn - 1) // bn)
-            scratch = torch.zeros(tiles * 128 * bn, device=x.device, dtype=torch.float32)
+            scratch = torch.empty(tiles * splits * 128 * bn, device=x.device, dtype=torch.float32)
             counters = torch.zeros(tiles, device=x.device, dtype=torch.int32)
         _check(lib().ob200_conv2d_fprop_ex(*args, bn, splits, _ptr(scratch), _ptr(counters), n, _stream()),
                "ob200_conv2d_fprop_ex")

@@ -148,10 +148,79 @@ def _act_of(node, mods):
     return 0
 
 
-def prepare_inference(model):
+class PlannedModel(nn.Module):
+    """A prepared model whose whole forward pass is one call into the adapter (`orion::plan_run`): the layers are
+    launched from C++ in order, so the interpreter is entered once per request, not once per layer."""
+
+    def __init__(self, gm, plan_id):
+        super().__init__()
+        self.gm = gm          # keeps the parameters / buffers of the plan alive; also the per-layer path
+        self.plan_id = plan_id
+
+    def forward(self, x):
+        return torch.ops.orion.plan_run(self.plan_id, x)
+
+
+def _build_plan(gm):
+    """Flatten a prepared GraphModule into an adapter-side plan; returns the plan id, or None when the graph has a
+    node the plan executor does not know (the per-layer GraphModule is used then)."""
+    ops = torch.ops.orion
+    mods = dict(gm.named_modules())
+    nodes = list(gm.graph.nodes)
+    placeholders = [n for n in nodes if n.op == "placeholder"]
+    outputs = [n for n in nodes if n.op == "output"]
+    if len(placeholders) != 1 or len(outputs) != 1 or not isinstance(outputs[0].args[0], fx.Node):
+        return None
+    slot = {placeholders[0]: 0}
+    steps = []
+
+    def new_slot(node):
+        slot[node] = len(slot)
+        return slot[node]
+
+    for node in nodes:
+        if node.op in ("placeholder", "output"):
+            continue
+        args = [a for a in node.args if isinstance(a, fx.Node)]
+        if not args or any(a not in slot for a in args) or node.kwargs and any(isinstance(v, fx.Node) for v in node.kwargs.values()):
+            return None
+        src = slot[args[0]]
+        if node.op == "call_module":
+            m = mods.get(node.target)
+            if isinstance(m, FusedConv):
+                res = slot[args[1]] if len(args) > 1 else -1
+                steps.append((1 if m.depthwise else 0, src, res, new_slot(node), m.weight, m.scale, m.shift, m.act, m.stride, m.padding,
+                              m.dilation))
+            elif isinstance(m, OrionMaxPool):
+                steps.append((2, src, -1, new_slot(node), None, None, None, 0, [m.stride], [m.pad], [m.k]))
+            elif isinstance(m, OrionAvgPool):
+                steps.append((3, src, -1, new_slot(node), None, None, None, 0, [], [], []))
+            elif isinstance(m, OrionLinear):
+                steps.append((4, src, -1, new_slot(node), m.weight, None, m.bias, 0, [], [], []))
+            elif isinstance(m, (nn.Dropout, nn.Identity)):
+                steps.append((7, src, -1, new_slot(node), None, None, None, 0, [], [], []))
+            else:
+                return None
+        elif node.op == "call_function" and node.target in (torch.flatten,) and (len(node.args) < 2 or node.args[1] == 1):
+            steps.append((6, src, -1, new_slot(node), None, None, None, 0, [], [], []))
+        elif node.op == "call_function" and node.target is F.adaptive_avg_pool2d and tuple(
+                node.args[1] if isinstance(node.args[1], (tuple, list)) else (node.args[1],) * 2) == (1, 1):
+            steps.append((3, src, -1, new_slot(node), None, None, None, 0, [], [], []))
+        elif node.op == "call_function" and node.target in (operator.add, operator.iadd, torch.add) and len(args) == 2 and not node.kwargs:
+            steps.append((5, src, slot[args[1]], new_slot(node), None, None, None, 0, [], [], []))
+        else:
+            return None
+    plan = ops.plan_create(len(slot), slot[outputs[0].args[0]])
+    for (kind, src, res, dst, w, scale, shift, act, stride, pad, dil) in steps:
+        ops.plan_add(plan, kind, src, res, dst, w, scale, shift, act, list(stride), list(pad), list(dil))
+    return plan
+
+
+def prepare_inference(model, plan=True):
     """Return an eval-mode copy of `model` (torchvision-style CNN, on its CUDA device,
     float32) whose conv/bn/add/relu groups, pooling layers and classifier run on the
-    orion kernels.  Grouped (depthwise) convolutions keep their stock implementation."""
+    orion kernels.  With `plan` (default) the result runs its whole forward pass from one adapter call
+    where every layer is one the adapter knows; otherwise, and for other graphs, layer by layer."""
     load()
     model = model.eval()
     with TRACE_LOCK:
@@ -225,4 +294,8 @@ def prepare_inference(model):
     g.lint()
     gm.delete_all_unused_submodules()
     gm.recompile()
+    if plan and os.environ.get("ORION_PLAN", "1") == "1":
+        plan_id = _build_plan(gm)
+        if plan_id is not None:
+            return PlannedModel(gm, plan_id)
     return gm

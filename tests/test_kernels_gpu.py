@@ -137,7 +137,7 @@ def test_conv_fused_epilogue(K):
 
 @pytest.mark.parametrize("bn,splits", [(128, 1), (64, 1), (128, 4), (64, 3), (64, 16)])
 def test_conv_tile_width_and_split_k(K, bn, splits):
-    """Split-K through caller-provided scratch; the kernel must leave scratch and counters zero."""
+    """Split-K through caller-provided scratch (one partial tile per split, summed in split order)."""
     x = torch.randn(4, 7, 7, 512, device="cuda")
     w = torch.randn(512, 3, 3, 512, device="cuda") / 68.0
     shift = torch.randn(512, device="cuda")
@@ -145,6 +145,48 @@ def test_conv_tile_width_and_split_k(K, bn, splits):
     y = K.conv2d_nhwc(x, w, (1, 1), (1, 1), shift=shift, relu=True, bn=bn, splits=splits)
     assert K.read_status() == 0
     assert O.rel_err(y, want) < FP32_TOL
+
+
+@pytest.mark.parametrize("shape", [(4, 7, 7, 512, 512, 3, 1, 1), (4, 14, 14, 256, 256, 3, 1, 1), (4, 7, 7, 2048, 512, 1, 1, 0),
+                                   (4, 14, 14, 1024, 256, 1, 1, 0), (4, 56, 56, 64, 64, 3, 1, 1)])
+def test_planned_schedule_is_bit_reproducible_for_every_sm_quota(K, shape):
+    """Inference batch (4): the entry point picks tile width and split-K factor from the problem and the device alone;
+    the SM quota only sets how many CTAs walk the planned units, and partial tiles are added in split order.  So the
+    output is the same bit for bit for any quota, and from launch to launch."""
+    Nb, H, W, C, Ko, R, stride, pad = shape
+    x = torch.randn(Nb, H, W, C, device="cuda")
+    w = torch.randn(Ko, R, R, C, device="cuda") / (C * R * R) ** 0.5
+    shift = torch.randn(Ko, device="cuda")
+    ref = K.conv2d_nhwc(x, w, (stride, stride), (pad, pad), shift=shift, relu=True, num_ctas=148)
+    assert O.rel_err(ref, O.conv2d_nhwc(x, w, (stride, stride), (pad, pad), shift=shift, act=1)) < FP32_TOL
+    for q in (148, 1, 5, 37, 64, 100, 147):
+        y = K.conv2d_nhwc(x, w, (stride, stride), (pad, pad), shift=shift, relu=True, num_ctas=q)
+        assert torch.equal(y, ref), q
+    assert K.read_status() == 0
+
+
+def test_split_k_sums_in_split_order_whatever_unit_finishes_first(K):
+    """Explicit split-K factor, repeated launches and different quotas (which change which CTA computes which split and
+    in what order they finish): identical bits."""
+    x = torch.randn(4, 7, 7, 512, device="cuda")
+    w = torch.randn(512, 3, 3, 512, device="cuda") / 68.0
+    ref = K.conv2d_nhwc(x, w, (1, 1), (1, 1), bn=64, splits=8, num_ctas=148)
+    for q in (148, 148, 3, 29, 128):
+        assert torch.equal(K.conv2d_nhwc(x, w, (1, 1), (1, 1), bn=64, splits=8, num_ctas=q), ref), q
+    assert K.read_status() == 0
+
+
+def test_long_reductions_keep_their_magnitude(K):
+    """A 3x3 512->512 layer on positive data (the worst case for an accumulator that truncates): with the cross terms of
+    the 3xTF32 product in an accumulator of their own the result stays within 1e-5 of float64 (it was 6e-5 low)."""
+    x = torch.rand(4, 7, 7, 512, device="cuda") + 0.5
+    w = (torch.rand(512, 3, 3, 512, device="cuda") + 0.5) / 4608.0
+    y = K.conv2d_nhwc(x, w, (1, 1), (1, 1))
+    want = O.conv2d_nhwc(x, w, (1, 1), (1, 1))
+    assert K.read_status() == 0
+    assert O.rel_err(y, want) < 1e-5
+    mean_ratio = (y.double().cpu() / want.double().cpu()).mean().item()
+    assert abs(mean_ratio - 1.0) < 1e-5
 
 
 def test_conv_result_does_not_depend_on_the_sm_quota(K):

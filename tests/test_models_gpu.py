@@ -39,12 +39,14 @@ def test_inference_matches_cpu_fp32(ops, name):
     from orion_b200 import kernels
     assert kernels.read_status() == 0
     assert mid > before and after > mid, "the orion kernels did not run"
-    # The tensor core adds into its fp32 accumulator by truncation, which shrinks every convolution's output by
-    # about 2e-6 of its magnitude; through the 104 convolutions of ResNet-101 that adds up to 1.0e-4 (5e-5 for
-    # ResNet-50).  Single layers stay within 5e-6 (tests/test_kernels_gpu.py).
-    tol = 2e-4 if name == "resnet101" else 1e-4
-    assert _rel(via_overrides, want) < tol
-    assert _rel(via_prepared, want) < tol
+    # The tensor core adds into its fp32 accumulator by truncation, which shrinks a long reduction slightly; with the
+    # cross terms of the 3xTF32 product kept in an accumulator of their own the 104 convolutions of ResNet-101 stay
+    # well inside the tolerance.
+    tol = 1e-4
+    e1, e2 = _rel(via_overrides, want), _rel(via_prepared, want)
+    print("%s: relative error %.2e through the overrides, %.2e prepared" % (name, e1, e2))
+    assert e1 < tol
+    assert e2 < tol
     if name == "resnet50":
         # 53 fused convolutions, max-pool, average pool, classifier: one launch each; one zero-padding of the image to 4 channels
         assert after - mid == 53 + 3 + 1

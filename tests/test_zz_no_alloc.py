@@ -5,8 +5,9 @@ example while a stream is being captured, from inside an allocator hook, or in a
 program that distributes all device memory at start-up.  Its split-K scratch is a fixed
 array inside the library, shared by all calls, so two things are checked here through
 the C ABI: the result equals the ordinary entry point's (which uses caller-provided
-scratch) within the fp32 tolerance of the kernel tests, and a second call right after the
-first — which finds the first call's leftovers in the array — is just as good.  Oversized
+scratch) and the CPU oracle's within the fp32 tolerance of the kernel tests, and a second
+call right after the first — which finds the first call's leftovers in the array — is
+just as good.  Oversized
 problems must be refused with a clear code instead of overrunning the array.
 
 The file sorts last on purpose: a run that stops at the first failure has then already
@@ -59,7 +60,7 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(lib, shape, bn,
         shift = torch.randn(K, device="cuda")
         want = torch.empty(Nb, P, P, K, device="cuda")
         got = torch.full_like(want, float("nan"))
-        scratch = torch.zeros(tiles * 128 * bn, device="cuda")
+        scratch = torch.empty(tiles * splits * 128 * bn, device="cuda")
         counters = torch.zeros(tiles, dtype=torch.int32, device="cuda")
         rc = lib.ob200_conv2d_fprop_ex(*_args(x, w, want, shift, 1, stride, pad), bn, splits, scratch.data_ptr(),
                                        counters.data_ptr(), 148, stream)
@@ -69,6 +70,9 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(lib, shape, bn,
         torch.cuda.synchronize()
         assert not torch.isnan(got).any()
         assert _rel(got, want) < TOL, "call %d differs from ob200_conv2d_fprop_ex" % attempt
+        from oracle import numeric_oracle as O
+        assert O.rel_err(got, O.conv2d_nhwc(x, w, (stride, stride), (pad, pad), shift=shift, act=1)) < TOL, \
+            "call %d differs from the CPU oracle" % attempt
 
 
 def test_noalloc_without_split_k_is_bit_identical(lib):
