@@ -84,6 +84,22 @@ int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, con
 int ob200_bn_backward_f32(const float* dy, const float* x, float* dx, const float* gamma, const float* save_mean,
                           const float* save_invstd, float* dgamma, float* dbeta, double* sums, long long rows, int C, int num_ctas,
                           void* stream);
+
+/* Training batch norm fused with the residual add and the activation around it: y = act(batch_norm(x) [+ residual]),
+ * act 0 none / 1 ReLU / 2 ReLU6, x [rows, C] float32, C % 4 == 0, C <= 8192.  Two launches per direction (a reduction
+ * whose last-arriving CTA finishes the statistics and cleans its own scratch, then one elementwise pass); the scratch
+ * belongs to the library (allocated once per stream).  The backward pass recomputes the activation's input from x, or
+ * reads it from the saved output `yout` when a residual was added (yout = NULL otherwise); dres receives the residual's
+ * gradient (NULL when there was none).  They take the place of cudnnBatchNormalizationForwardTrainingEx /
+ * cudnnBatchNormalizationBackwardEx (reference src/scheduler/utils_sched.cpp:297-339,398-438) plus the add / ReLU /
+ * ReLU-backward elementwise kernels that follow them in the reference's profiles
+ * (reference benchmarking/model_kernels/resnet50_32_fb1). */
+int ob200_bn_act_train_forward_f32(const float* x, const float* residual, float* y, const float* gamma, const float* beta,
+                                   float* running_mean, float* running_var, float* save_mean, float* save_invstd, float eps,
+                                   float momentum, long long rows, int C, int act, int num_ctas, void* stream);
+int ob200_bn_act_backward_f32(const float* dy, const float* x, const float* yout, float* dx, float* dres, const float* gamma,
+                              const float* beta, const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta,
+                              long long rows, int C, int act, int num_ctas, void* stream);
 /* dx = dy where y > 0, else 0 (threshold_backward kernels behind the reference's cudaLaunchKernel trap). */
 int ob200_relu_backward_f32(const float* dy, const float* y, float* dx, long long n, int num_ctas, void* stream);
 /* torch.optim.SGD step with momentum on one parameter tensor (the foreach kernels behind the same trap). */
@@ -124,6 +140,10 @@ int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int 
 int ob200_layernorm(const void* x, void* y, const float* gamma, const float* beta, float* mean_out, float* rstd_out,
                     long long rows, int D, float eps, int dtype, int num_ctas, void* stream);
 int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, int dtype, int num_ctas, void* stream);
+/* The same with the causal mask of a decoder: row r holds the scores of query position r % causal_period against keys
+ * 0..D-1, and keys after the query position get probability 0 (causal_period = 0: no mask). */
+int ob200_softmax_causal(const void* x, void* y, long long rows, int D, float scale, int causal_period, int dtype, int num_ctas,
+                         void* stream);
 int ob200_bias_gelu(const void* x, void* y, const float* bias, long long rows, int D, int dtype, int num_ctas, void* stream);
 /* torch.optim.AdamW step number `step` (>= 1) on one float32 tensor. */
 int ob200_adamw_f32(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1, float beta2, float eps,

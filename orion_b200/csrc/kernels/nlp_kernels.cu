@@ -133,11 +133,13 @@ __global__ void __launch_bounds__(ROW_THREADS) layernorm_regs_kernel(const T* __
 
 template <typename T, int CH>
 __global__ void __launch_bounds__(ROW_THREADS) softmax_regs_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int D,
-                                                                  float scale) {
+                                                                  float scale, int causal_period) {
     constexpr int N = VecIO<T>::N;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
         const T* xr = x + row * D;
+        // causal attention: row r holds the scores of query position r % period; later keys are masked out
+        const int last = causal_period > 0 ? (int)(row % causal_period) : D;
         float v[CH][8];
 #pragma unroll
         for (int c = 0; c < CH; c++) {
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(ROW_THREADS) softmax_regs_kernel(const T* __re
             if ((c * 32 + lane) * N < D) {
 #pragma unroll
                 for (int e = 0; e < N; e++) {
-                    v[c][e] *= scale;
+                    v[c][e] = ((c * 32 + lane) * N + e > last) ? -INFINITY : v[c][e] * scale;
                     m = fmaxf(m, v[c][e]);
                 }
             }
@@ -225,31 +227,34 @@ __global__ void __launch_bounds__(ROW_THREADS) layernorm_kernel(const T* __restr
 // y = softmax(x * scale) over the last dimension D.
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) softmax_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int D,
-                                                             float scale) {
+                                                             float scale, int causal_period) {
     constexpr int N = VecIO<T>::N;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
         const T* xr = x + row * D;
+        const int last = causal_period > 0 ? (int)(row % causal_period) : D;
         float v[8];
         float m = -INFINITY;
         for (int i = lane * N; i < D; i += 32 * N) {
             VecIO<T>::load(xr + i, v);
 #pragma unroll
-            for (int e = 0; e < N; e++) m = fmaxf(m, v[e] * scale);
+            for (int e = 0; e < N; e++)
+                if (i + e <= last) m = fmaxf(m, v[e] * scale);
         }
         m = warp_max(m);
         float s = 0.f;
         for (int i = lane * N; i < D; i += 32 * N) {
             VecIO<T>::load(xr + i, v);
 #pragma unroll
-            for (int e = 0; e < N; e++) s += __expf(v[e] * scale - m);
+            for (int e = 0; e < N; e++)
+                if (i + e <= last) s += __expf(v[e] * scale - m);
         }
         const float inv = 1.0f / warp_sum(s);
         T* yr = y + row * D;
         for (int i = lane * N; i < D; i += 32 * N) {
             VecIO<T>::load(xr + i, v);
 #pragma unroll
-            for (int e = 0; e < N; e++) v[e] = __expf(v[e] * scale - m) * inv;
+            for (int e = 0; e < N; e++) v[e] = (i + e <= last) ? __expf(v[e] * scale - m) * inv : 0.f;
             VecIO<T>::store(yr + i, v);
         }
     }
@@ -354,9 +359,10 @@ extern "C" int ob200_layernorm(const void* x, void* y, const float* gamma, const
     return (int)cudaGetLastError();
 }
 
-extern "C" int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, int dtype, int num_ctas, void* stream) {
+extern "C" int ob200_softmax_causal(const void* x, void* y, long long rows, int D, float scale, int causal_period, int dtype,
+                                    int num_ctas, void* stream) {
     if (rows <= 0) return 0;
-    if ((dtype != 0 && dtype != 1) || num_ctas <= 0) return -1;
+    if ((dtype != 0 && dtype != 1) || num_ctas <= 0 || causal_period < 0) return -1;
     if (!vec_ok(x, y, D, dtype)) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     const int grid = row_grid(rows, num_ctas);
@@ -364,21 +370,25 @@ extern "C" int ob200_softmax(const void* x, void* y, long long rows, int D, floa
 #define OB200_SM(T, CH)                                                                        \
     do {                                                                                       \
         OB200_ELASTIC_HBM((softmax_regs_kernel<T, CH>), 8);                                        \
-        softmax_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, rows, D, scale); \
+        softmax_regs_kernel<T, CH><<<grid, ROW_THREADS, 0, s>>>((const T*)x, (T*)y, rows, D, scale, causal_period); \
     } while (0)
     if (dtype == 0) {
         if (chunks <= 2) OB200_SM(float, 2);
         else if (chunks <= 4) OB200_SM(float, 4);
         else if (chunks <= 8) OB200_SM(float, 8);
-        else softmax_kernel<float><<<grid, ROW_THREADS, 0, s>>>((const float*)x, (float*)y, rows, D, scale);
+        else softmax_kernel<float><<<grid, ROW_THREADS, 0, s>>>((const float*)x, (float*)y, rows, D, scale, causal_period);
     } else {
         if (chunks <= 2) OB200_SM(__nv_bfloat16, 2);
         else if (chunks <= 4) OB200_SM(__nv_bfloat16, 4);
         else if (chunks <= 8) OB200_SM(__nv_bfloat16, 8);
-        else softmax_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, D, scale);
+        else softmax_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, D, scale, causal_period);
     }
 #undef OB200_SM
     return (int)cudaGetLastError();
+}
+
+extern "C" int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, int dtype, int num_ctas, void* stream) {
+    return ob200_softmax_causal(x, y, rows, D, scale, 0, dtype, num_ctas, stream);
 }
 
 extern "C" int ob200_bias_gelu(const void* x, void* y, const float* bias, long long rows, int D, int dtype, int num_ctas, void* stream) {

@@ -21,6 +21,7 @@
 #include <ATen/ATen.h>
 #include <ATen/NativeFunctions.h>
 #include <c10/cuda/CUDAStream.h>
+#include <torch/autograd.h>
 #include <torch/library.h>
 
 #include <atomic>
@@ -51,7 +52,8 @@ int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int 
 int ob200_filter_transpose(const void* w, void* wt, int K, int RS, int C, int elem_bytes, void* stream);
 int ob200_layernorm(const void* x, void* y, const float* gamma, const float* beta, float* mean_out, float* rstd_out, long long rows,
                     int D, float eps, int dtype, int num_ctas, void* stream);
-int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, int dtype, int num_ctas, void* stream);
+int ob200_softmax_causal(const void* x, void* y, long long rows, int D, float scale, int causal_period, int dtype, int num_ctas,
+                         void* stream);
 int ob200_bias_gelu(const void* x, void* y, const float* bias, long long rows, int D, int dtype, int num_ctas, void* stream);
 int ob200_linear_batched(const void* x, const void* w, void* y, int dtype, int batch, int M, int N, int K, long long stride_x,
                          long long stride_w, long long stride_y, int num_ctas, void* stream);
@@ -60,6 +62,12 @@ int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int 
 int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
                                float* running_var, float* save_mean, float* save_invstd, double* sums, float eps, float momentum,
                                long long rows, int C, int num_ctas, void* stream);
+int ob200_bn_act_train_forward_f32(const float* x, const float* residual, float* y, const float* gamma, const float* beta,
+                                   float* running_mean, float* running_var, float* save_mean, float* save_invstd, float eps,
+                                   float momentum, long long rows, int C, int act, int num_ctas, void* stream);
+int ob200_bn_act_backward_f32(const float* dy, const float* x, const float* yout, float* dx, float* dres, const float* gamma,
+                              const float* beta, const float* save_mean, const float* save_invstd, float* dgamma, float* dbeta,
+                              long long rows, int C, int act, int num_ctas, void* stream);
 int ob200_bn_backward_f32(const float* dy, const float* x, float* dx, const float* gamma, const float* save_mean,
                           const float* save_invstd, float* dgamma, float* dbeta, double* sums, long long rows, int C, int num_ctas,
                           void* stream);
@@ -190,20 +198,19 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_over
                     running_mean.has_value() && running_mean->defined() && running_var.has_value() && running_var->defined() &&
                     weight.defined() && weight.scalar_type() == at::kFloat && input.numel() > 0;
     const bool train_ok = g_overrides.load(std::memory_order_relaxed) && training && input.scalar_type() == at::kFloat &&
-                          is_nhwc(input) && input.size(1) % 4 == 0 && weight.defined() && weight.scalar_type() == at::kFloat &&
-                          input.numel() > 0;
+                          is_nhwc(input) && input.size(1) % 4 == 0 && input.size(1) <= 8192 && weight.defined() &&
+                          weight.scalar_type() == at::kFloat && input.numel() > 0;
     if (train_ok) {
         // cudnnBatchNormalizationForwardTrainingEx's role: batch statistics, normalise, update running statistics.
         const int64_t C = input.size(1);
         at::Tensor y = at::empty_like(input, at::MemoryFormat::ChannelsLast);
         at::Tensor save_mean = at::empty({C}, input.options()), save_invstd = at::empty({C}, input.options());
-        at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
         float* rm = (running_mean.has_value() && running_mean->defined()) ? running_mean->data_ptr<float>() : nullptr;
         float* rv = (running_var.has_value() && running_var->defined()) ? running_var->data_ptr<float>() : nullptr;
-        check(ob200_bn_train_forward_f32(input.data_ptr<float>(), y.data_ptr<float>(), weight.data_ptr<float>(), fptr(bias), rm, rv,
-                                         save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(), sums.data_ptr<double>(), (float)eps,
-                                         (float)momentum, input.numel() / C, (int)C, quota(), cur_stream()),
-              "ob200_bn_train_forward_f32");
+        check(ob200_bn_act_train_forward_f32(input.data_ptr<float>(), nullptr, y.data_ptr<float>(), weight.data_ptr<float>(), fptr(bias),
+                                             rm, rv, save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(), (float)eps,
+                                             (float)momentum, input.numel() / C, (int)C, 0, quota(), cur_stream()),
+              "ob200_bn_act_train_forward_f32");
         return std::make_tuple(y, save_mean, save_invstd, at::empty({0}, input.options().dtype(at::kByte)));
     }
     if (!ok) {
@@ -229,17 +236,16 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> cudnn_batch_norm_backward_overrid
     (void)reserve;
     const bool train = save_mean.has_value() && save_mean->defined() && save_mean->numel() > 0;
     if (g_overrides.load(std::memory_order_relaxed) && train && input.scalar_type() == at::kFloat && is_nhwc(input) &&
-        is_nhwc(grad_output) && input.size(1) % 4 == 0 && weight.defined() && save_var.has_value() && save_var->defined() &&
-        input.numel() > 0) {
+        is_nhwc(grad_output) && input.size(1) % 4 == 0 && input.size(1) <= 8192 && weight.defined() && save_var.has_value() &&
+        save_var->defined() && input.numel() > 0) {
         const int64_t C = input.size(1);
         at::Tensor dx = at::empty_like(input, at::MemoryFormat::ChannelsLast);
         at::Tensor dgamma = at::empty({C}, input.options()), dbeta = at::empty({C}, input.options());
-        at::Tensor sums = at::zeros({2 * C}, input.options().dtype(at::kDouble));
-        check(ob200_bn_backward_f32(grad_output.data_ptr<float>(), input.data_ptr<float>(), dx.data_ptr<float>(),
-                                    weight.data_ptr<float>(), save_mean->data_ptr<float>(), save_var->data_ptr<float>(),
-                                    dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), sums.data_ptr<double>(), input.numel() / C, (int)C,
-                                    quota(), cur_stream()),
-              "ob200_bn_backward_f32");
+        check(ob200_bn_act_backward_f32(grad_output.data_ptr<float>(), input.data_ptr<float>(), nullptr, dx.data_ptr<float>(), nullptr,
+                                        weight.data_ptr<float>(), nullptr, save_mean->data_ptr<float>(), save_var->data_ptr<float>(),
+                                        dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), input.numel() / C, (int)C, 0, quota(),
+                                        cur_stream()),
+              "ob200_bn_act_backward_f32");
         return std::make_tuple(dx, dgamma, dbeta);
     }
     g_fallbacks.fetch_add(1, std::memory_order_relaxed);
@@ -325,14 +331,22 @@ at::Tensor depthwise_bn_act(const at::Tensor& x, const at::Tensor& w, const c10:
     return depthwise_core(xin, w, w.size(0), w.size(1), true, fptr(scale), fptr(shift), (int)act, stride, padding, dilation);
 }
 
-at::Tensor linear_op(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias, bool relu) {
+at::Tensor linear_op(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias, bool relu,
+                     const c10::optional<at::Tensor>& residual) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.is_contiguous() && w.is_contiguous() && dtype_code(x) >= 0 &&
                     x.scalar_type() == w.scalar_type() && x.size(1) == w.size(1),
                 "orion::linear: contiguous [M,K] x [N,K] float32/bfloat16 expected");
     at::Tensor y = at::empty({x.size(0), w.size(0)}, x.options());
-    check(ob200_linear(x.data_ptr(), w.data_ptr(), y.data_ptr(), fptr(bias), relu ? 1 : 0, dtype_code(x), (int)x.size(0),
-                       (int)w.size(0), (int)x.size(1), quota(), cur_stream()),
-          "ob200_linear");
+    const bool has_res = residual.has_value() && residual->defined();
+    if (has_res)
+        TORCH_CHECK(residual->sizes() == y.sizes() && residual->is_contiguous() && residual->scalar_type() == x.scalar_type(),
+                    "orion::linear: the residual must have the output's shape and type");
+    if (x.size(0) == 0) return y;
+    // y = x . w^T + bias (+ residual, added in float32 before the result is rounded) (+ ReLU): a 1x1 convolution over M "pixels"
+    check(ob200_conv2d_fprop(x.data_ptr(), w.data_ptr(), y.data_ptr(), nullptr, fptr(bias), has_res ? residual->data_ptr() : nullptr,
+                             relu ? 1 : 0, dtype_code(x), (int)x.size(0), 1, 1, (int)x.size(1), (int)w.size(0), 1, 1, 1, 1, 0, 0, 1, 1,
+                             quota(), cur_stream()),
+          "ob200_conv2d_fprop (linear)");
     return y;
 }
 
@@ -377,12 +391,13 @@ at::Tensor layernorm_op(const at::Tensor& x, const c10::optional<at::Tensor>& ga
     return y;
 }
 
-at::Tensor softmax_op(const at::Tensor& x, double scale) {
+at::Tensor softmax_op(const at::Tensor& x, double scale, int64_t causal_period) {
     TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dtype_code(x) >= 0, "orion::softmax: contiguous float32/bfloat16 CUDA tensor expected");
     const int64_t D = x.size(-1);
     at::Tensor y = at::empty_like(x);
-    check(ob200_softmax(x.data_ptr(), y.data_ptr(), x.numel() / D, (int)D, (float)scale, dtype_code(x), quota(), cur_stream()),
-          "ob200_softmax");
+    check(ob200_softmax_causal(x.data_ptr(), y.data_ptr(), x.numel() / D, (int)D, (float)scale, (int)causal_period, dtype_code(x),
+                               quota(), cur_stream()),
+          "ob200_softmax_causal");
     return y;
 }
 
@@ -406,6 +421,62 @@ at::Tensor linear_batched_op(const at::Tensor& x, const at::Tensor& w) {
                                M * N, quota(), cur_stream()),
           "ob200_linear_batched");
     return y;
+}
+
+// ------------------------------------------------------------------ training: batch norm + residual + activation
+// y = act(batch_norm(x) + residual) as one differentiable op of two launches forward and two backward
+// (ob200_bn_act_train_forward_f32 / ob200_bn_act_backward_f32).  It stands in for the BatchNorm2d -> (+ identity) -> ReLU
+// groups of the training clients' networks, which otherwise cost a batch-norm call, an add kernel and a ReLU kernel
+// forward and their three counterparts backward.
+struct BnActTrain : public torch::autograd::Function<BnActTrain> {
+    static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& x, const c10::optional<at::Tensor>& residual,
+                              const at::Tensor& weight, const at::Tensor& bias, const c10::optional<at::Tensor>& running_mean,
+                              const c10::optional<at::Tensor>& running_var, double momentum, double eps, int64_t act) {
+        TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && is_nhwc(x) && x.size(1) % 4 == 0 && x.size(1) <= 8192,
+                    "orion::bn_act_train: channels-last float32 input with C % 4 == 0 expected");
+        const bool has_res = residual.has_value() && residual->defined();
+        if (has_res) TORCH_CHECK(residual->sizes() == x.sizes() && is_nhwc(*residual), "orion::bn_act_train: residual must match x");
+        const int64_t C = x.size(1);
+        at::Tensor y = at::empty_like(x, at::MemoryFormat::ChannelsLast);
+        at::Tensor save_mean = at::empty({C}, x.options()), save_invstd = at::empty({C}, x.options());
+        float* rm = (running_mean.has_value() && running_mean->defined()) ? running_mean->data_ptr<float>() : nullptr;
+        float* rv = (running_var.has_value() && running_var->defined()) ? running_var->data_ptr<float>() : nullptr;
+        check(ob200_bn_act_train_forward_f32(x.data_ptr<float>(), has_res ? residual->data_ptr<float>() : nullptr, y.data_ptr<float>(),
+                                             weight.data_ptr<float>(), bias.data_ptr<float>(), rm, rv, save_mean.data_ptr<float>(),
+                                             save_invstd.data_ptr<float>(), (float)eps, (float)momentum, x.numel() / C, (int)C, (int)act,
+                                             quota(), cur_stream()),
+              "ob200_bn_act_train_forward_f32");
+        ctx->saved_data["act"] = act;
+        ctx->saved_data["has_res"] = has_res;
+        // the saved output is only needed where the activation's input cannot be recomputed from x (a residual was added)
+        ctx->save_for_backward({x, weight, bias, save_mean, save_invstd, (has_res && act != 0) ? y : at::Tensor()});
+        return y;
+    }
+
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
+        auto saved = ctx->get_saved_variables();
+        const at::Tensor &x = saved[0], &weight = saved[1], &bias = saved[2], &save_mean = saved[3], &save_invstd = saved[4], &y = saved[5];
+        const int64_t act = ctx->saved_data["act"].toInt();
+        const bool has_res = ctx->saved_data["has_res"].toBool();
+        at::Tensor dy = is_nhwc(grads[0]) ? grads[0] : grads[0].contiguous(at::MemoryFormat::ChannelsLast);
+        const int64_t C = x.size(1);
+        at::Tensor dx = at::empty_like(x, at::MemoryFormat::ChannelsLast);
+        at::Tensor dres = has_res ? at::empty_like(x, at::MemoryFormat::ChannelsLast) : at::Tensor();
+        at::Tensor dgamma = at::empty({C}, x.options()), dbeta = at::empty({C}, x.options());
+        check(ob200_bn_act_backward_f32(dy.data_ptr<float>(), x.data_ptr<float>(), y.defined() ? y.data_ptr<float>() : nullptr,
+                                        dx.data_ptr<float>(), has_res ? dres.data_ptr<float>() : nullptr, weight.data_ptr<float>(),
+                                        bias.data_ptr<float>(), save_mean.data_ptr<float>(), save_invstd.data_ptr<float>(),
+                                        dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), x.numel() / C, (int)C, (int)act, quota(),
+                                        cur_stream()),
+              "ob200_bn_act_backward_f32");
+        return {dx, dres, dgamma, dbeta, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+    }
+};
+
+at::Tensor bn_act_train_op(const at::Tensor& x, const c10::optional<at::Tensor>& residual, const at::Tensor& weight, const at::Tensor& bias,
+                           const c10::optional<at::Tensor>& running_mean, const c10::optional<at::Tensor>& running_var, double momentum,
+                           double eps, int64_t act) {
+    return BnActTrain::apply(x, residual, weight, bias, running_mean, running_var, momentum, eps, act);
 }
 
 // ------------------------------------------------------------------ inference plans
@@ -490,7 +561,7 @@ at::Tensor plan_run(int64_t id, const at::Tensor& x) {
             case 1: out = depthwise_bn_act(in, st.w, st.scale, st.shift, st.act, st.stride, st.pad, st.dil); break;
             case 2: out = maxpool_op(in, st.dil[0], st.stride[0], st.pad[0]); break;   // dil carries the window size
             case 3: out = avgpool_op(in); break;
-            case 4: out = linear_op(in.dim() == 2 ? in : in.reshape({in.size(0), -1}), st.w, st.shift, st.act != 0); break;
+            case 4: out = linear_op(in.dim() == 2 ? in : in.reshape({in.size(0), -1}), st.w, st.shift, st.act != 0, c10::nullopt); break;
             case 5: out = add_act_op(in, slot[(size_t)st.res], st.act != 0); break;
             case 6: out = in.dim() == 2 ? in : in.reshape({in.size(0), -1}); break;
             default: out = in; break;
@@ -518,14 +589,15 @@ int64_t fallbacks() { return g_fallbacks.load(); }
 TORCH_LIBRARY(orion, m) {
     m.def("conv_bn_act(Tensor x, Tensor w, Tensor? scale, Tensor? shift, Tensor? residual, int act, int[] stride, int[] padding, int[] dilation) -> Tensor");
     m.def("depthwise_bn_act(Tensor x, Tensor w, Tensor? scale, Tensor? shift, int act, int[] stride, int[] padding, int[] dilation) -> Tensor");
-    m.def("linear(Tensor x, Tensor w, Tensor? bias, bool relu) -> Tensor");
+    m.def("linear(Tensor x, Tensor w, Tensor? bias, bool relu, Tensor? residual=None) -> Tensor");
     m.def("maxpool(Tensor x, int k, int stride, int pad) -> Tensor");
     m.def("avgpool(Tensor x) -> Tensor");
     m.def("add_act(Tensor a, Tensor b, bool relu) -> Tensor");
     m.def("layernorm(Tensor x, Tensor? gamma, Tensor? beta, float eps) -> Tensor");
-    m.def("softmax(Tensor x, float scale) -> Tensor");
+    m.def("softmax(Tensor x, float scale, int causal_period=0) -> Tensor");
     m.def("bias_gelu(Tensor x, Tensor? bias) -> Tensor");
     m.def("linear_batched(Tensor x, Tensor w) -> Tensor");
+    m.def("bn_act_train(Tensor x, Tensor? residual, Tensor weight, Tensor bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, float momentum, float eps, int act) -> Tensor");
     m.def("plan_create(int n_slots, int out_slot) -> int", &plan_create);
     m.def("plan_add(int plan, int kind, int src, int res, int dst, Tensor? w, Tensor? scale, Tensor? shift, int act, int[] stride, int[] pad, int[] dil) -> ()", &plan_add);
     m.def("plan_run(int plan, Tensor x) -> Tensor");
@@ -548,6 +620,10 @@ TORCH_LIBRARY_IMPL(orion, CUDA, m) {
     m.impl("bias_gelu", &bias_gelu_op);
     m.impl("linear_batched", &linear_batched_op);
     m.impl("plan_run", &plan_run);
+}
+
+TORCH_LIBRARY_IMPL(orion, Autograd, m) {
+    m.impl("bn_act_train", &bn_act_train_op);
 }
 
 TORCH_LIBRARY_IMPL(aten, CUDA, m) {

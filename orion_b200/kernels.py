@@ -35,11 +35,17 @@ def lib():
         L.ob200_bn_train_forward_f32.argtypes = [c_void_p] * 9 + [c_float, c_float, c_ll, c_int, c_int, c_void_p]
         L.ob200_bn_backward_f32.argtypes = [c_void_p] * 9 + [c_ll, c_int, c_int, c_void_p]
         L.ob200_relu_backward_f32.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_void_p]
+        L.ob200_bn_act_train_forward_f32.argtypes = [c_void_p] * 9 + [c_float, c_float, c_ll, c_int, c_int, c_int, c_void_p]
+        L.ob200_bn_act_train_forward_f32.restype = c_int
+        L.ob200_bn_act_backward_f32.argtypes = [c_void_p] * 11 + [c_ll, c_int, c_int, c_int, c_void_p]
+        L.ob200_bn_act_backward_f32.restype = c_int
         L.ob200_sgd_momentum_f32.argtypes = [c_void_p] * 3 + [c_ll, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]
         L.ob200_conv2d_wgrad.argtypes = [c_void_p] * 3 + [c_int] * 14 + [c_int, c_void_p]
         L.ob200_conv2d_wgrad.restype = c_int
         L.ob200_layernorm.argtypes = [c_void_p] * 6 + [c_ll, c_int, c_float, c_int, c_int, c_void_p]
         L.ob200_softmax.argtypes = [c_void_p] * 2 + [c_ll, c_int, c_float, c_int, c_int, c_void_p]
+        L.ob200_softmax_causal.argtypes = [c_void_p] * 2 + [c_ll, c_int, c_float, c_int, c_int, c_int, c_void_p]
+        L.ob200_softmax_causal.restype = c_int
         L.ob200_bias_gelu.argtypes = [c_void_p] * 3 + [c_ll, c_int, c_int, c_int, c_void_p]
         L.ob200_adamw_f32.argtypes = [c_void_p] * 4 + [c_ll] + [c_float] * 5 + [c_int, c_int, c_void_p]
         for name in ("ob200_layernorm", "ob200_softmax", "ob200_bias_gelu", "ob200_adamw_f32"):
@@ -249,6 +255,34 @@ def bn_backward(dy, x, gamma, save_mean, save_invstd, num_ctas=None):
     return dx, dgamma, dbeta
 
 
+def bn_act_train_forward(x, gamma, beta, running_mean, running_var, eps, momentum, act=0, residual=None, num_ctas=None):
+    """y = act(batch_norm_train(x) [+ residual]); x: [..., C] float32 -> (y, save_mean, save_invstd).  Two launches, no
+    scratch to clear; running statistics are updated in place.  act: 0 none, 1 ReLU, 2 ReLU6."""
+    assert x.is_contiguous() and x.dtype == torch.float32
+    C = x.shape[-1]
+    y = torch.empty_like(x)
+    save_mean, save_invstd = torch.empty(C, device=x.device), torch.empty(C, device=x.device)
+    _check(lib().ob200_bn_act_train_forward_f32(_ptr(x), _ptr(residual), _ptr(y), _ptr(gamma), _ptr(beta), _ptr(running_mean),
+                                                _ptr(running_var), _ptr(save_mean), _ptr(save_invstd), float(eps), float(momentum),
+                                                x.numel() // C, C, int(act), num_ctas or sm_count(), _stream()),
+           "ob200_bn_act_train_forward_f32")
+    return y, save_mean, save_invstd
+
+
+def bn_act_backward(dy, x, gamma, beta, save_mean, save_invstd, act=0, yout=None, want_dres=False, num_ctas=None):
+    """Backward of bn_act_train_forward -> (dx, dres or None, dgamma, dbeta).  `yout` (the saved forward output) is only
+    needed when the forward pass added a residual before an activation."""
+    assert dy.is_contiguous() and x.is_contiguous()
+    C = x.shape[-1]
+    dx = torch.empty_like(x)
+    dres = torch.empty_like(x) if want_dres else None
+    dgamma, dbeta = torch.empty(C, device=x.device), torch.empty(C, device=x.device)
+    _check(lib().ob200_bn_act_backward_f32(_ptr(dy), _ptr(x), _ptr(yout), _ptr(dx), _ptr(dres), _ptr(gamma), _ptr(beta),
+                                           _ptr(save_mean), _ptr(save_invstd), _ptr(dgamma), _ptr(dbeta), x.numel() // C, C, int(act),
+                                           num_ctas or sm_count(), _stream()), "ob200_bn_act_backward_f32")
+    return dx, dres, dgamma, dbeta
+
+
 def relu_backward(dy, y, num_ctas=None):
     dx = torch.empty_like(dy)
     _check(lib().ob200_relu_backward_f32(_ptr(dy), _ptr(y), _ptr(dx), dy.numel(), num_ctas or sm_count(), _stream()),
@@ -283,13 +317,14 @@ def layernorm(x, gamma, beta, eps=1e-5, num_ctas=None):
     return y
 
 
-def softmax(x, scale=1.0, num_ctas=None):
-    """softmax(x * scale) over the last dimension."""
+def softmax(x, scale=1.0, num_ctas=None, causal_period=0):
+    """softmax(x * scale) over the last dimension; with `causal_period` = sequence length, row r is query position
+    r % causal_period and later keys are masked out."""
     assert x.is_contiguous()
     D = x.shape[-1]
     y = torch.empty_like(x)
-    _check(lib().ob200_softmax(_ptr(x), _ptr(y), x.numel() // D, D, float(scale), _dtype_code(x), num_ctas or sm_count(), _stream()),
-           "ob200_softmax")
+    _check(lib().ob200_softmax_causal(_ptr(x), _ptr(y), x.numel() // D, D, float(scale), int(causal_period), _dtype_code(x),
+                                      num_ctas or sm_count(), _stream()), "ob200_softmax_causal")
     return y
 
 

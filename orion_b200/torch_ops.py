@@ -148,6 +148,84 @@ def _act_of(node, mods):
     return 0
 
 
+class FusedBNAct(nn.Module):
+    """BatchNorm2d (training mode) -> (+ residual) -> ReLU / ReLU6 as one differentiable op of two launches forward and
+    two backward (`orion::bn_act_train`).  The wrapped BatchNorm2d keeps its parameters and running statistics."""
+
+    def __init__(self, bn, act):
+        super().__init__()
+        self.bn = bn
+        self.act = act
+        self._pending_batches = 0   # num_batches_tracked is kept on the host and written back when the state is read
+        self.register_state_dict_pre_hook(lambda module, prefix, keep_vars: module.flush_batch_counter())
+
+    def flush_batch_counter(self):
+        if self._pending_batches and self.bn.num_batches_tracked is not None:
+            self.bn.num_batches_tracked += self._pending_batches
+        self._pending_batches = 0
+
+    def forward(self, x, residual=None):
+        bn = self.bn
+        fused = (bn.training and bn.track_running_stats and bn.momentum is not None and bn.affine and x.is_cuda and
+                 x.dtype == torch.float32 and x.dim() == 4 and x.shape[1] % 4 == 0 and x.shape[1] <= 8192 and
+                 x.is_contiguous(memory_format=torch.channels_last) and
+                 (residual is None or residual.is_contiguous(memory_format=torch.channels_last)))
+        if not fused:
+            y = bn(x)
+            if residual is not None:
+                y = y + residual
+            return F.relu(y) if self.act == 1 else F.relu6(y) if self.act == 2 else y
+        self._pending_batches += 1
+        return torch.ops.orion.bn_act_train(x, residual, bn.weight, bn.bias, bn.running_mean, bn.running_var, bn.momentum, bn.eps,
+                                            self.act)
+
+
+def prepare_training(model):
+    """Return a training-mode GraphModule of `model` (torchvision-style CNN) in which every BatchNorm2d -> ReLU / ReLU6 and
+    BatchNorm2d -> add -> ReLU group is one `FusedBNAct` module.  Parameters are the model's own objects (create the optimizer
+    before or after, as you like); convolutions keep going through the dispatcher overrides."""
+    load()
+    model = model.train()
+    with TRACE_LOCK:
+        gm = fx.symbolic_trace(model)
+    mods = dict(gm.named_modules())
+    g = gm.graph
+    n_fused = 0
+    for node in list(g.nodes):
+        if node.op != "call_module" or not isinstance(mods.get(node.target), nn.BatchNorm2d):
+            continue
+        bn = mods[node.target]
+        users = list(node.users)
+        if len(users) != 1:
+            continue
+        u = users[0]
+        act, act_node, add_node, res = _act_of(u, mods), None, None, None
+        if act:
+            act_node = u
+        elif u.op == "call_function" and u.target in (operator.add, operator.iadd, torch.add) and len(u.args) == 2 and not u.kwargs \
+                and all(isinstance(a, fx.Node) for a in u.args):
+            other = u.args[1] if u.args[0] is node else u.args[0]
+            uu = list(u.users)
+            if other is not node and len(uu) == 1 and _act_of(uu[0], mods):
+                add_node, res, act, act_node = u, other, _act_of(uu[0], mods), uu[0]
+        if not act:
+            continue
+        name = "orion_bn_%d" % n_fused
+        n_fused += 1
+        gm.add_module(name, FusedBNAct(bn, act))
+        with g.inserting_before(act_node):
+            new = g.call_module(name, (node.args[0],) if res is None else (node.args[0], res))
+        act_node.replace_all_uses_with(new)
+        for dead in (act_node, add_node, node):
+            if dead is not None and len(dead.users) == 0:
+                g.erase_node(dead)
+    g.lint()
+    gm.delete_all_unused_submodules()
+    gm.recompile()
+    gm.train()
+    return gm
+
+
 class PlannedModel(nn.Module):
     """A prepared model whose whole forward pass is one call into the adapter (`orion::plan_run`): the layers are
     launched from C++ in order, so the interpreter is entered once per request, not once per layer."""

@@ -1,0 +1,238 @@
+"""Parity at the sizes of the benchmark configurations (the oracle is eager PyTorch on the CPU, the reference's numeric
+path, in float32 for inference and float64 for gradients) and short co-location runs of configurations 3, 4 and 5.
+
+Tolerances are the benchmark's: float32 relative 1e-4, bfloat16 relative 2e-2, relative to the largest expected
+magnitude of the tensor that is compared."""
+import os
+
+import pytest
+import torch
+import torchvision
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(built):
+    from orion_b200 import torch_ops
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    torch_ops.load()
+    return torch_ops
+
+
+def _rel(a, b):
+    return ((a.double().cpu() - b.double().cpu()).abs().max() / b.double().abs().max()).item()
+
+
+def test_bert_base_batch8_seq384_matches_cpu_fp32(ops):
+    """Configuration 4's HP request: BERT-base (12 layers, hidden 768, 12 heads, FFN 3072), batch 8, sequence 384, bfloat16
+    on the orion kernels, against float32 CPU math on the same bfloat16-rounded weights."""
+    from benchmarking.benchmark_suite.transformer_trainer import BertQA
+    from orion_b200 import kernels
+    torch.manual_seed(21)
+    model = BertQA().to(torch.bfloat16).eval()
+    ids = torch.randint(0, 30522, (8, 384))
+    with torch.no_grad():
+        want = model.float()(ids)
+        model = model.to(torch.bfloat16).cuda()
+        before = int(torch.ops.orion.own_launches())
+        got = model(ids.cuda(), orion=True)
+        after = int(torch.ops.orion.own_launches())
+    assert kernels.read_status() == 0
+    assert after - before == 12 * 10                   # per layer: 4 GEMMs, 2 batched GEMMs, softmax, GELU, 2 LayerNorms
+    err = _rel(got.float(), want)
+    print("BERT-base b8x384: relative error %.2e" % err)
+    assert err < 2e-2
+
+
+def test_decoder_lm_batch16_seq512_matches_cpu_fp32(ops):
+    """Configuration 5's language model (16 layers, d_model 1024, 16 heads, FFN 4096, vocabulary 32000), batch 16, sequence
+    512: forward pass with causal attention on the orion kernels against float32 CPU math on the same weights."""
+    from benchmarking.benchmark_suite.transformer_trainer import DecoderLM
+    from orion_b200 import kernels
+    torch.manual_seed(22)
+    model = DecoderLM().to(torch.bfloat16).eval()
+    tokens = torch.randint(0, 32000, (16, 512))
+    with torch.no_grad():
+        want = model.float()(tokens)
+        model = model.to(torch.bfloat16).cuda()
+        before = int(torch.ops.orion.own_launches())
+        got = model(tokens.cuda(), orion=True)
+        after = int(torch.ops.orion.own_launches())
+    assert kernels.read_status() == 0
+    assert after - before == 16 * 10 + 2               # + final LayerNorm and the vocabulary projection
+    err = _rel(got.float(), want)
+    print("decoder LM b16x512: relative error %.2e" % err)
+    assert err < 2e-2
+    # the causal mask: a change of the last token must not change any earlier position's logits
+    with torch.no_grad():
+        tokens2 = tokens.clone()
+        tokens2[:, -1] = (tokens2[:, -1] + 1) % 32000
+        got2 = model(tokens2.cuda(), orion=True)
+    assert torch.equal(got2[:, :-1], got[:, :-1])
+
+
+def _no_dropout(model):
+    for m in model.modules():
+        if isinstance(m, torch.nn.Dropout):
+            m.p = 0.0          # the CPU and GPU random streams differ; the comparison needs the same function
+    return model
+
+
+class _MaskedAct(torch.nn.Module):
+    """Stands in for ReLU / ReLU6 in the float64 oracle: multiplies by the 0/1 pattern the float32 run produced at the same
+    place (taken from a queue in call order)."""
+
+    def __init__(self, queue):
+        super().__init__()
+        self.queue = queue
+
+    def forward(self, x):
+        return x * self.queue.pop(0).to(x.dtype)
+
+
+def _mask_activations(model, queue):
+    for name, child in model.named_children():
+        if isinstance(child, (torch.nn.ReLU, torch.nn.ReLU6)):
+            setattr(model, name, _MaskedAct(queue))
+        else:
+            _mask_activations(child, queue)
+    return model
+
+
+def _record_activation_patterns(prepared, ops):
+    """Forward hooks on every fused batch-norm group of a prepared model: the pattern (input passed / was clipped) of each
+    activation, in call order, as CPU bool tensors in NCHW."""
+    patterns, handles = [], []
+
+    def hook(module, inputs, output):
+        y = output.detach()
+        passed = (y > 0) & (y < 6) if module.act == 2 else (y > 0)
+        patterns.append(passed.cpu())
+    for m in prepared.modules():
+        if isinstance(m, ops.FusedBNAct):
+            handles.append(m.register_forward_hook(hook))
+    return patterns, handles
+
+
+def _grad_errors(model, ref_grads, names):
+    """Per parameter: largest absolute gradient difference over the tensor's largest float64 entry.  Tensors whose true
+    gradient is structurally zero (a per-channel shift in front of another batch norm) are left out: float32 leaves rounding
+    noise there and a relative error means nothing."""
+    scale = max(g.abs().max().item() for g in ref_grads.values())
+    out, skipped = {}, 0
+    for p in model.parameters():
+        g_ref = ref_grads[names[id(p)]]
+        if g_ref.abs().max().item() < 1e-6 * scale:
+            assert p.grad.abs().max().item() < 1e-4 * scale
+            skipped += 1
+            continue
+        out[names[id(p)]] = ((p.grad.double().cpu() - g_ref).abs().max() / g_ref.abs().max()).item()
+    return out, skipped
+
+
+def _training_step_parity(ops, name, batch, lr, expected_fallbacks, n_activations):
+    """One SGD step of the BE client (prepared for training: fused batch-norm groups, convolutions through the overrides):
+    loss and every parameter gradient against float64 on the CPU at the benchmark's float32 tolerance.
+
+    The float64 oracle applies the activation pattern of the float32 run.  Without that the comparison measures something
+    else: a pre-activation within rounding distance of the kink falls on either side, a few hundred of the 3e8 do, and one
+    flipped element moves an entry of a late layer's filter gradient (a sum over 1568 pixels) by per cent — the stock
+    cuDNN float32 path differs from plain float64 by 1.5e-1 of a tensor's largest entry on this very step."""
+    from orion_b200 import kernels
+    torch.manual_seed(31)
+    ref = _no_dropout(torchvision.models.__dict__[name](num_classes=1000)).train()
+    state = {k: v.clone() for k, v in ref.state_dict().items()}
+    x = torch.randn(batch, 3, 224, 224)
+    y = torch.randint(0, 1000, (batch,))
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    model = _no_dropout(torchvision.models.__dict__[name](num_classes=1000))
+    model.load_state_dict(state)
+    model = model.cuda().to(memory_format=torch.channels_last).train()
+    names = {id(p): n for n, p in model.named_parameters()}
+    model = ops.prepare_training(model)
+    patterns, handles = _record_activation_patterns(model, ops)
+    opt = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9)
+    fb0, own0 = int(torch.ops.orion.fallbacks()), int(torch.ops.orion.own_launches())
+    opt.zero_grad()
+    loss = torch.nn.functional.cross_entropy(model(x.cuda().contiguous(memory_format=torch.channels_last)), y.cuda())
+    loss.backward()
+    torch.cuda.synchronize()
+    fallbacks, own = int(torch.ops.orion.fallbacks()) - fb0, int(torch.ops.orion.own_launches()) - own0
+    for h in handles:
+        h.remove()
+    assert kernels.read_status() == 0
+    assert len(patterns) == n_activations
+
+    ref = _mask_activations(ref.double(), patterns)
+    loss_ref = torch.nn.functional.cross_entropy(ref(x.double()), y)
+    loss_ref.backward()
+    assert not patterns, "the oracle must meet the activations in the order the prepared model ran them"
+    errs, skipped = _grad_errors(model, {n: p.grad for n, p in ref.named_parameters()}, names)
+    worst = max(errs, key=errs.get)
+    print("%s b%d: loss %.6f (float64 %.6f); largest gradient error %.2e of the tensor's largest entry (%s), median %.2e; "
+          "%d tensors with a structurally zero gradient left out; %d orion launches, %d fallbacks" % (
+              name, batch, loss.item(), loss_ref.item(), errs[worst], worst, sorted(errs.values())[len(errs) // 2], skipped, own,
+              fallbacks))
+    assert abs(loss.item() - loss_ref.item()) / abs(loss_ref.item()) < 1e-5
+    assert errs[worst] < 1e-4
+    assert fallbacks == expected_fallbacks
+    opt.step()
+    torch.cuda.synchronize()
+    return own
+
+
+def test_resnet50_batch32_training_step_gradients_match_cpu_float64(ops):
+    """Configuration 2's BE iteration.  Every convolution (forward, data gradient, filter gradient) and batch norm
+    (fused with its residual add and ReLU) runs on the orion kernels; the one fallback is the filter gradient of the
+    3-channel stem."""
+    own = _training_step_parity(ops, "resnet50", 32, 0.1, expected_fallbacks=1, n_activations=49)
+    assert own > 53 * 3 + 53 * 2
+
+
+def test_mobilenet_v2_batch64_training_step_gradients_match_cpu_float64(ops):
+    """Configuration 3's BE iteration: the pointwise convolutions and batch norms on the orion kernels; the depthwise
+    layers' backward passes and the stem's filter gradient fall back to the stock kernels."""
+    _training_step_parity(ops, "mobilenet_v2", 64, 0.05, expected_fallbacks=18, n_activations=35)
+
+
+def _colocate(tmp_path, hp_name, be_name, rps, requests):
+    from orion_b200 import experiments as E
+    out = str(tmp_path)
+    env = {"ORION_GATE_TIMEOUT_S": 20}
+    hp = E.profile_client(hp_name, os.path.join(out, "profiles"), timeout=300)
+    be = E.profile_client(be_name, os.path.join(out, "profiles"), timeout=300)
+    solo = E.run_launch_jobs([E.client_entry(hp_name, hp, requests, rps=rps)], os.path.join(out, "solo"), extra_env=env, timeout=300)
+    hp_solo = solo["clients"][0]
+    assert hp_solo["iterations"] == requests and hp_solo["p50_latency"] > 0
+    depth = int(0.025 * hp_solo["p50_latency"] * 1e6)
+    pair = [E.client_entry(be_name, be, 100000), E.client_entry(hp_name, hp, requests, rps=rps)]
+    co = E.run_launch_jobs(pair, os.path.join(out, "pair"), depth=depth, extra_env=env, timeout=300)
+    be_c, hp_c = co["clients"]
+    st = co["scheduler"]["stats"]
+    assert hp_c["iterations"] == requests
+    assert be_c["iterations"] >= 11 and be_c["samples_per_s"] > 0
+    assert st["hp_submits"] > 0 and st["be_submits"] > 0 and st["join_timeouts"] == 0 and st["forced_iter_ends"] == 0
+    assert hp_c["p99_latency"] < 20 * hp_solo["p99_latency"]
+    print("%s + %s: HP p50 %.2f -> %.2f ms, p99 %.2f -> %.2f ms, BE %.0f samples/s" % (
+        hp_name, be_name, hp_solo["p50_latency"], hp_c["p50_latency"], hp_solo["p99_latency"], hp_c["p99_latency"],
+        be_c["samples_per_s"]))
+    return hp, be, co
+
+
+def test_configuration3_mobilenet_pair_colocates(built, tmp_path):
+    hp, be, co = _colocate(tmp_path, "mobilenet_v2_hp", "mobilenet_v2_be", 0, 150)
+    assert co["scheduler"]["own_launches"] > 150 * 50
+
+
+def test_configuration4_bert_pair_colocates(built, tmp_path):
+    hp, be, co = _colocate(tmp_path, "bert_hp", "bert_be", 20, 60)
+    assert hp[3] == 12 * 10 + 5 or hp[3] > 100     # the orion kernels of the 12 layers plus the embedding and head kernels
+    assert co["scheduler"]["own_launches"] >= 60 * 120
+
+
+def test_configuration5_resnet101_with_lm_training_colocates(built, tmp_path):
+    hp, be, co = _colocate(tmp_path, "resnet101_hp", "transformer_be", 40, 80)
+    assert hp[3] == 104 + 3 + 1                       # 104 fused convolutions, two pools, the classifier, one channel padding

@@ -94,6 +94,42 @@ def test_bn_training_forward_and_backward(K, shape):
     assert O.rel_err(dgamma, gd.grad) < 1e-4 and O.rel_err(dbeta, bd.grad) < 1e-4
 
 
+@pytest.mark.parametrize("shape", [(32, 14, 14, 256), (8, 7, 7, 2048), (4, 9, 11, 24), (64, 28, 28, 32)])
+@pytest.mark.parametrize("act,with_res", [(0, False), (1, False), (2, False), (1, True), (0, True)])
+def test_bn_fused_with_residual_and_activation(K, shape, act, with_res):
+    """y = act(batch_norm_train(x) + residual) in two launches forward and two backward, twice in a row (the second call
+    finds the scratch the first one's finishing CTAs cleaned), against float64 autograd on the CPU."""
+    C = shape[-1]
+    for attempt in range(2):
+        x = (torch.randn(*shape, device="cuda") * 2.0 + 0.7)
+        res = torch.randn(*shape, device="cuda") if with_res else None
+        g, b = torch.rand(C, device="cuda") + 0.5, torch.randn(C, device="cuda") * 0.5
+        rm, rv = torch.randn(C, device="cuda"), torch.rand(C, device="cuda") + 0.5
+        rm_ref, rv_ref = rm.double().cpu().clone(), rv.double().cpu().clone()
+        xd = x.double().cpu().reshape(-1, C).requires_grad_(True)
+        rd = res.double().cpu().reshape(-1, C).requires_grad_(True) if with_res else None
+        gd, bd = g.double().cpu().requires_grad_(True), b.double().cpu().requires_grad_(True)
+        pre = F.batch_norm(xd, rm_ref, rv_ref, gd, bd, True, 0.1, 1e-5)
+        if with_res:
+            pre = pre + rd
+        want = F.relu(pre) if act == 1 else F.relu6(pre) if act == 2 else pre
+        y, mean, invstd = K.bn_act_train_forward(x, g, b, rm, rv, 1e-5, 0.1, act=act, residual=res)
+        assert O.rel_err(y.reshape(-1, C), want.detach()) < 1e-5
+        assert O.rel_err(rm, rm_ref) < 1e-5 and O.rel_err(rv, rv_ref) < 1e-5
+        dy = torch.randn(*shape, device="cuda")
+        # The gradient reference uses the activation pattern of the float32 forward pass: an input within rounding
+        # distance of the activation's kink may fall on either side, and that is not what this test is about.
+        yc = y.double().cpu().reshape(-1, C)
+        mask = torch.ones_like(yc) if act == 0 else ((yc > 0) & (yc < 6)).double() if act == 2 else (yc > 0).double()
+        (pre * mask).backward(dy.double().cpu().reshape(-1, C))
+        dx, dres, dgamma, dbeta = K.bn_act_backward(dy, x, g, b, mean, invstd, act=act, yout=y if (with_res and act) else None,
+                                                    want_dres=with_res)
+        assert O.rel_err(dx.reshape(-1, C), xd.grad) < 1e-4
+        assert O.rel_err(dgamma, gd.grad) < 1e-4 and O.rel_err(dbeta, bd.grad) < 1e-4
+        if with_res:
+            assert O.rel_err(dres.reshape(-1, C), rd.grad) < 1e-6
+
+
 def test_relu_backward_and_sgd(K):
     y = torch.randn(4, 28, 28, 130, device="cuda")
     dy = torch.randn_like(y)
