@@ -214,7 +214,11 @@ def imagenet_loop(model_name, batchsize, train, num_iters, rps, uniform, dummy_d
                 model = torch_ops.prepare_training(model)   # batch norm + residual + ReLU groups as one op each
             momentum = 0.0 if reference_data else 0.9
             lr = 0.05 if (model_name == "mobilenet_v2" and not reference_data) else 0.1
-            optimizer = torch.optim.SGD(model.parameters(), lr=lr, momentum=momentum)
+            if os.environ.get("ORION_PREPARE", "1") == "1" and os.environ.get("ORION_DISABLE_OVERRIDES", "0") != "1":
+                from orion_b200.optim import SGD   # the whole update in one or two launches
+                optimizer = SGD(model.parameters(), lr=lr, momentum=momentum)
+            else:
+                optimizer = torch.optim.SGD(model.parameters(), lr=lr, momentum=momentum)
             criterion = torch.nn.CrossEntropyLoss().to(device)
 
             def step(batch_idx):

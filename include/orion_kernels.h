@@ -105,6 +105,10 @@ int ob200_relu_backward_f32(const float* dy, const float* y, float* dx, long lon
 /* torch.optim.SGD step with momentum on one parameter tensor (the foreach kernels behind the same trap). */
 int ob200_sgd_momentum_f32(float* p, const float* g, float* m, long long n, float lr, float mu, float wd, int nesterov,
                            int first_step, int num_ctas, void* stream);
+/* The same update over `count` tensors (host arrays of device pointers and element counts) in ceil(count / 96) launches:
+ * the role of the multi-tensor (foreach) optimizer kernels in the reference's training profiles. */
+int ob200_sgd_momentum_multi_f32(float* const* p, const float* const* g, float* const* m, const long long* n, int count, float lr,
+                                 float mu, float wd, int nesterov, int first_step, int num_ctas, void* stream);
 
 /* y[M,N] = x[M,K] . w[N,K]^T + bias, optional ReLU.  Takes the place of cublasSgemm_v2
  * (reference src/scheduler/utils_sched.cpp:490-501, trapped at src/cuda_capture/intercept_cublas.cpp:5-56). */
@@ -131,6 +135,12 @@ int ob200_binary_f32(const float* a, const float* b, float* y, long long n_elems
  * the mean reduce kernel in the reference's profiles). */
 int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, int W, int C, int k, int stride, int pad, int num_ctas,
                            void* stream);
+/* Gradient of the max-pool: the output gradient goes to the first largest element of each window in row-major order (the
+ * element the stock forward kernel records; ties are frequent behind a ReLU); dx is cleared on `stream` first.  Stands in for
+ * the max_pool_backward_nhwc kernel that reaches the reference through its cudaLaunchKernel trap
+ * (reference src/cuda_capture/intercept_temp.cpp:418-458). */
+int ob200_maxpool_backward_nhwc_f32(const float* dy, const float* x, float* dx, int Nb, int H, int W, int C, int k, int stride,
+                                    int pad, int num_ctas, void* stream);
 int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream);
 
 /* Row kernels of the transformer clients; dtype 0 = float32, 1 = bfloat16 (float32 math), D a multiple of

@@ -19,6 +19,7 @@
 #include <cudnn.h>
 #include <dlfcn.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "capture_core.h"
 
@@ -99,17 +100,45 @@ cudaError_t cudaLaunchKernelExC(const cudaLaunchConfig_t* config, const void* fu
 }
 
 static cudaError_t (*real_cudaMemcpyAsync)(void*, const void*, size_t, enum cudaMemcpyKind, cudaStream_t);
+static cudaError_t (*real_cudaStreamSynchronize)(cudaStream_t);
+
+// Host-to-device copies of a best-effort client larger than this are issued in pieces, each one waited for before the
+// next is queued.  The copy engine serves copies in the order they were queued, whatever the priority of their streams: a
+// best-effort batch of tens of megabytes queued in one piece would hold a high-priority request's input copy back for its
+// whole duration (hundreds of microseconds on PCIe).  In pieces, the high-priority copy waits for one piece at most.  This
+// is the copy engine's counterpart of the SM quota; the policy sees one memcpy record either way.  ORION_BE_COPY_CHUNK
+// sets the piece size in bytes (0: never split).
+static size_t be_copy_chunk() {
+    static const size_t v = [] {
+        const char* e = getenv("ORION_BE_COPY_CHUNK");
+        return e ? (size_t)strtoull(e, nullptr, 10) : (size_t)1 << 20;
+    }();
+    return v;
+}
+
 cudaError_t cudaMemcpyAsync(void* dst, const void* src, size_t count, enum cudaMemcpyKind kind, cudaStream_t stream) {
     REAL(cudaMemcpyAsync);
     Gate g;
     if (!gate_begin(&g, ORION_MEMCPY_RECORD, stream, 0)) return real_cudaMemcpyAsync(dst, src, count, kind, stream);
-    cudaError_t e = real_cudaMemcpyAsync(dst, src, count, kind, (cudaStream_t)g.stream);
+    cudaError_t e = cudaSuccess;
+    const size_t chunk = be_copy_chunk();
+    const orion_shared* sh = orion_capture_shared();
+    const bool best_effort = g.idx >= 0 && sh->num_clients > 1 && g.idx < sh->num_clients - 1;
+    if (best_effort && kind == cudaMemcpyHostToDevice && chunk > 0 && count > chunk) {
+        REAL(cudaStreamSynchronize);
+        for (size_t off = 0; off < count && e == cudaSuccess; off += chunk) {
+            const size_t n = count - off < chunk ? count - off : chunk;
+            e = real_cudaMemcpyAsync((char*)dst + off, (const char*)src + off, n, kind, (cudaStream_t)g.stream);
+            if (e == cudaSuccess && off + n < count) e = real_cudaStreamSynchronize((cudaStream_t)g.stream);
+        }
+    } else {
+        e = real_cudaMemcpyAsync(dst, src, count, kind, (cudaStream_t)g.stream);
+    }
     gate_end(&g);
     return e;
 }
 
 static cudaError_t (*real_cudaMemcpy)(void*, const void*, size_t, enum cudaMemcpyKind);
-static cudaError_t (*real_cudaStreamSynchronize)(cudaStream_t);
 cudaError_t cudaMemcpy(void* dst, const void* src, size_t count, enum cudaMemcpyKind kind) {
     REAL(cudaMemcpy);
     Gate g;

@@ -172,6 +172,45 @@ __global__ void __launch_bounds__(ELT_THREADS) maxpool3x3s2_nhwc_f32_kernel(cons
     }
 }
 
+// Max-pool backward over NHWC: one thread per 4 channels of one output pixel finds, per channel, the FIRST largest element
+// of its window in row-major scan order (the element torch's forward kernel records, so ties -- frequent behind a ReLU,
+// where whole windows are zero -- are routed the same way) and adds the output gradient there.  Windows overlap, so the
+// additions are atomic; dx is zero on entry.
+__global__ void __launch_bounds__(ELT_THREADS) maxpool_backward_nhwc_f32_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                              float* __restrict__ dx, int Nb, int H, int W, int C,
+                                                                              int P, int Q, int k, int stride, int pad) {
+    const int c4 = C >> 2;
+    const long long total = (long long)Nb * P * Q * c4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % c4) * 4;
+        long long t = i / c4;
+        const int q = (int)(t % Q); t /= Q;
+        const int p = (int)(t % P);
+        const int n = (int)(t / P);
+        float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        long long at[4] = {-1, -1, -1, -1};
+        for (int r = 0; r < k; r++) {
+            const int h = p * stride - pad + r;
+            if (h < 0 || h >= H) continue;
+            for (int s = 0; s < k; s++) {
+                const int w = q * stride - pad + s;
+                if (w < 0 || w >= W) continue;
+                const long long off = (((long long)n * H + h) * W + w) * C + c;
+                const float4 v = __ldg(reinterpret_cast<const float4*>(x + off));
+                const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (e[j] > m[j] || at[j] < 0) { m[j] = e[j]; at[j] = off + j; }
+            }
+        }
+        const float4 g = __ldcs(reinterpret_cast<const float4*>(dy + (((long long)n * P + p) * Q + q) * C + c));
+        const float ge[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (at[j] >= 0) atomicAdd(dx + at[j], ge[j]);
+    }
+}
+
 // Global average pool NHWC [Nb, HW, C] -> [Nb, C]; one thread per (image, channel),
 // consecutive threads read consecutive channels so every row read is coalesced.
 __global__ void __launch_bounds__(ELT_THREADS) avgpool_nhwc_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int Nb,
@@ -255,6 +294,23 @@ extern "C" int ob200_maxpool_nhwc_f32(const float* x, float* y, int Nb, int H, i
     OB200_ELASTIC_HBM(maxpool_nhwc_f32_kernel, ELT_CTAS_PER_SM);
     maxpool_nhwc_f32_kernel<<<elt_grid(total, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, H, W, C, P, Q, k, stride,
                                                                                                pad);
+    return (int)cudaGetLastError();
+}
+
+// dx = gradient of ob200_maxpool_nhwc_f32 (same arguments); dx is cleared on `stream` first.
+extern "C" int ob200_maxpool_backward_nhwc_f32(const float* dy, const float* x, float* dx, int Nb, int H, int W, int C, int k,
+                                               int stride, int pad, int num_ctas, void* stream) {
+    if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || (C & 3) || k <= 0 || stride <= 0 || pad < 0 || pad >= k || num_ctas <= 0) return -1;
+    if (Nb == 0) return 0;
+    const int P = (H + 2 * pad - k) / stride + 1, Q = (W + 2 * pad - k) / stride + 1;
+    if (P <= 0 || Q <= 0) return -1;
+    if (((uintptr_t)dy | (uintptr_t)x | (uintptr_t)dx) % 16) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)Nb * H * W * C * sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    const long long total = (long long)Nb * P * Q * (C / 4);
+    OB200_ELASTIC_HBM(maxpool_backward_nhwc_f32_kernel, ELT_CTAS_PER_SM);
+    maxpool_backward_nhwc_f32_kernel<<<elt_grid(total, num_ctas), ELT_THREADS, 0, s>>>(dy, x, dx, Nb, H, W, C, P, Q, k, stride, pad);
     return (int)cudaGetLastError();
 }
 

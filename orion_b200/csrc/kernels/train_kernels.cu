@@ -265,6 +265,69 @@ __global__ void __launch_bounds__(TR_THREADS) sgd_momentum_kernel(float* __restr
     }
 }
 
+// The same update for a whole list of parameter tensors in one launch.  The pointers travel in the kernel's parameter
+// block (no table in device memory to build or copy); the work is cut into chunks of SGD_CHUNK elements and the blocks of
+// a persistent grid walk the chunks.
+constexpr int SGD_MAX_TENSORS = 96;
+constexpr int SGD_CHUNK = 16384;
+struct SgdTable {
+    float* p[SGD_MAX_TENSORS];
+    const float* g[SGD_MAX_TENSORS];
+    float* m[SGD_MAX_TENSORS];
+    int first_chunk[SGD_MAX_TENSORS + 1];   // prefix sum of ceil(n / SGD_CHUNK)
+    long long n[SGD_MAX_TENSORS];
+    int count;
+};
+__global__ void __launch_bounds__(TR_THREADS) sgd_momentum_multi_kernel(const __grid_constant__ SgdTable t, float lr, float mu, float wd,
+                                                                       int nesterov, int first_step) {
+    const int total_chunks = t.first_chunk[t.count];
+    for (int chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+        int lo = 0, hi = t.count - 1;   // last tensor whose first chunk is <= chunk
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (t.first_chunk[mid] <= chunk) lo = mid; else hi = mid - 1;
+        }
+        const long long begin = (long long)(chunk - t.first_chunk[lo]) * SGD_CHUNK;
+        const long long end = begin + SGD_CHUNK < t.n[lo] ? begin + SGD_CHUNK : t.n[lo];
+        float* __restrict__ p = t.p[lo];
+        const float* __restrict__ g = t.g[lo];
+        float* __restrict__ m = t.m[lo];
+        if ((((uintptr_t)p | (uintptr_t)g | (uintptr_t)m) & 15) == 0) {
+            const long long e4 = begin + ((end - begin) & ~3LL);
+            for (long long i = begin + 4LL * threadIdx.x; i < e4; i += 4LL * blockDim.x) {
+                float4 pv = *reinterpret_cast<float4*>(p + i);
+                const float4 gv = __ldcs(reinterpret_cast<const float4*>(g + i));
+                float4 mv = first_step ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<float4*>(m + i);
+                float* pe = &pv.x;
+                float* me = &mv.x;
+                const float* ge = &gv.x;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float grad = ge[e] + wd * pe[e];
+                    const float mom = first_step ? grad : mu * me[e] + grad;
+                    me[e] = mom;
+                    pe[e] -= lr * (nesterov ? grad + mu * mom : mom);
+                }
+                *reinterpret_cast<float4*>(m + i) = mv;
+                *reinterpret_cast<float4*>(p + i) = pv;
+            }
+            for (long long i = e4 + threadIdx.x; i < end; i += blockDim.x) {
+                const float grad = g[i] + wd * p[i];
+                const float mom = first_step ? grad : mu * m[i] + grad;
+                m[i] = mom;
+                p[i] -= lr * (nesterov ? grad + mu * mom : mom);
+            }
+        } else {
+            for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+                const float grad = g[i] + wd * p[i];
+                const float mom = first_step ? grad : mu * m[i] + grad;
+                m[i] = mom;
+                p[i] -= lr * (nesterov ? grad + mu * mom : mom);
+            }
+        }
+    }
+}
+
 // Grid for the per-channel elementwise kernels: like grid_for, rounded down so that the grid stride (grid *
 // TR_THREADS float4 elements) is a multiple of the channel-quad count whenever that costs little.
 static inline int grid_for_channels(long long items, int num_ctas, int per_sm, int c4);
@@ -379,4 +442,36 @@ extern "C" int ob200_sgd_momentum_f32(float* p, const float* g, float* m, long l
     OB200_ELASTIC_HBM(sgd_momentum_kernel, 4);
     sgd_momentum_kernel<<<grid_for(n, num_ctas, 4), TR_THREADS, 0, (cudaStream_t)stream>>>(p, g, m, n, lr, mu, wd, nesterov, first_step);
     return (int)cudaGetLastError();
+}
+
+// SGD with momentum over `count` parameter tensors (host arrays of device pointers and element counts) in
+// ceil(count / 96) launches instead of one per tensor.
+extern "C" int ob200_sgd_momentum_multi_f32(float* const* p, const float* const* g, float* const* m, const long long* n, int count,
+                                            float lr, float mu, float wd, int nesterov, int first_step, int num_ctas, void* stream) {
+    if (count <= 0) return 0;
+    if (!p || !g || !m || !n || num_ctas <= 0) return -1;
+    for (int base = 0; base < count; base += SGD_MAX_TENSORS) {
+        SgdTable t;
+        t.count = 0;
+        t.first_chunk[0] = 0;
+        for (int i = base; i < count && t.count < SGD_MAX_TENSORS; i++) {
+            if (n[i] <= 0) continue;
+            if (!p[i] || !g[i] || !m[i]) return -1;
+            const int k = t.count++;
+            t.p[k] = p[i];
+            t.g[k] = g[i];
+            t.m[k] = m[i];
+            t.n[k] = n[i];
+            t.first_chunk[k + 1] = t.first_chunk[k] + (int)((n[i] + SGD_CHUNK - 1) / SGD_CHUNK);
+        }
+        if (t.count == 0) continue;
+        const int chunks = t.first_chunk[t.count];
+        const long long cap = (long long)num_ctas * 4;
+        OB200_ELASTIC_HBM(sgd_momentum_multi_kernel, 4);
+        sgd_momentum_multi_kernel<<<(unsigned)(chunks < cap ? chunks : cap), TR_THREADS, 0, (cudaStream_t)stream>>>(t, lr, mu, wd, nesterov,
+                                                                                                              first_step);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
 }

@@ -180,10 +180,24 @@ class FusedBNAct(nn.Module):
                                             self.act)
 
 
+class OrionMaxPoolTrain(nn.Module):
+    """MaxPool2d with a gradient kernel of its own (no index tensor is stored)."""
+
+    def __init__(self, k, stride, pad):
+        super().__init__()
+        self.k, self.stride, self.pad = k, stride, pad
+
+    def forward(self, x):
+        if x.is_cuda and x.dtype == torch.float32 and x.shape[1] % 4 == 0 and x.is_contiguous(memory_format=torch.channels_last):
+            return torch.ops.orion.maxpool_train(x, self.k, self.stride, self.pad)
+        return F.max_pool2d(x, self.k, self.stride, self.pad)
+
+
 def prepare_training(model):
     """Return a training-mode GraphModule of `model` (torchvision-style CNN) in which every BatchNorm2d -> ReLU / ReLU6 and
-    BatchNorm2d -> add -> ReLU group is one `FusedBNAct` module.  Parameters are the model's own objects (create the optimizer
-    before or after, as you like); convolutions keep going through the dispatcher overrides."""
+    BatchNorm2d -> add -> ReLU group is one `FusedBNAct` module and max-pools run on the orion kernels in both directions.
+    Parameters are the model's own objects (create the optimizer before or after, as you like); convolutions keep going
+    through the dispatcher overrides."""
     load()
     model = model.train()
     with TRACE_LOCK:
@@ -192,6 +206,17 @@ def prepare_training(model):
     g = gm.graph
     n_fused = 0
     for node in list(g.nodes):
+        m = mods.get(node.target) if node.op == "call_module" else None
+        if isinstance(m, nn.MaxPool2d) and not m.ceil_mode and _one(m.dilation) == 1 and not m.return_indices and \
+                _square(m.kernel_size) and _square(m.stride or m.kernel_size) and _square(m.padding) and _square(m.dilation):
+            name = "orion_pool_%d" % n_fused
+            n_fused += 1
+            gm.add_module(name, OrionMaxPoolTrain(_one(m.kernel_size), _one(m.stride or m.kernel_size), _one(m.padding)))
+            with g.inserting_before(node):
+                new = g.call_module(name, node.args)
+            node.replace_all_uses_with(new)
+            g.erase_node(node)
+            continue
         if node.op != "call_module" or not isinstance(mods.get(node.target), nn.BatchNorm2d):
             continue
         bn = mods[node.target]

@@ -8,6 +8,10 @@ the committed files.
 
     python tests/golden/make_golden.py            # regenerate everything
     python tests/golden/make_golden.py --check    # verify the committed logs instead
+    python tests/golden/make_golden.py --import-recorded <recorded.script> [--name c2_recorded] [--iters 60]
+        # adopt an arrival script the live scheduler recorded on a GPU (ORION_RECORD_SCRIPT) as a further case: its
+        # profile files (real per-kernel profiles of that run) are copied next to it, the run is cut to --iters
+        # requests per client, and the reference scheduler's log for it is committed like the others
 
 Profiles are synthetic rows in the model_kernels format (same five columns, value
 ranges modelled on profiled convolution / batch-norm / elementwise kernels: SM
@@ -143,18 +147,53 @@ def run_ref(script, log):
     return json.loads(out.stdout.strip().splitlines()[-1])
 
 
+# Cases recorded from live runs on a GPU (see --import-recorded); their scripts and profiles are committed as they are.
+RECORDED = ["c2_recorded"]
+
+
+def import_recorded(src, name, iters):
+    """Copy a recorded arrival script into this directory as case `name`: profile paths become local copies, every client
+    runs `iters` requests (the open-loop gap list is cut to match)."""
+    out, client = [], -1
+    for line in open(src):
+        tok = line.split()
+        if tok[:1] == ["client"]:
+            client = int(tok[1])
+        if tok[:1] == ["profile"]:
+            local = "%s.c%d.profile" % (name, client)
+            with open(tok[1]) as f, open(os.path.join(HERE, local), "w") as g:
+                g.write(f.read())
+            line = "  profile %s %s\n" % (local, tok[2])
+        elif tok[:1] == ["train"]:
+            tok[tok.index("num_iters") + 1] = str(iters)
+            line = "  " + " ".join(tok) + "\n"
+        elif tok[:2] == ["gaps", "open"]:
+            gaps = tok[2:2 + iters]
+            gaps += ["0"] * (iters - len(gaps))
+            line = "  gaps open " + " ".join(gaps) + "\n"
+        out.append(line)
+    with open(os.path.join(HERE, name + ".script"), "w") as f:
+        f.writelines(out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--import-recorded", default="")
+    ap.add_argument("--name", default="c2_recorded")
+    ap.add_argument("--iters", type=int, default=60)
     args = ap.parse_args()
     if not os.path.exists(os.path.join(REF_DIR, "ref_replay")):
         sys.exit("build the reference first: make -C oracle ref")
+    if args.import_recorded:
+        import_recorded(args.import_recorded, args.name, args.iters)
     index = {}
     tmp = os.path.join(HERE, "_tmp.log")
-    for case in CASES:
+    recorded = [dict(name=n, recorded=True) for n in RECORDED if os.path.exists(os.path.join(HERE, n + ".script"))]
+    for case in CASES + recorded:
         kw = dict(case)
         name = kw.pop("name")
-        if not args.check:
+        if not args.check and not kw.pop("recorded", False):
             build_case(name, out_dir=HERE, **kw)
         script = os.path.join(HERE, name + ".script")
         info = run_ref(script, tmp)

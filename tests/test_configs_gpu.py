@@ -164,7 +164,8 @@ def _training_step_parity(ops, name, batch, lr, expected_fallbacks, n_activation
     names = {id(p): n for n, p in model.named_parameters()}
     model = ops.prepare_training(model)
     patterns, handles = _record_activation_patterns(model, ops)
-    opt = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9)
+    from orion_b200.optim import SGD
+    opt = SGD(model.parameters(), lr=lr, momentum=0.9)
     fb0, own0 = int(torch.ops.orion.fallbacks()), int(torch.ops.orion.own_launches())
     opt.zero_grad()
     loss = torch.nn.functional.cross_entropy(model(x.cuda().contiguous(memory_format=torch.channels_last)), y.cuda())
@@ -198,9 +199,9 @@ def _training_step_parity(ops, name, batch, lr, expected_fallbacks, n_activation
 
 
 def test_resnet50_batch32_training_step_gradients_match_cpu_float64(ops):
-    """Configuration 2's BE iteration.  Every convolution (forward, data gradient, filter gradient) and batch norm
-    (fused with its residual add and ReLU) runs on the orion kernels; the one fallback is the filter gradient of the
-    3-channel stem."""
+    """Configuration 2's BE iteration.  Every convolution (forward, data gradient, filter gradient), every batch norm (fused
+    with its residual add and ReLU), the max-pool in both directions and the SGD update run on the orion kernels; the one
+    fallback is the filter gradient of the 3-channel stem."""
     own = _training_step_parity(ops, "resnet50", 32, 0.1, expected_fallbacks=1, n_activations=49)
     assert own > 53 * 3 + 53 * 2
 

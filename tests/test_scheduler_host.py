@@ -46,7 +46,8 @@ DRIVER = textwrap.dedent('''
     st = threading.Thread(target=ps.run_scheduler, args=(
         barriers, [t.native_id for t in ths], ["m"] * N, [c["profile"] for c in cfg["clients"]], [None] * N,
         [c["num_kernels"] for c in cfg["clients"]], [None] * N, [c["iters"] for c in cfg["clients"]], True, True,
-        cfg.get("reef", False), False, cfg.get("depth", 160000), 1, 1, [c["train"] for c in cfg["clients"]]))
+        cfg.get("reef", False), False, cfg.get("depth", 160000), cfg.get("hp_limit", 1), cfg.get("update_start", 1),
+        [c["train"] for c in cfg["clients"]]))
     t0 = time.time(); st.start()
     for t in ths: t.join()
     st.join()
@@ -198,3 +199,35 @@ def ctypes_lib(path):
     lib.orion_capture_clamp_grid.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_int]
     lib.orion_capture_clamp_grid.restype = ctypes.c_uint
     return lib
+
+
+def test_two_best_effort_clients_share_the_device_with_one_high_priority_client(built, tmp_path):
+    """Three live clients (the reference's benchmarking/multi_client_example.json has this shape): both best-effort clients
+    make progress round-robin, each is stopped when the high-priority client is done, every op reaches the client that
+    queued it."""
+    be = _profile(tmp_path, "be", [(1, 40, 9000), (0, 60, 5000), (-1, 30, 3000)] * 6)
+    be2 = _profile(tmp_path, "be2", [(0, 20, 4000), (1, 50, 7000)] * 10)
+    hp = _profile(tmp_path, "hp", [(1, 60, 8000), (0, 20, 2000)] * 6)
+    r = _run({"clients": [{"profile": be, "num_kernels": 18, "iters": 100000, "train": True, "ops": [1] + [0] * 18},
+                          {"profile": be2, "num_kernels": 20, "iters": 100000, "train": True, "ops": [0] * 20},
+                          {"profile": hp, "num_kernels": 12, "iters": 80, "train": False, "ops": [1] + [0] * 12}],
+              "depth": 30000}, env_extra={"ORION_MAX_SMS": "148"})
+    assert r["done"][2] == 80 and not r["wrong"]
+    assert 10 <= r["done"][0] < 100000 and 10 <= r["done"][1] < 100000
+    assert r["stats"]["be_submits"] >= 10 * (19 + 20) and r["stats"]["join_timeouts"] == 0 and r["stats"]["forced_iter_ends"] == 0
+    assert r["quotas"][2] == [0]
+
+
+def test_high_priority_training_client_runs_the_update_phase_rule(built, tmp_path):
+    """The high-priority client trains (reference scheduler_eval.cpp:338,427-445): best-effort ops are also admitted once
+    the high-priority iteration has reached its update phase (op index >= update_start) and the op before it has completed,
+    if they need no more than the SM threshold, which is bisected every ten iterations against the tolerated iteration time."""
+    be = _profile(tmp_path, "be", [(1, 20, 9000), (0, 30, 5000)] * 8)
+    hp = _profile(tmp_path, "hp", [(1, 60, 8000)] * 8 + [(0, 10, 2000)] * 6)
+    r = _run({"clients": [{"profile": be, "num_kernels": 16, "iters": 100000, "train": True, "ops": [0] * 16},
+                          {"profile": hp, "num_kernels": 14, "iters": 45, "train": True, "ops": [1] + [0] * 14}],
+              "depth": 20000, "hp_limit": 1000, "update_start": 8}, env_extra={"ORION_MAX_SMS": "148"})
+    assert r["done"][1] == 45 and not r["wrong"]
+    assert r["done"][0] >= 10
+    assert r["stats"]["queries"] > 0 and r["stats"]["join_timeouts"] == 0
+    assert r["hp_samples"] == 45

@@ -190,3 +190,39 @@ def test_conv_wgrad_fp32(K, shape):
     dw = K.conv2d_wgrad_nhwc(x, dy, (R, R), (stride, stride), (pad, pad))
     assert K.read_status() == 0
     assert O.rel_err(dw, _wgrad_ref(x, dy, (R, R), stride, pad, 1)) < TOL
+
+
+@pytest.mark.parametrize("shape,k,stride,pad", [((32, 112, 112, 64), 3, 2, 1), ((2, 9, 11, 8), 3, 2, 1), ((3, 8, 8, 12), 2, 2, 0)])
+def test_maxpool_backward_routes_like_torch_including_ties(K, shape, k, stride, pad):
+    """Behind a ReLU whole windows are zero: the gradient must go to the first element of the window, as torch's does."""
+    import torch.nn.functional as F
+    from orion_b200 import torch_ops
+    torch_ops.load()
+    x = torch.relu(torch.randn(*shape, device="cuda")).permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+    x1 = x.clone().requires_grad_(True)
+    x2 = x.clone().requires_grad_(True)
+    y1 = torch.ops.orion.maxpool_train(x1, k, stride, pad)
+    y2 = F.max_pool2d(x2, k, stride, pad)
+    assert torch.equal(y1, y2)
+    dy = torch.randn_like(y2)
+    y1.backward(dy)
+    y2.backward(dy)
+    assert (x1.grad - x2.grad).abs().max().item() <= 1e-6 * x2.grad.abs().max().item()
+
+
+def test_multi_tensor_sgd_matches_torch(K):
+    from orion_b200.optim import SGD
+    torch.manual_seed(3)
+    shapes = [(64, 3, 7, 7), (64,), (1000, 2048), (1001,), (3, 5, 7), (512, 512, 3, 3)] + [(17,)] * 120
+    ours = [torch.nn.Parameter(torch.randn(*s, device="cuda")) for s in shapes]
+    ref = [torch.nn.Parameter(p.detach().clone()) for p in ours]
+    o1 = SGD(ours, lr=0.1, momentum=0.9, weight_decay=1e-4)
+    o2 = torch.optim.SGD(ref, lr=0.1, momentum=0.9, weight_decay=1e-4)
+    for step in range(3):
+        for a, b in zip(ours, ref):
+            g = torch.randn_like(a)
+            a.grad, b.grad = g.clone(), g.clone()
+        o1.step()
+        o2.step()
+        for a, b in zip(ours, ref):
+            assert (a - b).abs().max().item() <= 2e-6 * max(1.0, b.abs().max().item()), step
