@@ -22,6 +22,9 @@ import torch.nn.functional as F
 
 from .train_imagenet import run_client
 
+# Training clients use the orion LayerNorm / GELU / cross-entropy / AdamW kernels unless ORION_PREPARE=0 or the overrides are off.
+ORION_TRAIN_KERNELS = os.environ.get("ORION_PREPARE", "1") == "1" and os.environ.get("ORION_DISABLE_OVERRIDES", "0") != "1"
+
 BERT = dict(layers=12, hidden=768, heads=12, ffn=3072, vocab=30528, max_pos=512, seq=384)
 LM = dict(layers=16, hidden=1024, heads=16, ffn=4096, vocab=32000, seq=512)
 
@@ -41,6 +44,12 @@ class BertLayer(nn.Module):
         b, s, h = x.shape
         q, k, v = self.qkv(x).view(b, s, 3, self.heads, h // self.heads).permute(2, 0, 3, 1, 4)
         ctx = F.scaled_dot_product_attention(q, k, v, is_causal=causal).transpose(1, 2).reshape(b, s, h)
+        if ORION_TRAIN_KERNELS and x.is_cuda and self.training:
+            # LayerNorm and bias + GELU, forward and backward, on the orion kernels (the GEMMs and the attention stay stock)
+            ops = torch.ops.orion
+            x = ops.layernorm_train((x + self.out(ctx)).contiguous(), self.ln1.weight, self.ln1.bias, self.ln1.eps)
+            hid = ops.bias_gelu_train(F.linear(x, self.fc1.weight), self.fc1.bias)
+            return ops.layernorm_train((x + self.fc2(hid)).contiguous(), self.ln2.weight, self.ln2.bias, self.ln2.eps)
         x = self.ln1(x + self.out(ctx))
         return self.ln2(x + self.fc2(F.gelu(self.fc1(x))))
 
@@ -112,6 +121,13 @@ class DecoderLM(nn.Module):
         return ops.linear(y, self.head.weight, None, False).view(b, s, -1)
 
 
+def _adamw(params, lr):
+    if ORION_TRAIN_KERNELS and torch.cuda.is_available():
+        from orion_b200.optim import AdamW
+        return AdamW(params, lr=lr)
+    return torch.optim.AdamW(params, lr=lr)
+
+
 def _pinned(t):
     return t.pin_memory() if torch.cuda.is_available() else t
 
@@ -127,7 +143,7 @@ def bert_loop(batchsize, train, num_iters, rps, uniform, dummy_data, local_rank,
         state = {"ids": ids.to(device, non_blocking=True), "lab": labels.to(device, non_blocking=True)}
         if train:
             model.train()
-            opt = torch.optim.AdamW(model.parameters(), lr=3e-5)
+            opt = _adamw(model.parameters(), lr=3e-5)
 
             def step(batch_idx):
                 if not resident:
@@ -162,14 +178,17 @@ def transformer_loop(batchsize, train, num_iters, rps, uniform, dummy_data, loca
         state = {"tok": tokens.to(device, non_blocking=True)}
         if train:
             model.train()
-            opt = torch.optim.AdamW(model.parameters(), lr=3e-4)
+            opt = _adamw(model.parameters(), lr=3e-4)
 
             def step(batch_idx):
                 if not resident:
                     state["tok"] = tokens.to(device, non_blocking=True)
                 opt.zero_grad()
                 logits = model(state["tok"][:, :-1])
-                loss = F.cross_entropy(logits.float().view(-1, vocab), state["tok"][:, 1:].reshape(-1))
+                if ORION_TRAIN_KERNELS:   # loss and its gradient straight from the bfloat16 logits, one pass each
+                    loss = torch.ops.orion.cross_entropy(logits.reshape(-1, vocab), state["tok"][:, 1:].reshape(-1))
+                else:
+                    loss = F.cross_entropy(logits.float().view(-1, vocab), state["tok"][:, 1:].reshape(-1))
                 loss.backward()
                 opt.step()
                 return loss

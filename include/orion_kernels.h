@@ -154,6 +154,29 @@ int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, in
  * 0..D-1, and keys after the query position get probability 0 (causal_period = 0: no mask). */
 int ob200_softmax_causal(const void* x, void* y, long long rows, int D, float scale, int causal_period, int dtype, int num_ctas,
                          void* stream);
+
+/* Training side of the transformer clients (dtype 0 float32, 1 bfloat16; parameters in the activations' type).  They
+ * stand in for the kernels the reference's BERT training profile lists (reference benchmarking/model_kernels/bert_8_fb1:
+ * vectorized_layer_norm_kernel, layer_norm_grad_input_kernel, GammaBetaBackwardCUDAKernel, the GELU elementwise kernels,
+ * softmax / nll_loss forward and backward, multi_tensor_apply_kernel), which reach the reference through its cudaLaunchKernel
+ * trap (reference src/cuda_capture/intercept_temp.cpp:418-458).  Per-column parameter gradients are summed in a fixed order. */
+int ob200_layernorm_train_forward(const void* x, void* y, const void* gamma, const void* beta, float* mean, float* rstd, long long rows,
+                                  int D, float eps, int dtype, int num_ctas, void* stream);
+int ob200_layernorm_backward(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                             void* dgamma, void* dbeta, long long rows, int D, int dtype, int num_ctas, void* stream);
+int ob200_bias_gelu_train_forward(const void* x, const void* bias, void* y, long long rows, int D, int dtype, int num_ctas, void* stream);
+int ob200_bias_gelu_backward(const void* dy, const void* x, const void* bias, void* dx, void* dbias, long long rows, int D, int dtype,
+                             int num_ctas, void* stream);
+/* Cross-entropy over a large vocabulary straight from the logits' own type: loss[row] and logsumexp[row]; the gradient of the
+ * mean loss, (softmax - onehot) * grad[0] / rows, is written in the logits' type. */
+int ob200_cross_entropy_forward(const void* logits, const long long* target, float* loss, float* lse, long long rows, int V, int dtype,
+                                void* stream);
+int ob200_cross_entropy_backward(const void* logits, const long long* target, const float* lse, const float* grad, void* dlogits,
+                                 long long rows, int V, int dtype, void* stream);
+/* torch.optim.AdamW over `count` tensors of one type (host arrays of device pointers; state in the parameters' type) in
+ * ceil(count / 72) launches. */
+int ob200_adamw_multi(void* const* p, const void* const* g, void* const* m, void* const* v, const long long* n, int count, float lr,
+                      float beta1, float beta2, float eps, float weight_decay, int step, int dtype, int num_ctas, void* stream);
 int ob200_bias_gelu(const void* x, void* y, const float* bias, long long rows, int D, int dtype, int num_ctas, void* stream);
 /* torch.optim.AdamW step number `step` (>= 1) on one float32 tensor. */
 int ob200_adamw_f32(float* p, const float* g, float* m, float* v, long long n, float lr, float beta1, float beta2, float eps,

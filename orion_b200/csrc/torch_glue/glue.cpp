@@ -62,6 +62,19 @@ int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int 
 int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
                                float* running_var, float* save_mean, float* save_invstd, double* sums, float eps, float momentum,
                                long long rows, int C, int num_ctas, void* stream);
+int ob200_layernorm_train_forward(const void* x, void* y, const void* gamma, const void* beta, float* mean, float* rstd, long long rows,
+                                  int D, float eps, int dtype, int num_ctas, void* stream);
+int ob200_layernorm_backward(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                             void* dgamma, void* dbeta, long long rows, int D, int dtype, int num_ctas, void* stream);
+int ob200_bias_gelu_train_forward(const void* x, const void* bias, void* y, long long rows, int D, int dtype, int num_ctas, void* stream);
+int ob200_bias_gelu_backward(const void* dy, const void* x, const void* bias, void* dx, void* dbias, long long rows, int D, int dtype,
+                             int num_ctas, void* stream);
+int ob200_cross_entropy_forward(const void* logits, const long long* target, float* loss, float* lse, long long rows, int V, int dtype,
+                                void* stream);
+int ob200_cross_entropy_backward(const void* logits, const long long* target, const float* lse, const float* grad, void* dlogits,
+                                 long long rows, int V, int dtype, void* stream);
+int ob200_adamw_multi(void* const* p, const void* const* g, void* const* m, void* const* v, const long long* n, int count, float lr,
+                      float beta1, float beta2, float eps, float weight_decay, int step, int dtype, int num_ctas, void* stream);
 int ob200_maxpool_backward_nhwc_f32(const float* dy, const float* x, float* dx, int Nb, int H, int W, int C, int k, int stride,
                                     int pad, int num_ctas, void* stream);
 int ob200_sgd_momentum_multi_f32(float* const* p, const float* const* g, float* const* m, const long long* n, int count, float lr,
@@ -534,6 +547,123 @@ void sgd_step_op(at::TensorList params, at::TensorList grads, at::TensorList buf
           "ob200_sgd_momentum_multi_f32");
 }
 
+// ------------------------------------------------------------------ training ops of the transformer clients
+struct LayerNormTrain : public torch::autograd::Function<LayerNormTrain> {
+    static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta,
+                              double eps) {
+        TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dtype_code(x) >= 0 && gamma.scalar_type() == x.scalar_type() &&
+                        beta.scalar_type() == x.scalar_type() && gamma.is_contiguous() && beta.is_contiguous(),
+                    "orion::layernorm_train: contiguous float32/bfloat16 input with parameters of the same type expected");
+        const int64_t D = x.size(-1), rows = x.numel() / D;
+        at::Tensor y = at::empty_like(x);
+        at::Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat)), rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+        check(ob200_layernorm_train_forward(x.data_ptr(), y.data_ptr(), gamma.data_ptr(), beta.data_ptr(), mean.data_ptr<float>(),
+                                            rstd.data_ptr<float>(), rows, (int)D, (float)eps, dtype_code(x), quota(), cur_stream()),
+              "ob200_layernorm_train_forward");
+        ctx->save_for_backward({x, gamma, mean, rstd});
+        return y;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
+        auto saved = ctx->get_saved_variables();
+        const at::Tensor &x = saved[0], &gamma = saved[1], &mean = saved[2], &rstd = saved[3];
+        at::Tensor dy = grads[0].contiguous();
+        const int64_t D = x.size(-1), rows = x.numel() / D;
+        at::Tensor dx = at::empty_like(x), dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
+        check(ob200_layernorm_backward(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                       dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), rows, (int)D, dtype_code(x), quota(),
+                                       cur_stream()),
+              "ob200_layernorm_backward");
+        g_own_launches.fetch_add(1, std::memory_order_relaxed);   // two kernels behind that call
+        return {dx, dgamma, dbeta, at::Tensor()};
+    }
+};
+at::Tensor layernorm_train_op(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps) {
+    return LayerNormTrain::apply(x, gamma, beta, eps);
+}
+
+struct BiasGeluTrain : public torch::autograd::Function<BiasGeluTrain> {
+    static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& x, const at::Tensor& bias) {
+        TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dtype_code(x) >= 0 && bias.scalar_type() == x.scalar_type() && bias.is_contiguous() &&
+                        bias.numel() == x.size(-1),
+                    "orion::bias_gelu_train: contiguous float32/bfloat16 input and a bias of the same type expected");
+        const int64_t D = x.size(-1);
+        at::Tensor y = at::empty_like(x);
+        check(ob200_bias_gelu_train_forward(x.data_ptr(), bias.data_ptr(), y.data_ptr(), x.numel() / D, (int)D, dtype_code(x), quota(),
+                                            cur_stream()),
+              "ob200_bias_gelu_train_forward");
+        ctx->save_for_backward({x, bias});
+        return y;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
+        auto saved = ctx->get_saved_variables();
+        const at::Tensor &x = saved[0], &bias = saved[1];
+        at::Tensor dy = grads[0].contiguous();
+        const int64_t D = x.size(-1);
+        at::Tensor dx = at::empty_like(x), dbias = at::empty_like(bias);
+        check(ob200_bias_gelu_backward(dy.data_ptr(), x.data_ptr(), bias.data_ptr(), dx.data_ptr(), dbias.data_ptr(), x.numel() / D, (int)D,
+                                       dtype_code(x), quota(), cur_stream()),
+              "ob200_bias_gelu_backward");
+        g_own_launches.fetch_add(1, std::memory_order_relaxed);
+        return {dx, dbias};
+    }
+};
+at::Tensor bias_gelu_train_op(const at::Tensor& x, const at::Tensor& bias) { return BiasGeluTrain::apply(x, bias); }
+
+// Mean cross-entropy of logits [rows, V] (float32 or bfloat16, read as they are) against int64 targets.
+struct CrossEntropy : public torch::autograd::Function<CrossEntropy> {
+    static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& logits, const at::Tensor& target) {
+        TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() && dtype_code(logits) >= 0 &&
+                        target.scalar_type() == at::kLong && target.is_contiguous() && target.numel() == logits.size(0),
+                    "orion::cross_entropy: contiguous [rows, V] float32/bfloat16 logits and int64 targets expected");
+        const int64_t rows = logits.size(0), V = logits.size(1);
+        at::Tensor loss = at::empty({rows}, logits.options().dtype(at::kFloat)), lse = at::empty({rows}, logits.options().dtype(at::kFloat));
+        check(ob200_cross_entropy_forward(logits.data_ptr(), (const long long*)target.data_ptr<int64_t>(), loss.data_ptr<float>(),
+                                          lse.data_ptr<float>(), rows, (int)V, dtype_code(logits), cur_stream()),
+              "ob200_cross_entropy_forward");
+        ctx->save_for_backward({logits, target, lse});
+        return loss.mean();
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
+        auto saved = ctx->get_saved_variables();
+        const at::Tensor &logits = saved[0], &target = saved[1], &lse = saved[2];
+        at::Tensor g = grads[0].to(at::kFloat).contiguous();
+        at::Tensor dlogits = at::empty_like(logits);
+        check(ob200_cross_entropy_backward(logits.data_ptr(), (const long long*)target.data_ptr<int64_t>(), lse.data_ptr<float>(),
+                                           g.data_ptr<float>(), dlogits.data_ptr(), logits.size(0), (int)logits.size(1), dtype_code(logits),
+                                           cur_stream()),
+              "ob200_cross_entropy_backward");
+        return {dlogits, at::Tensor()};
+    }
+};
+at::Tensor cross_entropy_op(const at::Tensor& logits, const at::Tensor& target) { return CrossEntropy::apply(logits, target); }
+
+// One AdamW step over all parameters of one type in a few launches (torch.optim.AdamW semantics; state in the parameters' type).
+void adamw_step_op(at::TensorList params, at::TensorList grads, at::TensorList exp_avg, at::TensorList exp_avg_sq, double lr, double beta1,
+                   double beta2, double eps, double weight_decay, int64_t step) {
+    const size_t n = params.size();
+    TORCH_CHECK(n > 0 && grads.size() == n && exp_avg.size() == n && exp_avg_sq.size() == n, "orion::adamw_step: four lists of equal length expected");
+    const int dt = dtype_code(params[0]);
+    TORCH_CHECK(dt >= 0, "orion::adamw_step: float32 or bfloat16 parameters expected");
+    std::vector<void*> p(n), m(n), v(n);
+    std::vector<const void*> g(n);
+    std::vector<long long> cnt(n);
+    for (size_t i = 0; i < n; i++) {
+        TORCH_CHECK(params[i].is_cuda() && dtype_code(params[i]) == dt && dtype_code(grads[i]) == dt && dtype_code(exp_avg[i]) == dt &&
+                        dtype_code(exp_avg_sq[i]) == dt && params[i].is_non_overlapping_and_dense() &&
+                        grads[i].strides() == params[i].strides() && exp_avg[i].strides() == params[i].strides() &&
+                        exp_avg_sq[i].strides() == params[i].strides(),
+                    "orion::adamw_step: dense CUDA tensors of one type and matching layout expected");
+        p[i] = params[i].data_ptr();
+        g[i] = grads[i].data_ptr();
+        m[i] = exp_avg[i].data_ptr();
+        v[i] = exp_avg_sq[i].data_ptr();
+        cnt[i] = params[i].numel();
+    }
+    check(ob200_adamw_multi(p.data(), g.data(), m.data(), v.data(), cnt.data(), (int)n, (float)lr, (float)beta1, (float)beta2, (float)eps,
+                            (float)weight_decay, (int)step, dt, quota(), cur_stream()),
+          "ob200_adamw_multi");
+}
+
 // ------------------------------------------------------------------ inference plans
 // A prepared inference model as a flat list of kernel launches over numbered tensor slots, run by ONE
 // call from Python.  The interpreter lock is taken once per request instead of once per layer, so a
@@ -654,6 +784,10 @@ TORCH_LIBRARY(orion, m) {
     m.def("linear_batched(Tensor x, Tensor w) -> Tensor");
     m.def("bn_act_train(Tensor x, Tensor? residual, Tensor weight, Tensor bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, float momentum, float eps, int act) -> Tensor");
     m.def("maxpool_train(Tensor x, int k, int stride, int pad) -> Tensor");
+    m.def("layernorm_train(Tensor x, Tensor gamma, Tensor beta, float eps) -> Tensor");
+    m.def("bias_gelu_train(Tensor x, Tensor bias) -> Tensor");
+    m.def("cross_entropy(Tensor logits, Tensor target) -> Tensor");
+    m.def("adamw_step(Tensor(a!)[] params, Tensor[] grads, Tensor(b!)[] exp_avg, Tensor(c!)[] exp_avg_sq, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()");
     m.def("sgd_step(Tensor(a!)[] params, Tensor[] grads, Tensor(b!)[] bufs, float lr, float momentum, float weight_decay, bool nesterov, bool first_step) -> ()");
     m.def("plan_create(int n_slots, int out_slot) -> int", &plan_create);
     m.def("plan_add(int plan, int kind, int src, int res, int dst, Tensor? w, Tensor? scale, Tensor? shift, int act, int[] stride, int[] pad, int[] dil) -> ()", &plan_add);
@@ -678,11 +812,15 @@ TORCH_LIBRARY_IMPL(orion, CUDA, m) {
     m.impl("linear_batched", &linear_batched_op);
     m.impl("plan_run", &plan_run);
     m.impl("sgd_step", &sgd_step_op);
+    m.impl("adamw_step", &adamw_step_op);
 }
 
 TORCH_LIBRARY_IMPL(orion, Autograd, m) {
     m.impl("bn_act_train", &bn_act_train_op);
     m.impl("maxpool_train", &maxpool_train_op);
+    m.impl("layernorm_train", &layernorm_train_op);
+    m.impl("bias_gelu_train", &bias_gelu_train_op);
+    m.impl("cross_entropy", &cross_entropy_op);
 }
 
 TORCH_LIBRARY_IMPL(aten, CUDA, m) {

@@ -1,5 +1,8 @@
 """Optimizers of the training clients on the orion kernels.
 
+`AdamW` has torch.optim.AdamW's constructor and semantics (decoupled weight decay, bias correction, state in the
+parameters' type) and performs the step in a few launches over all parameters (ob200_adamw_multi).
+
 `SGD` has torch.optim.SGD's constructor and semantics (momentum, weight decay, Nesterov; dampening 0) and performs the
 whole step in one or two kernel launches over all parameters (ob200_sgd_momentum_multi_f32) — the role the multi-tensor
 ("foreach") kernels play in the reference's training profiles (reference benchmarking/model_kernels/resnet50_32_fb1)."""
@@ -48,3 +51,33 @@ class SGD(torch.optim.Optimizer):
         bufs = [self.state[p]["momentum_buffer"] for p in params]
         torch.ops.orion.sgd_step(params, [p.grad for p in params], bufs, group["lr"], group["momentum"], group["weight_decay"],
                                  group["nesterov"], first)
+
+
+class AdamW(torch.optim.Optimizer):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        torch_ops.load()
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            by_step = {}
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                st["step"] += 1
+                by_step.setdefault((st["step"], p.dtype), []).append(p)
+            for (step, _), params in by_step.items():
+                torch.ops.orion.adamw_step(params, [p.grad for p in params], [self.state[p]["exp_avg"] for p in params],
+                                           [self.state[p]["exp_avg_sq"] for p in params], group["lr"], group["betas"][0],
+                                           group["betas"][1], group["eps"], group["weight_decay"], step)
+        return loss

@@ -44,3 +44,24 @@ def test_profile_then_colocate(built, tmp_path):
     assert st["hp_submits"] > 0 and st["be_submits"] > 0 and st["join_timeouts"] == 0
     assert co["scheduler"]["own_launches"] > 130 * 50
     assert hp_c["p99_latency"] < 20 * hp_solo["p99_latency"]
+
+
+def test_best_effort_stream_inside_a_green_context_partition(built, tmp_path):
+    """ORION_BE_SM_QUOTA=64: the scheduler creates the best-effort client's stream inside a green context that owns 64 SMs
+    (the hardware keeps that client's kernels off the other 84), reports the partition it got, and the pair still runs to
+    completion with every op scheduled."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from orion_b200 import experiments as E
+    out = str(tmp_path)
+    env = {"ORION_GATE_TIMEOUT_S": 15, "ORION_BE_SM_QUOTA": 64}
+    hp = E.profile_client("resnet50_hp", os.path.join(out, "profiles"), timeout=240)
+    be = E.profile_client("resnet50_be", os.path.join(out, "profiles"), timeout=240)
+    pair = [E.client_entry("resnet50_be", be, 100000), E.client_entry("resnet50_hp", hp, 100, rps=80)]
+    co = E.run_launch_jobs(pair, os.path.join(out, "pair"), depth=34000, extra_env=env, timeout=240)
+    be_c, hp_c = co["clients"]
+    st = co["scheduler"]["stats"]
+    assert st["green_be_sms"] == 64, "the driver granted a partition of another size (granularity is 8 SMs on B200)"
+    assert hp_c["iterations"] == 100 and be_c["iterations"] >= 11
+    assert st["join_timeouts"] == 0 and st["forced_iter_ends"] == 0

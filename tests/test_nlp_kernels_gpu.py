@@ -72,3 +72,86 @@ def test_batched_gemm_attention_shapes(K, dtype, tol):
     assert O.rel_err(ctx, torch.bmm(pr.double().cpu(), vt.double().cpu().transpose(1, 2))) < tol
     odd = K.linear_batched(torch.randn(3, 130, 72, device="cuda"), torch.randn(3, 50, 72, device="cuda"))
     assert odd.shape == (3, 130, 50) and K.read_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------- training side
+@pytest.fixture(scope="module")
+def tops(built):
+    from orion_b200 import torch_ops
+    torch_ops.load()
+    return torch.ops.orion
+
+
+@pytest.mark.parametrize("rows,D,dtype", [(3072, 768, torch.bfloat16), (8192, 1024, torch.bfloat16), (37, 256, torch.float32),
+                                          (1000, 512, torch.float32), (5, 8, torch.bfloat16)])
+def test_layernorm_training_forward_and_backward(tops, rows, D, dtype):
+    """y = LayerNorm(x) and its three gradients through the autograd op, against float64 on the CPU (bfloat16: inputs and
+    parameters rounded to bfloat16 first, tolerance 2e-2 of the tensor's largest entry; float32: 1e-4)."""
+    torch.manual_seed(5)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    x = (torch.randn(rows, D, device="cuda") * 1.5 + 0.3).to(dtype).requires_grad_(True)
+    g = (torch.rand(D, device="cuda") + 0.5).to(dtype).requires_grad_(True)
+    b = torch.randn(D, device="cuda").to(dtype).requires_grad_(True)
+    dy = torch.randn(rows, D, device="cuda").to(dtype)
+    y = tops.layernorm_train(x, g, b, 1e-5)
+    y.backward(dy)
+    xd, gd, bd = (t.detach().double().cpu().requires_grad_(True) for t in (x, g, b))
+    want = F.layer_norm(xd, (D,), gd, bd, 1e-5)
+    want.backward(dy.double().cpu())
+    assert O.rel_err(y.detach(), want.detach()) < tol
+    assert O.rel_err(x.grad, xd.grad) < tol
+    assert O.rel_err(g.grad, gd.grad) < tol and O.rel_err(b.grad, bd.grad) < tol
+
+
+@pytest.mark.parametrize("rows,D,dtype", [(3072, 3072, torch.bfloat16), (8192, 4096, torch.bfloat16), (33, 64, torch.float32),
+                                          (700, 96, torch.bfloat16)])
+def test_bias_gelu_training_forward_and_backward(tops, rows, D, dtype):
+    torch.manual_seed(6)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    x = torch.randn(rows, D, device="cuda").to(dtype).requires_grad_(True)
+    b = (torch.randn(D, device="cuda") * 0.5).to(dtype).requires_grad_(True)
+    dy = torch.randn(rows, D, device="cuda").to(dtype)
+    y = tops.bias_gelu_train(x, b)
+    y.backward(dy)
+    xd, bd = (t.detach().double().cpu().requires_grad_(True) for t in (x, b))
+    want = F.gelu(xd + bd)
+    want.backward(dy.double().cpu())
+    assert O.rel_err(y.detach(), want.detach()) < tol
+    assert O.rel_err(x.grad, xd.grad) < tol
+    assert O.rel_err(b.grad, bd.grad) < tol
+
+
+@pytest.mark.parametrize("rows,V,dtype", [(1024, 32000, torch.bfloat16), (64, 1000, torch.float32), (7, 8, torch.bfloat16)])
+def test_cross_entropy_forward_and_backward_from_the_logits_own_type(tops, rows, V, dtype):
+    """Mean cross-entropy over a vocabulary-sized row and its gradient (written in the logits' type) against float64."""
+    torch.manual_seed(7)
+    logits = (torch.randn(rows, V, device="cuda") * 2.0).to(dtype).requires_grad_(True)
+    target = torch.randint(0, V, (rows,), device="cuda")
+    loss = tops.cross_entropy(logits, target)
+    (loss * 3.0).backward()
+    ld = logits.detach().double().cpu().requires_grad_(True)
+    want = F.cross_entropy(ld, target.cpu())
+    (want * 3.0).backward()
+    assert abs(loss.item() - want.item()) / want.item() < 1e-5
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert O.rel_err(logits.grad, ld.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_multi_tensor_adamw_matches_torch(tops, dtype):
+    from orion_b200.optim import AdamW
+    torch.manual_seed(8)
+    shapes = [(768, 768), (768,), (3072, 768), (30528, 64), (2,), (5, 7)] + [(33,)] * 150
+    ours = [torch.nn.Parameter(torch.randn(*s, device="cuda").to(dtype)) for s in shapes]
+    ref = [torch.nn.Parameter(p.detach().clone().float()) for p in ours]     # float32 reference of the same arithmetic
+    o1 = AdamW(ours, lr=1e-2, weight_decay=0.01)
+    o2 = torch.optim.AdamW(ref, lr=1e-2, weight_decay=0.01)
+    for step in range(3):
+        for a, b in zip(ours, ref):
+            g = torch.randn_like(b).to(dtype)
+            a.grad, b.grad = g.clone(), g.float()
+        o1.step()
+        o2.step()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    for a, b in zip(ours, ref):
+        assert (a.float() - b).abs().max().item() <= tol * max(1.0, b.abs().max().item())
