@@ -28,7 +28,8 @@ Printed JSON (one line, rank 0):
              co-located phase next to the product's policy core (same decision log or not)
 With N > 1 (torchrun) every rank runs an independent replica on its own GPU and its own
 cores; nothing is exchanged on the data path; `value` sums the ranks and the latency ratio is
-the worst rank (every rank's figures are listed under `ranks`).
+the worst rank (every rank's figures are listed under `ranks`).  Scaling runs also carry `c5`: a short
+run of configs[4] (HP ResNet-101 at 40 req/s with BE decoder-LM training) on every GPU.
 """
 import argparse
 import json
@@ -49,10 +50,10 @@ STEP_REQUESTS = 100
 # written over the 53 launches in one ncu pass of `python -m orion_b200.kernel_replay --batch 32 --iters 1 --warm 1`;
 # the algorithmic bytes (activations + filters + outputs) are 54.5 MB per launch, most outputs stay in L2.
 ROOFLINE_TRAFFIC_BYTES_PER_LAUNCH = 31.14e6
-# DRAM bytes of one ob200_bn_backward_f32 call on 32x56x56x256 (statistics pass 205.9 MB + apply pass 251.3 MB,
-# one ncu pass of `python -m orion_b200.eltwise_replay --iters 1 --warm 0`); algorithmic 513.8 MB (20 B per element:
-# the apply pass finds part of dy and x still in L2).
-HBM_TRAFFIC_BN_BACKWARD = 457.2e6
+# DRAM bytes of one ob200_bn_act_backward_f32 call on 32x56x56x256 (reduction pass + apply pass, one ncu pass of
+# `python -m orion_b200.eltwise_replay --iters 1 --warm 0`; profiles/hbm_bound_kernels.md); algorithmic 513.8 MB (20 B per
+# element: the apply pass finds part of dy and x still in L2).
+HBM_TRAFFIC_BN_BACKWARD = 455.9e6
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -124,14 +125,15 @@ def hbm_roofline(peaks, iters=5, warm=3):
     """The HBM-bound kernels of the BE ResNet-50 training step at its two dominant activation sizes, one C-ABI call
     each per iteration with CUDA events around it and L2 flushed before (orion_b200/eltwise_replay.py)."""
     from orion_b200 import eltwise_replay
-    rows = eltwise_replay.replay(iters, warm, only=("bn_", "add+relu", "relu_backward", "maxpool", "sgd_momentum"))
+    rows = eltwise_replay.replay(iters, warm, only=("bn_act", "maxpool", "sgd_momentum_multi"))
     total_bytes = sum(r["algorithmic_bytes"] for r in rows)
     total_us = sum(r["us"] for r in rows)
-    dom = next((r for r in rows if r["kernel"].startswith("bn_backward 32x56x56x256")), rows[0])
+    dom = next((r for r in rows if r["kernel"].startswith("bn_act_backward+relu 32x56x56x256")), rows[0])
     return {"bound": "hbm", "achieved": dom["GBps"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": dom["GBps"] / peaks["hbm_gbs"],
             "traffic": HBM_TRAFFIC_BN_BACKWARD, "peak_source": peaks["source"],
-            "kernel": "ob200_bn_backward_f32 (bn_reduce_kernel + bn_backward_apply_kernel), 32x56x56x256 fp32: the largest "
-                      "HBM-bound entry of the BE training step; algorithmic 20 B per element",
+            "kernel": "ob200_bn_act_backward_f32 (bn_reduce_finish_kernel<1,1> + bn_act_backward_apply_kernel<1>: batch-norm "
+                      "backward fused with the ReLU backward), 32x56x56x256 fp32: the largest HBM-bound entry of the BE training "
+                      "step; algorithmic 20 B per element",
             "set_achieved": total_bytes / total_us / 1e3, "set_frac": total_bytes / total_us / 1e3 / peaks["hbm_gbs"],
             "set": [{"kernel": r["kernel"], "GBps": round(r["GBps"], 1), "us": round(r["us"], 1)} for r in rows]}
 
@@ -249,7 +251,7 @@ def be_rate_in_window(be_client, t0, t1):
     return (len(ends) - 1) * be_client["batchsize"] / (ends[-1] - ends[0]), len(ends)
 
 
-def run_replica(gpu, steps, warm_steps, out_dir, be_quota):
+def run_replica(gpu, steps, warm_steps, out_dir, be_quota, with_c5=False):
     from orion_b200 import experiments as E
     env = {"CUDA_VISIBLE_DEVICES": gpu, "ORION_PIN_THREADS": os.environ.get("ORION_PIN_THREADS", "2"),
            "ORION_EXTRA_WARMUP_REQUESTS": warm_steps * STEP_REQUESTS}
@@ -270,8 +272,35 @@ def run_replica(gpu, steps, warm_steps, out_dir, be_quota):
     script = os.path.join(out_dir, "coloc_resident", "recorded.script")
     env_res.update({"ORION_RESIDENT_INPUTS": 1, "ORION_READBACK": 0, "ORION_RECORD_SCRIPT": script, "ORION_RECORD_MAX_ITERS": 400})
     res = E.run_launch_jobs(pair, os.path.join(out_dir, "coloc_resident"), depth=depth, extra_env=env_res)
-    return {"hp_solo": hp_solo, "be_solo": be_solo, "e2e": e2e, "resident": res, "depth": depth,
-            "profile_rows": {"hp": hp_prof[3], "be": be_prof[3]}, "script": script if os.path.exists(script) else None}
+    out = {"hp_solo": hp_solo, "be_solo": be_solo, "e2e": e2e, "resident": res, "depth": depth,
+           "profile_rows": {"hp": hp_prof[3], "be": be_prof[3]}, "script": script if os.path.exists(script) else None}
+    if with_c5:
+        out["c5"] = run_c5(E, env, out_dir)
+    return out
+
+
+def run_c5(E, env, out_dir, requests=250, rps=40):
+    """configs[4] on this replica's GPU, a short run beside the headline: HP ResNet-101 inference (fp32, batch 4, Poisson
+    40 req/s) with BE decoder-LM training (16 layers, d_model 1024, sequence 512, batch 16, bf16, AdamW)."""
+    env = dict(env)
+    env["ORION_EXTRA_WARMUP_REQUESTS"] = 0
+    hp_prof = E.profile_client("resnet101_hp", os.path.join(out_dir, "profiles"), extra_env=env)
+    be_prof = E.profile_client("transformer_be", os.path.join(out_dir, "profiles"), extra_env=env)
+    n_hp = 10 + requests
+    hp_solo = E.run_launch_jobs([E.client_entry("resnet101_hp", hp_prof, n_hp, rps=rps)], os.path.join(out_dir, "c5_hp_solo"),
+                                extra_env=env)["clients"][0]
+    be_solo = E.run_launch_jobs([E.client_entry("transformer_be", be_prof, 60)], os.path.join(out_dir, "c5_be_solo"),
+                                extra_env=env)["clients"][0]
+    depth = int(0.025 * hp_solo["p50_latency"] * 1e6)
+    pair = [E.client_entry("transformer_be", be_prof, 1000000), E.client_entry("resnet101_hp", hp_prof, n_hp, rps=rps)]
+    be_c, hp_c = E.run_launch_jobs(pair, os.path.join(out_dir, "c5_coloc"), depth=depth, extra_env=env)["clients"]
+    be_sps, _ = be_rate_in_window(be_c, hp_c["measure_start_time"], hp_c["measure_end_time"])
+    return {"workload": "configs[4]: HP ResNet-101 b4 Poisson %d req/s x %d requests + BE decoder LM 16x1024 b16x512 bf16 AdamW" % (rps, requests),
+            "hp_p99_x_solo": hp_c["p99_latency"] / hp_solo["p99_latency"], "hp_p50_ms": hp_c["p50_latency"],
+            "hp_solo_p50_ms": hp_solo["p50_latency"], "hp_p99_ms": hp_c["p99_latency"], "hp_solo_p99_ms": hp_solo["p99_latency"],
+            "p99_ratio_ci95": paired_bootstrap_p99_ratio(hp_c["latencies_ms"], hp_solo["latencies_ms"]),
+            "be_samples_per_s": be_sps, "be_solo_samples_per_s": be_solo["samples_per_s"],
+            "be_fraction_of_solo": be_sps / max(1e-9, be_solo["samples_per_s"]), "dur_threshold_ns": depth}
 
 
 def main():
@@ -329,7 +358,9 @@ def main():
     torch.cuda.synchronize()
     sampler.start()
     t0 = time.time()
-    rep = run_replica(gpu, steps, warm_steps, out_dir, be_quota)
+    # the second configuration pair rides along in scaling runs (or with ORION_BENCH_C5=1)
+    with_c5 = os.environ.get("ORION_BENCH_C5", "1" if (world > 1 or args.gpus > 1) else "0") == "1"
+    rep = run_replica(gpu, steps, warm_steps, out_dir, be_quota, with_c5)
     torch.cuda.synchronize()
     wall = time.time() - t0
     clocks = sampler.stop()
@@ -350,7 +381,7 @@ def main():
              "p99_ratio_resident_ci95": paired_bootstrap_p99_ratio(hp_res["latencies_ms"], hp_solo["latencies_ms"]),
              "timed_s": hp_res["measure_end_time"] - hp_res["measure_start_time"],
              "launches": rep["resident"]["scheduler"].get("own_launches", 0),
-             "sched": rep["resident"]["scheduler"]["stats"], "wall": wall, "cores": mine}
+             "sched": rep["resident"]["scheduler"]["stats"], "wall": wall, "cores": mine, "c5": rep.get("c5")}
     if world > 1:
         gathered = [None] * world
         dist.all_gather_object(gathered, local)
@@ -412,6 +443,13 @@ def main():
         line["ranks"] = [{"hp_p99_x_solo": g["hp_p99"] / g["hp_solo_p99"], "hp_p99_x_solo_ci95": g["p99_ratio_ci95"],
                           "be_fraction_of_solo": g["be_sps"] / max(1e-9, g["be_solo_sps"]), "be_samples_per_s": g["be_sps"],
                           "cores": g["cores"]} for g in gathered]
+    if any(g.get("c5") for g in gathered):
+        c5 = [g["c5"] for g in gathered if g.get("c5")]
+        worst5 = max(c5, key=lambda c: c["hp_p99_x_solo"])
+        line["c5"] = dict(worst5, be_samples_per_s=sum(c["be_samples_per_s"] for c in c5),
+                          be_solo_samples_per_s=sum(c["be_solo_samples_per_s"] for c in c5),
+                          be_fraction_of_solo=sum(c["be_samples_per_s"] for c in c5) / max(1e-9, sum(c["be_solo_samples_per_s"] for c in c5)),
+                          ranks=[{"hp_p99_x_solo": c["hp_p99_x_solo"], "be_fraction_of_solo": c["be_fraction_of_solo"]} for c in c5])
     print(json.dumps(line))
     if not args.keep and not os.environ.get("ORION_BENCH_DIR"):
         shutil.rmtree(base_dir, ignore_errors=True)

@@ -34,6 +34,14 @@ def cases():
         _, sm, si = K.bn_train_forward(x, g, b, rm, rv, 1e-5, 0.1)
         e = x.numel()
         tag = "%dx%dx%dx%d" % (n, h, h, c)
+        # the fused entry points the training clients use: statistics + finish in one launch, activation and residual in the other
+        y_res, _, _ = K.bn_act_train_forward(x, g, b, rm, rv, 1e-5, 0.1, act=1, residual=dy)
+        add("bn_act_forward+relu " + tag, 12 * e, lambda x=x, g=g, b=b, rm=rm, rv=rv: K.bn_act_train_forward(x, g, b, rm, rv, 1e-5, 0.1, act=1))
+        add("bn_act_forward+add+relu " + tag, 16 * e,
+            lambda x=x, g=g, b=b, rm=rm, rv=rv, dy=dy: K.bn_act_train_forward(x, g, b, rm, rv, 1e-5, 0.1, act=1, residual=dy))
+        add("bn_act_backward+relu " + tag, 20 * e, lambda dy=dy, x=x, g=g, b=b, sm=sm, si=si: K.bn_act_backward(dy, x, g, b, sm, si, act=1))
+        add("bn_act_backward+add+relu " + tag, 28 * e,
+            lambda dy=dy, x=x, g=g, b=b, sm=sm, si=si, y=y_res: K.bn_act_backward(dy, x, g, b, sm, si, act=1, yout=y, want_dres=True))
         add("bn_train_forward " + tag, 12 * e, lambda x=x, g=g, b=b, rm=rm, rv=rv: K.bn_train_forward(x, g, b, rm, rv, 1e-5, 0.1))
         add("bn_backward " + tag, 20 * e, lambda dy=dy, x=x, g=g, sm=sm, si=si: K.bn_backward(dy, x, g, sm, si))
         add("bn_inference+relu " + tag, 8 * e, lambda x=x, g=g, b=b, rm=rm, rv=rv: K.bn_inference(x, g, b, rm, rv, 1e-5, relu=True))
@@ -41,6 +49,8 @@ def cases():
         add("relu_backward " + tag, 12 * e, lambda x=x, dy=dy: K.relu_backward(dy, x))
     x = torch.randn(32, 112, 112, 64, **f32)
     add("maxpool 3x3/2 32x112x112x64", 4 * (x.numel() + x.numel() // 4), lambda x=x: K.maxpool_nhwc(x, 3, 2, 1))
+    dyp = torch.randn(32, 56, 56, 64, **f32)
+    add("maxpool_backward 3x3/2 32x112x112x64", 4 * (2 * x.numel() + 2 * dyp.numel()), lambda x=x, dyp=dyp: K.maxpool_backward_nhwc(dyp, x, 3, 2, 1))
     x = torch.randn(256, 7, 7, 2048, **f32)
     add("avgpool 256x7x7x2048", 4 * (x.numel() + 256 * 2048), lambda x=x: K.avgpool_nhwc(x))
     # MobileNetV2 batch 64: depthwise 3x3 on 112x112x96 (stride 2) and 56x56x144 (stride 1), fused scale/shift/ReLU6
@@ -65,6 +75,11 @@ def cases():
     v_.abs_()
     add("sgd_momentum 25.6M", 20 * p_.numel(), lambda: K.sgd_momentum_(p_, g_, m_, 0.1, 0.9))
     add("adamw 25.6M", 28 * p_.numel(), lambda: K.adamw_(p_, g_, m_, v_, 10, 1e-3))
+    # the same 25.6 M parameters as 161 tensors of ResNet-50's sizes in two launches
+    chunks = torch.split(p_, [150_000] * 160 + [25_600_000 - 160 * 150_000])
+    gch = torch.split(g_, [150_000] * 160 + [25_600_000 - 160 * 150_000])
+    mch = torch.split(m_, [150_000] * 160 + [25_600_000 - 160 * 150_000])
+    add("sgd_momentum_multi 25.6M in 161 tensors", 20 * p_.numel(), lambda: K.sgd_momentum_multi_(list(chunks), list(gch), list(mch), 0.1, 0.9))
     return out
 
 

@@ -295,6 +295,31 @@ def sgd_momentum_(p, g, m, lr, mu, wd=0.0, nesterov=False, first_step=False, num
                                         num_ctas or sm_count(), _stream()), "ob200_sgd_momentum_f32")
 
 
+def sgd_momentum_multi_(params, grads, bufs, lr, mu, wd=0.0, nesterov=False, first_step=False, num_ctas=None):
+    """SGD with momentum over lists of tensors in ceil(len / 96) launches."""
+    n = len(params)
+    vp = ctypes.c_void_p * n
+    cnt = (c_ll * n)(*[p.numel() for p in params])
+    L = lib()
+    L.ob200_sgd_momentum_multi_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_int, c_int,
+                                               c_int, c_void_p]
+    L.ob200_sgd_momentum_multi_f32.restype = c_int
+    _check(L.ob200_sgd_momentum_multi_f32(vp(*[p.data_ptr() for p in params]), vp(*[g.data_ptr() for g in grads]),
+                                          vp(*[m.data_ptr() for m in bufs]), cnt, n, lr, mu, wd, int(nesterov), int(first_step),
+                                          num_ctas or sm_count(), _stream()), "ob200_sgd_momentum_multi_f32")
+
+
+def maxpool_backward_nhwc(dy, x, k, stride, pad, num_ctas=None):
+    Nb, H, W, C = x.shape
+    dx = torch.empty_like(x)
+    L = lib()
+    L.ob200_maxpool_backward_nhwc_f32.argtypes = [c_void_p] * 3 + [c_int] * 7 + [c_int, c_void_p]
+    L.ob200_maxpool_backward_nhwc_f32.restype = c_int
+    _check(L.ob200_maxpool_backward_nhwc_f32(_ptr(dy), _ptr(x), _ptr(dx), Nb, H, W, C, k, stride, pad, num_ctas or sm_count(), _stream()),
+           "ob200_maxpool_backward_nhwc_f32")
+    return dx
+
+
 def linear_batched(x, w, num_ctas=None, tf32=False):
     """x: [B, M, K], w: [B, N, K] -> [B, M, N] (y_b = x_b . w_b^T)."""
     assert x.is_contiguous() and w.is_contiguous() and x.dtype == w.dtype and x.shape[0] == w.shape[0]
