@@ -197,6 +197,14 @@ void ob200_set_debug_buffer(long long* dev_buf);
 int ob200_depthwise_conv2d_f32(const float* x, const float* w, float* y, const float* scale, const float* shift, int relu, int Nb,
                                int H, int W, int C, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
                                int dil_w, int w_tap_major, int num_ctas, void* stream);
+/* Its gradients (filter [C][R][S], dilation 1): the data gradient for any filter size and stride, the filter gradient for
+ * 3x3 filters (dw is cleared on `stream` and accumulated with atomic adds).  They stand in for the
+ * conv_depthwise2d_backward_kernel / conv_depthwise2d_grad_weight_kernel rows of the reference's MobileNetV2 training profile
+ * (reference benchmarking/model_kernels/mobilenetv2_64_fb1). */
+int ob200_depthwise_conv2d_dgrad_f32(const float* dy, const float* w, float* dx, int Nb, int H, int W, int C, int R, int S,
+                                     int stride_h, int stride_w, int pad_h, int pad_w, int num_ctas, void* stream);
+int ob200_depthwise_conv2d_wgrad3x3_f32(const float* dy, const float* x, float* dw, int Nb, int H, int W, int C, int stride, int pad,
+                                        int num_ctas, void* stream);
 /* Number of implicit-GEMM launches of this process whose operands were fed by TMA tensor maps (the others
  * gathered with 16-byte asynchronous copies: strided data gradients, filter gradients, channel counts below
  * one k-block or k-blocks that straddle filter taps).  No counterpart in the reference. */

@@ -428,7 +428,9 @@ namespace ob200 {
 template <int STRIDE>
 __global__ void __launch_bounds__(ELT_THREADS) depthwise3x3_nhwc_f32_kernel(
     const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, const float* __restrict__ scale,
-    const float* __restrict__ shift, int relu, int Nb, int H, int W, int C, int P, int Q, int pad_h, int pad_w, int w_tap_major) {
+    const float* __restrict__ shift, int relu, int Nb, int H, int W, int C, int P, int Q, int pad_h, int pad_w, int w_tap_major,
+    int flip) {
+    // flip = 1 uses the filter rotated by 180 degrees: the data gradient of a stride-1 layer is this same convolution of dy
     constexpr int TW = 4, NCOL = (TW - 1) * STRIDE + 3;
     const int c4 = C / 4, qb_n = (Q + TW - 1) / TW;
     const long long total = (long long)Nb * P * qb_n * c4;
@@ -443,9 +445,10 @@ __global__ void __launch_bounds__(ELT_THREADS) depthwise3x3_nhwc_f32_kernel(
         float4 f[9];
 #pragma unroll
         for (int t = 0; t < 9; t++) {
-            if (w_tap_major) f[t] = __ldg(reinterpret_cast<const float4*>(w + (long long)t * C + c));
-            else f[t] = make_float4(__ldg(w + (long long)c * 9 + t), __ldg(w + (long long)(c + 1) * 9 + t), __ldg(w + (long long)(c + 2) * 9 + t),
-                                    __ldg(w + (long long)(c + 3) * 9 + t));
+            const int tw = flip ? 8 - t : t;
+            if (w_tap_major) f[t] = __ldg(reinterpret_cast<const float4*>(w + (long long)tw * C + c));
+            else f[t] = make_float4(__ldg(w + (long long)c * 9 + tw), __ldg(w + (long long)(c + 1) * 9 + tw), __ldg(w + (long long)(c + 2) * 9 + tw),
+                                    __ldg(w + (long long)(c + 3) * 9 + tw));
         }
         float4 acc[TW];
 #pragma unroll
@@ -507,10 +510,10 @@ extern "C" int ob200_depthwise_conv2d_f32(const float* x, const float* w, float*
         OB200_ELASTIC_HBM(ob200::depthwise3x3_nhwc_f32_kernel<2>, 4);
         if (stride_h == 1)
             ob200::depthwise3x3_nhwc_f32_kernel<1><<<grid4, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, P,
-                                                                                                Q, pad_h, pad_w, w_tap_major);
+                                                                                                Q, pad_h, pad_w, w_tap_major, 0);
         else
             ob200::depthwise3x3_nhwc_f32_kernel<2><<<grid4, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, P,
-                                                                                                Q, pad_h, pad_w, w_tap_major);
+                                                                                                Q, pad_h, pad_w, w_tap_major, 0);
         return (int)cudaGetLastError();
     }
     const long long total = (long long)Nb * P * Q * (C / 4);
@@ -521,5 +524,201 @@ extern "C" int ob200_depthwise_conv2d_f32(const float* x, const float* w, float*
     ob200::depthwise_conv_nhwc_f32_kernel<<<grid, ELT_THREADS, 0, (cudaStream_t)stream>>>(x, w, y, scale, shift, relu, Nb, H, W, C, R, S,
                                                                                          P, Q, stride_h, stride_w, pad_h, pad_w, dil_h,
                                                                                          dil_w, w_tap_major);
+    return (int)cudaGetLastError();
+}
+
+
+// ---------------------------------------------------------------- depthwise convolution, backward
+// Gradients of ob200_depthwise_conv2d_f32 (filter [C][R][S] as torch holds it, dilation 1).  They take the place of the
+// conv_depthwise2d_backward_kernel / conv_depthwise2d_grad_weight_kernel launches of the reference's MobileNetV2 training
+// profile (reference benchmarking/model_kernels/mobilenetv2_64_fb1), which reach it through the cudaLaunchKernel trap
+// (reference src/cuda_capture/intercept_temp.cpp:418-458).
+namespace ob200 {
+
+// dx[n,h,w,c] = sum over taps (r,s) with (h + pad - r) and (w + pad - s) divisible by the stride of
+//               dy[n, (h + pad - r) / stride, (w + pad - s) / stride, c] * w[c][r][s].
+__global__ void __launch_bounds__(ELT_THREADS) depthwise_dgrad_nhwc_f32_kernel(const float* __restrict__ dy, const float* __restrict__ w,
+                                                                             float* __restrict__ dx, int Nb, int H, int W, int C, int R,
+                                                                             int S, int P, int Q, int stride_h, int stride_w, int pad_h,
+                                                                             int pad_w) {
+    const int c4 = C / 4;
+    const long long total = (long long)Nb * H * W * c4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % c4) * 4;
+        long long t = i / c4;
+        const int wi = (int)(t % W); t /= W;
+        const int hi = (int)(t % H);
+        const int n = (int)(t / H);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        // only taps r = (h + pad) mod stride, + stride, ... reach an output row: walk those
+        for (int r = (hi + pad_h) % stride_h; r < R; r += stride_h) {
+            const int hn = hi + pad_h - r;
+            if (hn < 0) break;
+            const int p = hn / stride_h;
+            if (p >= P) continue;
+            for (int sx = (wi + pad_w) % stride_w; sx < S; sx += stride_w) {
+                const int wn = wi + pad_w - sx;
+                if (wn < 0) break;
+                const int q = wn / stride_w;
+                if (q >= Q) continue;
+                const float4 g = __ldg(reinterpret_cast<const float4*>(dy + (((long long)n * P + p) * Q + q) * C + c));
+                const int tap = r * S + sx, RS = R * S;
+                acc.x = fmaf(g.x, __ldg(w + (long long)(c + 0) * RS + tap), acc.x);
+                acc.y = fmaf(g.y, __ldg(w + (long long)(c + 1) * RS + tap), acc.y);
+                acc.z = fmaf(g.z, __ldg(w + (long long)(c + 2) * RS + tap), acc.z);
+                acc.w = fmaf(g.w, __ldg(w + (long long)(c + 3) * RS + tap), acc.w);
+            }
+        }
+        *reinterpret_cast<float4*>(dx + i * 4) = acc;
+    }
+}
+
+// dw[c][r][s] = sum over output pixels of dy[n,p,q,c] * x[n, p*stride - pad + r, q*stride - pad + s, c]  (3x3 filters).
+// Threads are (channel quad, pixel lane); every thread keeps the 9 x 4 sums of its channel quad over the pixels it walks, a
+// shared-memory tree adds the lanes of a CTA and one atomicAdd per entry adds the CTAs (dw is cleared first).
+__global__ void __launch_bounds__(ELT_THREADS) depthwise_wgrad3x3_nhwc_f32_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                                float* __restrict__ dw, int Nb, int H, int W, int C, int P,
+                                                                                int Q, int stride, int pad, int slabs) {
+    extern __shared__ float sh[];   // [blockDim.y][blockDim.x][36]
+    const int cq = blockDim.x, ry = blockDim.y;
+    const int c_groups = (C / 4 + cq - 1) / cq;
+    const int cg = blockIdx.x % c_groups, slab = blockIdx.x / c_groups;
+    const int c = (cg * cq + threadIdx.x) * 4;
+    float acc[9][4];
+#pragma unroll
+    for (int t = 0; t < 9; t++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[t][e] = 0.f;
+    if (c < C && slab < slabs) {
+        // work items are (image, output row, block of four output columns); a thread loads the 3 x NCOL input window of its
+        // block once (NCOL = 6 for stride 1, 9 for stride 2) instead of 9 values per output pixel
+        const int qb_n = (Q + 3) / 4;
+        const long long items = (long long)Nb * P * qb_n;
+        const long long per = (items + slabs - 1) / slabs;
+        const long long m0 = slab * per, m1 = m0 + per < items ? m0 + per : items;
+        for (long long m = m0 + threadIdx.y; m < m1; m += ry) {
+            const int qb = (int)(m % qb_n);
+            const long long t2 = m / qb_n;
+            const int p = (int)(t2 % P);
+            const int n = (int)(t2 / P);
+            const int q0 = qb * 4;
+            float4 g[4];
+#pragma unroll
+            for (int t = 0; t < 4; t++)
+                g[t] = q0 + t < Q ? __ldcs(reinterpret_cast<const float4*>(dy + ((((long long)n * P + p) * Q + q0 + t) * C + c)))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+            const int w0 = q0 * stride - pad;
+#pragma unroll
+            for (int r = 0; r < 3; r++) {
+                const int h = p * stride - pad + r;
+                if ((unsigned)h >= (unsigned)H) continue;
+                const float* xrow = x + (((long long)n * H + h) * W) * C + c;
+                if (stride == 1) {
+                    float4 v[6];
+#pragma unroll
+                    for (int j = 0; j < 6; j++)
+                        v[j] = (unsigned)(w0 + j) < (unsigned)W ? __ldg(reinterpret_cast<const float4*>(xrow + (long long)(w0 + j) * C))
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int t = 0; t < 4; t++)
+#pragma unroll
+                        for (int sx = 0; sx < 3; sx++) {
+                            const float4 a = v[t + sx];
+                            acc[r * 3 + sx][0] = fmaf(g[t].x, a.x, acc[r * 3 + sx][0]);
+                            acc[r * 3 + sx][1] = fmaf(g[t].y, a.y, acc[r * 3 + sx][1]);
+                            acc[r * 3 + sx][2] = fmaf(g[t].z, a.z, acc[r * 3 + sx][2]);
+                            acc[r * 3 + sx][3] = fmaf(g[t].w, a.w, acc[r * 3 + sx][3]);
+                        }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 4; t++)
+#pragma unroll
+                        for (int sx = 0; sx < 3; sx++) {
+                            const int wv = w0 + t * stride + sx;
+                            if ((unsigned)wv >= (unsigned)W) continue;
+                            const float4 a = __ldg(reinterpret_cast<const float4*>(xrow + (long long)wv * C));
+                            acc[r * 3 + sx][0] = fmaf(g[t].x, a.x, acc[r * 3 + sx][0]);
+                            acc[r * 3 + sx][1] = fmaf(g[t].y, a.y, acc[r * 3 + sx][1]);
+                            acc[r * 3 + sx][2] = fmaf(g[t].z, a.z, acc[r * 3 + sx][2]);
+                            acc[r * 3 + sx][3] = fmaf(g[t].w, a.w, acc[r * 3 + sx][3]);
+                        }
+                }
+            }
+        }
+    }
+    float* mine = sh + ((size_t)threadIdx.y * cq + threadIdx.x) * 36;
+#pragma unroll
+    for (int t = 0; t < 9; t++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) mine[t * 4 + e] = acc[t][e];
+    __syncthreads();
+    for (int half = ry / 2; half > 0; half >>= 1) {
+        if ((int)threadIdx.y < half) {
+            const float* other = sh + ((size_t)(threadIdx.y + half) * cq + threadIdx.x) * 36;
+#pragma unroll
+            for (int k = 0; k < 36; k++) mine[k] += other[k];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.y == 0 && c < C && slab < slabs) {
+#pragma unroll
+        for (int t = 0; t < 9; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) atomicAdd(dw + (long long)(c + e) * 9 + t, mine[t * 4 + e]);
+    }
+}
+
+}  // namespace ob200
+
+extern "C" int ob200_depthwise_conv2d_dgrad_f32(const float* dy, const float* w, float* dx, int Nb, int H, int W, int C, int R, int S,
+                                                int stride_h, int stride_w, int pad_h, int pad_w, int num_ctas, void* stream) {
+    if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || (C & 3) || R <= 0 || S <= 0 || stride_h <= 0 || stride_w <= 0 || pad_h < 0 || pad_w < 0 ||
+        num_ctas <= 0)
+        return -1;
+    if (Nb == 0) return 0;
+    const int P = (H + 2 * pad_h - R) / stride_h + 1, Q = (W + 2 * pad_w - S) / stride_w + 1;
+    if (P <= 0 || Q <= 0) return -1;
+    if (((uintptr_t)dy | (uintptr_t)dx) % 16) return -2;
+    if (R == 3 && S == 3 && stride_h == 1 && stride_w == 1 && pad_h <= 2 && pad_w <= 2) {
+        // dx = dy convolved with the filter rotated by 180 degrees, padding 2 - pad: the forward kernel itself
+        const long long total4 = (long long)Nb * H * ((W + 3) / 4) * (C / 4);
+        long long want4 = (total4 + ELT_THREADS - 1) / ELT_THREADS, cap4 = (long long)num_ctas * 4;
+        OB200_ELASTIC_HBM(ob200::depthwise3x3_nhwc_f32_kernel<1>, 4);
+        ob200::depthwise3x3_nhwc_f32_kernel<1><<<(int)(want4 < cap4 ? want4 : cap4), ELT_THREADS, 0, (cudaStream_t)stream>>>(
+            dy, w, dx, nullptr, nullptr, 0, Nb, P, Q, C, H, W, 2 - pad_h, 2 - pad_w, 0, 1);
+        return (int)cudaGetLastError();
+    }
+    const long long total = (long long)Nb * H * W * (C / 4);
+    long long want = (total + ELT_THREADS - 1) / ELT_THREADS, cap = (long long)num_ctas * 8;
+    OB200_ELASTIC_HBM(ob200::depthwise_dgrad_nhwc_f32_kernel, 8);
+    ob200::depthwise_dgrad_nhwc_f32_kernel<<<(int)(want < cap ? want : cap), ELT_THREADS, 0, (cudaStream_t)stream>>>(
+        dy, w, dx, Nb, H, W, C, R, S, P, Q, stride_h, stride_w, pad_h, pad_w);
+    return (int)cudaGetLastError();
+}
+
+// 3x3 filters, equal strides and paddings in both directions; dw [C][3][3] is cleared on `stream` first.
+extern "C" int ob200_depthwise_conv2d_wgrad3x3_f32(const float* dy, const float* x, float* dw, int Nb, int H, int W, int C, int stride,
+                                                   int pad, int num_ctas, void* stream) {
+    if (Nb < 0 || H <= 0 || W <= 0 || C <= 0 || (C & 3) || stride <= 0 || pad < 0 || num_ctas <= 0) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(dw, 0, (size_t)C * 9 * sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    if (Nb == 0) return 0;
+    const int P = (H + 2 * pad - 3) / stride + 1, Q = (W + 2 * pad - 3) / stride + 1;
+    if (P <= 0 || Q <= 0) return -1;
+    if (((uintptr_t)dy | (uintptr_t)x) % 16) return -2;
+    int cq = C / 4 < 32 ? C / 4 : 32;
+    int ry = ELT_THREADS / cq, pow2 = 1;
+    while (pow2 * 2 <= ry) pow2 *= 2;
+    ry = pow2;
+    const int c_groups = (C / 4 + cq - 1) / cq;
+    const long long items = (long long)Nb * P * ((Q + 3) / 4);   // blocks of four output columns
+    long long slabs = (long long)num_ctas * 4 / c_groups;
+    if (slabs > (items + ry - 1) / ry) slabs = (items + ry - 1) / ry;
+    if (slabs < 1) slabs = 1;
+    const size_t smem = (size_t)cq * ry * 36 * sizeof(float);   // <= 256 * 144 B = 36 KB
+    OB200_HBM_BOUND();
+    ob200::depthwise_wgrad3x3_nhwc_f32_kernel<<<(unsigned)(slabs * c_groups), dim3(cq, ry), smem, s>>>(dy, x, dw, Nb, H, W, C, P, Q, stride, pad,
+                                                                                                   (int)slabs);
     return (int)cudaGetLastError();
 }

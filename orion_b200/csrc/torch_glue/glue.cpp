@@ -46,6 +46,10 @@ int ob200_sm_count(void);
 int ob200_depthwise_conv2d_f32(const float* x, const float* w, float* y, const float* scale, const float* shift, int relu, int Nb,
                                int H, int W, int C, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
                                int dil_w, int w_tap_major, int num_ctas, void* stream);
+int ob200_depthwise_conv2d_dgrad_f32(const float* dy, const float* w, float* dx, int Nb, int H, int W, int C, int R, int S,
+                                     int stride_h, int stride_w, int pad_h, int pad_w, int num_ctas, void* stream);
+int ob200_depthwise_conv2d_wgrad3x3_f32(const float* dy, const float* x, float* dw, int Nb, int H, int W, int C, int stride, int pad,
+                                        int num_ctas, void* stream);
 int ob200_pad_channels(const void* src, void* dst, long long pixels, int C, int Cpad, int elem_bytes, int num_ctas, void* stream);
 int ob200_conv2d_dgrad(const void* dy, const void* wt, void* dx, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int num_ctas, void* stream);
@@ -277,6 +281,32 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_override(
     const at::Tensor& grad_output, const at::Tensor& input, const at::Tensor& weight, at::OptionalIntArrayRef bias_sizes,
     at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, at::IntArrayRef output_padding,
     int64_t groups, std::array<bool, 3> output_mask) {
+    // depthwise (groups = C, multiplier 1), float32, 3x3, dilation 1, square stride / padding: both gradients on the orion kernels
+    const bool dw_ok = g_overrides.load(std::memory_order_relaxed) && input.dim() == 4 && weight.dim() == 4 && !transposed && groups > 1 &&
+                       groups == input.size(1) && weight.size(0) == groups && weight.size(1) == 1 && groups % 4 == 0 &&
+                       input.scalar_type() == at::kFloat && weight.scalar_type() == at::kFloat && grad_output.scalar_type() == at::kFloat &&
+                       weight.size(2) == 3 && weight.size(3) == 3 && stride.size() == 2 && stride[0] == stride[1] && padding.size() == 2 &&
+                       padding[0] == padding[1] && dilation.size() == 2 && dilation[0] == 1 && dilation[1] == 1 && input.numel() > 0 &&
+                       (weight.is_contiguous() || weight.is_contiguous(at::MemoryFormat::ChannelsLast)) && !output_mask[2];
+    if (dw_ok) {
+        at::Tensor dy = is_nhwc(grad_output) ? grad_output : grad_output.contiguous(at::MemoryFormat::ChannelsLast);
+        at::Tensor x = is_nhwc(input) ? input : input.contiguous(at::MemoryFormat::ChannelsLast);
+        const int Nb = (int)input.size(0), C = (int)input.size(1), H = (int)input.size(2), W = (int)input.size(3);
+        at::Tensor dx, dwt;
+        if (output_mask[0]) {
+            dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::ChannelsLast));
+            check(ob200_depthwise_conv2d_dgrad_f32(dy.data_ptr<float>(), weight.data_ptr<float>(), dx.data_ptr<float>(), Nb, H, W, C, 3, 3,
+                                                   (int)stride[0], (int)stride[1], (int)padding[0], (int)padding[1], quota(), cur_stream()),
+                  "ob200_depthwise_conv2d_dgrad_f32");
+        }
+        if (output_mask[1]) {
+            dwt = at::empty_like(weight);   // [C][1][3][3]: the same bytes in either memory format, the strides follow the weight's
+            check(ob200_depthwise_conv2d_wgrad3x3_f32(dy.data_ptr<float>(), x.data_ptr<float>(), dwt.data_ptr<float>(), Nb, H, W, C,
+                                                      (int)stride[0], (int)padding[0], quota(), cur_stream()),
+                  "ob200_depthwise_conv2d_wgrad3x3_f32");
+        }
+        return std::make_tuple(dx, dwt, at::Tensor());
+    }
     const bool base_ok = g_overrides.load(std::memory_order_relaxed) && input.dim() == 4 && weight.dim() == 4 && !transposed &&
                          groups == 1 && dtype_code(input) >= 0 && input.scalar_type() == weight.scalar_type() &&
                          grad_output.scalar_type() == input.scalar_type() && stride.size() == 2 && padding.size() == 2 &&

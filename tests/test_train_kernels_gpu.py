@@ -226,3 +226,29 @@ def test_multi_tensor_sgd_matches_torch(K):
         o2.step()
         for a, b in zip(ours, ref):
             assert (a - b).abs().max().item() <= 2e-6 * max(1.0, b.abs().max().item()), step
+
+
+@pytest.mark.parametrize("shape,stride", [((64, 56, 56, 144), 1), ((64, 112, 112, 96), 2), ((3, 9, 11, 8), 2), ((2, 7, 7, 960), 1),
+                                          ((5, 10, 6, 32), 1)])
+def test_depthwise_backward_through_the_overrides(K, shape, stride):
+    """MobileNetV2's depthwise 3x3 layers: data and filter gradient of the convolution override against float64 on the CPU,
+    with no fallback to the stock kernels."""
+    import torch.nn.functional as F
+    from orion_b200 import torch_ops
+    torch_ops.load()
+    Nb, H, W, C = shape
+    torch.manual_seed(12)
+    x = torch.randn(Nb, C, H, W, device="cuda").contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    w = (torch.randn(C, 1, 3, 3, device="cuda") / 3.0).requires_grad_(True)
+    fb0 = int(torch.ops.orion.fallbacks())
+    y = F.conv2d(x, w, None, stride, 1, 1, C)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert int(torch.ops.orion.fallbacks()) == fb0
+    xd = x.detach().double().cpu().requires_grad_(True)
+    wd = w.detach().double().cpu().requires_grad_(True)
+    yd = F.conv2d(xd, wd, None, stride, 1, 1, C)
+    yd.backward(dy.double().cpu())
+    assert O.rel_err(y.detach(), yd.detach()) < 1e-5
+    assert O.rel_err(x.grad, xd.grad) < 1e-5
+    assert O.rel_err(w.grad, wd.grad) < 1e-4
