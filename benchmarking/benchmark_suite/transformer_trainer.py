@@ -25,6 +25,8 @@ from .train_imagenet import run_client
 # Training clients use the orion LayerNorm / GELU / cross-entropy / AdamW kernels unless ORION_PREPARE=0 or the overrides are off.
 ORION_TRAIN_KERNELS = os.environ.get("ORION_PREPARE", "1") == "1" and os.environ.get("ORION_DISABLE_OVERRIDES", "0") != "1"
 
+FUSED_ATTENTION = os.environ.get("ORION_FUSED_ATTENTION", "1") == "1"
+
 BERT = dict(layers=12, hidden=768, heads=12, ffn=3072, vocab=30528, max_pos=512, seq=384)
 LM = dict(layers=16, hidden=1024, heads=16, ffn=4096, vocab=32000, seq=512)
 
@@ -59,12 +61,17 @@ class BertLayer(nn.Module):
         b, s, h = x.shape
         d = h // self.heads
         flat = x.reshape(b * s, h)
-        qkv = ops.linear(flat, self.qkv.weight, self.qkv.bias.float(), False).view(b, s, 3, self.heads, d)
-        q = qkv[:, :, 0].permute(0, 2, 1, 3).reshape(b * self.heads, s, d).contiguous()
-        k = qkv[:, :, 1].permute(0, 2, 1, 3).reshape(b * self.heads, s, d).contiguous()
-        vt = qkv[:, :, 2].permute(0, 2, 3, 1).reshape(b * self.heads, d, s).contiguous()
-        probs = ops.softmax(ops.linear_batched(q, k), 1.0 / math.sqrt(d), s if causal else 0)
-        ctx = ops.linear_batched(probs, vt).view(b, self.heads, s, d).permute(0, 2, 1, 3).reshape(b * s, h).contiguous()
+        qkv = ops.linear(flat, self.qkv.weight, self.qkv.bias.float(), False)
+        if d == 64 and s <= 384 and x.dtype == torch.bfloat16 and FUSED_ATTENTION:
+            # scores, softmax and the context product in one kernel, read straight from the projection's output
+            ctx = ops.attention(qkv.view(b, s, 3 * h), self.heads, 1.0 / math.sqrt(d), causal)
+        else:
+            qkv = qkv.view(b, s, 3, self.heads, d)
+            q = qkv[:, :, 0].permute(0, 2, 1, 3).reshape(b * self.heads, s, d).contiguous()
+            k = qkv[:, :, 1].permute(0, 2, 1, 3).reshape(b * self.heads, s, d).contiguous()
+            vt = qkv[:, :, 2].permute(0, 2, 3, 1).reshape(b * self.heads, d, s).contiguous()
+            probs = ops.softmax(ops.linear_batched(q, k), 1.0 / math.sqrt(d), s if causal else 0)
+            ctx = ops.linear_batched(probs, vt).view(b, self.heads, s, d).permute(0, 2, 1, 3).reshape(b * s, h).contiguous()
         # the residual stream is added in the GEMM epilogue, in float32, before the sum is rounded to bfloat16
         attn = ops.linear(ctx, self.out.weight, self.out.bias.float(), False, flat)
         y = ops.layernorm(attn, self.ln1.weight.float(), self.ln1.bias.float(), self.ln1.eps)

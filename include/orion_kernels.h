@@ -154,6 +154,12 @@ int ob200_softmax(const void* x, void* y, long long rows, int D, float scale, in
  * 0..D-1, and keys after the query position get probability 0 (causal_period = 0: no mask). */
 int ob200_softmax_causal(const void* x, void* y, long long rows, int D, float scale, int causal_period, int dtype, int num_ctas,
                          void* stream);
+/* Fused self-attention forward (bfloat16, head dimension 64, S <= 384): ctx [B, S, H*64] = softmax(Q K^T * scale [+ causal
+ * mask]) V, read straight from the fused projection output qkv [B, S, 3, H, 64]; scores and probabilities stay in tensor
+ * memory / shared memory.  Takes the place of the two cublasSgemmStridedBatched calls around a softmax kernel
+ * (reference src/scheduler/utils_sched.cpp:502-513). */
+int ob200_attention_fwd_bf16(const void* qkv, void* ctx, int B, int S, int H, int head_dim, float scale, int causal, int num_ctas,
+                             void* stream);
 
 /* Training side of the transformer clients (dtype 0 float32, 1 bfloat16; parameters in the activations' type).  They
  * stand in for the kernels the reference's BERT training profile lists (reference benchmarking/model_kernels/bert_8_fb1:

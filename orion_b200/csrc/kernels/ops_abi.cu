@@ -84,6 +84,13 @@ static int plan_sm_count() {
     return n;
 }
 
+// Device status word of the current device, for the other translation units of the library.
+extern "C" int* ob200_status_word_for_current_device(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    return status_word(dev);
+}
+
 extern "C" int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out) {
     const int bk = dtype == 1 ? 64 : 32;
     const int kblocks = R * ((S * C + bk - 1) / bk);

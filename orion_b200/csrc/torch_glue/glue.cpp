@@ -66,6 +66,8 @@ int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int 
 int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
                                float* running_var, float* save_mean, float* save_invstd, double* sums, float eps, float momentum,
                                long long rows, int C, int num_ctas, void* stream);
+int ob200_attention_fwd_bf16(const void* qkv, void* ctx, int B, int S, int H, int head_dim, float scale, int causal, int num_ctas,
+                             void* stream);
 int ob200_layernorm_train_forward(const void* x, void* y, const void* gamma, const void* beta, float* mean, float* rstd, long long rows,
                                   int D, float eps, int dtype, int num_ctas, void* stream);
 int ob200_layernorm_backward(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
@@ -459,6 +461,18 @@ at::Tensor bias_gelu_op(const at::Tensor& x, const c10::optional<at::Tensor>& bi
     return y;
 }
 
+// qkv: [B, S, 3*H*64] bfloat16 (the fused projection's output) -> ctx [B*S, H*64]
+at::Tensor attention_op(const at::Tensor& qkv, int64_t heads, double scale, bool causal) {
+    TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 3 && qkv.is_contiguous() && qkv.scalar_type() == at::kBFloat16 &&
+                    qkv.size(2) == 3 * heads * 64 && qkv.size(1) <= 384,
+                "orion::attention: contiguous bfloat16 [B, S <= 384, 3 * heads * 64] expected");
+    at::Tensor ctx = at::empty({qkv.size(0) * qkv.size(1), heads * 64}, qkv.options());
+    check(ob200_attention_fwd_bf16(qkv.data_ptr(), ctx.data_ptr(), (int)qkv.size(0), (int)qkv.size(1), (int)heads, 64, (float)scale,
+                                   causal ? 1 : 0, quota(), cur_stream()),
+          "ob200_attention_fwd_bf16");
+    return ctx;
+}
+
 // x: [B, M, K], w: [B, N, K] -> [B, M, N]
 at::Tensor linear_batched_op(const at::Tensor& x, const at::Tensor& w) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 3 && w.dim() == 3 && x.is_contiguous() && w.is_contiguous() && dtype_code(x) >= 0 &&
@@ -812,6 +826,7 @@ TORCH_LIBRARY(orion, m) {
     m.def("softmax(Tensor x, float scale, int causal_period=0) -> Tensor");
     m.def("bias_gelu(Tensor x, Tensor? bias) -> Tensor");
     m.def("linear_batched(Tensor x, Tensor w) -> Tensor");
+    m.def("attention(Tensor qkv, int heads, float scale, bool causal) -> Tensor");
     m.def("bn_act_train(Tensor x, Tensor? residual, Tensor weight, Tensor bias, Tensor(a!)? running_mean, Tensor(b!)? running_var, float momentum, float eps, int act) -> Tensor");
     m.def("maxpool_train(Tensor x, int k, int stride, int pad) -> Tensor");
     m.def("layernorm_train(Tensor x, Tensor gamma, Tensor beta, float eps) -> Tensor");
@@ -840,6 +855,7 @@ TORCH_LIBRARY_IMPL(orion, CUDA, m) {
     m.impl("softmax", &softmax_op);
     m.impl("bias_gelu", &bias_gelu_op);
     m.impl("linear_batched", &linear_batched_op);
+    m.impl("attention", &attention_op);
     m.impl("plan_run", &plan_run);
     m.impl("sgd_step", &sgd_step_op);
     m.impl("adamw_step", &adamw_step_op);

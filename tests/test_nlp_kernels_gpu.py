@@ -155,3 +155,18 @@ def test_multi_tensor_adamw_matches_torch(tops, dtype):
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
     for a, b in zip(ours, ref):
         assert (a.float() - b).abs().max().item() <= tol * max(1.0, b.abs().max().item())
+
+
+@pytest.mark.parametrize("B,S,H,causal", [(8, 384, 12, False), (2, 384, 12, True), (3, 200, 4, False), (1, 128, 2, True), (2, 37, 3, False),
+                                          (1, 300, 1, True)])
+def test_fused_attention_matches_float64(tops, B, S, H, causal):
+    """softmax(Q K^T / 8 [+ causal mask]) V from the fused projection output [B, S, 3, H, 64], against float64 on the CPU
+    (bfloat16 inputs, tolerance 2e-2 of the largest output); ragged sequence lengths use zero-filled key tiles and masks."""
+    from orion_b200 import kernels
+    torch.manual_seed(40 + S)
+    qkv = torch.randn(B, S, 3 * H * 64, device="cuda").to(torch.bfloat16)
+    ctx = tops.attention(qkv, H, 0.125, causal).view(B, S, H, 64)
+    assert kernels.read_status() == 0
+    q, k, v = qkv.double().cpu().view(B, S, 3, H, 64).permute(2, 0, 3, 1, 4)
+    want = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=0.125).permute(0, 2, 1, 3)
+    assert O.rel_err(ctx, want) < 2e-2
