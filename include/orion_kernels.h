@@ -50,6 +50,9 @@ int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y, const floa
                                const void* residual, int relu, int dtype, int Nb, int H, int W, int C, int Kout, int R, int S,
                                int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int bn, int splits,
                                int num_ctas, void* stream);
+/* Its status word (kept inside the same built-in array; reading it synchronises the device and allocates nothing): the code
+ * of a bounded in-kernel wait that expired since the last call, 0 if none.  No counterpart in the reference. */
+int ob200_conv2d_fprop_noalloc_status(void);
 
 /* Tile width and split-K factor of the one-unit-per-tile / split-K schedule for a problem size (host logic only). */
 int ob200_plan_conv(int dtype, long long M, int Kout, int R, int S, int C, int num_ctas, int* bn_out, int* splits_out);

@@ -35,6 +35,7 @@ constexpr int kMaxDevices = 64;
 struct StaticScratch {
     float partial[kScratchFloats];
     int counters[kCounterInts];
+    int status;   // receives the code of a bounded wait that expired inside a kernel launched from here (0: none)
 };
 
 // Device-resident.  In host code this name is only a handle for the runtime's symbol
@@ -106,7 +107,7 @@ extern "C" int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y,
     int rc = scratch_for_current_device(&sc);
     if (rc != 0) return rc;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    p.status = nullptr;   // the status word of the other entry points is heap-allocated; this path has none
+    p.status = &sc->status;   // device address inside the static array: the other entry points' status word is heap-allocated
     if (splits > 1) {
         // The array still holds the previous call's leftovers.  Every unit overwrites its own partial tile before
         // anyone reads it, so only the arrival counters have to start at zero.
@@ -118,4 +119,16 @@ extern "C" int ob200_conv2d_fprop_noalloc(const void* x, const void* w, void* y,
     const long long units = tiles * splits;
     const int grid = units < num_ctas ? (int)units : num_ctas;
     return ob200_igemm_launch(&p, bn, grid, stream);
+}
+
+// Reads and clears the status word of the allocation-free entry point on the current device (synchronises the device; no
+// allocation).  0 = no kernel launched through ob200_conv2d_fprop_noalloc reported a timed-out wait since the last call.
+extern "C" int ob200_conv2d_fprop_noalloc_status(void) {
+    StaticScratch* sc = nullptr;
+    int rc = scratch_for_current_device(&sc);
+    if (rc != 0) return -1;
+    int v = 0;
+    if (cudaMemcpy(&v, &sc->status, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v && cudaMemset(&sc->status, 0, sizeof v) != cudaSuccess) return -1;
+    return v;
 }

@@ -73,6 +73,8 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(lib, shape, bn,
         from oracle import numeric_oracle as O
         assert O.rel_err(got, O.conv2d_nhwc(x, w, (stride, stride), (pad, pad), shift=shift, act=1)) < TOL, \
             "call %d differs from the CPU oracle" % attempt
+    lib.ob200_conv2d_fprop_noalloc_status.restype = ctypes.c_int
+    assert lib.ob200_conv2d_fprop_noalloc_status() == 0, "a kernel wait ran out"
 
 
 def test_noalloc_without_split_k_is_bit_identical(lib):
