@@ -20,6 +20,12 @@
 // clock advances one tick per non-pop queue lock, per submit and per event query.
 // The same rules are implemented independently by the product's simulator; equal
 // logs mean equal call sequences.
+//
+// Second mode, `ref_replay --observations <trace> <ref_dir>`: no simulation at all.  The trace
+// (orion_b200/csrc/sched/observation.hpp) holds every answer the live scheduler got from its
+// queues, events, clock and stop flags, and every op it released.  The same hooks hand those
+// answers to the reference at the calls where it asks for them and compare what it releases,
+// closes and stops with what the live run did, token by token.
 #include <dlfcn.h>
 #include <pwd.h>
 
@@ -27,6 +33,8 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <fstream>
+#include <sstream>
 #include <string>
 #include <vector>
 
@@ -140,6 +148,155 @@ void on_unlock(int i) {
     }
 }
 
+
+// ------------------------------------------------------------------ observation mode
+struct ObsTok {
+    char kind;
+    int a, b, c, d, e;
+    int64_t t;
+};
+struct ObsLine {
+    uint64_t rep;
+    std::vector<ObsTok> toks;
+};
+struct Obs {
+    bool on = false, truncated = false;
+    const std::vector<ObsLine>* lines = nullptr;
+    size_t line = 0, tok = 0;
+    uint64_t rep = 0;
+    uint64_t decisions = 0, closed = 0, queries = 0, tokens = 0, polls = 0;
+    int64_t last_t = 0;
+    std::vector<int> it;            // requests closed per client
+    std::vector<char> stop_told;    // X tokens seen
+    FILE* json_out = nullptr;
+    int phase = 0;
+} o;
+
+[[noreturn]] void obs_finish(bool matched, const char* why) {
+    fprintf(o.json_out,
+            "{\"impl\": \"reference\", \"mode\": \"observations\", \"matched\": %s, \"truncated\": %s, \"decisions\": %llu, "
+            "\"requests_closed\": %llu, \"queries\": %llu, \"polls\": %llu, \"phase\": %d, \"detail\": \"%s\"}\n",
+            matched ? "true" : "false", o.truncated ? "true" : "false", (unsigned long long)o.decisions,
+            (unsigned long long)o.closed, (unsigned long long)o.queries, (unsigned long long)o.polls, o.phase, why);
+    fflush(o.json_out);
+    _exit(matched ? 0 : 3);
+}
+
+const ObsTok* obs_cur() {
+    while (o.line < o.lines->size()) {
+        const ObsLine& l = (*o.lines)[o.line];
+        if (o.tok < l.toks.size()) return &l.toks[o.tok];
+        o.tok = 0;
+        o.polls++;
+        if (++o.rep >= l.rep) {
+            o.rep = 0;
+            o.line++;
+        }
+    }
+    return nullptr;
+}
+void obs_advance() {
+    o.tok++;
+    o.tokens++;
+}
+// Tokens no call of the reference stands for: the stop-acknowledgement mask (the reference reads its flag from
+// memory) and a stop request made while the client's lock is already held.
+const ObsTok* obs_next(const char* who) {
+    while (true) {
+        const ObsTok* t = obs_cur();
+        if (!t) {
+            if (o.truncated) obs_finish(true, "the trace ends here (recording limit); every decision up to it agrees");
+            static char msg[128];
+            snprintf(msg, sizeof msg, "the reference made a call (%s) the live run did not make", who);
+            obs_finish(false, msg);
+        }
+        if (t->kind == 'K') {
+            for (int i = 0; i < g.n; i++) g.client_stop_ack[i] = (t->a >> i) & 1;
+            obs_advance();
+        } else if (t->kind == 'X' && t->b == 1) {
+            o.stop_told[t->a] = 1;
+            obs_advance();
+        } else if (t->kind == 'B') {
+            obs_finish(true, "the live run closed an iteration early (profile longer than the op stream); compared up to there");
+        } else {
+            return t;
+        }
+    }
+}
+[[noreturn]] void obs_mismatch(const char* what, const ObsTok* t, int a, int b, int c, int d, int e) {
+    static char msg[256];
+    snprintf(msg, sizeof msg, "%s: reference %d:%d:%d:%d:%d, live token %c%d:%d:%d:%d:%d", what, a, b, c, d, e, t->kind, t->a, t->b,
+             t->c, t->d, t->e);
+    obs_finish(false, msg);
+}
+
+void obs_lock(int i) {
+    if (g.pending) {   // the pop that follows a launch: this is the decision
+        int type = (int)g.kqueues[i]->front().type;
+        int stream = (int)g.pend_stream - 1;
+        uintptr_t ev = g.pend_event - 1;
+        int evl = (int)(ev / kEventsPerList), evs = (int)(ev % kEventsPerList);
+        const ObsTok* t = obs_next("release");
+        if (t->kind != 'S' || t->a != i || t->b != type || t->c != stream || t->d != evl || t->e != evs)
+            obs_mismatch("release", t, i, type, stream, evl, evs);
+        obs_advance();
+        o.decisions++;
+        g.pending = false;
+        return;
+    }
+    const ObsTok* t = obs_next("queue lock");
+    if ((t->kind != 'P' && t->kind != 'L' && t->kind != 'X') || t->a != i) obs_mismatch("queue lock", t, i, 0, 0, 0, 0);
+    if (t->kind == 'P') {
+        std::queue<func_record>* q = g.kqueues[i];
+        if (t->b >= 0) {
+            if (q->empty()) {
+                func_record r;
+                memset((void*)&r, 0, sizeof r);
+                r.type = (func_type)t->b;
+                if (r.type == MEMCPY_RECORD) r.data.mrecord.async = true;
+                if (r.type == MEMSET_RECORD) r.data.msetrecord.async = true;
+                q->push(r);
+            } else if ((int)q->front().type != t->b) {
+                obs_mismatch("queue head", t, i, (int)q->front().type, 0, 0, 0);
+            }
+        } else if (!q->empty()) {
+            obs_mismatch("queue should be empty", t, i, (int)q->front().type, 0, 0, 0);
+        }
+    } else if (t->kind == 'X') {
+        o.stop_told[i] = 1;
+    }
+    obs_advance();
+}
+
+void obs_unlock(int i) {
+    if (o.it[i] >= 0 && g.request_status[i][o.it[i]]) {
+        const ObsTok* t = obs_next("request closed");
+        if (t->kind != 'D' || t->a != i || t->b != o.it[i]) obs_mismatch("request closed", t, i, o.it[i], 0, 0, 0);
+        obs_advance();
+        o.it[i] += 1;
+        o.closed++;
+    }
+}
+
+bool obs_query(uintptr_t ev) {
+    int evl = (int)(ev / kEventsPerList), evs = (int)(ev % kEventsPerList);
+    const ObsTok* t = obs_next("event query");
+    if (t->kind != 'Q' || t->a != evl || t->b != evs) obs_mismatch("event query", t, evl, evs, 0, 0, 0);
+    bool done = t->c != 0;
+    obs_advance();
+    o.queries++;
+    return done;
+}
+
+int64_t obs_now() {
+    const ObsTok* t = obs_cur();
+    if (t && t->kind == 'T') {
+        o.last_t = t->t;
+        obs_advance();
+    }
+    return o.last_t;
+}
+
 int client_of(pthread_mutex_t* m) {
     if (!g.active) return -1;
     for (int i = 0; i < g.n; i++)
@@ -159,6 +316,10 @@ extern "C" int pthread_mutex_lock(pthread_mutex_t* m) {
         if (!real_lock) real_lock = (mutex_fn)dlsym(RTLD_NEXT, "pthread_mutex_lock");
         return real_lock(m);
     }
+    if (o.on) {
+        obs_lock(i);
+        return 0;
+    }
     detect_stops();
     if (g.pending)
         finalize_submit(i);
@@ -172,6 +333,10 @@ extern "C" int pthread_mutex_unlock(pthread_mutex_t* m) {
     if (i < 0) {
         if (!real_unlock) real_unlock = (mutex_fn)dlsym(RTLD_NEXT, "pthread_mutex_unlock");
         return real_unlock(m);
+    }
+    if (o.on) {
+        obs_unlock(i);
+        return 0;
     }
     detect_stops();
     on_unlock(i);
@@ -192,6 +357,7 @@ namespace std {
 namespace chrono {
 inline namespace _V2 {
 system_clock::time_point system_clock::now() noexcept {
+    if (o.on) return time_point(duration(obs_now() * 1000));
     return time_point(duration(g.now * 1000));   // 1 tick = 1 us; duration is ns
 }
 }  // namespace _V2
@@ -220,6 +386,7 @@ cudaError_t cudaEventRecord(cudaEvent_t e, cudaStream_t s) {
     return cudaSuccess;
 }
 cudaError_t cudaEventQuery(cudaEvent_t e) {
+    if (o.on) return obs_query((uintptr_t)e - 1) ? cudaSuccess : cudaErrorNotReady;
     detect_stops();
     g.now += 1;
     uintptr_t ev = (uintptr_t)e - 1;
@@ -241,9 +408,199 @@ typedef void (*setup_fn)(void*, int, int*, char**, char**, int*, int*, bool*, bo
 typedef void (*setup_change_fn)(void*, int, char*, int);
 typedef void* (*schedule_fn)(void*, int, bool, int, bool, int, bool, bool, int, int, int);
 
+struct Ref {
+    void* shim = nullptr;
+    sched_init_fn sched_init = nullptr;
+    setup_fn setup = nullptr;
+    setup_change_fn setup_change = nullptr;
+    schedule_fn schedule = nullptr;
+    int* max_sms = nullptr;
+};
+
+static bool load_ref(const std::string& ref_dir, Ref& r) {
+    void* sched_lib = dlopen((ref_dir + "/scheduler_eval.so").c_str(), RTLD_NOW | RTLD_GLOBAL);
+    if (!sched_lib) {
+        fprintf(stderr, "ref_replay: %s\n", dlerror());
+        return false;
+    }
+    r.shim = dlopen((ref_dir + "/home/orion/src/cuda_capture/libinttemp.so").c_str(), RTLD_NOW | RTLD_GLOBAL);
+    if (!r.shim) {
+        fprintf(stderr, "ref_replay: %s\n", dlerror());
+        return false;
+    }
+    r.sched_init = (sched_init_fn)dlsym(sched_lib, "sched_init");
+    r.setup = (setup_fn)dlsym(sched_lib, "setup");
+    r.setup_change = (setup_change_fn)dlsym(sched_lib, "setup_change");
+    r.schedule = (schedule_fn)dlsym(sched_lib, "schedule");
+    r.max_sms = (int*)dlsym(sched_lib, "max_sms");
+    if (!r.sched_init || !r.setup || !r.setup_change || !r.schedule || !r.max_sms) {
+        fprintf(stderr, "ref_replay: scheduler_eval.so lacks an expected symbol\n");
+        return false;
+    }
+    return true;
+}
+
+static void bind_shim_globals(void* shim) {
+    g.kqueues = *(std::queue<func_record>***)dlsym(shim, "kqueues");
+    g.mutexes = *(pthread_mutex_t***)dlsym(shim, "mutexes");
+    g.request_status = *(volatile bool***)dlsym(shim, "client_request_status");
+    g.client_stop = *(volatile bool**)dlsym(shim, "client_stop");
+    g.client_stop_ack = *(volatile bool**)dlsym(shim, "client_stop_ack");
+}
+
+// ---- observation mode: the trace file and its replay -------------------------------------------------
+struct ObsCommand {
+    enum Kind { PHASE, SETUP_CHANGE } kind;
+    int args[7] = {0, 0, 0, 0, 0, 0, 0};   // phase: warmup, warmup_iters, reef, seq, depth, hp_limit, update_start
+    std::vector<ObsLine> lines;
+    int client = 0, num_kernels = 0;
+    std::string file;
+};
+
+static bool parse_tokens(std::istringstream& in, std::vector<ObsTok>& out) {
+    std::string w;
+    while (in >> w) {
+        ObsTok t{w[0], 0, 0, 0, 0, 0, 0};
+        const char* p = w.c_str() + 1;
+        if (t.kind == 'T') {
+            t.t = strtoll(p, nullptr, 10);
+        } else {
+            int* f[5] = {&t.a, &t.b, &t.c, &t.d, &t.e};
+            for (int k = 0; k < 5 && *p; k++) {
+                char* end = nullptr;
+                *f[k] = (int)strtol(p, &end, 10);
+                p = (*end == ':') ? end + 1 : end;
+            }
+        }
+        if (!strchr("PQTKBSLDX", t.kind)) return false;
+        out.push_back(t);
+    }
+    return true;
+}
+
+static int run_observations(const std::string& trace, const std::string& ref_dir) {
+    std::ifstream in(trace);
+    if (!in.is_open()) {
+        fprintf(stderr, "ref_replay: cannot open %s\n", trace.c_str());
+        return 1;
+    }
+    int max_sms = 80, reef_streams = 0, n = 0;
+    std::vector<int> num_kernels, num_iters, trains;
+    std::vector<std::string> profiles;
+    std::vector<ObsCommand> cmds;
+    bool truncated = false;
+    std::string line, key;
+    while (std::getline(in, line)) {
+        std::istringstream ls(line);
+        if (!(ls >> key)) continue;
+        if (key == "orion_observations") continue;
+        if (key == "max_sms") {
+            std::string k2;
+            ls >> max_sms >> k2 >> reef_streams;
+        } else if (key == "nclients") {
+            ls >> n;
+            num_kernels.assign(n, 0);
+            num_iters.assign(n, 0);
+            trains.assign(n, 0);
+            profiles.assign(n, "");
+        } else if (key == "client") {
+            int i;
+            std::string k;
+            ls >> i;
+            if (i < 0 || i >= n) return 1;
+            ls >> k >> trains[i] >> k >> num_iters[i] >> k >> profiles[i] >> num_kernels[i];
+        } else if (key == "phase") {
+            ObsCommand c;
+            c.kind = ObsCommand::PHASE;
+            for (int k = 0; k < 7; k++) ls >> c.args[k];
+            cmds.push_back(c);
+        } else if (key == "p") {
+            if (cmds.empty() || cmds.back().kind != ObsCommand::PHASE) return 1;
+            ObsLine l;
+            ls >> l.rep;
+            if (!parse_tokens(ls, l.toks)) {
+                fprintf(stderr, "ref_replay: unknown token in %s\n", trace.c_str());
+                return 1;
+            }
+            if (!l.toks.empty() && l.rep > 0) cmds.back().lines.push_back(l);
+        } else if (key == "setup_change") {
+            ObsCommand c;
+            c.kind = ObsCommand::SETUP_CHANGE;
+            ls >> c.client >> c.file >> c.num_kernels;
+            cmds.push_back(c);
+        } else if (key == "truncated") {
+            truncated = true;
+        } else if (key == "endphase" || key == "reset") {
+            // `reset` only clears counters that are already zero between phases
+        } else {
+            fprintf(stderr, "ref_replay: unknown line '%s' in %s\n", key.c_str(), trace.c_str());
+            return 1;
+        }
+    }
+    if (n < 1 || cmds.empty()) {
+        fprintf(stderr, "ref_replay: %s holds no phase\n", trace.c_str());
+        return 1;
+    }
+    snprintf(g_home_base, sizeof g_home_base, "%s/home", ref_dir.c_str());
+    o.json_out = fdopen(dup(1), "w");
+    if (!freopen("/dev/null", "w", stdout)) return 1;
+    Ref ref;
+    if (!load_ref(ref_dir, ref)) return 1;
+    *ref.max_sms = max_sms;
+
+    std::vector<int> tids(n);
+    std::vector<char*> models(n), files(n);
+    bool* train = new bool[n];
+    for (int i = 0; i < n; i++) {
+        tids[i] = 100000 + i;
+        models[i] = (char*)"model";
+        files[i] = (char*)profiles[i].c_str();
+        train[i] = trains[i] != 0;
+    }
+    g.n = n;
+    void* sched = ref.sched_init();
+    ref.setup(sched, n, tids.data(), models.data(), files.data(), num_kernels.data(), num_iters.data(), train, reef_streams != 0);
+    bind_shim_globals(ref.shim);
+    g.active = true;
+    o.on = true;
+    o.truncated = truncated;
+    o.it.assign(n, 0);
+    o.stop_told.assign(n, 0);
+    for (size_t c = 0; c < cmds.size(); c++) {
+        ObsCommand& cmd = cmds[c];
+        if (cmd.kind == ObsCommand::SETUP_CHANGE) {
+            ref.setup_change(sched, cmd.client, (char*)cmd.file.c_str(), cmd.num_kernels);
+            continue;
+        }
+        o.lines = &cmd.lines;
+        o.line = o.tok = 0;
+        o.rep = 0;
+        ref.schedule(sched, n, true, 0, cmd.args[0] != 0, cmd.args[1], cmd.args[2] != 0, cmd.args[3] != 0, cmd.args[4], cmd.args[5],
+                     cmd.args[6]);
+        // the reference came back by itself: it must have used up the phase's tokens
+        while (const ObsTok* t = obs_cur()) {
+            if (t->kind == 'K' || (t->kind == 'X' && t->b == 1)) {
+                if (t->kind == 'X') o.stop_told[t->a] = 1;
+                obs_advance();
+                continue;
+            }
+            if (o.truncated) break;
+            obs_mismatch("the reference ended the phase, the live run went on", t, 0, 0, 0, 0, 0);
+        }
+        for (int k = 0; k < n; k++)
+            if ((g.client_stop[k] ? 1 : 0) != o.stop_told[k]) {
+                ObsTok x{'X', k, 0, 0, 0, 0, 0};
+                obs_mismatch("stop request", &x, k, g.client_stop[k] ? 1 : 0, 0, 0, 0);
+            }
+        o.phase++;
+    }
+    obs_finish(true, "every release, closed request and stop request of the live run is the reference's");
+}
+
 int main(int argc, char** argv) {
+    if (argc >= 4 && std::string(argv[1]) == "--observations") return run_observations(argv[2], argv[3]);
     if (argc < 4) {
-        fprintf(stderr, "usage: ref_replay <script> <ref_dir> <log|-> [--quiet]\n");
+        fprintf(stderr, "usage: ref_replay <script> <ref_dir> <log|-> [--quiet]\n       ref_replay --observations <trace> <ref_dir>\n");
         return 64;
     }
     std::string ref_dir = argv[2];
@@ -262,26 +619,14 @@ int main(int argc, char** argv) {
     FILE* json_out = fdopen(dup(1), "w");
     if (!freopen("/dev/null", "w", stdout)) return 1;
 
-    void* sched_lib = dlopen((ref_dir + "/scheduler_eval.so").c_str(), RTLD_NOW | RTLD_GLOBAL);
-    if (!sched_lib) {
-        fprintf(stderr, "ref_replay: %s\n", dlerror());
-        return 1;
-    }
-    void* shim = dlopen((ref_dir + "/home/orion/src/cuda_capture/libinttemp.so").c_str(), RTLD_NOW | RTLD_GLOBAL);
-    if (!shim) {
-        fprintf(stderr, "ref_replay: %s\n", dlerror());
-        return 1;
-    }
-    sched_init_fn sched_init = (sched_init_fn)dlsym(sched_lib, "sched_init");
-    setup_fn setup = (setup_fn)dlsym(sched_lib, "setup");
-    setup_change_fn setup_change = (setup_change_fn)dlsym(sched_lib, "setup_change");
-    schedule_fn schedule = (schedule_fn)dlsym(sched_lib, "schedule");
-    int* ref_max_sms = (int*)dlsym(sched_lib, "max_sms");
-    if (!sched_init || !setup || !setup_change || !schedule || !ref_max_sms) {
-        fprintf(stderr, "ref_replay: scheduler_eval.so lacks an expected symbol\n");
-        return 1;
-    }
-    *ref_max_sms = s.max_sms;
+    Ref ref;
+    if (!load_ref(ref_dir, ref)) return 1;
+    sched_init_fn sched_init = ref.sched_init;
+    setup_fn setup = ref.setup;
+    setup_change_fn setup_change = ref.setup_change;
+    schedule_fn schedule = ref.schedule;
+    void* shim = ref.shim;
+    *ref.max_sms = s.max_sms;
 
     std::vector<int> tids(n), num_kernels(n), num_iters(n);
     std::vector<char*> models(n), files(n);
@@ -311,11 +656,7 @@ int main(int argc, char** argv) {
                 (unsigned long)g_events, (unsigned long)g_streams, n * kEventsPerList, n);
         return 1;
     }
-    g.kqueues = *(std::queue<func_record>***)dlsym(shim, "kqueues");
-    g.mutexes = *(pthread_mutex_t***)dlsym(shim, "mutexes");
-    g.request_status = *(volatile bool***)dlsym(shim, "client_request_status");
-    g.client_stop = *(volatile bool**)dlsym(shim, "client_stop");
-    g.client_stop_ack = *(volatile bool**)dlsym(shim, "client_stop_ack");
+    bind_shim_globals(shim);
     g.active = true;
 
     double secs = 0;

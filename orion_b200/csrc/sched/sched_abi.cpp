@@ -18,7 +18,9 @@
 //     quota (ORION_BE_SM_QUOTA), which turns the profile-trusted SM budget into a
 //     hardware partition;
 //   * optional: the run can be recorded as an arrival script (ORION_RECORD_SCRIPT)
-//     for replay through orion_replay and through the reference scheduler.
+//     for replay through orion_replay and through the reference scheduler, and as an
+//     observation trace (ORION_RECORD_OBS, observation.hpp): every answer the policy got
+//     and every decision it took, for a check of the live decisions against the reference.
 #include <dlfcn.h>
 #include <pthread.h>
 #include <sched.h>
@@ -35,6 +37,7 @@
 #include "../capture/capture_state.h"
 #include "../policy/policy.hpp"
 #include "green_ctx.hpp"
+#include "observation.hpp"
 
 #if defined(__x86_64__)
 #include <immintrin.h>
@@ -247,6 +250,7 @@ struct Scheduler {
     bool ready = false;
     std::vector<std::string> profile_paths;
     std::string record_path;
+    orion::ObsRecorder obs;
     int phases_run = 0;
 };
 
@@ -333,6 +337,7 @@ void setup_change(Scheduler* s, int client_id, char* file, int num_kernels) {
     s->core.max_sms_clients[client_id] = orion::max_sm_used(s->core.op_info[client_id]);
     s->core.num_kernels[client_id] = num_kernels;   // written into the caller's array, like the reference
     s->profile_paths[client_id] = file;
+    if (s->obs.f) s->obs.raw("setup_change " + std::to_string(client_id) + " " + file + " " + std::to_string(num_kernels));
 }
 
 void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files, int* num_kernels, int* num_iters, bool* train,
@@ -500,6 +505,22 @@ void setup(Scheduler* s, int num_clients, int* tids, char** models, char** files
         env.rec_iters.assign(num_clients, {});
         env.iter_start_us.assign(num_clients, {});
     }
+    if (const char* e = getenv("ORION_RECORD_OBS")) {
+        uint64_t cap = 400000;   // distinct poll lines; a trace stops there and says so
+        if (const char* c = getenv("ORION_RECORD_OBS_MAX_LINES")) cap = strtoull(c, nullptr, 10);
+        s->obs.close();
+        s->obs = orion::ObsRecorder();
+        if (s->obs.open(e, cap)) {
+            std::string h = "orion_observations 1\nmax_sms " + std::to_string(core.max_sms) + " reef " + (reef ? "1" : "0") +
+                            "\nnclients " + std::to_string(num_clients);
+            for (int i = 0; i < num_clients; i++)
+                h += "\nclient " + std::to_string(i) + " train " + (train[i] ? "1" : "0") + " num_iters " +
+                     std::to_string(num_iters[i]) + " profile " + files[i] + " " + std::to_string(num_kernels[i]);
+            s->obs.raw(h);
+        } else {
+            fprintf(stderr, "orion: cannot write the observation trace %s\n", e);
+        }
+    }
     sh->epoch.fetch_add(1);
     sh->active.store(1, std::memory_order_release);
     s->ready = true;
@@ -522,7 +543,20 @@ void* schedule(Scheduler* s, int num_clients, bool profile_mode, int iter, bool 
         s->env.skip_inner_events = !seq && !(e && e[0] == '0');   // the sequential policy shares one event list
     }
     s->sh->polling.store(1, std::memory_order_release);
-    s->core.run_phase(s->env, a);
+    if (s->obs.on()) {
+        char line[160];
+        snprintf(line, sizeof line, "phase %d %d %d %d %d %d %d", warmup ? 1 : 0, warmup_iters, reef ? 1 : 0, seq ? 1 : 0, reef_depth,
+                 hp_limit, update_start);
+        s->obs.raw(line);
+        orion::ObsEnv<LiveEnv> watched(s->env, s->obs, s->num_clients);
+        watched.begin_phase();
+        s->core.run_phase(watched, a);
+        watched.end_phase();
+        s->obs.raw("endphase");
+        if (!warmup || s->obs.truncated) s->obs.close();
+    } else {
+        s->core.run_phase(s->env, a);
+    }
     s->sh->polling.store(0, std::memory_order_release);
     s->phases_run++;
     if (s->core.error == 2) {
@@ -541,6 +575,7 @@ void* schedule(Scheduler* s, int num_clients, bool profile_mode, int iter, bool 
 void* reset(Scheduler* s, int num_clients) {
     (void)num_clients;
     if (s) s->core.reset();
+    if (s && s->obs.f) s->obs.raw("reset");
     return nullptr;
 }
 
