@@ -158,7 +158,23 @@ def policy_replay(script, repeat=1):
     return out
 
 
-def cpu_baseline(sample_hp=12, sample_be=2, recorded_script=None):
+def live_decision_check(trace):
+    """The decisions the live scheduler took in this run's co-located phase, checked against the compiled reference
+    scheduler fed the same queue heads, event-query answers, clock reads and stop acknowledgements (observation trace,
+    orion_b200/csrc/sched/observation.hpp; checker oracle/ref_driver.cpp)."""
+    ref = os.path.join(ROOT, "oracle", "_ref", "ref_replay")
+    if not trace or not os.path.exists(trace) or not os.path.exists(ref):
+        return None
+    try:
+        r = subprocess.run([ref, "--observations", trace, os.path.join(ROOT, "oracle", "_ref")], capture_output=True, text=True,
+                           timeout=240)
+        rep = json.loads(r.stdout.strip().splitlines()[-1])
+        return {k: rep[k] for k in ("matched", "truncated", "decisions", "requests_closed", "polls", "detail")}
+    except (OSError, ValueError, KeyError, subprocess.SubprocessError, IndexError) as e:
+        return {"error": repr(e)[:200]}
+
+
+def cpu_baseline(sample_hp=12, sample_be=2, recorded_script=None, observations=None):
     """Eager PyTorch on the host cores: the reference's numeric path for this workload
     (reference benchmarking/benchmark_suite/train_imagenet.py:111-116), on a bounded sample; plus the reference
     scheduler's decisions on an arrival script (this run's recorded one when given)."""
@@ -198,7 +214,8 @@ def cpu_baseline(sample_hp=12, sample_be=2, recorded_script=None):
                       "ResNet-50 b4 forwards" % (sample_be, sample_hp),
             "hp_p50_ms": float(np.percentile(lat, 50)) * 1e3, "hp_p99_ms": float(np.percentile(lat, 99)) * 1e3,
             "policy": dict(policy_replay(script, repeat=1 if recorded_script else 3),
-                           trace="recorded from this run's co-located phase" if recorded_script else "committed synthetic script")}
+                           trace="recorded from this run's co-located phase" if recorded_script else "committed synthetic script",
+                           live_decisions=live_decision_check(observations))}
 
 
 def paired_bootstrap_p99_ratio(coloc, solo, n_boot=1000, seed=7):
@@ -270,10 +287,13 @@ def run_replica(gpu, steps, warm_steps, out_dir, be_quota, with_c5=False):
     e2e = E.run_launch_jobs(pair, os.path.join(out_dir, "coloc_e2e"), depth=depth, extra_env=env)
     env_res = dict(env)
     script = os.path.join(out_dir, "coloc_resident", "recorded.script")
-    env_res.update({"ORION_RESIDENT_INPUTS": 1, "ORION_READBACK": 0, "ORION_RECORD_SCRIPT": script, "ORION_RECORD_MAX_ITERS": 400})
+    obs = os.path.join(out_dir, "coloc_resident", "observations.trace")
+    env_res.update({"ORION_RESIDENT_INPUTS": 1, "ORION_READBACK": 0, "ORION_RECORD_SCRIPT": script, "ORION_RECORD_MAX_ITERS": 400,
+                    "ORION_RECORD_OBS": obs, "ORION_RECORD_OBS_MAX_LINES": 300000})
     res = E.run_launch_jobs(pair, os.path.join(out_dir, "coloc_resident"), depth=depth, extra_env=env_res)
     out = {"hp_solo": hp_solo, "be_solo": be_solo, "e2e": e2e, "resident": res, "depth": depth,
-           "profile_rows": {"hp": hp_prof[3], "be": be_prof[3]}, "script": script if os.path.exists(script) else None}
+           "profile_rows": {"hp": hp_prof[3], "be": be_prof[3]}, "script": script if os.path.exists(script) else None,
+           "observations": obs if os.path.exists(obs) else None}
     if with_c5:
         out["c5"] = run_c5(E, env, out_dir)
     return out
@@ -395,7 +415,7 @@ def main():
     peaks = read_peaks()
     roof = kernel_roofline(batch=32, iters=5, warm=3)
     roof_hbm = hbm_roofline(peaks)
-    base = cpu_baseline(recorded_script=rep["script"])
+    base = cpu_baseline(recorded_script=rep["script"], observations=rep.get("observations"))
     worst = max(gathered, key=lambda g: g["hp_p99"] / g["hp_solo_p99"])
     value = sum(g["be_sps"] for g in gathered)
     e2e_value = sum(g["be_sps_e2e"] for g in gathered)

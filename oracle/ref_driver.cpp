@@ -167,6 +167,7 @@ struct Obs {
     uint64_t decisions = 0, closed = 0, queries = 0, tokens = 0, polls = 0;
     int64_t last_t = 0;
     std::vector<int> it;            // requests closed per client
+    std::vector<int> max_it;        // length of the reference's request_status rows
     std::vector<char> stop_told;    // X tokens seen
     FILE* json_out = nullptr;
     int phase = 0;
@@ -269,7 +270,7 @@ void obs_lock(int i) {
 }
 
 void obs_unlock(int i) {
-    if (o.it[i] >= 0 && g.request_status[i][o.it[i]]) {
+    if (o.it[i] < o.max_it[i] && g.request_status[i][o.it[i]]) {
         const ObsTok* t = obs_next("request closed");
         if (t->kind != 'D' || t->a != i || t->b != o.it[i]) obs_mismatch("request closed", t, i, o.it[i], 0, 0, 0);
         obs_advance();
@@ -565,6 +566,7 @@ static int run_observations(const std::string& trace, const std::string& ref_dir
     o.on = true;
     o.truncated = truncated;
     o.it.assign(n, 0);
+    o.max_it = num_iters;
     o.stop_told.assign(n, 0);
     for (size_t c = 0; c < cmds.size(); c++) {
         ObsCommand& cmd = cmds[c];

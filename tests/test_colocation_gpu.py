@@ -36,7 +36,8 @@ def test_profile_then_colocate(built, tmp_path):
 
     pair = [E.client_entry("resnet50_be", be, 100000), E.client_entry("resnet50_hp", hp, 130, rps=80)]
     depth = int(0.025 * hp_solo["p50_latency"] * 1e6)
-    co = E.run_launch_jobs(pair, os.path.join(out, "pair"), depth=depth, extra_env=env, timeout=240)
+    trace = os.path.join(out, "pair.obs")
+    co = E.run_launch_jobs(pair, os.path.join(out, "pair"), depth=depth, extra_env=dict(env, ORION_RECORD_OBS=trace), timeout=240)
     be_c, hp_c = co["clients"]
     assert hp_c["iterations"] == 130
     assert be_c["iterations"] >= 11 and be_c["samples_per_s"] > 0
@@ -44,6 +45,22 @@ def test_profile_then_colocate(built, tmp_path):
     assert st["hp_submits"] > 0 and st["be_submits"] > 0 and st["join_timeouts"] == 0
     assert co["scheduler"]["own_launches"] > 130 * 50
     assert hp_c["p99_latency"] < 20 * hp_solo["p99_latency"]
+
+    # The decisions this run took on the GPU, checked against the compiled reference scheduler fed the same queue heads,
+    # event-query answers, clock reads and stop acknowledgements (oracle/ref_driver.cpp, observation mode).
+    import json
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.path.join(root, "oracle", "_ref", "ref_replay")
+    assert os.path.exists(trace)
+    if os.path.exists(ref):
+        r = subprocess.run([ref, "--observations", trace, os.path.join(root, "oracle", "_ref")], capture_output=True, text=True,
+                           timeout=300)
+        rep = json.loads(r.stdout.strip().splitlines()[-1])
+        assert r.returncode == 0 and rep["matched"] is True, rep
+        assert rep["decisions"] > 130 * 50
+        if not rep["truncated"] and st["forced_iter_ends"] == 0:
+            assert rep["decisions"] >= st["hp_submits"] + st["be_submits"]
 
 
 def test_best_effort_stream_inside_a_green_context_partition(built, tmp_path):

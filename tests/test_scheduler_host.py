@@ -231,3 +231,96 @@ def test_high_priority_training_client_runs_the_update_phase_rule(built, tmp_pat
     assert r["done"][0] >= 10
     assert r["stats"]["queries"] > 0 and r["stats"]["join_timeouts"] == 0
     assert r["hp_samples"] == 45
+
+
+REF_REPLAY = os.path.join(ROOT, "oracle", "_ref", "ref_replay")
+
+
+def _check_observations(trace, expect_match=True):
+    """Feeds an observation trace to the compiled reference scheduler (oracle/ref_driver.cpp, second mode)."""
+    out = subprocess.run([REF_REPLAY, "--observations", str(trace), os.path.join(ROOT, "oracle", "_ref")], capture_output=True,
+                         text=True, timeout=300)
+    line = out.stdout.strip().splitlines()[-1] if out.stdout.strip() else "{}"
+    rep = json.loads(line)
+    if expect_match:
+        assert out.returncode == 0 and rep.get("matched") is True, (out.returncode, line, out.stderr[-2000:])
+    return out.returncode, rep
+
+
+def _live_scenarios(tmp_path):
+    be = _profile(tmp_path, "be", [(1, 40, 9000), (0, 200, 5000), (-1, 30, 3000)] * 8)
+    be2 = _profile(tmp_path, "be2", [(0, 20, 4000), (1, 50, 7000)] * 10)
+    hp = _profile(tmp_path, "hp", [(1, 60, 8000), (0, 20, 2000)] * 5)
+    hpt = _profile(tmp_path, "hpt", [(1, 60, 8000)] * 8 + [(0, 10, 2000)] * 6)
+    bes = _profile(tmp_path, "bes", [(1, 20, 9000), (0, 30, 5000)] * 8)
+    pair = [{"profile": be, "num_kernels": 24, "iters": 100000, "train": True, "ops": [1] + [0] * 24, "after": [2]},
+            {"profile": hp, "num_kernels": 10, "iters": 60, "train": False, "ops": [1] + [0] * 10}]
+    return {
+        "pair": ({"clients": pair, "depth": 20000}, {}),
+        "pair_tight_threshold": ({"clients": pair, "depth": 6000}, {"ORION_MAX_SMS": "148"}),
+        "reef": ({"clients": pair, "depth": 12, "reef": True}, {}),
+        "two_best_effort": ({"clients": [
+            {"profile": be, "num_kernels": 24, "iters": 100000, "train": True, "ops": [1] + [0] * 24},
+            {"profile": be2, "num_kernels": 20, "iters": 100000, "train": True, "ops": [0] * 20},
+            {"profile": hp, "num_kernels": 10, "iters": 60, "train": False, "ops": [1] + [0] * 10}], "depth": 30000},
+            {"ORION_MAX_SMS": "148"}),
+        "hp_training": ({"clients": [
+            {"profile": bes, "num_kernels": 16, "iters": 100000, "train": True, "ops": [0] * 16},
+            {"profile": hpt, "num_kernels": 14, "iters": 45, "train": True, "ops": [1] + [0] * 14}],
+            "depth": 20000, "hp_limit": 1000, "update_start": 8}, {"ORION_MAX_SMS": "148"}),
+        "single": ({"clients": [{"profile": hp, "num_kernels": 10, "iters": 30, "train": False, "ops": [1] + [0] * 10}]}, {}),
+    }
+
+
+import pytest
+
+
+@pytest.mark.skipif(not os.path.exists(REF_REPLAY), reason="the reference scheduler was not compiled on this machine")
+@pytest.mark.parametrize("name", ["pair", "pair_tight_threshold", "reef", "two_best_effort", "hp_training", "single"])
+def test_live_decisions_are_the_reference_schedulers_on_the_same_observations(built, tmp_path, name):
+    """ORION_RECORD_OBS: the live scheduler writes every answer it got (queue heads, event queries, clock reads, stop
+    acknowledgements) and every decision it took.  The compiled reference scheduler, handed the same answers at the same
+    calls, must release the same ops on the same streams with the same events, close the same requests and stop the same
+    clients (src/scheduler/scheduler_eval.cpp:238-487 against the live run itself, not against a re-simulation)."""
+    cfg, env = _live_scenarios(tmp_path)[name]
+    trace = tmp_path / "trace.obs"
+    r = _run(cfg, env_extra=dict(env, ORION_RECORD_OBS=str(trace)))
+    assert not r["wrong"] and r["stats"]["forced_iter_ends"] == 0
+    rc, rep = _check_observations(trace)
+    live = r["stats"]["hp_submits"] + r["stats"]["be_submits"] if not cfg.get("reef") and len(cfg["clients"]) > 1 else None
+    assert rep["decisions"] > 100 and not rep["truncated"] and rep["phase"] == 3
+    if live is not None:
+        assert rep["decisions"] == live
+    assert rep["requests_closed"] >= sum(min(c["iters"], 10) for c in cfg["clients"])
+
+
+@pytest.mark.skipif(not os.path.exists(REF_REPLAY), reason="the reference scheduler was not compiled on this machine")
+def test_a_tampered_observation_trace_is_reported(built, tmp_path):
+    """The checker must notice a decision the reference would not have taken: move one release of the measured phase to
+    the other stream, drop one, and cut a trace short without the `truncated` mark."""
+    import re
+    cfg, env = _live_scenarios(tmp_path)["pair"]
+    trace = tmp_path / "trace.obs"
+    _run(cfg, env_extra=dict(env, ORION_RECORD_OBS=str(trace)))
+    text = trace.read_text()
+    _check_observations(trace)
+    body = text.split("\nphase 0 ", 1)
+    assert len(body) == 2
+    m = list(re.finditer(r" S0:0:0:0:(\d+)", body[1]))[5]
+    for bad_tail in (body[1][:m.start()] + " S0:0:1:0:" + m.group(1) + body[1][m.end():],     # other stream
+                     body[1][:m.start()] + body[1][m.end():],                                 # release missing
+                     body[1][:m.start()].rsplit("\n", 1)[0] + "\nendphase\n"):               # live run "stopped" early
+        bad = tmp_path / "bad.obs"
+        bad.write_text(body[0] + "\nphase 0 " + bad_tail)
+        rc, rep = _check_observations(bad, expect_match=False)
+        assert rc == 3 and rep["matched"] is False, rep
+
+
+@pytest.mark.skipif(not os.path.exists(REF_REPLAY), reason="the reference scheduler was not compiled on this machine")
+def test_a_trace_cut_by_the_recording_limit_is_compared_up_to_the_cut(built, tmp_path):
+    cfg, env = _live_scenarios(tmp_path)["pair"]
+    trace = tmp_path / "trace.obs"
+    _run(cfg, env_extra=dict(env, ORION_RECORD_OBS=str(trace), ORION_RECORD_OBS_MAX_LINES="700"))
+    assert trace.read_text().rstrip().endswith("truncated")
+    rc, rep = _check_observations(trace)
+    assert rep["truncated"] and rep["decisions"] > 100
