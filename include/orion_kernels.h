@@ -124,6 +124,20 @@ int ob200_linear(const void* x, const void* w, void* y, const float* bias, int r
 int ob200_linear_batched(const void* x, const void* w, void* y, int dtype, int batch, int M, int N, int K, long long stride_x,
                          long long stride_w, long long stride_y, int num_ctas, void* stream);
 
+/* bfloat16 GEMM with transpose flags, strides and two batch levels (float32 accumulation):
+ *   C[bo][bi][m, n] = alpha * sum_k A[bo][bi][m, k] * B[bo][bi][n, k] (+ bias[n]),   bi < batch_inner, bo < batch_outer.
+ * a_mn = 0: A lies as [M, K] rows `lda` elements apart; a_mn = 1: as [K, M] rows (the reduction index is the slow one).
+ * b_mn likewise for B ([N, K] rows or [K, N] rows).  C rows are `ldc` apart; *_si / *_so are the element offsets between
+ * problems of the inner / outer batch level.  lda, ldb and the operand batch offsets must be multiples of 8 elements, the
+ * operand pointers 16-byte aligned.  out_f32 selects a float32 or bfloat16 C.  Few output tiles with a long reduction are cut
+ * along K into float32 partial matrices summed in split order (same result for every num_ctas).
+ * Takes the place of cublasSgemm_v2 / cublasSgemmStridedBatched with CUBLAS_OP_T / CUBLAS_OP_N operands (reference
+ * src/scheduler/utils_sched.cpp:490-513, trapped at src/cuda_capture/intercept_cublas.cpp:5-56,114-170): the data and weight
+ * gradients of linear layers and the attention products of training (the sgemm rows of benchmarking/model_kernels/bert_8_fb1). */
+int ob200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, int a_mn, int b_mn, long long lda,
+                    long long ldb, long long ldc, int batch_inner, int batch_outer, long long a_si, long long a_so, long long b_si,
+                    long long b_so, long long c_si, long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
+
 /* Batch-norm inference over the innermost (channel) dimension.  Takes the place of
  * cudnnBatchNormalizationForwardInference (reference src/scheduler/utils_sched.cpp:340-353). */
 int ob200_bn_inference_f32(const float* x, float* y, const float* gamma, const float* beta, const float* mean, const float* var,

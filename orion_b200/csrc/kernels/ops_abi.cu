@@ -84,6 +84,18 @@ static int plan_sm_count() {
     return n;
 }
 
+// For the other translation units of the library: the planning SM count and the calling stream's scratch for partial
+// sums (contents arbitrary between launches; launches of one stream use it one after the other).
+extern "C" int ob200_plan_sm_count(void) { return plan_sm_count(); }
+extern "C" float* ob200_stream_slabs(void* stream, size_t* bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    Scratch* sc = scratch_for(dev, (cudaStream_t)stream);
+    if (!sc) return nullptr;
+    if (bytes) *bytes = sc->slab_bytes;
+    return sc->slabs;
+}
+
 // Device status word of the current device, for the other translation units of the library.
 extern "C" int* ob200_status_word_for_current_device(void) {
     int dev = 0;

@@ -52,6 +52,8 @@ def lib():
             getattr(L, name).restype = c_int
         L.ob200_linear_batched.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_ll] * 3 + [c_int, c_void_p]
         L.ob200_linear_batched.restype = c_int
+        L.ob200_gemm_bf16.argtypes = [c_void_p] * 4 + [c_int] * 5 + [c_ll] * 3 + [c_int] * 2 + [c_ll] * 6 + [c_float, c_int, c_int, c_void_p]
+        L.ob200_gemm_bf16.restype = c_int
         for name in ("ob200_conv2d_dgrad", "ob200_filter_transpose", "ob200_bn_train_forward_f32", "ob200_bn_backward_f32",
                      "ob200_relu_backward_f32", "ob200_sgd_momentum_f32"):
             getattr(L, name).restype = c_int
@@ -330,6 +332,32 @@ def linear_batched(x, w, num_ctas=None, tf32=False):
     _check(lib().ob200_linear_batched(_ptr(x), _ptr(w), _ptr(y), code, B, M, N, K, M * K, N * K, M * N, num_ctas or sm_count(),
                                       _stream()), "ob200_linear_batched")
     return y
+
+
+def gemm_bf16(a, b, trans_a=False, trans_b=False, bias=None, alpha=1.0, out_dtype=None, num_ctas=None):
+    """C = alpha * op(A) . op(B)^T (+ bias) for bfloat16 matrices or stacks of matrices [..., rows, cols] (at most two
+    leading batch dimensions, any strides that are multiples of 8 elements, innermost dimension contiguous).
+    op(A) is [M, K]: `a` itself, or with trans_a `a` is stored [K, M].  op(B) is [N, K]: `b` itself, or with trans_b `b`
+    is stored [K, N].  Returns a contiguous [..., M, N] tensor of `out_dtype` (bfloat16 or float32)."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == b.dim() and 2 <= a.dim() <= 4
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and a.shape[:-2] == b.shape[:-2]
+    K, M = (a.shape[-2], a.shape[-1]) if trans_a else (a.shape[-1], a.shape[-2])
+    Kb, N = (b.shape[-2], b.shape[-1]) if trans_b else (b.shape[-1], b.shape[-2])
+    assert K == Kb
+    lead = list(a.shape[:-2])
+    nbo, nbi = ([1, 1] + lead)[-2:]
+    out_dtype = out_dtype or torch.bfloat16
+    c = torch.empty(lead + [M, N], device=a.device, dtype=out_dtype)
+
+    def strides(t):
+        st = [0, 0] + list(t.stride()[:-2])
+        return st[-1], st[-2]
+    a_si, a_so = strides(a)
+    b_si, b_so = strides(b)
+    _check(lib().ob200_gemm_bf16(_ptr(a), _ptr(b), _ptr(c), _ptr(bias) if bias is not None else None, M, N, K, int(trans_a), int(trans_b),
+                                 a.stride(-2), b.stride(-2), N, nbi, nbo, a_si, a_so, b_si, b_so, M * N, nbi * M * N, float(alpha),
+                                 int(out_dtype == torch.float32), num_ctas or sm_count(), _stream()), "ob200_gemm_bf16")
+    return c
 
 
 def layernorm(x, gamma, beta, eps=1e-5, num_ctas=None):
