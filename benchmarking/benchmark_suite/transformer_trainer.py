@@ -9,9 +9,11 @@ sequence 384; the training "transformer" client is the benchmark configuration's
 (16 layers, d_model 1024, 16 heads, FFN 4096, vocabulary 32000, sequence 512) — the reference's
 Transformer-XL is not reproduced.  Everything is bfloat16 with synthetic token ids.
 
-Inference runs on the orion kernels (tcgen05 GEMM and batched GEMM, LayerNorm, softmax, GELU);
-training uses stock PyTorch modules, whose cuBLASLt / flash-attention / elementwise launches are
-captured and scheduled like any other op.
+Inference runs on the orion kernels (tcgen05 GEMM and fused attention, LayerNorm, softmax, GELU), and so does
+training (ORION_PREPARE=1, the default): linear layers and attention with all their gradient products on the
+bfloat16 GEMM, LayerNorm / GELU / softmax / embedding / cross-entropy forward and backward, one-launch AdamW.
+With ORION_PREPARE=0 training uses stock PyTorch modules, whose cuBLASLt / flash-attention / elementwise
+launches are captured and scheduled like any other op.
 """
 import math
 import os
@@ -26,6 +28,8 @@ from .train_imagenet import run_client
 ORION_TRAIN_KERNELS = os.environ.get("ORION_PREPARE", "1") == "1" and os.environ.get("ORION_DISABLE_OVERRIDES", "0") != "1"
 
 FUSED_ATTENTION = os.environ.get("ORION_FUSED_ATTENTION", "1") == "1"
+# ORION_OWN_GEMM_TRAINING=0 leaves the GEMMs, the attention and the embeddings of the training clients on the stock kernels
+OWN_GEMM_TRAINING = os.environ.get("ORION_OWN_GEMM_TRAINING", "1") == "1"
 
 BERT = dict(layers=12, hidden=768, heads=12, ffn=3072, vocab=30528, max_pos=512, seq=384)
 LM = dict(layers=16, hidden=1024, heads=16, ffn=4096, vocab=32000, seq=512)
@@ -44,6 +48,15 @@ class BertLayer(nn.Module):
 
     def forward(self, x, causal=False):
         b, s, h = x.shape
+        if ORION_TRAIN_KERNELS and OWN_GEMM_TRAINING and x.is_cuda and self.training and x.dtype == torch.bfloat16:
+            # every op of the layer, forward and backward, on the orion kernels; residual adds ride in the GEMM epilogues
+            ops = torch.ops.orion
+            qkv = ops.linear_train(x, self.qkv.weight, self.qkv.bias)
+            ctx = ops.attention_train(qkv, self.heads, 1.0 / math.sqrt(h // self.heads), causal)
+            x = ops.layernorm_train(ops.linear_train(ctx, self.out.weight, self.out.bias, x), self.ln1.weight, self.ln1.bias, self.ln1.eps)
+            hid = ops.bias_gelu_train(ops.linear_train(x, self.fc1.weight, None), self.fc1.bias)
+            return ops.layernorm_train(ops.linear_train(hid, self.fc2.weight, self.fc2.bias, x), self.ln2.weight, self.ln2.bias,
+                                       self.ln2.eps)
         q, k, v = self.qkv(x).view(b, s, 3, self.heads, h // self.heads).permute(2, 0, 3, 1, 4)
         ctx = F.scaled_dot_product_attention(q, k, v, is_causal=causal).transpose(1, 2).reshape(b, s, h)
         if ORION_TRAIN_KERNELS and x.is_cuda and self.training:
@@ -91,7 +104,14 @@ class BertQA(nn.Module):
         self.layers = nn.ModuleList([BertLayer(h, cfg["heads"], cfg["ffn"]) for _ in range(cfg["layers"])])
         self.qa = nn.Linear(h, 2)
 
+    def _own_training(self, ids):
+        return ORION_TRAIN_KERNELS and OWN_GEMM_TRAINING and ids.is_cuda and self.training and self.word.weight.dtype == torch.bfloat16
+
     def embed(self, ids):
+        if self._own_training(ids):
+            ops = torch.ops.orion
+            return ops.layernorm_train(ops.embedding_train(ids, self.word.weight, self.pos.weight, self.typ.weight), self.ln.weight,
+                                       self.ln.bias, self.ln.eps)
         pos = torch.arange(ids.shape[1], device=ids.device)
         return self.ln(self.word(ids) + self.pos(pos)[None] + self.typ.weight[0])
 
@@ -100,6 +120,16 @@ class BertQA(nn.Module):
         for layer in self.layers:
             x = layer.forward_orion(x) if orion else layer(x)
         return self.qa(x)   # [B, S, 2]: start / end logits
+
+    def span_logits(self, ids):
+        """Training on the orion kernels: the start / end logits as [2, B, S] (positions contiguous, the layout the
+        loss reads), computed as qa.weight . x^T.  The head's bias is left out: it shifts all positions of a row alike,
+        so the position softmax, the loss and every gradient are the same without it (its own gradient is zero)."""
+        b, s = ids.shape
+        x = self.embed(ids)
+        for layer in self.layers:
+            x = layer(x)
+        return torch.ops.orion.linear_train(self.qa.weight, x.view(b * s, -1), None).view(2, b, s)
 
 
 class DecoderLM(nn.Module):
@@ -113,6 +143,13 @@ class DecoderLM(nn.Module):
         self.head = nn.Linear(h, cfg["vocab"], bias=False)
 
     def forward(self, ids, orion=False):
+        if (not orion and ORION_TRAIN_KERNELS and OWN_GEMM_TRAINING and ids.is_cuda and self.training
+                and self.word.weight.dtype == torch.bfloat16):
+            ops = torch.ops.orion
+            x = ops.embedding_train(ids.contiguous(), self.word.weight, self.pos.weight)
+            for layer in self.layers:
+                x = layer(x, causal=True)
+            return ops.linear_train(ops.layernorm_train(x, self.ln.weight, self.ln.bias, self.ln.eps), self.head.weight, None)
         pos = torch.arange(ids.shape[1], device=ids.device)
         x = self.word(ids) + self.pos(pos)[None]
         if not orion:
@@ -157,8 +194,13 @@ def bert_loop(batchsize, train, num_iters, rps, uniform, dummy_data, local_rank,
                     state["ids"] = ids.to(device, non_blocking=True)
                     state["lab"] = labels.to(device, non_blocking=True)
                 opt.zero_grad()
-                logits = model(state["ids"]).float()
-                loss = F.cross_entropy(logits[:, :, 0], state["lab"][0]) + F.cross_entropy(logits[:, :, 1], state["lab"][1])
+                if ORION_TRAIN_KERNELS and OWN_GEMM_TRAINING:
+                    # both span losses in one pass over the [2 * B, S] logits: mean over 2B rows = half the sum of the two means
+                    lt = model.span_logits(state["ids"])
+                    loss = 2.0 * torch.ops.orion.cross_entropy(lt.view(-1, seq), state["lab"].view(-1))
+                else:
+                    logits = model(state["ids"]).float()
+                    loss = F.cross_entropy(logits[:, :, 0], state["lab"][0]) + F.cross_entropy(logits[:, :, 1], state["lab"][1])
                 loss.backward()
                 opt.step()
                 return loss

@@ -138,6 +138,33 @@ int ob200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, in
                     long long ldb, long long ldc, int batch_inner, int batch_outer, long long a_si, long long a_so, long long b_si,
                     long long b_so, long long c_si, long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
 
+/* ob200_gemm_bf16 with two more epilogue addends: the bias given in bfloat16 (a parameter of a bfloat16 model; either bias
+ * pointer may be NULL) and a bfloat16 `residual` laid out like C, added in float32 before the result is rounded (the
+ * residual stream of a transformer layer: the elementwise add rows of benchmarking/model_kernels/bert_8_fb1). */
+int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual, int M,
+                       int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
+                       int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
+                       long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
+
+/* out[col] = sum over rows of x[row, col] (rows `ld` elements apart), summed in a fixed order: the bias gradient of a linear
+ * layer.  dtype 0 float32, 1 bfloat16.  Stands where the reference's clients launch ATen's reduce_kernel
+ * (benchmarking/model_kernels/bert_8_fb1), trapped at src/cuda_capture/intercept_temp.cpp:418-458 like the three below. */
+int ob200_colsum(const void* x, void* out, long long rows, int D, long long ld, int dtype, int num_ctas, void* stream);
+
+/* ds = scale * prob * (dprob - rowsum(prob * dprob)): gradient of softmax(scale * s) with respect to s; ds may alias dprob.
+ * Stands for softmax_warp_backward of the same profile. */
+int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int dtype,
+                           int num_ctas, void* stream);
+
+/* out[t, :] = sum of up to three embedding rows: table_k[ids_k[t], :], or table_k[t % periods[k], :] where ids_k is NULL
+ * (position table).  Stands for vectorized_gather_kernel + the adds behind it. */
+int ob200_embedding_sum(const void* const* tables, const long long* const* ids, const long long* periods, int count, void* out,
+                        long long tokens, int D, int dtype, int num_ctas, void* stream);
+
+/* dtable = 0; dtable[row(t), :] += dy[t, :] with atomic adds.  Stands for embedding_backward_feature_kernel. */
+int ob200_embedding_backward(const void* dy, const long long* ids, long long period, void* dtable, long long table_rows,
+                             long long tokens, int D, int dtype, int num_ctas, void* stream);
+
 /* Batch-norm inference over the innermost (channel) dimension.  Takes the place of
  * cudnnBatchNormalizationForwardInference (reference src/scheduler/utils_sched.cpp:340-353). */
 int ob200_bn_inference_f32(const float* x, float* y, const float* gamma, const float* beta, const float* mean, const float* var,

@@ -47,6 +47,8 @@ struct GemmParams {
     void* c;
     float* slabs;            // split-K partial matrices [splits][batch][M][N], or null
     const float* bias;
+    const __nv_bfloat16* bias_bf16;   // the same addend given in bfloat16 (a parameter of a bfloat16 model)
+    const __nv_bfloat16* residual;    // optional bfloat16 tensor laid out like C, added in float32 before rounding
     int* status;
     int M, N, K;
     int batch, nb_inner;
@@ -241,6 +243,28 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
                     for (int j = 0; j < 32; j++)
                         if (full || n + j < p.N) f[j] += __ldg(p.bias + n + j);
                 }
+                if (p.bias_bf16) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (full || n + j < p.N) f[j] += __bfloat162float(p.bias_bf16[n + j]);
+                }
+                if (p.residual) {
+                    const __nv_bfloat16* res = p.residual + c_off + n;
+                    if (full && p.vec_ok) {
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            const uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + ch * 8));
+                            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                f[ch * 8 + e * 2] += __low2float(h2[e]);
+                                f[ch * 8 + e * 2 + 1] += __high2float(h2[e]);
+                            }
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && n + j < p.N; j++) f[j] += __bfloat162float(res[j]);
+                    }
+                }
                 if (p.out_f32) {
                     float* out = reinterpret_cast<float*>(p.c) + c_off + n;
                     if (full && p.vec_ok) {
@@ -282,7 +306,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
 
 // Sums the split-K partial matrices in split order, applies alpha and the bias, writes C.
 __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __restrict__ slabs, void* __restrict__ c,
-                                                                 const float* __restrict__ bias, int splits, int batch, int nb_inner,
+                                                                 const float* __restrict__ bias,
+                                                                 const __nv_bfloat16* __restrict__ bias_bf16,
+                                                                 const __nv_bfloat16* __restrict__ residual, int splits, int batch, int nb_inner,
                                                                  int M, int N, long long ldc, long long c_si, long long c_so,
                                                                  int out_f32, float alpha) {
     const long long per_split = (long long)batch * M * N;
@@ -292,8 +318,9 @@ __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __
         const int n = (int)(i % N);
         const long long bm = i / N;
         const int m = (int)(bm % M), b = (int)(bm / M);
-        acc = acc * alpha + (bias ? bias[n] : 0.f);
+        acc = acc * alpha + (bias ? bias[n] : 0.f) + (bias_bf16 ? __bfloat162float(bias_bf16[n]) : 0.f);
         const long long off = (long long)(b / nb_inner) * c_so + (long long)(b % nb_inner) * c_si + (long long)m * ldc + n;
+        if (residual) acc += __bfloat162float(residual[off]);
         if (out_f32) reinterpret_cast<float*>(c)[off] = acc;
         else reinterpret_cast<__nv_bfloat16*>(c)[off] = __float2bfloat16_rn(acc);
     }
@@ -351,10 +378,23 @@ extern "C" float* ob200_stream_slabs(void* stream, size_t* bytes);
 extern "C" int ob200_plan_sm_count(void);
 
 // See include/orion_kernels.h.  Returns 0, -1 (unsupported sizes), -2 (misaligned pointers or strides), -4 (no TMA descriptor).
+extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual,
+                                  int M, int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
+                                  int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
+                                  long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
+
 extern "C" int ob200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, int a_mn, int b_mn,
                                long long lda, long long ldb, long long ldc, int batch_inner, int batch_outer, long long a_si,
                                long long a_so, long long b_si, long long b_so, long long c_si, long long c_so, float alpha, int out_f32,
                                int num_ctas, void* stream) {
+    return ob200_gemm_bf16_ex(a, b, c, bias, nullptr, nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldc, batch_inner, batch_outer, a_si, a_so,
+                              b_si, b_so, c_si, c_so, alpha, out_f32, num_ctas, stream);
+}
+
+extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual,
+                                  int M, int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
+                                  int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
+                                  long long c_so, float alpha, int out_f32, int num_ctas, void* stream) {
     using namespace ob200;
     if (M < 0 || N < 0 || K <= 0 || batch_inner < 0 || batch_outer < 0 || num_ctas <= 0 || lda <= 0 || ldb <= 0 || ldc < N) return -1;
     if (M == 0 || N == 0 || batch_inner == 0 || batch_outer == 0) return 0;
@@ -365,6 +405,8 @@ extern "C" int ob200_gemm_bf16(const void* a, const void* b, void* c, const floa
     GemmParams p;
     memset(&p, 0, sizeof p);
     p.c = c; p.bias = bias;
+    p.bias_bf16 = reinterpret_cast<const __nv_bfloat16*>(bias_bf16);
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
     p.status = ob200_status_word_for_current_device();
     p.M = M; p.N = N; p.K = K;
     p.batch = (int)batch_ll; p.nb_inner = batch_inner;
@@ -373,12 +415,18 @@ extern "C" int ob200_gemm_bf16(const void* a, const void* b, void* c, const floa
     p.a_mn = a_mn ? 1 : 0; p.b_mn = b_mn ? 1 : 0;
     p.alpha = alpha;
     const int cal = out_f32 ? 4 : 8;   // elements per 16 bytes of C
-    p.vec_ok = ((uintptr_t)c % 16 == 0) && (ldc % cal == 0) && (batch_inner == 1 || c_si % cal == 0) && (batch_outer == 1 || c_so % cal == 0);
+    p.vec_ok = ((uintptr_t)c % 16 == 0) && ((uintptr_t)residual % 16 == 0) && (!residual || !out_f32) && (ldc % cal == 0) && (batch_inner == 1 || c_si % cal == 0) && (batch_outer == 1 || c_so % cal == 0);
     const int plan = ob200_plan_sm_count();
     const int tiles_m = (M + GM_BM - 1) / GM_BM;
     // Tile width: 256 columns halve the re-reads of A where the grid still fills the device; 64 for narrow outputs.
+    // A 128 x 128 tile is bound by operand traffic (32 KB per k-block), a 128 x 256 tile takes about 1.5 times as long for
+    // twice the work: pick the width whose number of waves times that cost is smaller.
     int bn = N <= 64 ? 64 : 128;
-    if (N >= 256 && batch_ll * tiles_m * ((N + 255) / 256) >= 2LL * plan) bn = 256;
+    if (N >= 256) {
+        const long long t128 = batch_ll * tiles_m * ((N + 127) / 128), t256 = batch_ll * tiles_m * ((N + 255) / 256);
+        const long long w128 = (t128 + plan - 1) / plan, w256 = (t256 + plan - 1) / plan;
+        if (w256 * 3 < w128 * 2 + 1 && t256 * 2 > plan) bn = 256;
+    }
     p.tiles_m = tiles_m;
     p.tiles_n = (N + bn - 1) / bn;
     p.kblocks = (K + GM_BK - 1) / GM_BK;
@@ -421,7 +469,7 @@ extern "C" int ob200_gemm_bf16(const void* a, const void* b, void* c, const floa
     long long blocks = (elems + 255) / 256;
     if (blocks > 4LL * num_ctas) blocks = 4LL * num_ctas;
     OB200_ELASTIC_HBM(gemm_splitk_finish_kernel, 4);
-    gemm_splitk_finish_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(p.slabs, c, bias, p.splits, p.batch, p.nb_inner, M, N, ldc, c_si,
+    gemm_splitk_finish_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(p.slabs, c, bias, p.bias_bf16, p.residual, p.splits, p.batch, p.nb_inner, M, N, ldc, c_si,
                                                                             c_so, p.out_f32, alpha);
     return (int)cudaGetLastError();
 }

@@ -66,6 +66,17 @@ int ob200_conv2d_wgrad(const void* x, const void* dy, float* dw, int dtype, int 
 int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, const float* beta, float* running_mean,
                                float* running_var, float* save_mean, float* save_invstd, double* sums, float eps, float momentum,
                                long long rows, int C, int num_ctas, void* stream);
+int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual, int M,
+                       int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
+                       int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
+                       long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
+int ob200_colsum(const void* x, void* out, long long rows, int D, long long ld, int dtype, int num_ctas, void* stream);
+int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int dtype,
+                           int num_ctas, void* stream);
+int ob200_embedding_sum(const void* const* tables, const long long* const* ids, const long long* periods, int count, void* out,
+                        long long tokens, int D, int dtype, int num_ctas, void* stream);
+int ob200_embedding_backward(const void* dy, const long long* ids, long long period, void* dtable, long long table_rows,
+                             long long tokens, int D, int dtype, int num_ctas, void* stream);
 int ob200_attention_fwd_bf16(const void* qkv, void* ctx, int B, int S, int H, int head_dim, float scale, int causal, int num_ctas,
                              void* stream);
 int ob200_layernorm_train_forward(const void* x, void* y, const void* gamma, const void* beta, float* mean, float* rstd, long long rows,
@@ -681,6 +692,193 @@ struct CrossEntropy : public torch::autograd::Function<CrossEntropy> {
 };
 at::Tensor cross_entropy_op(const at::Tensor& logits, const at::Tensor& target) { return CrossEntropy::apply(logits, target); }
 
+// ------------------------------------------------------------------ training: linear layers and attention on the own GEMM
+// One plain (unbatched) bfloat16 GEMM call: C[M, N] = op(A) . op(B)^T, see ob200_gemm_bf16.
+void gemm2d(const void* a, const void* b, void* c, const void* bias_bf16, const void* residual, int64_t M, int64_t N, int64_t K, bool a_mn,
+            bool b_mn, int64_t lda, int64_t ldb, int64_t ldc, const char* what) {
+    check(ob200_gemm_bf16_ex(a, b, c, nullptr, bias_bf16, residual, (int)M, (int)N, (int)K, a_mn ? 1 : 0, b_mn ? 1 : 0, lda, ldb, ldc, 1, 1,
+                             0, 0, 0, 0, 0, 0, 1.0f, 0, quota(), cur_stream()),
+          what);
+}
+
+// y = x . w^T + bias (+ residual): forward and both gradients on ob200_gemm_bf16 (dX = dY . W with W read as it lies,
+// dW = dY^T . X with both operands read as they lie), the bias gradient by ob200_colsum.
+struct LinearTrain : public torch::autograd::Function<LinearTrain> {
+    static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& x, const at::Tensor& w,
+                              const c10::optional<at::Tensor>& bias, const c10::optional<at::Tensor>& residual) {
+        const bool has_bias = bias.has_value() && bias->defined(), has_res = residual.has_value() && residual->defined();
+        TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
+                        w.is_contiguous() && w.dim() == 2 && x.dim() >= 2 && x.size(-1) == w.size(1) && w.size(1) % 8 == 0,
+                    "orion::linear_train: contiguous bfloat16 [..., K] x [N, K] with K a multiple of 8 expected");
+        const int64_t K = w.size(1), N = w.size(0), M = x.numel() / K;
+        auto shape = x.sizes().vec();
+        shape.back() = N;
+        at::Tensor y = at::empty(shape, x.options());
+        if (has_bias) TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == N, "orion::linear_train: bias");
+        if (has_res)
+            TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->is_contiguous() && residual->sizes() == y.sizes(),
+                        "orion::linear_train: the residual must have the output's shape");
+        if (M > 0)
+            gemm2d(x.data_ptr(), w.data_ptr(), y.data_ptr(), has_bias ? bias->data_ptr() : nullptr, has_res ? residual->data_ptr() : nullptr, M,
+                   N, K, false, false, K, K, N, "ob200_gemm_bf16 (linear forward)");
+        ctx->save_for_backward({x, w});
+        ctx->saved_data["has_bias"] = has_bias;
+        ctx->saved_data["has_res"] = has_res;
+        return y;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
+        auto saved = ctx->get_saved_variables();
+        const at::Tensor &x = saved[0], &w = saved[1];
+        at::Tensor dy = grads[0].contiguous();
+        const int64_t K = w.size(1), N = w.size(0), M = x.numel() / K;
+        at::Tensor dx, dw, db, dres;
+        if (ctx->needs_input_grad(0)) {
+            dx = at::empty_like(x);
+            // dx[m, k] = sum_n dy[m, n] w[n, k]: w is [reduction, columns] as it lies
+            if (M > 0) gemm2d(dy.data_ptr(), w.data_ptr(), dx.data_ptr(), nullptr, nullptr, M, K, N, false, true, N, K, K, "ob200_gemm_bf16 (dX)");
+        }
+        if (ctx->needs_input_grad(1)) {
+            dw = at::empty_like(w);
+            // dw[n, k] = sum_m dy[m, n] x[m, k]: both operands are [reduction, ...] as they lie
+            if (M > 0) gemm2d(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), nullptr, nullptr, N, K, M, true, true, N, K, K, "ob200_gemm_bf16 (dW)");
+            else dw.zero_();
+        }
+        if (ctx->saved_data["has_bias"].toBool() && ctx->needs_input_grad(2)) {
+            db = at::empty({N}, dy.options());
+            if (N % 8 == 0) {
+                check(ob200_colsum(dy.data_ptr(), db.data_ptr(), M, (int)N, N, 1, quota(), cur_stream()), "ob200_colsum");
+                g_own_launches.fetch_add(1, std::memory_order_relaxed);
+            } else {
+                db = dy.reshape({M, N}).sum(0);
+                g_fallbacks.fetch_add(1, std::memory_order_relaxed);
+            }
+        }
+        if (ctx->saved_data["has_res"].toBool()) dres = grads[0];
+        return {dx, dw, db, dres};
+    }
+};
+at::Tensor linear_train_op(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+                           const c10::optional<at::Tensor>& residual) {
+    return LinearTrain::apply(x, w, bias, residual);
+}
+
+// Self-attention for training, straight on the fused projection qkv [B, S, 3 * heads * d]: scores, softmax, context and all
+// five gradient products on ob200_gemm_bf16 (no re-laid-out copy of Q, K, V or of their gradients), softmax and its gradient on
+// the row kernels.  The probabilities are kept for the backward pass.
+struct AttentionTrain : public torch::autograd::Function<AttentionTrain> {
+    static void bgemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, bool a_mn, bool b_mn, int64_t lda, int64_t ldb,
+                      int64_t ldc, int64_t H, int64_t B, int64_t a_si, int64_t a_so, int64_t b_si, int64_t b_so, int64_t c_si, int64_t c_so,
+                      const char* what) {
+        check(ob200_gemm_bf16_ex(a, b, c, nullptr, nullptr, nullptr, (int)M, (int)N, (int)K, a_mn ? 1 : 0, b_mn ? 1 : 0, lda, ldb, ldc, (int)H,
+                                 (int)B, a_si, a_so, b_si, b_so, c_si, c_so, 1.0f, 0, quota(), cur_stream()),
+              what);
+    }
+    static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& qkv, int64_t heads, double scale, bool causal) {
+        TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 3 && qkv.is_contiguous() && qkv.scalar_type() == at::kBFloat16 && heads > 0 &&
+                        qkv.size(2) % (3 * heads) == 0 && (qkv.size(2) / (3 * heads)) % 8 == 0 && qkv.size(1) % 8 == 0,
+                    "orion::attention_train: contiguous bfloat16 [B, S, 3 * heads * d] with S and d multiples of 8 expected");
+        const int64_t B = qkv.size(0), S = qkv.size(1), H = heads, d = qkv.size(2) / (3 * H), row = 3 * H * d;
+        const char* q = (const char*)qkv.data_ptr();
+        const char* k = q + H * d * 2;
+        const char* v = q + 2 * H * d * 2;
+        at::Tensor scores = at::empty({B, H, S, S}, qkv.options());
+        bgemm(q, k, scores.data_ptr(), S, S, d, false, false, row, row, S, H, B, d, S * row, d, S * row, S * S, H * S * S,
+              "ob200_gemm_bf16 (Q.K^T)");
+        at::Tensor prob = at::empty_like(scores);
+        check(ob200_softmax_causal(scores.data_ptr(), prob.data_ptr(), B * H * S, (int)S, (float)scale, causal ? (int)S : 0, 1, quota(),
+                                   cur_stream()),
+              "ob200_softmax_causal");
+        at::Tensor out = at::empty({B, S, H * d}, qkv.options());
+        bgemm(prob.data_ptr(), v, out.data_ptr(), S, d, S, false, true, S, row, H * d, H, B, S * S, H * S * S, d, S * row, d, S * H * d,
+              "ob200_gemm_bf16 (P.V)");
+        ctx->save_for_backward({qkv, prob});
+        ctx->saved_data["heads"] = heads;
+        ctx->saved_data["scale"] = scale;
+        return out;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
+        auto saved = ctx->get_saved_variables();
+        const at::Tensor &qkv = saved[0], &prob = saved[1];
+        const int64_t H = ctx->saved_data["heads"].toInt();
+        const double scale = ctx->saved_data["scale"].toDouble();
+        const int64_t B = qkv.size(0), S = qkv.size(1), d = qkv.size(2) / (3 * H), row = 3 * H * d;
+        at::Tensor dout = grads[0].contiguous();   // [B, S, H*d]
+        at::Tensor dqkv = at::empty_like(qkv);
+        const char* q = (const char*)qkv.data_ptr();
+        const char* k = q + H * d * 2;
+        const char* v = q + 2 * H * d * 2;
+        char* dq = (char*)dqkv.data_ptr();
+        char* dk = dq + H * d * 2;
+        char* dv = dq + 2 * H * d * 2;
+        const int64_t pS = S * S, pB = H * S * S;   // batch offsets of the [B, H, S, S] tensors
+        // dV[key, :] = sum_q P[q, key] dO[q, :]
+        bgemm(prob.data_ptr(), dout.data_ptr(), dv, S, d, S, true, true, S, H * d, row, H, B, pS, pB, d, S * H * d, d, S * row,
+              "ob200_gemm_bf16 (dV)");
+        // dP[q, key] = sum_c dO[q, c] V[key, c]
+        at::Tensor dp = at::empty_like(prob);
+        bgemm(dout.data_ptr(), v, dp.data_ptr(), S, S, d, false, false, H * d, row, S, H, B, d, S * H * d, d, S * row, pS, pB,
+              "ob200_gemm_bf16 (dP)");
+        check(ob200_softmax_backward(prob.data_ptr(), dp.data_ptr(), dp.data_ptr(), B * H * S, (int)S, (float)scale, 1, quota(), cur_stream()),
+              "ob200_softmax_backward");
+        // dQ[q, :] = sum_key dS[q, key] K[key, :];  dK[key, :] = sum_q dS[q, key] Q[q, :]
+        bgemm(dp.data_ptr(), k, dq, S, d, S, false, true, S, row, row, H, B, pS, pB, d, S * row, d, S * row, "ob200_gemm_bf16 (dQ)");
+        bgemm(dp.data_ptr(), q, dk, S, d, S, true, true, S, row, row, H, B, pS, pB, d, S * row, d, S * row, "ob200_gemm_bf16 (dK)");
+        return {dqkv, at::Tensor(), at::Tensor(), at::Tensor()};
+    }
+};
+at::Tensor attention_train_op(const at::Tensor& qkv, int64_t heads, double scale, bool causal) {
+    return AttentionTrain::apply(qkv, heads, scale, causal);
+}
+
+// x[b, s, :] = word[ids[b, s], :] + pos[s, :] (+ typ[0, :]): the embedding sum of the transformer clients in one pass, with
+// the three table gradients behind it.
+struct EmbeddingTrain : public torch::autograd::Function<EmbeddingTrain> {
+    static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& ids, const at::Tensor& word, const at::Tensor& pos,
+                              const c10::optional<at::Tensor>& typ) {
+        const bool has_typ = typ.has_value() && typ->defined();
+        TORCH_CHECK(ids.is_cuda() && ids.dim() == 2 && ids.scalar_type() == at::kLong && ids.is_contiguous() && word.dim() == 2 &&
+                        pos.dim() == 2 && word.is_contiguous() && pos.is_contiguous() && dtype_code(word) >= 0 &&
+                        pos.scalar_type() == word.scalar_type() && pos.size(1) == word.size(1) && pos.size(0) >= ids.size(1),
+                    "orion::embedding_train: int64 ids [B, S], word and position tables of one type and width expected");
+        const int64_t B = ids.size(0), S = ids.size(1), D = word.size(1);
+        at::Tensor out = at::empty({B, S, D}, word.options());
+        const void* tables[3] = {word.data_ptr(), pos.data_ptr(), has_typ ? typ->data_ptr() : nullptr};
+        const long long* idv[3] = {(const long long*)ids.data_ptr<int64_t>(), nullptr, nullptr};
+        const long long periods[3] = {1, (long long)S, 1};
+        check(ob200_embedding_sum(tables, idv, periods, has_typ ? 3 : 2, out.data_ptr(), B * S, (int)D, dtype_code(word), quota(), cur_stream()),
+              "ob200_embedding_sum");
+        ctx->save_for_backward({ids});
+        ctx->saved_data["word_rows"] = word.size(0);
+        ctx->saved_data["pos_rows"] = pos.size(0);
+        ctx->saved_data["typ_rows"] = has_typ ? typ->size(0) : (int64_t)0;
+        return out;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
+        auto saved = ctx->get_saved_variables();
+        const at::Tensor& ids = saved[0];
+        at::Tensor dy = grads[0].contiguous();
+        const int64_t B = ids.size(0), S = ids.size(1), D = dy.size(-1);
+        const int code = dtype_code(dy);
+        at::Tensor dword = at::empty({ctx->saved_data["word_rows"].toInt(), D}, dy.options());
+        at::Tensor dpos = at::empty({ctx->saved_data["pos_rows"].toInt(), D}, dy.options());
+        check(ob200_embedding_backward(dy.data_ptr(), (const long long*)ids.data_ptr<int64_t>(), 1, dword.data_ptr(), dword.size(0), B * S, (int)D,
+                                       code, quota(), cur_stream()),
+              "ob200_embedding_backward (word)");
+        check(ob200_embedding_backward(dy.data_ptr(), nullptr, S, dpos.data_ptr(), dpos.size(0), B * S, (int)D, code, quota(), cur_stream()),
+              "ob200_embedding_backward (position)");
+        at::Tensor dtyp;
+        const int64_t typ_rows = ctx->saved_data["typ_rows"].toInt();
+        if (typ_rows > 0) {
+            dtyp = at::zeros({typ_rows, D}, dy.options());
+            check(ob200_colsum(dy.data_ptr(), dtyp.data_ptr(), B * S, (int)D, D, code, quota(), cur_stream()), "ob200_colsum (segment row)");
+        }
+        return {at::Tensor(), dword, dpos, dtyp};
+    }
+};
+at::Tensor embedding_train_op(const at::Tensor& ids, const at::Tensor& word, const at::Tensor& pos, const c10::optional<at::Tensor>& typ) {
+    return EmbeddingTrain::apply(ids, word, pos, typ);
+}
+
 // One AdamW step over all parameters of one type in a few launches (torch.optim.AdamW semantics; state in the parameters' type).
 void adamw_step_op(at::TensorList params, at::TensorList grads, at::TensorList exp_avg, at::TensorList exp_avg_sq, double lr, double beta1,
                    double beta2, double eps, double weight_decay, int64_t step) {
@@ -832,6 +1030,9 @@ TORCH_LIBRARY(orion, m) {
     m.def("layernorm_train(Tensor x, Tensor gamma, Tensor beta, float eps) -> Tensor");
     m.def("bias_gelu_train(Tensor x, Tensor bias) -> Tensor");
     m.def("cross_entropy(Tensor logits, Tensor target) -> Tensor");
+    m.def("linear_train(Tensor x, Tensor w, Tensor? bias, Tensor? residual=None) -> Tensor");
+    m.def("attention_train(Tensor qkv, int heads, float scale, bool causal) -> Tensor");
+    m.def("embedding_train(Tensor ids, Tensor word, Tensor pos, Tensor? typ=None) -> Tensor");
     m.def("adamw_step(Tensor(a!)[] params, Tensor[] grads, Tensor(b!)[] exp_avg, Tensor(c!)[] exp_avg_sq, float lr, float beta1, float beta2, float eps, float weight_decay, int step) -> ()");
     m.def("sgd_step(Tensor(a!)[] params, Tensor[] grads, Tensor(b!)[] bufs, float lr, float momentum, float weight_decay, bool nesterov, bool first_step) -> ()");
     m.def("plan_create(int n_slots, int out_slot) -> int", &plan_create);
@@ -867,6 +1068,9 @@ TORCH_LIBRARY_IMPL(orion, Autograd, m) {
     m.impl("layernorm_train", &layernorm_train_op);
     m.impl("bias_gelu_train", &bias_gelu_train_op);
     m.impl("cross_entropy", &cross_entropy_op);
+    m.impl("linear_train", &linear_train_op);
+    m.impl("attention_train", &attention_train_op);
+    m.impl("embedding_train", &embedding_train_op);
 }
 
 TORCH_LIBRARY_IMPL(aten, CUDA, m) {

@@ -170,3 +170,101 @@ def test_fused_attention_matches_float64(tops, B, S, H, causal):
     q, k, v = qkv.double().cpu().view(B, S, 3, H, 64).permute(2, 0, 3, 1, 4)
     want = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=0.125).permute(0, 2, 1, 3)
     assert O.rel_err(ctx, want) < 2e-2
+
+
+# ---------------------------------------------------------------------------------------------- training on the own GEMM
+@pytest.mark.parametrize("rows,K,N,bias,res", [(3072, 768, 2304, True, False), (3072, 768, 768, True, True), (520, 256, 136, False, True),
+                                               (64, 3072, 768, True, True), (8192, 1024, 1024, False, False)])
+def test_linear_training_forward_and_three_gradients(tops, rows, K, N, bias, res):
+    """y = x w^T + b + residual and dx, dw, db, dresidual through the autograd op, against float64 on the CPU from the same
+    bfloat16 values (tolerance 2e-2 of each tensor's largest entry)."""
+    from orion_b200 import kernels
+    torch.manual_seed(rows + N)
+    bf = torch.bfloat16
+    x = torch.randn(rows, K, device="cuda").to(bf).requires_grad_(True)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(bf).requires_grad_(True)
+    b = torch.randn(N, device="cuda").to(bf).requires_grad_(True) if bias else None
+    r = torch.randn(rows, N, device="cuda").to(bf).requires_grad_(True) if res else None
+    dy = torch.randn(rows, N, device="cuda").to(bf)
+    y = tops.linear_train(x, w, b, r)
+    y.backward(dy)
+    assert kernels.read_status() == 0
+    xd, wd = (t.detach().double().cpu().requires_grad_(True) for t in (x, w))
+    bd = b.detach().double().cpu().requires_grad_(True) if bias else None
+    rd = r.detach().double().cpu().requires_grad_(True) if res else None
+    want = F.linear(xd, wd, bd) + (rd if res else 0)
+    want.backward(dy.double().cpu())
+    assert O.rel_err(y.detach(), want.detach()) < 2e-2
+    assert O.rel_err(x.grad, xd.grad) < 2e-2 and O.rel_err(w.grad, wd.grad) < 2e-2
+    if bias:
+        assert O.rel_err(b.grad, bd.grad) < 2e-2
+    if res:
+        assert O.rel_err(r.grad, rd.grad) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,H,d,causal", [(2, 384, 12, 64, False), (1, 512, 16, 64, True), (2, 200, 3, 64, True), (1, 64, 2, 32, False)])
+def test_attention_training_forward_and_gradient(tops, B, S, H, d, causal):
+    """Context and d(qkv) of softmax(Q K^T scale [+ causal mask]) V on the fused projection layout, against float64 autograd on
+    the CPU from the same bfloat16 qkv (2e-2 of the largest entry)."""
+    from orion_b200 import kernels
+    torch.manual_seed(S + H)
+    scale = 1.0 / d ** 0.5
+    qkv = (torch.randn(B, S, 3 * H * d, device="cuda") * 0.7).to(torch.bfloat16).requires_grad_(True)
+    dout = torch.randn(B, S, H * d, device="cuda").to(torch.bfloat16)
+    out = tops.attention_train(qkv, H, scale, causal)
+    out.backward(dout)
+    assert kernels.read_status() == 0
+    qd = qkv.detach().double().cpu().requires_grad_(True)
+    q, k, v = qd.view(B, S, 3, H, d).permute(2, 0, 3, 1, 4)
+    want = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale).permute(0, 2, 1, 3).reshape(B, S, H * d)
+    want.backward(dout.double().cpu())
+    assert O.rel_err(out.detach(), want.detach()) < 2e-2
+    assert O.rel_err(qkv.grad, qd.grad) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_embedding_sum_and_table_gradients(tops, dtype):
+    torch.manual_seed(9)
+    B, S, D, V = 4, 96, 256, 1000
+    ids = torch.randint(0, V, (B, S), device="cuda")
+    ids[0, :10] = 7   # repeated rows: their gradients add up
+    word, pos, typ = (torch.randn(n, D, device="cuda").to(dtype).requires_grad_(True) for n in (V, 128, 2))
+    dy = torch.randn(B, S, D, device="cuda").to(dtype)
+    out = tops.embedding_train(ids, word, pos, typ)
+    out.backward(dy)
+    wd, pd, td = (t.detach().double().cpu().requires_grad_(True) for t in (word, pos, typ))
+    want = wd[ids.cpu()] + pd[torch.arange(S)][None] + td[0]
+    want.backward(dy.double().cpu())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert O.rel_err(out.detach(), want.detach()) < tol
+    assert O.rel_err(word.grad, wd.grad) < tol and O.rel_err(pos.grad, pd.grad) < tol and O.rel_err(typ.grad, td.grad) < tol
+    out2 = tops.embedding_train(ids, word, pos, None)
+    assert O.rel_err(out2.detach(), (wd[ids.cpu()] + pd[torch.arange(S)][None]).detach()) < tol
+
+
+def test_transformer_layer_trains_on_own_kernels_only(tops):
+    """One encoder layer of the training clients (causal and not): output and every parameter gradient of the orion path against
+    the stock-module path in float64 on the CPU; no stock GEMM, attention, softmax or LayerNorm kernel may be needed
+    (torch.ops.orion.fallbacks() stays put)."""
+    import importlib
+    tt = importlib.import_module("benchmarking.benchmark_suite.transformer_trainer")
+    assert tt.ORION_TRAIN_KERNELS and tt.OWN_GEMM_TRAINING
+    torch.manual_seed(21)
+    h, heads, ffn, b, s = 256, 4, 512, 2, 128
+    for causal in (False, True):
+        layer = tt.BertLayer(h, heads, ffn).cuda().to(torch.bfloat16).train()
+        ref = tt.BertLayer(h, heads, ffn).double().train()
+        ref.load_state_dict({k: v.double().cpu() for k, v in layer.state_dict().items()})
+        x = torch.randn(b, s, h, device="cuda").to(torch.bfloat16).requires_grad_(True)
+        dy = torch.randn(b, s, h, device="cuda").to(torch.bfloat16)
+        before = tops.fallbacks()
+        y = layer(x, causal=causal)
+        y.backward(dy)
+        assert tops.fallbacks() == before
+        xd = x.detach().double().cpu().requires_grad_(True)
+        want = ref(xd, causal=causal)
+        want.backward(dy.double().cpu())
+        assert O.rel_err(y.detach(), want.detach()) < 2e-2
+        assert O.rel_err(x.grad, xd.grad) < 3e-2
+        for (name, p), (_, pr) in zip(layer.named_parameters(), ref.named_parameters()):
+            assert O.rel_err(p.grad, pr.grad) < 3e-2, name
