@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "elastic.h"
@@ -39,7 +40,8 @@ template <int BN>
 struct GemmCfg {
     static constexpr int STAGE_BYTES = GM_A_BYTES + BN * 128;
     static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int EPI_BYTES = 4 * 2 * 4096;   // per epilogue warp two slabs of 32 rows x 128 bytes for the TMA stores
+    static constexpr int SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 };
 
@@ -57,9 +59,11 @@ struct GemmParams {
     int a_mn, b_mn;
     int tiles_m, tiles_n, kblocks, splits, kb_per_split;
     int vec_ok;              // C rows and batch offsets are 16-byte aligned
+    int c_tma;               // C is written by TMA stores from swizzled shared-memory slabs (tmap_c)
     float alpha;
     alignas(64) unsigned char tmap_a[128];
     alignas(64) unsigned char tmap_b[128];
+    alignas(64) unsigned char tmap_c[128];
 };
 
 struct GemmCtl {
@@ -78,7 +82,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
     using C = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    GemmCtl* ctl = reinterpret_cast<GemmCtl*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint8_t* epi_smem = smem + C::STAGES * C::STAGE_BYTES;
+    GemmCtl* ctl = reinterpret_cast<GemmCtl*>(epi_smem + C::EPI_BYTES);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
@@ -96,6 +101,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
     if (warp == 0 && lane == 0) {
         prefetch_tensormap(p.tmap_a);
         prefetch_tensormap(p.tmap_b);
+        if (p.c_tma) prefetch_tensormap(p.tmap_c);
     }
     if (warp == 1) {
         tmem_alloc(&ctl->tmem_base, C::TMEM_COLS);
@@ -197,6 +203,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
         const int q = warp & 3;                       // tensor-memory lane group this warp may read
         const int r = q * 32 + lane;
         uint32_t local = 0;
+        uint32_t slab_i = 0;
         for (long long u = blockIdx.x; u < units; u += gridDim.x, local++) {
             const int sp = (int)(u % p.splits);
             const int tile = (int)(u / p.splits);
@@ -213,28 +220,34 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
             const int n0 = tn * BN;
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + ab * BN;
             const bool to_slab = p.splits > 1;
+            const bool row_ok = m < p.M;
             float* srow = to_slab ? p.slabs + (((long long)sp * p.batch + b) * p.M + m) * p.N : nullptr;
             const long long c_off = (long long)bo * p.c_so + (long long)bi * p.c_si + (long long)m * p.ldc;
+            const bool by_tma = p.c_tma && !to_slab;
+            const int m0w = tm * GM_BM + q * 32;      // first row of this warp's 32
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= p.N) break;            // warp-uniform
                 uint32_t v[32];
                 tmem_ld_32x32(t_row + c0, v);
                 tmem_ld_wait();
-                if (m >= p.M) continue;
                 const int n = n0 + c0;
                 const bool full = n + 32 <= p.N;
                 if (to_slab) {
+                    if (!row_ok) continue;
                     if (full && (p.N & 3) == 0) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
                             *reinterpret_cast<float4*>(srow + n + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
                                                                                    __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
                     } else {
-                        for (int j = 0; j < 32 && n + j < p.N; j++) srow[n + j] = __uint_as_float(v[j]);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (n + j < p.N) srow[n + j] = __uint_as_float(v[j]);
                     }
                     continue;
                 }
+                if (!row_ok && !by_tma) continue;
                 float f[32];
 #pragma unroll
                 for (int j = 0; j < 32; j++) f[j] = __uint_as_float(v[j]) * p.alpha;
@@ -248,7 +261,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
                     for (int j = 0; j < 32; j++)
                         if (full || n + j < p.N) f[j] += __bfloat162float(p.bias_bf16[n + j]);
                 }
-                if (p.residual) {
+                if (p.residual && row_ok) {
                     const __nv_bfloat16* res = p.residual + c_off + n;
                     if (full && p.vec_ok) {
 #pragma unroll
@@ -262,8 +275,50 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
                             }
                         }
                     } else {
-                        for (int j = 0; j < 32 && n + j < p.N; j++) f[j] += __bfloat162float(res[j]);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (n + j < p.N) f[j] += __bfloat162float(res[j]);
                     }
+                }
+                if (by_tma) {
+                    // Stage the warp's 32 rows x 128 bytes in a swizzled slab (16-byte chunk index XOR row % 8: conflict-free
+                    // stores), then one TMA store per slab: 64 bfloat16 or 32 float32 columns.  Two slabs alternate; before a
+                    // slab is rewritten the store issued from it two slabs ago must have read it.
+                    const int half = p.out_f32 ? 0 : ((c0 >> 5) & 1);
+                    uint8_t* slab = epi_smem + (warp - 2) * 8192 + (slab_i & 1) * 4096;
+                    if (half == 0) {
+                        if (lane == 0) bulk_wait_group_read<1>();
+                        __syncwarp();
+                    }
+                    uint8_t* rowp = slab + lane * 128;
+                    if (p.out_f32) {
+#pragma unroll
+                        for (int ch = 0; ch < 8; ch++)
+                            *reinterpret_cast<float4*>(rowp + ((ch ^ (lane & 7)) << 4)) = make_float4(f[ch * 4], f[ch * 4 + 1], f[ch * 4 + 2], f[ch * 4 + 3]);
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            uint4 pk;
+                            uint32_t* w = &pk.x;
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const __nv_bfloat162 h2 = __floats2bfloat162_rn(f[ch * 8 + e * 2], f[ch * 8 + e * 2 + 1]);
+                                w[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                            }
+                            *reinterpret_cast<uint4*>(rowp + (((half * 4 + ch) ^ (lane & 7)) << 4)) = pk;
+                        }
+                    }
+                    const bool slab_done = p.out_f32 || half == 1 || c0 + 32 >= BN || n + 32 >= p.N;
+                    if (slab_done) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && m0w < p.M) {
+                            tma_store_tile_4d(p.tmap_c, smem_u32(slab), n - half * 32, m0w, bi, bo);
+                            bulk_commit_group();
+                        }
+                        slab_i++;
+                    }
+                    continue;
                 }
                 if (p.out_f32) {
                     float* out = reinterpret_cast<float*>(p.c) + c_off + n;
@@ -271,7 +326,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
                     } else {
-                        for (int j = 0; j < 32 && n + j < p.N; j++) out[j] = f[j];
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (n + j < p.N) out[j] = f[j];
                     }
                 } else {
                     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.c) + c_off + n;
@@ -288,7 +345,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
                             *reinterpret_cast<uint4*>(out + ch * 8) = pk;
                         }
                     } else {
-                        for (int j = 0; j < 32 && n + j < p.N; j++) out[j] = __float2bfloat16_rn(f[j]);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (n + j < p.N) out[j] = __float2bfloat16_rn(f[j]);
                     }
                 }
             }
@@ -296,6 +355,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->acc_empty[ab]);
         }
+        if (lane == 0) bulk_wait_group<0>();   // the slabs must outlive the stores that read them
     }
     __syncthreads();
     if (warp == 1) {
@@ -455,6 +515,25 @@ extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const f
     const bool ok_b = b_mn ? gm_make_map(p.tmap_b, b, N, K, ldb, batch_inner, b_si, batch_outer, b_so, 64, GM_BK)
                            : gm_make_map(p.tmap_b, b, K, N, ldb, batch_inner, b_si, batch_outer, b_so, GM_BK, bn);
     if (!ok_a || !ok_b) return -4;
+    // C by TMA stores when its rows and batch offsets are 16-byte multiples (always true for the layouts of the clients)
+    {
+        const int es = out_f32 ? 4 : 2;
+        const bool aligned = ((uintptr_t)c % 16 == 0) && (ldc * es) % 16 == 0 && (batch_inner == 1 || (c_si * es) % 16 == 0) &&
+                             (batch_outer == 1 || (c_so * es) % 16 == 0);
+        static const bool tma_off = [] { const char* e = getenv("ORION_GEMM_TMA_STORE"); return e && e[0] == '0'; }();
+        if (aligned && !tma_off && p.splits == 1) {
+            GmEncodeTiledFn enc = gm_encode_fn();
+            const long long si = batch_inner > 1 ? c_si : ldc * M, so = batch_outer > 1 ? c_so : si * (batch_inner > 1 ? batch_inner : 1);
+            cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)batch_inner, (cuuint64_t)batch_outer};
+            cuuint64_t strides[3] = {(cuuint64_t)ldc * es, (cuuint64_t)si * es, (cuuint64_t)so * es};
+            cuuint32_t box[4] = {(cuuint32_t)(128 / es), 32, 1, 1};
+            cuuint32_t steps[4] = {1, 1, 1, 1};
+            if (enc && enc(reinterpret_cast<CUtensorMap*>(p.tmap_c), out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                           c, dims, strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+                p.c_tma = 1;
+        }
+    }
     const long long units = tiles * p.splits;
     const int grid = units < num_ctas ? (int)units : num_ctas;
     {

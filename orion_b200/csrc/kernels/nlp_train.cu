@@ -191,17 +191,34 @@ __global__ void __launch_bounds__(NT_THREADS) ln_backward_kernel(const T* __rest
     }
 }
 
-// out[which][col] = sum over parts of partial[part][which][col], parts added in order; written as T.
+// out[which][col] = sum over parts of partial[part][which][col]; written as T.  A CTA of 256 threads owns 32 consecutive
+// (which, col) entries: thread (g, c) adds parts g, g + 8, ... of entry c (one coalesced 128-byte read per part and group),
+// then the eight group sums are added in group order, so the order of the additions is fixed.
 template <typename T>
-__global__ void colsum_finish_kernel(const float* __restrict__ partial, int parts, int D, int n_which, T* __restrict__ out0,
-                                     T* __restrict__ out1) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_which * D) return;
-    const int which = i / D, col = i - which * D;
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int parts, int D, int n_which,
+                                                            T* __restrict__ out0, T* __restrict__ out1) {
+    __shared__ float sh[8][33];
+    const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + c;
+    const int total = n_which * D;
     float s = 0.f;
-    for (int p = 0; p < parts; p++) s += partial[((long long)p * n_which + which) * D + col];
-    T* out = which == 0 ? out0 : out1;
-    if (out) out[col] = (T)s;
+    if (i < total) {
+        const int which = i / D, col = i - which * D;
+        const float* src = partial + (long long)which * D + col;
+        const long long step = (long long)n_which * D;
+#pragma unroll 4
+        for (int p = g; p < parts; p += 8) s += src[p * step];
+    }
+    sh[g][c] = s;
+    __syncthreads();
+    if (g == 0 && i < total) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) t += sh[k][c];
+        const int which = i / D, col = i - which * D;
+        T* out = which == 0 ? out0 : out1;
+        if (out) out[col] = (T)t;
+    }
 }
 
 // ------------------------------------------------------------------ bias + GELU (bias in the activations' type)
@@ -465,7 +482,7 @@ extern "C" int ob200_layernorm_backward(const void* dy, const void* x, const voi
         ln_backward_kernel<T, CH><<<grid, NT_THREADS, smem, s>>>((const T*)dy, (const T*)x, (const T*)gamma, mean, rstd, (T*)dx, partial, \
                                                                  rows, D);                                                           \
         OB200_HBM_BOUND();                                                                                                           \
-        colsum_finish_kernel<T><<<(2 * D + 255) / 256, 256, 0, s>>>(partial, grid, D, 2, (T*)dgamma, (T*)dbeta);                      \
+        colsum_finish_kernel<T><<<(2 * D + 31) / 32, 256, 0, s>>>(partial, grid, D, 2, (T*)dgamma, (T*)dbeta);                      \
     } while (0)
     if (dtype == 0) {
         if (chunks <= 2) OB200_LNB(float, 2); else OB200_LNB(float, 4);
@@ -523,8 +540,8 @@ extern "C" int ob200_bias_gelu_backward(const void* dy, const void* x, const voi
                                                                                (const __nv_bfloat16*)bias, (__nv_bfloat16*)dx, partial, rows, D);
     if (dbias) {
         OB200_HBM_BOUND();
-        if (dtype == 0) colsum_finish_kernel<float><<<(D + 255) / 256, 256, 0, s>>>(partial, grid, D, 1, (float*)dbias, (float*)nullptr);
-        else colsum_finish_kernel<__nv_bfloat16><<<(D + 255) / 256, 256, 0, s>>>(partial, grid, D, 1, (__nv_bfloat16*)dbias, (__nv_bfloat16*)nullptr);
+        if (dtype == 0) colsum_finish_kernel<float><<<(D + 31) / 32, 256, 0, s>>>(partial, grid, D, 1, (float*)dbias, (float*)nullptr);
+        else colsum_finish_kernel<__nv_bfloat16><<<(D + 31) / 32, 256, 0, s>>>(partial, grid, D, 1, (__nv_bfloat16*)dbias, (__nv_bfloat16*)nullptr);
     }
     return (int)cudaGetLastError();
 }

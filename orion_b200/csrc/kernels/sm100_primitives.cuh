@@ -112,6 +112,24 @@ __device__ __forceinline__ void tma_load_tile_5d(uint32_t dst, const void* tmap,
         : "memory");
 }
 
+// TMA store of the map's box from shared memory to (c0, c1, c2, c3); elements outside the tensor are not written.  The
+// copy belongs to the issuing thread's bulk async-group: commit, then wait (for the reads of shared memory, or for all of it).
+__device__ __forceinline__ void tma_store_tile_4d(const void* tmap, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
 // while the kernel before it in the stream is still running; pdl_wait() blocks the calling thread until that kernel
 // has completed and its writes are visible (a no-op for a normally launched kernel).  pdl_launch_dependents() tells the
