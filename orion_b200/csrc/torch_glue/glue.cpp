@@ -25,6 +25,7 @@
 #include <torch/library.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -404,6 +405,15 @@ at::Tensor linear_op(const at::Tensor& x, const at::Tensor& w, const c10::option
         TORCH_CHECK(residual->sizes() == y.sizes() && residual->is_contiguous() && residual->scalar_type() == x.scalar_type(),
                     "orion::linear: the residual must have the output's shape and type");
     if (x.size(0) == 0) return y;
+    static const bool gemm_off = [] { const char* e = getenv("ORION_LINEAR_GEMM"); return e && e[0] == '0'; }();
+    if (x.scalar_type() == at::kBFloat16 && !relu && x.size(1) % 8 == 0 && !gemm_off) {
+        // bfloat16: the GEMM kernel with the TMA-store epilogue (bias in float32, residual added before the rounding)
+        check(ob200_gemm_bf16_ex(x.data_ptr(), w.data_ptr(), y.data_ptr(), fptr(bias), nullptr, has_res ? residual->data_ptr() : nullptr,
+                                 (int)x.size(0), (int)w.size(0), (int)x.size(1), 0, 0, x.size(1), x.size(1), w.size(0), 1, 1, 0, 0, 0, 0, 0, 0,
+                                 1.0f, 0, quota(), cur_stream()),
+              "ob200_gemm_bf16 (linear)");
+        return y;
+    }
     // y = x . w^T + bias (+ residual, added in float32 before the result is rounded) (+ ReLU): a 1x1 convolution over M "pixels"
     check(ob200_conv2d_fprop(x.data_ptr(), w.data_ptr(), y.data_ptr(), nullptr, fptr(bias), has_res ? residual->data_ptr() : nullptr,
                              relu ? 1 : 0, dtype_code(x), (int)x.size(0), 1, 1, (int)x.size(1), (int)w.size(0), 1, 1, 1, 1, 0, 0, 1, 1,
@@ -491,6 +501,12 @@ at::Tensor linear_batched_op(const at::Tensor& x, const at::Tensor& w) {
                 "orion::linear_batched: contiguous [B,M,K] x [B,N,K] float32/bfloat16 expected");
     const int64_t B = x.size(0), M = x.size(1), K = x.size(2), N = w.size(1);
     at::Tensor y = at::empty({B, M, N}, x.options());
+    if (x.scalar_type() == at::kBFloat16 && K % 8 == 0 && (M * K) % 8 == 0 && (N * K) % 8 == 0) {
+        check(ob200_gemm_bf16_ex(x.data_ptr(), w.data_ptr(), y.data_ptr(), nullptr, nullptr, nullptr, (int)M, (int)N, (int)K, 0, 0, K, K, N,
+                                 (int)B, 1, M * K, 0, N * K, 0, M * N, 0, 1.0f, 0, quota(), cur_stream()),
+              "ob200_gemm_bf16 (batched)");
+        return y;
+    }
     check(ob200_linear_batched(x.data_ptr(), w.data_ptr(), y.data_ptr(), dtype_code(x), (int)B, (int)M, (int)N, (int)K, M * K, N * K,
                                M * N, quota(), cur_stream()),
           "ob200_linear_batched");
