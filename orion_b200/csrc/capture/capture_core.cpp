@@ -145,6 +145,12 @@ static inline bool is_default_stream(void* s) {
     return v == 0 || v == 1 || v == 2;   // NULL, cudaStreamLegacy, cudaStreamPerThread
 }
 
+// A client's ring has one producer at a time.  Several threads can act for one client (its registered thread, the autograd
+// thread replaying its stream, registered helpers); they take turns here, from the push of a record to the launch behind its
+// grant, so that records, grants and events stay paired.  Uncontended in the clients of the benchmark (forward and backward
+// of one client never overlap).
+static std::atomic<uint32_t> g_producer_lock[ORION_MAX_CLIENTS];
+
 bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
     orion_shared& sh = g_shared;
     if (tls_in_gate) return false;
@@ -169,6 +175,10 @@ bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
         return false;
     }
     orion_ring& r = sh.rings[idx];
+    for (uint32_t spins = 0; g_producer_lock[idx].exchange(1, std::memory_order_acquire) != 0;) {
+        ORION_PAUSE();
+        if ((++spins & 0x3f) == 0) sched_yield();
+    }
     uint64_t seq = r.tail.load(std::memory_order_relaxed);
     orion_record& rec = r.recs[seq % ORION_RING_CAP];
     rec.type = type;
@@ -231,6 +241,7 @@ void gate_end(Gate* g) {
     orion_ring& r = g_shared.rings[g->idx];
     if (g->event) real_event_record(g->event, g->stream);
     r.submitted.store(g->seq + 1, std::memory_order_release);
+    g_producer_lock[g->idx].store(0, std::memory_order_release);
 }
 
 }  // namespace orion_capture

@@ -226,6 +226,40 @@ __global__ void __launch_bounds__(ELT_THREADS) avgpool_nhwc_f32_kernel(const flo
     }
 }
 
+// The same for C % 4 == 0: a CTA of 256 threads owns 32 float4 channel chunks (128 channels) of one image and splits the
+// HW rows over 8 thread rows (independent 16-byte loads, then a fixed-order sum through shared memory), so that even a
+// batch-4 request spreads over Nb * C / 128 CTAs instead of a handful.
+__global__ void __launch_bounds__(256) avgpool_nhwc_f32_v4_kernel(const float4* __restrict__ x, float4* __restrict__ y, int Nb, int HW, int C4) {
+    __shared__ float4 sh[8][32];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int groups = (C4 + 31) / 32;
+    for (int item = blockIdx.x; item < Nb * groups; item += gridDim.x) {
+        const int n = item / groups, c4 = (item - n * groups) * 32 + cx;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c4 < C4) {
+            const float4* p = x + (long long)n * HW * C4 + c4;
+#pragma unroll 4
+            for (int j = ry; j < HW; j += 8) {
+                const float4 v = __ldg(p + (long long)j * C4);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        }
+        sh[ry][cx] = acc;
+        __syncthreads();
+        if (ry == 0 && c4 < C4) {
+            float4 t = sh[0][cx];
+#pragma unroll
+            for (int k = 1; k < 8; k++) {
+                const float4 v = sh[k][cx];
+                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+            }
+            const float inv = 1.0f / (float)HW;
+            y[(long long)n * C4 + c4] = make_float4(t.x * inv, t.y * inv, t.z * inv, t.w * inv);
+        }
+        __syncthreads();
+    }
+}
+
 static inline int elt_grid(long long work_items, int num_ctas) {
     long long want = (work_items + ELT_THREADS - 1) / ELT_THREADS;
     long long cap = (long long)num_ctas * ELT_CTAS_PER_SM;
@@ -317,6 +351,12 @@ extern "C" int ob200_maxpool_backward_nhwc_f32(const float* dy, const float* x, 
 extern "C" int ob200_avgpool_nhwc_f32(const float* x, float* y, int Nb, int HW, int C, int num_ctas, void* stream) {
     if (Nb <= 0) return 0;
     if (HW <= 0 || C <= 0 || num_ctas <= 0) return -1;
+    if ((C & 3) == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0) {
+        const long long items = (long long)Nb * ((C / 4 + 31) / 32), cap = (long long)num_ctas * 8;
+        OB200_ELASTIC_HBM(avgpool_nhwc_f32_v4_kernel, 8);
+        avgpool_nhwc_f32_v4_kernel<<<(int)(items < cap ? items : cap), 256, 0, (cudaStream_t)stream>>>((const float4*)x, (float4*)y, Nb, HW, C / 4);
+        return (int)cudaGetLastError();
+    }
     OB200_ELASTIC_HBM(avgpool_nhwc_f32_kernel, ELT_CTAS_PER_SM);
     avgpool_nhwc_f32_kernel<<<elt_grid((long long)Nb * C, num_ctas), ELT_THREADS, 0, (cudaStream_t)stream>>>(x, y, Nb, HW, C);
     return (int)cudaGetLastError();

@@ -535,7 +535,15 @@ extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const f
         }
     }
     const long long units = tiles * p.splits;
-    const int grid = units < num_ctas ? (int)units : num_ctas;
+    int grid = units < num_ctas ? (int)units : num_ctas;
+    // ORION_GEMM_TILES_PER_CTA=t (t > 0): a CTA retires after about t work units instead of staying for the whole launch, so
+    // that the blocks of a higher-priority kernel find a free SM after a few microseconds (the grid is then wider than the
+    // quota; the scheduler's cut to the quota, where it applies, still holds).
+    static const int tiles_per_cta = [] { const char* e = getenv("ORION_GEMM_TILES_PER_CTA"); return e ? atoi(e) : 0; }();
+    if (tiles_per_cta > 0) {
+        const long long want = (units + tiles_per_cta - 1) / tiles_per_cta;
+        if (want > grid) grid = want > 0x7fffffffLL ? 0x7fffffff : (int)want;
+    }
     {
         const double flop = 2.0 * batch_ll * M * (double)N * K;
         const double bytes = 2.0 * batch_ll * ((double)M * K + (double)N * K) + (out_f32 ? 4.0 : 2.0) * batch_ll * (double)M * N;

@@ -13,6 +13,7 @@
 #include <math.h>
 #include <stdint.h>
 #include "elastic.h"
+#include "fast_gelu.cuh"
 
 namespace ob200 {
 
@@ -267,33 +268,38 @@ __global__ void __launch_bounds__(ROW_THREADS) bias_gelu_kernel(const T* __restr
     constexpr int N = VecIO<T>::N;
     const long long stride = (long long)gridDim.x * blockDim.x;
     long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    // the column of a vector is carried along with 32-bit adds: one 64-bit remainder per thread, not one per vector
+    const int step = (int)((stride * N) % D);
+    int col = (int)((i * N) % D);
     for (; i + 3 * stride < n_vec; i += 4 * stride) {   // four independent 16-byte loads in flight per thread
         float v[4][8];
 #pragma unroll
         for (int u = 0; u < 4; u++) VecIO<T>::load(x + (i + u * stride) * N, v[u]);
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            const int col = (int)(((i + u * stride) * N) % D);
             float b[8];
             load_cols<N>(bias, col, 0.f, b);
 #pragma unroll
             for (int e = 0; e < N; e++) {
                 const float a = v[u][e] + b[e];
-                v[u][e] = 0.5f * a * (1.0f + erff(a * 0.70710678118654752f));
+                v[u][e] = a * gauss_cdf(a);
             }
             VecIO<T>::store(y + (i + u * stride) * N, v[u]);
+            col += step;
+            if (col >= D) col -= D;
         }
     }
     for (; i < n_vec; i += stride) {
         float v[8];
         VecIO<T>::load(x + i * N, v);
-        const int col = (int)((i * N) % D);
 #pragma unroll
         for (int e = 0; e < N; e++) {
             const float a = v[e] + (bias ? __ldg(bias + col + e) : 0.f);
-            v[e] = 0.5f * a * (1.0f + erff(a * 0.70710678118654752f));
+            v[e] = a * gauss_cdf(a);
         }
         VecIO<T>::store(y + i * N, v);
+        col += step;
+        if (col >= D) col -= D;
     }
 }
 

@@ -19,6 +19,7 @@
 #include <unordered_map>
 
 #include "elastic.h"
+#include "fast_gelu.cuh"
 
 namespace ob200 {
 
@@ -226,17 +227,49 @@ template <typename T>
 __global__ void __launch_bounds__(NT_THREADS) bias_gelu_forward_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ y,
                                                                       long long n_vec, int D) {
     constexpr int N = Vec8<T>::N;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
-        float v[8], b[8];
-        Vec8<T>::load(x + i * N, v);
-        const int col = (int)((i * N) % D);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const int step = (int)((stride * N) % D);   // the column is carried along with 32-bit adds
+    int col = (int)((i * N) % D);
+    for (; i + stride < n_vec; i += 2 * stride) {   // two independent 16-byte loads in flight per thread
+        float v0[8], v1[8], b[8];
+        Vec8<T>::load(x + i * N, v0);
+        Vec8<T>::load(x + (i + stride) * N, v1);
+#pragma unroll
+        for (int e = 0; e < 8; e++) b[e] = 0.f;
         if (bias) Vec8<T>::load(bias + col, b);
 #pragma unroll
         for (int e = 0; e < N; e++) {
-            const float a = v[e] + (bias ? b[e] : 0.f);
-            v[e] = 0.5f * a * (1.0f + erff(a * 0.70710678118654752f));
+            const float a = v0[e] + b[e];
+            v0[e] = a * gauss_cdf(a);
+        }
+        Vec8<T>::store(y + i * N, v0);
+        col += step;
+        if (col >= D) col -= D;
+        if (bias) Vec8<T>::load(bias + col, b);
+#pragma unroll
+        for (int e = 0; e < N; e++) {
+            const float a = v1[e] + b[e];
+            v1[e] = a * gauss_cdf(a);
+        }
+        Vec8<T>::store(y + (i + stride) * N, v1);
+        col += step;
+        if (col >= D) col -= D;
+    }
+    for (; i < n_vec; i += stride) {
+        float v[8], b[8];
+        Vec8<T>::load(x + i * N, v);
+#pragma unroll
+        for (int e = 0; e < 8; e++) b[e] = 0.f;
+        if (bias) Vec8<T>::load(bias + col, b);
+#pragma unroll
+        for (int e = 0; e < N; e++) {
+            const float a = v[e] + b[e];
+            v[e] = a * gauss_cdf(a);
         }
         Vec8<T>::store(y + i * N, v);
+        col += step;
+        if (col >= D) col -= D;
     }
 }
 
@@ -266,8 +299,9 @@ __global__ void __launch_bounds__(NT_THREADS) bias_gelu_backward_kernel(const T*
 #pragma unroll
                 for (int e = 0; e < N; e++) {
                     const float a = v[e] + b[e];
-                    const float cdf = 0.5f * (1.0f + erff(a * 0.70710678118654752f));
-                    const float pdf = 0.3989422804014327f * __expf(-0.5f * a * a);
+                    const float ex = __expf(-0.5f * a * a);
+                    const float cdf = gauss_cdf_with_exp(a, ex);
+                    const float pdf = 0.3989422804014327f * ex;
                     d[e] *= cdf + a * pdf;
                     acc[e] += d[e];
                 }

@@ -324,3 +324,58 @@ def test_a_trace_cut_by_the_recording_limit_is_compared_up_to_the_cut(built, tmp
     assert trace.read_text().rstrip().endswith("truncated")
     rc, rep = _check_observations(trace)
     assert rep["truncated"] and rep["decisions"] > 100
+
+
+def test_two_threads_of_one_client_take_turns_on_its_ring(built, tmp_path):
+    """A helper thread registered to the best-effort client queues ops while the client's own thread does: every op of both is
+    granted exactly once and the scheduler's count matches (the ring has one producer at a time)."""
+    code = textwrap.dedent('''
+        import ctypes, json, sys, threading
+        sys.path.insert(0, %(root)r)
+        from src.scheduler_frontend import PyScheduler
+        cap = ctypes.CDLL(%(root)r + "/orion_b200/lib/liborion_capture.so", mode=ctypes.RTLD_GLOBAL)
+        sched = ctypes.CDLL(%(root)r + "/orion_b200/lib/liborion_sched.so")
+        cap.stop.restype = ctypes.c_bool
+        prof = sys.argv[1]
+        N, ITERS, OPS = 1, 30, 40
+        barriers = [threading.Barrier(N + 1)]
+        got = {"main": 0, "helper": 0, "wrong": 0}
+        go = threading.Event(); done_iter = threading.Event()
+        def helper():
+            cap.orion_capture_register_thread(0)
+            while True:
+                go.wait(); go.clear()
+                if got.get("quit"): return
+                for _ in range(OPS // 2):
+                    r = cap.orion_capture_op(0)
+                    got["helper"] += 1
+                    if r != 0: got["wrong"] += 1
+                done_iter.set()
+        def client():
+            barriers[0].wait()
+            h = threading.Thread(target=helper); h.start()
+            for it in range(ITERS):
+                go.set()
+                for _ in range(OPS // 2):
+                    r = cap.orion_capture_op(0)
+                    got["main"] += 1
+                    if r != 0: got["wrong"] += 1
+                done_iter.wait(); done_iter.clear()
+                cap.block(it)
+                if it == 0 or it == 9: barriers[0].wait()
+            got["quit"] = True; go.set(); h.join()
+            barriers[0].wait()
+        th = threading.Thread(target=client); th.start()
+        ps = PyScheduler(sched, N)
+        st = threading.Thread(target=ps.run_scheduler, args=(barriers, [th.native_id], ["m"], [prof], [None], [OPS], [None], [ITERS],
+                                                             True, True, False, False, 160000, 1, 1, [True]))
+        st.start(); th.join(); st.join()
+        print(json.dumps({"got": {k: v for k, v in got.items() if k != "quit"}, "stats": ps.stats()}))
+    ''')
+    prof = _profile(tmp_path, "p", [(1, 40, 9000)] * 40)
+    out = subprocess.run([sys.executable, "-c", code % {"root": ROOT}, prof], capture_output=True, text=True, timeout=120,
+                         env=dict(os.environ, ORION_FAKE_GPU="1", ORION_GATE_TIMEOUT_S="5"))
+    assert out.returncode == 0, out.stderr[-3000:]
+    r = json.loads(out.stdout.strip().splitlines()[-1])
+    assert r["got"] == {"main": 30 * 20, "helper": 30 * 20, "wrong": 0}
+    assert r["stats"]["hp_submits"] + r["stats"]["be_submits"] >= 30 * 40 and r["stats"]["join_timeouts"] == 0
