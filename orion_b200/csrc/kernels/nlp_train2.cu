@@ -69,7 +69,18 @@ __global__ void __launch_bounds__(N2_THREADS) colsum_rows_kernel(const T* __rest
 #pragma unroll
         for (int e = 0; e < 8; e++) acc[e] = 0.f;
         if (ty < rows_per_pass) {
-            for (long long row = (long long)blockIdx.x * rows_per_pass + ty; row < rows; row += (long long)gridDim.x * rows_per_pass) {
+            const long long step = (long long)gridDim.x * rows_per_pass;
+            long long row = (long long)blockIdx.x * rows_per_pass + ty;
+            for (; row + 3 * step < rows; row += 4 * step) {   // four independent 16-byte loads in flight
+                float v[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; u++) Ld8<T>::load(x + (row + u * step) * ld + col, v[u]);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+#pragma unroll
+                    for (int e = 0; e < N; e++) acc[e] += v[u][e];
+            }
+            for (; row < rows; row += step) {
                 float v[8];
                 Ld8<T>::load(x + row * ld + col, v);
 #pragma unroll

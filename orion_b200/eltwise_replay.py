@@ -70,6 +70,12 @@ def cases():
     x = torch.randn(32 * 384, 3072, device=dev).bfloat16()
     bias = torch.randn(3072, **f32)
     add("bias+gelu bf16 12288x3072", 4 * x.numel(), lambda x=x, bias=bias: K.bias_gelu(x, bias))
+    # gradient side of the transformer clients: softmax backward on the LM's probabilities, a bias gradient
+    pr = torch.softmax(torch.randn(16 * 16 * 512, 512, device=dev), -1).bfloat16()
+    dp = torch.randn(16 * 16 * 512, 512, device=dev).bfloat16()
+    add("softmax_backward bf16 131072x512", 6 * pr.numel(), lambda pr=pr, dp=dp: K.softmax_backward(pr, dp, 0.125))
+    dyl = torch.randn(8192, 4096, device=dev).bfloat16()
+    add("colsum bf16 8192x4096", 2 * dyl.numel(), lambda dyl=dyl: K.colsum(dyl))
     # optimizer steps over 25.6 M parameters (ResNet-50)
     p_, g_, m_, v_ = (torch.randn(25_600_000, **f32) for _ in range(4))
     v_.abs_()

@@ -54,6 +54,10 @@ def lib():
         L.ob200_linear_batched.restype = c_int
         L.ob200_gemm_bf16.argtypes = [c_void_p] * 4 + [c_int] * 5 + [c_ll] * 3 + [c_int] * 2 + [c_ll] * 6 + [c_float, c_int, c_int, c_void_p]
         L.ob200_gemm_bf16.restype = c_int
+        L.ob200_colsum.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_int, c_void_p]
+        L.ob200_colsum.restype = c_int
+        L.ob200_softmax_backward.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_int, c_void_p]
+        L.ob200_softmax_backward.restype = c_int
         for name in ("ob200_conv2d_dgrad", "ob200_filter_transpose", "ob200_bn_train_forward_f32", "ob200_bn_backward_f32",
                      "ob200_relu_backward_f32", "ob200_sgd_momentum_f32"):
             getattr(L, name).restype = c_int
@@ -358,6 +362,25 @@ def gemm_bf16(a, b, trans_a=False, trans_b=False, bias=None, alpha=1.0, out_dtyp
                                  a.stride(-2), b.stride(-2), N, nbi, nbo, a_si, a_so, b_si, b_so, M * N, nbi * M * N, float(alpha),
                                  int(out_dtype == torch.float32), num_ctas or sm_count(), _stream()), "ob200_gemm_bf16")
     return c
+
+
+def colsum(x, num_ctas=None):
+    """Column sums of a contiguous [rows, D] float32 / bfloat16 matrix, in x's type (the bias gradient of a linear layer)."""
+    assert x.dim() == 2 and x.is_contiguous()
+    out = torch.empty(x.shape[1], device=x.device, dtype=x.dtype)
+    _check(lib().ob200_colsum(_ptr(x), _ptr(out), x.shape[0], x.shape[1], x.shape[1], _dtype_code(x), num_ctas or sm_count(), _stream()),
+           "ob200_colsum")
+    return out
+
+
+def softmax_backward(prob, dprob, scale=1.0, num_ctas=None):
+    """scale * prob * (dprob - rowsum(prob * dprob)) over the last dimension."""
+    assert prob.is_contiguous() and dprob.is_contiguous() and prob.shape == dprob.shape and prob.dtype == dprob.dtype
+    D = prob.shape[-1]
+    ds = torch.empty_like(prob)
+    _check(lib().ob200_softmax_backward(_ptr(prob), _ptr(dprob), _ptr(ds), prob.numel() // D, D, float(scale), _dtype_code(prob),
+                                        num_ctas or sm_count(), _stream()), "ob200_softmax_backward")
+    return ds
 
 
 def layernorm(x, gamma, beta, eps=1e-5, num_ctas=None):

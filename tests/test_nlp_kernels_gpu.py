@@ -268,3 +268,16 @@ def test_transformer_layer_trains_on_own_kernels_only(tops):
         assert O.rel_err(x.grad, xd.grad) < 3e-2
         for (name, p), (_, pr) in zip(layer.named_parameters(), ref.named_parameters()):
             assert O.rel_err(p.grad, pr.grad) < 3e-2, name
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_column_sums_and_softmax_backward_through_the_c_abi(K, dtype, tol):
+    torch.manual_seed(12)
+    x = torch.randn(3000, 768, device="cuda").to(dtype)
+    assert O.rel_err(K.colsum(x), x.double().cpu().sum(0)) < tol
+    s = torch.randn(640, 384, device="cuda", dtype=torch.float64)
+    p = torch.softmax(s * 0.125, -1).to(dtype)
+    dp = torch.randn(640, 384, device="cuda").to(dtype)
+    pd, dpd = p.double().cpu(), dp.double().cpu()
+    want = 0.125 * pd * (dpd - (pd * dpd).sum(-1, keepdim=True))
+    assert O.rel_err(K.softmax_backward(p, dp, 0.125), want) < tol
