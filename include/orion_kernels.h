@@ -140,11 +140,15 @@ int ob200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, in
 
 /* ob200_gemm_bf16 with two more epilogue addends: the bias given in bfloat16 (a parameter of a bfloat16 model; either bias
  * pointer may be NULL) and a bfloat16 `residual` laid out like C, added in float32 before the result is rounded (the
- * residual stream of a transformer layer: the elementwise add rows of benchmarking/model_kernels/bert_8_fb1). */
+ * residual stream of a transformer layer: the elementwise add rows of benchmarking/model_kernels/bert_8_fb1), and `tri` for the
+ * products of causal attention, whose probability matrix P[q, key] is zero for key > q: 0 = plain; 1 = only output tiles that
+ * reach n <= m are computed, the others are left unwritten (scores, dP); 2 = A[m, k] is zero for k > m, the reduction stops
+ * behind the tile's last row (P.V, dS.K); 3 = A[m, k] is zero for k < m, the reduction starts at the tile's first row
+ * (P^T.dO, dS^T.Q). */
 int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual, int M,
                        int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
                        int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
-                       long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
+                       long long c_so, float alpha, int out_f32, int tri, int num_ctas, void* stream);
 
 /* out[col] = sum over rows of x[row, col] (rows `ld` elements apart), summed in a fixed order: the bias gradient of a linear
  * layer.  dtype 0 float32, 1 bfloat16.  Stands where the reference's clients launch ATen's reduce_kernel
@@ -152,9 +156,10 @@ int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias,
 int ob200_colsum(const void* x, void* out, long long rows, int D, long long ld, int dtype, int num_ctas, void* stream);
 
 /* ds = scale * prob * (dprob - rowsum(prob * dprob)): gradient of softmax(scale * s) with respect to s; ds may alias dprob.
- * Stands for softmax_warp_backward of the same profile. */
-int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int dtype,
-                           int num_ctas, void* stream);
+ * causal_period > 0: row r belongs to query position r % causal_period; columns behind it are not read (dprob may be
+ * unwritten there) and get ds = 0.  Stands for softmax_warp_backward of the same profile. */
+int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int causal_period,
+                           int dtype, int num_ctas, void* stream);
 
 /* out[t, :] = sum of up to three embedding rows: table_k[ids_k[t], :], or table_k[t % periods[k], :] where ids_k is NULL
  * (position table).  Stands for vectorized_gather_kernel + the adds behind it. */

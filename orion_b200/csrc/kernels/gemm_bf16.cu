@@ -60,6 +60,9 @@ struct GemmParams {
     int tiles_m, tiles_n, kblocks, splits, kb_per_split;
     int vec_ok;              // C rows and batch offsets are 16-byte aligned
     int c_tma;               // C is written by TMA stores from swizzled shared-memory slabs (tmap_c)
+    int tri;                 // causal attention: 1 = only output tiles that touch n <= m are computed (the rest is left unwritten),
+                             // 2 = A[m, k] is zero for k > m (reduction stops behind the tile's last row),
+                             // 3 = A[m, k] is zero for k < m (reduction starts at the tile's first row)
     float alpha;
     alignas(64) unsigned char tmap_a[128];
     alignas(64) unsigned char tmap_b[128];
@@ -75,6 +78,28 @@ struct GemmCtl {
 __device__ __forceinline__ uint64_t gm_desc_mn(uint32_t addr) {
     return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(8192 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
+}
+
+// k-blocks [kb0, kb1) of work unit (tile row tm, split sp); at least one block, the same for every warp role.
+__device__ __forceinline__ void gm_kb_range(const GemmParams& p, int sp, int tm, int& kb0, int& kb1) {
+    kb0 = sp * p.kb_per_split;
+    kb1 = kb0 + p.kb_per_split < p.kblocks ? kb0 + p.kb_per_split : p.kblocks;
+    if (p.tri == 2) {
+        const int lim = (tm * GM_BM + GM_BM + GM_BK - 1) / GM_BK;
+        if (lim < kb1) kb1 = lim > kb0 ? lim : kb0 + 1;
+    } else if (p.tri == 3) {
+        const int lo = (tm * GM_BM) / GM_BK;
+        if (lo > kb0) kb0 = lo < kb1 ? lo : kb1 - 1;
+    }
+}
+// With a causal mode the work per tile depends on its row, and a CTA's units (u = blockIdx.x + i * gridDim.x) would keep
+// hitting the same rows of every problem.  Rotating the tile index by the problem index gives every CTA a mix of rows.
+__device__ __forceinline__ int gm_rotate(const GemmParams& p, int t, int b, int tiles_per_problem) {
+    return p.tri ? (t + b) % tiles_per_problem : t;
+}
+template <int BN>
+__device__ __forceinline__ bool gm_tile_skipped(const GemmParams& p, int tm, int tn) {
+    return p.tri == 1 && tn * BN > tm * GM_BM + GM_BM - 1;
 }
 
 template <int BN>
@@ -126,11 +151,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
             for (long long u = blockIdx.x; u < units && !dead; u += gridDim.x) {
                 const int sp = (int)(u % p.splits);
                 const int tile = (int)(u / p.splits);
-                const int b = tile / tiles_per_problem, t = tile - b * tiles_per_problem;
+                const int b = tile / tiles_per_problem, t = gm_rotate(p, tile - b * tiles_per_problem, b, tiles_per_problem);
                 const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
                 const int bi = b % p.nb_inner, bo = b / p.nb_inner;
-                const int kb0 = sp * p.kb_per_split;
-                const int kb1 = kb0 + p.kb_per_split < p.kblocks ? kb0 + p.kb_per_split : p.kblocks;
+                if (gm_tile_skipped<BN>(p, tm, tn)) continue;
+                int kb0, kb1;
+                gm_kb_range(p, sp, tm, kb0, kb1);
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag)) {
                         if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_EMPTY); }
@@ -166,11 +192,16 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
             uint32_t ph = 0;
             uint32_t local = 0;
             bool dead = false;
-            for (long long u = blockIdx.x; u < units && !dead; u += gridDim.x, local++) {
+            for (long long u = blockIdx.x; u < units && !dead; u += gridDim.x) {
                 const int sp = (int)(u % p.splits);
-                const int kb0 = sp * p.kb_per_split;
-                const int kb1 = kb0 + p.kb_per_split < p.kblocks ? kb0 + p.kb_per_split : p.kblocks;
+                const int tile = (int)(u / p.splits);
+                const int t = gm_rotate(p, tile % tiles_per_problem, tile / tiles_per_problem, tiles_per_problem);
+                const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+                if (gm_tile_skipped<BN>(p, tm, tn)) continue;
+                int kb0, kb1;
+                gm_kb_range(p, sp, tm, kb0, kb1);
                 const uint32_t ab = local & 1u, use = local >> 1;
+                local++;
                 if (!mbar_wait(&ctl->acc_empty[ab], (use & 1u) ^ 1u, abort_flag)) {
                     if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_EMPTY); }
                     break;
@@ -204,13 +235,15 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_bf16_kernel(const __grid_c
         const int r = q * 32 + lane;
         uint32_t local = 0;
         uint32_t slab_i = 0;
-        for (long long u = blockIdx.x; u < units; u += gridDim.x, local++) {
+        for (long long u = blockIdx.x; u < units; u += gridDim.x) {
             const int sp = (int)(u % p.splits);
             const int tile = (int)(u / p.splits);
-            const int b = tile / tiles_per_problem, t = tile - b * tiles_per_problem;
+            const int b = tile / tiles_per_problem, t = gm_rotate(p, tile - b * tiles_per_problem, b, tiles_per_problem);
             const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
             const int bi = b % p.nb_inner, bo = b / p.nb_inner;
+            if (gm_tile_skipped<BN>(p, tm, tn)) continue;
             const uint32_t ab = local & 1u, use = local >> 1;
+            local++;
             if (!mbar_wait(&ctl->acc_full[ab], use & 1u, abort_flag)) {
                 if (!*abort_flag) { ctl->abort_flag = 1; if (p.status) atomicExch(p.status, OB200_ERR_WAIT_TMEM_FULL); }
                 break;
@@ -441,21 +474,22 @@ extern "C" int ob200_plan_sm_count(void);
 extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual,
                                   int M, int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
                                   int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
-                                  long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
+                                  long long c_so, float alpha, int out_f32, int tri, int num_ctas, void* stream);
 
 extern "C" int ob200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, int a_mn, int b_mn,
                                long long lda, long long ldb, long long ldc, int batch_inner, int batch_outer, long long a_si,
                                long long a_so, long long b_si, long long b_so, long long c_si, long long c_so, float alpha, int out_f32,
                                int num_ctas, void* stream) {
     return ob200_gemm_bf16_ex(a, b, c, bias, nullptr, nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldc, batch_inner, batch_outer, a_si, a_so,
-                              b_si, b_so, c_si, c_so, alpha, out_f32, num_ctas, stream);
+                              b_si, b_so, c_si, c_so, alpha, out_f32, 0, num_ctas, stream);
 }
 
 extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual,
                                   int M, int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
                                   int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
-                                  long long c_so, float alpha, int out_f32, int num_ctas, void* stream) {
+                                  long long c_so, float alpha, int out_f32, int tri, int num_ctas, void* stream) {
     using namespace ob200;
+    if (tri < 0 || tri > 3) return -1;
     if (M < 0 || N < 0 || K <= 0 || batch_inner < 0 || batch_outer < 0 || num_ctas <= 0 || lda <= 0 || ldb <= 0 || ldc < N) return -1;
     if (M == 0 || N == 0 || batch_inner == 0 || batch_outer == 0) return 0;
     if (((uintptr_t)a | (uintptr_t)b) % 16 || (lda | ldb) % 8) return -2;
@@ -474,6 +508,7 @@ extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const f
     p.out_f32 = out_f32 ? 1 : 0;
     p.a_mn = a_mn ? 1 : 0; p.b_mn = b_mn ? 1 : 0;
     p.alpha = alpha;
+    p.tri = tri;
     const int cal = out_f32 ? 4 : 8;   // elements per 16 bytes of C
     p.vec_ok = ((uintptr_t)c % 16 == 0) && ((uintptr_t)residual % 16 == 0) && (!residual || !out_f32) && (ldc % cal == 0) && (batch_inner == 1 || c_si % cal == 0) && (batch_outer == 1 || c_so % cal == 0);
     const int plan = ob200_plan_sm_count();
@@ -495,7 +530,7 @@ extern "C" int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const f
     // Split-K: few tiles, long reduction.  Planned for the device's SM count, never for the quota of the call, so the
     // summation order (and the result, bit for bit) is the same for every quota.
     int splits = 1;
-    if (tiles * 2 <= plan && p.kblocks >= 8) {
+    if (tiles * 2 <= plan && p.kblocks >= 8 && tri == 0) {
         splits = (int)(plan / tiles);
         if (splits > p.kblocks / 4) splits = p.kblocks / 4;
         if (splits > 16) splits = 16;

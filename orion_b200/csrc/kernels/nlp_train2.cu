@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256) colsum_parts_kernel(const float* __restri
 // ------------------------------------------------------------------ softmax backward, one warp per row
 template <typename T>
 __global__ void __launch_bounds__(N2_THREADS) softmax_backward_kernel(const T* __restrict__ prob, const T* __restrict__ dprob, T* __restrict__ ds,
-                                                                     long long rows, int D, float scale) {
+                                                                     long long rows, int D, float scale, int causal_period) {
     constexpr int N = Ld8<T>::N;
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -131,23 +131,31 @@ __global__ void __launch_bounds__(N2_THREADS) softmax_backward_kernel(const T* _
     for (long long row = warp; row < rows; row += nwarps) {
         const T* p = prob + row * D;
         const T* g = dprob + row * D;
+        // causal: columns behind the query's own position hold prob = 0 and possibly unwritten dprob
+        const int last = causal_period > 0 ? (int)(row % causal_period) : D;
         float dot = 0.f;
-        for (int c = lane; c < chunks; c += 32) {
+        for (int c = lane; c < chunks && c * N <= last; c += 32) {
             float a[8], b[8];
             Ld8<T>::load(p + c * N, a);
             Ld8<T>::load(g + c * N, b);
 #pragma unroll
-            for (int e = 0; e < N; e++) dot = fmaf(a[e], b[e], dot);
+            for (int e = 0; e < N; e++)
+                if (c * N + e <= last) dot = fmaf(a[e], b[e], dot);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         T* out = ds + row * D;
         for (int c = lane; c < chunks; c += 32) {   // second read of the row comes from L1 / L2
             float a[8], b[8];
-            Ld8<T>::load(p + c * N, a);
-            Ld8<T>::load(g + c * N, b);
+            if (c * N <= last) {
+                Ld8<T>::load(p + c * N, a);
+                Ld8<T>::load(g + c * N, b);
 #pragma unroll
-            for (int e = 0; e < N; e++) a[e] = scale * a[e] * (b[e] - dot);
+                for (int e = 0; e < N; e++) a[e] = (c * N + e <= last) ? scale * a[e] * (b[e] - dot) : 0.f;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) a[e] = 0.f;
+            }
             Ld8<T>::store(out + c * N, a);
         }
     }
@@ -256,8 +264,9 @@ extern "C" int ob200_colsum(const void* x, void* out, long long rows, int D, lon
 }
 
 // ds[row, :] = scale * prob[row, :] * (dprob[row, :] - sum_j prob[row, j] dprob[row, j]); ds may alias dprob.
-extern "C" int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int dtype,
-                                      int num_ctas, void* stream) {
+// causal_period > 0: columns behind position row % causal_period are skipped (ds = 0 there).
+extern "C" int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int causal_period,
+                                      int dtype, int num_ctas, void* stream) {
     const int n = dtype == 1 ? 8 : 4;
     if ((dtype != 0 && dtype != 1) || num_ctas <= 0 || D <= 0 || D % n || rows < 0) return -1;
     if (rows == 0) return 0;
@@ -267,10 +276,10 @@ extern "C" int ob200_softmax_backward(const void* prob, const void* dprob, void*
     OB200_ELASTIC_HBM(softmax_backward_kernel<float>, 8);
     OB200_ELASTIC(softmax_backward_kernel<__nv_bfloat16>, 8);
     if (dtype == 0)
-        softmax_backward_kernel<float><<<grid, N2_THREADS, 0, (cudaStream_t)stream>>>((const float*)prob, (const float*)dprob, (float*)ds, rows, D, scale);
+        softmax_backward_kernel<float><<<grid, N2_THREADS, 0, (cudaStream_t)stream>>>((const float*)prob, (const float*)dprob, (float*)ds, rows, D, scale, causal_period);
     else
         softmax_backward_kernel<__nv_bfloat16><<<grid, N2_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)prob, (const __nv_bfloat16*)dprob,
-                                                                                         (__nv_bfloat16*)ds, rows, D, scale);
+                                                                                         (__nv_bfloat16*)ds, rows, D, scale, causal_period);
     return (int)cudaGetLastError();
 }
 

@@ -70,10 +70,10 @@ int ob200_bn_train_forward_f32(const float* x, float* y, const float* gamma, con
 int ob200_gemm_bf16_ex(const void* a, const void* b, void* c, const float* bias, const void* bias_bf16, const void* residual, int M,
                        int N, int K, int a_mn, int b_mn, long long lda, long long ldb, long long ldc, int batch_inner,
                        int batch_outer, long long a_si, long long a_so, long long b_si, long long b_so, long long c_si,
-                       long long c_so, float alpha, int out_f32, int num_ctas, void* stream);
+                       long long c_so, float alpha, int out_f32, int tri, int num_ctas, void* stream);
 int ob200_colsum(const void* x, void* out, long long rows, int D, long long ld, int dtype, int num_ctas, void* stream);
-int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int dtype,
-                           int num_ctas, void* stream);
+int ob200_softmax_backward(const void* prob, const void* dprob, void* ds, long long rows, int D, float scale, int causal_period,
+                           int dtype, int num_ctas, void* stream);
 int ob200_embedding_sum(const void* const* tables, const long long* const* ids, const long long* periods, int count, void* out,
                         long long tokens, int D, int dtype, int num_ctas, void* stream);
 int ob200_embedding_backward(const void* dy, const long long* ids, long long period, void* dtable, long long table_rows,
@@ -410,7 +410,7 @@ at::Tensor linear_op(const at::Tensor& x, const at::Tensor& w, const c10::option
         // bfloat16: the GEMM kernel with the TMA-store epilogue (bias in float32, residual added before the rounding)
         check(ob200_gemm_bf16_ex(x.data_ptr(), w.data_ptr(), y.data_ptr(), fptr(bias), nullptr, has_res ? residual->data_ptr() : nullptr,
                                  (int)x.size(0), (int)w.size(0), (int)x.size(1), 0, 0, x.size(1), x.size(1), w.size(0), 1, 1, 0, 0, 0, 0, 0, 0,
-                                 1.0f, 0, quota(), cur_stream()),
+                                 1.0f, 0, 0, quota(), cur_stream()),
               "ob200_gemm_bf16 (linear)");
         return y;
     }
@@ -503,7 +503,7 @@ at::Tensor linear_batched_op(const at::Tensor& x, const at::Tensor& w) {
     at::Tensor y = at::empty({B, M, N}, x.options());
     if (x.scalar_type() == at::kBFloat16 && K % 8 == 0 && (M * K) % 8 == 0 && (N * K) % 8 == 0) {
         check(ob200_gemm_bf16_ex(x.data_ptr(), w.data_ptr(), y.data_ptr(), nullptr, nullptr, nullptr, (int)M, (int)N, (int)K, 0, 0, K, K, N,
-                                 (int)B, 1, M * K, 0, N * K, 0, M * N, 0, 1.0f, 0, quota(), cur_stream()),
+                                 (int)B, 1, M * K, 0, N * K, 0, M * N, 0, 1.0f, 0, 0, quota(), cur_stream()),
               "ob200_gemm_bf16 (batched)");
         return y;
     }
@@ -713,7 +713,7 @@ at::Tensor cross_entropy_op(const at::Tensor& logits, const at::Tensor& target) 
 void gemm2d(const void* a, const void* b, void* c, const void* bias_bf16, const void* residual, int64_t M, int64_t N, int64_t K, bool a_mn,
             bool b_mn, int64_t lda, int64_t ldb, int64_t ldc, const char* what) {
     check(ob200_gemm_bf16_ex(a, b, c, nullptr, bias_bf16, residual, (int)M, (int)N, (int)K, a_mn ? 1 : 0, b_mn ? 1 : 0, lda, ldb, ldc, 1, 1,
-                             0, 0, 0, 0, 0, 0, 1.0f, 0, quota(), cur_stream()),
+                             0, 0, 0, 0, 0, 0, 1.0f, 0, 0, quota(), cur_stream()),
           what);
 }
 
@@ -780,13 +780,14 @@ at::Tensor linear_train_op(const at::Tensor& x, const at::Tensor& w, const c10::
 
 // Self-attention for training, straight on the fused projection qkv [B, S, 3 * heads * d]: scores, softmax, context and all
 // five gradient products on ob200_gemm_bf16 (no re-laid-out copy of Q, K, V or of their gradients), softmax and its gradient on
-// the row kernels.  The probabilities are kept for the backward pass.
+// the row kernels.  The probabilities are kept for the backward pass.  Causal attention computes only the score tiles that reach
+// the diagonal and cuts the reductions over keys / queries at it (the `tri` modes of the GEMM).
 struct AttentionTrain : public torch::autograd::Function<AttentionTrain> {
     static void bgemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, bool a_mn, bool b_mn, int64_t lda, int64_t ldb,
                       int64_t ldc, int64_t H, int64_t B, int64_t a_si, int64_t a_so, int64_t b_si, int64_t b_so, int64_t c_si, int64_t c_so,
-                      const char* what) {
+                      int tri, const char* what) {
         check(ob200_gemm_bf16_ex(a, b, c, nullptr, nullptr, nullptr, (int)M, (int)N, (int)K, a_mn ? 1 : 0, b_mn ? 1 : 0, lda, ldb, ldc, (int)H,
-                                 (int)B, a_si, a_so, b_si, b_so, c_si, c_so, 1.0f, 0, quota(), cur_stream()),
+                                 (int)B, a_si, a_so, b_si, b_so, c_si, c_so, 1.0f, 0, tri, quota(), cur_stream()),
               what);
     }
     static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& qkv, int64_t heads, double scale, bool causal) {
@@ -799,17 +800,18 @@ struct AttentionTrain : public torch::autograd::Function<AttentionTrain> {
         const char* v = q + 2 * H * d * 2;
         at::Tensor scores = at::empty({B, H, S, S}, qkv.options());
         bgemm(q, k, scores.data_ptr(), S, S, d, false, false, row, row, S, H, B, d, S * row, d, S * row, S * S, H * S * S,
-              "ob200_gemm_bf16 (Q.K^T)");
+              causal ? 1 : 0, "ob200_gemm_bf16 (Q.K^T)");
         at::Tensor prob = at::empty_like(scores);
         check(ob200_softmax_causal(scores.data_ptr(), prob.data_ptr(), B * H * S, (int)S, (float)scale, causal ? (int)S : 0, 1, quota(),
                                    cur_stream()),
               "ob200_softmax_causal");
         at::Tensor out = at::empty({B, S, H * d}, qkv.options());
         bgemm(prob.data_ptr(), v, out.data_ptr(), S, d, S, false, true, S, row, H * d, H, B, S * S, H * S * S, d, S * row, d, S * H * d,
-              "ob200_gemm_bf16 (P.V)");
+              causal ? 2 : 0, "ob200_gemm_bf16 (P.V)");
         ctx->save_for_backward({qkv, prob});
         ctx->saved_data["heads"] = heads;
         ctx->saved_data["scale"] = scale;
+        ctx->saved_data["causal"] = causal;
         return out;
     }
     static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::variable_list grads) {
@@ -817,6 +819,7 @@ struct AttentionTrain : public torch::autograd::Function<AttentionTrain> {
         const at::Tensor &qkv = saved[0], &prob = saved[1];
         const int64_t H = ctx->saved_data["heads"].toInt();
         const double scale = ctx->saved_data["scale"].toDouble();
+        const bool causal = ctx->saved_data["causal"].toBool();
         const int64_t B = qkv.size(0), S = qkv.size(1), d = qkv.size(2) / (3 * H), row = 3 * H * d;
         at::Tensor dout = grads[0].contiguous();   // [B, S, H*d]
         at::Tensor dqkv = at::empty_like(qkv);
@@ -829,16 +832,17 @@ struct AttentionTrain : public torch::autograd::Function<AttentionTrain> {
         const int64_t pS = S * S, pB = H * S * S;   // batch offsets of the [B, H, S, S] tensors
         // dV[key, :] = sum_q P[q, key] dO[q, :]
         bgemm(prob.data_ptr(), dout.data_ptr(), dv, S, d, S, true, true, S, H * d, row, H, B, pS, pB, d, S * H * d, d, S * row,
-              "ob200_gemm_bf16 (dV)");
+              causal ? 3 : 0, "ob200_gemm_bf16 (dV)");
         // dP[q, key] = sum_c dO[q, c] V[key, c]
         at::Tensor dp = at::empty_like(prob);
         bgemm(dout.data_ptr(), v, dp.data_ptr(), S, S, d, false, false, H * d, row, S, H, B, d, S * H * d, d, S * row, pS, pB,
-              "ob200_gemm_bf16 (dP)");
-        check(ob200_softmax_backward(prob.data_ptr(), dp.data_ptr(), dp.data_ptr(), B * H * S, (int)S, (float)scale, 1, quota(), cur_stream()),
+              causal ? 1 : 0, "ob200_gemm_bf16 (dP)");
+        check(ob200_softmax_backward(prob.data_ptr(), dp.data_ptr(), dp.data_ptr(), B * H * S, (int)S, (float)scale, causal ? (int)S : 0, 1, quota(),
+                                     cur_stream()),
               "ob200_softmax_backward");
         // dQ[q, :] = sum_key dS[q, key] K[key, :];  dK[key, :] = sum_q dS[q, key] Q[q, :]
-        bgemm(dp.data_ptr(), k, dq, S, d, S, false, true, S, row, row, H, B, pS, pB, d, S * row, d, S * row, "ob200_gemm_bf16 (dQ)");
-        bgemm(dp.data_ptr(), q, dk, S, d, S, true, true, S, row, row, H, B, pS, pB, d, S * row, d, S * row, "ob200_gemm_bf16 (dK)");
+        bgemm(dp.data_ptr(), k, dq, S, d, S, false, true, S, row, row, H, B, pS, pB, d, S * row, d, S * row, causal ? 2 : 0, "ob200_gemm_bf16 (dQ)");
+        bgemm(dp.data_ptr(), q, dk, S, d, S, true, true, S, row, row, H, B, pS, pB, d, S * row, d, S * row, causal ? 3 : 0, "ob200_gemm_bf16 (dK)");
         return {dqkv, at::Tensor(), at::Tensor(), at::Tensor()};
     }
 };

@@ -54,9 +54,11 @@ def lib():
         L.ob200_linear_batched.restype = c_int
         L.ob200_gemm_bf16.argtypes = [c_void_p] * 4 + [c_int] * 5 + [c_ll] * 3 + [c_int] * 2 + [c_ll] * 6 + [c_float, c_int, c_int, c_void_p]
         L.ob200_gemm_bf16.restype = c_int
+        L.ob200_gemm_bf16_ex.argtypes = [c_void_p] * 6 + [c_int] * 5 + [c_ll] * 3 + [c_int] * 2 + [c_ll] * 6 + [c_float, c_int, c_int, c_int, c_void_p]
+        L.ob200_gemm_bf16_ex.restype = c_int
         L.ob200_colsum.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_int, c_void_p]
         L.ob200_colsum.restype = c_int
-        L.ob200_softmax_backward.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_int, c_void_p]
+        L.ob200_softmax_backward.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_int, c_int, c_void_p]
         L.ob200_softmax_backward.restype = c_int
         for name in ("ob200_conv2d_dgrad", "ob200_filter_transpose", "ob200_bn_train_forward_f32", "ob200_bn_backward_f32",
                      "ob200_relu_backward_f32", "ob200_sgd_momentum_f32"):
@@ -338,11 +340,12 @@ def linear_batched(x, w, num_ctas=None, tf32=False):
     return y
 
 
-def gemm_bf16(a, b, trans_a=False, trans_b=False, bias=None, alpha=1.0, out_dtype=None, num_ctas=None):
+def gemm_bf16(a, b, trans_a=False, trans_b=False, bias=None, alpha=1.0, out_dtype=None, num_ctas=None, tri=0):
     """C = alpha * op(A) . op(B)^T (+ bias) for bfloat16 matrices or stacks of matrices [..., rows, cols] (at most two
     leading batch dimensions, any strides that are multiples of 8 elements, innermost dimension contiguous).
     op(A) is [M, K]: `a` itself, or with trans_a `a` is stored [K, M].  op(B) is [N, K]: `b` itself, or with trans_b `b`
-    is stored [K, N].  Returns a contiguous [..., M, N] tensor of `out_dtype` (bfloat16 or float32)."""
+    is stored [K, N].  Returns a contiguous [..., M, N] tensor of `out_dtype` (bfloat16 or float32).  `tri`: the causal-attention
+    modes of ob200_gemm_bf16_ex (1: output tiles above the diagonal are left unwritten; 2 / 3: A is lower / upper triangular)."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == b.dim() and 2 <= a.dim() <= 4
     assert a.stride(-1) == 1 and b.stride(-1) == 1 and a.shape[:-2] == b.shape[:-2]
     K, M = (a.shape[-2], a.shape[-1]) if trans_a else (a.shape[-1], a.shape[-2])
@@ -358,9 +361,10 @@ def gemm_bf16(a, b, trans_a=False, trans_b=False, bias=None, alpha=1.0, out_dtyp
         return st[-1], st[-2]
     a_si, a_so = strides(a)
     b_si, b_so = strides(b)
-    _check(lib().ob200_gemm_bf16(_ptr(a), _ptr(b), _ptr(c), _ptr(bias) if bias is not None else None, M, N, K, int(trans_a), int(trans_b),
-                                 a.stride(-2), b.stride(-2), N, nbi, nbo, a_si, a_so, b_si, b_so, M * N, nbi * M * N, float(alpha),
-                                 int(out_dtype == torch.float32), num_ctas or sm_count(), _stream()), "ob200_gemm_bf16")
+    _check(lib().ob200_gemm_bf16_ex(_ptr(a), _ptr(b), _ptr(c), _ptr(bias) if bias is not None else None, None, None, M, N, K, int(trans_a),
+                                    int(trans_b), a.stride(-2), b.stride(-2), N, nbi, nbo, a_si, a_so, b_si, b_so, M * N, nbi * M * N,
+                                    float(alpha), int(out_dtype == torch.float32), int(tri), num_ctas or sm_count(), _stream()),
+           "ob200_gemm_bf16_ex")
     return c
 
 
@@ -373,13 +377,14 @@ def colsum(x, num_ctas=None):
     return out
 
 
-def softmax_backward(prob, dprob, scale=1.0, num_ctas=None):
-    """scale * prob * (dprob - rowsum(prob * dprob)) over the last dimension."""
+def softmax_backward(prob, dprob, scale=1.0, num_ctas=None, causal_period=0):
+    """scale * prob * (dprob - rowsum(prob * dprob)) over the last dimension; with `causal_period` = sequence length, row r is
+    query position r % causal_period and the columns behind it are skipped (result 0)."""
     assert prob.is_contiguous() and dprob.is_contiguous() and prob.shape == dprob.shape and prob.dtype == dprob.dtype
     D = prob.shape[-1]
     ds = torch.empty_like(prob)
-    _check(lib().ob200_softmax_backward(_ptr(prob), _ptr(dprob), _ptr(ds), prob.numel() // D, D, float(scale), _dtype_code(prob),
-                                        num_ctas or sm_count(), _stream()), "ob200_softmax_backward")
+    _check(lib().ob200_softmax_backward(_ptr(prob), _ptr(dprob), _ptr(ds), prob.numel() // D, D, float(scale), int(causal_period),
+                                        _dtype_code(prob), num_ctas or sm_count(), _stream()), "ob200_softmax_backward")
     return ds
 
 

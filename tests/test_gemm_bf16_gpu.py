@@ -89,3 +89,24 @@ def test_attention_products_on_the_fused_projection_layout(built, B, S, H):
     dk = K_.gemm_bf16(ds, q, trans_a=True, trans_b=True)                   # dK = dS^T . Q
     _check(dk, _ref(ds, q, True, True, None, 1.0), S)
     assert K_.read_status() == 0
+
+
+@pytest.mark.parametrize("S", [512, 384, 200])
+def test_causal_modes_skip_only_what_is_zero_or_unused(built, S):
+    """tri = 1 leaves tiles strictly above the diagonal unwritten and computes the rest; tri = 2 / 3 give the full product when
+    A is lower / upper triangular (the probabilities of causal attention and their transpose)."""
+    from orion_b200 import kernels as K_
+    torch.manual_seed(S)
+    B, H, d = 2, 3, 64
+    q = torch.randn(B, H, S, d, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, H, S, d, device="cuda").to(torch.bfloat16)
+    s = K_.gemm_bf16(q, k, tri=1)
+    ref = _ref(q, k, False, False, None, 1.0)
+    mask = torch.tril(torch.ones(S, S, dtype=torch.bool, device="cuda"))
+    err = torch.where(mask, (s.double() - ref).abs(), torch.zeros_like(ref)).max().item() / ref.abs().max().item()
+    assert err < 2e-2
+    p = (torch.softmax(torch.randn(B, H, S, S, device="cuda"), -1) * mask).to(torch.bfloat16)     # lower triangular
+    v = torch.randn(B, H, S, d, device="cuda").to(torch.bfloat16)
+    _check(K_.gemm_bf16(p, v, trans_b=True, tri=2), _ref(p, v, False, True, None, 1.0), S)                   # P . V
+    _check(K_.gemm_bf16(p, v, trans_a=True, trans_b=True, tri=3), _ref(p, v, True, True, None, 1.0), S)      # P^T . dO
+    assert K_.read_status() == 0

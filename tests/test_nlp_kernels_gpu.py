@@ -281,3 +281,13 @@ def test_column_sums_and_softmax_backward_through_the_c_abi(K, dtype, tol):
     pd, dpd = p.double().cpu(), dp.double().cpu()
     want = 0.125 * pd * (dpd - (pd * dpd).sum(-1, keepdim=True))
     assert O.rel_err(K.softmax_backward(p, dp, 0.125), want) < tol
+    # causal rows: columns behind the query position are not read (NaN there must not matter) and come out as zero
+    S = 128
+    mask = torch.tril(torch.ones(S, S, dtype=torch.bool, device="cuda")).repeat(5, 1)
+    pc = (torch.softmax(torch.randn(5 * S, S, device="cuda"), -1) * mask).to(dtype)
+    dpc = torch.randn(5 * S, S, device="cuda").to(dtype)
+    pcd, dpcd = pc.double().cpu(), (dpc.double() * mask).cpu()
+    wantc = 0.5 * pcd * (dpcd - (pcd * dpcd).sum(-1, keepdim=True))
+    dpc = torch.where(mask, dpc, torch.full_like(dpc, float("nan")))
+    got = K.softmax_backward(pc, dpc, 0.5, causal_period=S)
+    assert torch.isfinite(got).all() and O.rel_err(got, wantc) < tol
