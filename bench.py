@@ -23,6 +23,8 @@ Printed JSON (one line, rank 0):
   roofline   the implicit-GEMM convolution kernel, timed here with CUDA events
   roofline_hbm  the HBM-bound kernels of the BE training step (batch norm, add+ReLU, ReLU
              backward, pooling, SGD), timed the same way
+  roofline_gemm_bf16  the bf16 GEMM kernel of the transformer clients (forward, dX, dW of one
+             decoder-LM layer), timed the same way
   cpu_baseline  the same workload in eager PyTorch on the host cores (bounded sample), and the
              reference scheduler replaying the arrival script recorded from this run's
              co-located phase next to the product's policy core (same decision log or not)
@@ -136,6 +138,46 @@ def hbm_roofline(peaks, iters=5, warm=3):
                       "step; algorithmic 20 B per element",
             "set_achieved": total_bytes / total_us / 1e3, "set_frac": total_bytes / total_us / 1e3 / peaks["hbm_gbs"],
             "set": [{"kernel": r["kernel"], "GBps": round(r["GBps"], 1), "us": round(r["us"], 1)} for r in rows]}
+
+
+def gemm_roofline(peaks, iters=10, warm=3):
+    """The bf16 GEMM kernel behind the transformer clients (configs[3], configs[4]) on the linear-layer shapes of one
+    decoder-LM layer at batch 16 x 512 tokens: forward, dX = dY.W (W read MN-major) and dW = dY^T.X (both read MN-major),
+    one C-ABI call each per iteration, CUDA events on the launching stream, L2 flushed between iterations."""
+    import torch
+    from orion_b200 import kernels as K
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T = 16 * 512
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    calls = []
+    for (i, o) in ((1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024)):
+        x = torch.randn(T, i, device=dev).bfloat16()
+        w = (torch.randn(o, i, device=dev) * 0.03).bfloat16()
+        dy = torch.randn(T, o, device=dev).bfloat16()
+        calls += [(2.0 * T * i * o, lambda x=x, w=w: K.gemm_bf16(x, w)),
+                  (2.0 * T * i * o, lambda dy=dy, w=w: K.gemm_bf16(dy, w, trans_b=True)),
+                  (2.0 * T * i * o, lambda dy=dy, x=x: K.gemm_bf16(dy, x, trans_a=True, trans_b=True))]
+    flop = us = 0.0
+    n = 0
+    for it in range(warm + iters):
+        for f, fn in calls:
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            if it >= warm:
+                flop += f
+                us += e0.elapsed_time(e1) * 1e3
+                n += 1
+    if K.read_status() != 0:
+        raise RuntimeError("a kernel reported a timed-out wait")
+    tf = flop / us / 1e6
+    return {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
+            "traffic": None, "peak_source": peaks["source"], "avg_launch_us": us / n, "launches_timed": n,
+            "kernel": "gemm_bf16_kernel (tcgen05 kind::f16, TMA loads and stores, operands K-major or MN-major): the 12 linear-layer "
+                      "products (forward, dX, dW) of one decoder-LM layer at 8192 tokens, L2 flushed before every launch"}
 
 
 def policy_replay(script, repeat=1):
@@ -299,7 +341,7 @@ def run_replica(gpu, steps, warm_steps, out_dir, be_quota, with_c5=False):
     return out
 
 
-def run_c5(E, env, out_dir, requests=250, rps=40):
+def run_c5(E, env, out_dir, requests=500, rps=40):
     """configs[4] on this replica's GPU, a short run beside the headline: HP ResNet-101 inference (fp32, batch 4, Poisson
     40 req/s) with BE decoder-LM training (16 layers, d_model 1024, sequence 512, batch 16, bf16, AdamW)."""
     env = dict(env)
@@ -415,6 +457,7 @@ def main():
     peaks = read_peaks()
     roof = kernel_roofline(batch=32, iters=5, warm=3)
     roof_hbm = hbm_roofline(peaks)
+    roof_gemm = gemm_roofline(peaks)
     base = cpu_baseline(recorded_script=rep["script"], observations=rep.get("observations"))
     worst = max(gathered, key=lambda g: g["hp_p99"] / g["hp_solo_p99"])
     value = sum(g["be_sps"] for g in gathered)
@@ -455,6 +498,7 @@ def main():
                      "avg_launch_us": roof["avg_launch_us"], "launches_timed": roof["launches"],
                      "note": "peak is the bf16 dense figure; fp32 runs three TF32 MMAs per product"},
         "roofline_hbm": roof_hbm,
+        "roofline_gemm_bf16": roof_gemm,
         "cpu_baseline": base,
         "clocks": clocks,
         "wall_s": wall,

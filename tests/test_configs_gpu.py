@@ -46,6 +46,103 @@ def test_bert_base_batch8_seq384_matches_cpu_fp32(ops):
     assert err < 2e-2
 
 
+def _param_grad_errors(model, ref):
+    worst = {}
+    for (name, p), (_, pr) in zip(model.named_parameters(), ref.named_parameters()):
+        if pr.grad is None or pr.grad.abs().max() < 1e-12:   # no gradient, or one that is zero up to float64 rounding
+            continue
+        assert p.grad is not None, name
+        worst[name] = _rel(p.grad, pr.grad)
+    return worst
+
+
+def test_bert_training_step_on_own_kernels_matches_cpu_float64(ops):
+    """One fine-tuning step of the BERT client (configuration 4's BE job: embeddings, encoder layers, span head, both span
+    losses) with every op on the orion kernels: loss and every parameter gradient against the stock-module path in float64 on
+    the CPU from the same bfloat16 weights.  BERT-base width (768 / 12 heads / FFN 3072, sequence 384), 3 layers, batch 4.
+    Bars: loss within 2e-2; gradient errors (relative to each tensor's largest entry) within 2e-2, or, where a chain of bfloat16
+    activations and gradients through several layers exceeds that whatever kernels compute it, no worse than the stock bfloat16
+    modules on the same GPU against the same float64 oracle: median within 1.25x of theirs, worst tensor within 1.5x (measured:
+    median 3.1e-2 against 2.9e-2, worst 5.5e-2 against 5.8e-2)."""
+    import torch.nn.functional as F
+    from benchmarking.benchmark_suite import transformer_trainer as tt
+    from orion_b200 import kernels
+    assert tt.ORION_TRAIN_KERNELS and tt.OWN_GEMM_TRAINING
+    torch.manual_seed(31)
+    cfg = dict(tt.BERT, layers=3)
+    model = tt.BertQA(cfg).to(torch.bfloat16).cuda().train()
+    ref = tt.BertQA(cfg).double().train()
+    ref.load_state_dict({k: v.double().cpu() for k, v in model.state_dict().items()})
+    ids = torch.randint(0, 30522, (4, 384))
+    lab = torch.randint(0, 384, (2, 4))
+    fb = int(torch.ops.orion.fallbacks())
+    lt = model.span_logits(ids.cuda())
+    loss = 2.0 * torch.ops.orion.cross_entropy(lt.view(-1, 384), lab.cuda().view(-1))
+    loss.backward()
+    assert kernels.read_status() == 0 and int(torch.ops.orion.fallbacks()) == fb
+    logits = ref(ids)
+    want = F.cross_entropy(logits[:, :, 0], lab[0]) + F.cross_entropy(logits[:, :, 1], lab[1])
+    want.backward()
+    assert abs(loss.item() - want.item()) < 2e-2 * abs(want.item())
+    errs = _param_grad_errors(model, ref)
+    errs.pop("qa.bias", None)          # shifts all positions of a row alike: its gradient is exactly zero in both
+    assert len(errs) >= 3 * 12 + 4
+    # the same step through the stock bfloat16 modules on the GPU (cuBLASLt, fused attention, ATen): the yardstick for what
+    # bfloat16 activations and gradients cost against float64 over three layers
+    model.zero_grad(set_to_none=True)
+    tt.OWN_GEMM_TRAINING = False
+    try:
+        lg = model(ids.cuda()).float()
+        (F.cross_entropy(lg[:, :, 0], lab[0].cuda()) + F.cross_entropy(lg[:, :, 1], lab[1].cuda())).backward()
+    finally:
+        tt.OWN_GEMM_TRAINING = True
+    stock = _param_grad_errors(model, ref)
+    stock.pop("qa.bias", None)
+    worst = max(errs, key=errs.get)
+    print("BERT step: loss %.4f vs %.4f; gradient error worst %.2e (%s), median %.2e; stock bfloat16 modules: worst %.2e, median %.2e"
+          % (loss.item(), want.item(), errs[worst], worst, sorted(errs.values())[len(errs) // 2], max(stock.values()),
+             sorted(stock.values())[len(stock) // 2]))
+    assert sorted(errs.values())[len(errs) // 2] < max(2e-2, 1.25 * sorted(stock.values())[len(stock) // 2])
+    assert max(errs.values()) < max(2e-2, 1.5 * max(stock.values()))
+
+
+def test_decoder_lm_training_step_on_own_kernels_matches_cpu_float64(ops):
+    """One training step of the language-model client (configuration 5's BE job): causal attention, vocabulary projection
+    and cross-entropy on the orion kernels against float64 on the CPU.  Model width of the benchmark (1024 / 16 heads / FFN
+    4096, vocabulary 32000, sequence 512), 2 layers, batch 2."""
+    import torch.nn.functional as F
+    from benchmarking.benchmark_suite import transformer_trainer as tt
+    from orion_b200 import kernels
+    torch.manual_seed(32)
+    cfg = dict(tt.LM, layers=2)
+    model = tt.DecoderLM(cfg).to(torch.bfloat16).cuda().train()
+    ref = tt.DecoderLM(cfg).double().train()
+    ref.load_state_dict({k: v.double().cpu() for k, v in model.state_dict().items()})
+    tok = torch.randint(0, 32000, (2, 513))
+    fb = int(torch.ops.orion.fallbacks())
+    logits = model(tok[:, :-1].cuda())
+    loss = torch.ops.orion.cross_entropy(logits.reshape(-1, 32000), tok[:, 1:].cuda().reshape(-1))
+    loss.backward()
+    assert kernels.read_status() == 0 and int(torch.ops.orion.fallbacks()) == fb
+    want = F.cross_entropy(ref(tok[:, :-1]).view(-1, 32000), tok[:, 1:].reshape(-1))
+    want.backward()
+    assert abs(loss.item() - want.item()) < 2e-2 * abs(want.item())
+    errs = _param_grad_errors(model, ref)
+    model.zero_grad(set_to_none=True)
+    tt.OWN_GEMM_TRAINING = False
+    try:
+        F.cross_entropy(model(tok[:, :-1].cuda()).float().view(-1, 32000), tok[:, 1:].cuda().reshape(-1)).backward()
+    finally:
+        tt.OWN_GEMM_TRAINING = True
+    stock = _param_grad_errors(model, ref)
+    worst = max(errs, key=errs.get)
+    print("LM step: loss %.4f vs %.4f; gradient error worst %.2e (%s), median %.2e; stock bfloat16 modules: worst %.2e, median %.2e"
+          % (loss.item(), want.item(), errs[worst], worst, sorted(errs.values())[len(errs) // 2], max(stock.values()),
+             sorted(stock.values())[len(stock) // 2]))
+    assert sorted(errs.values())[len(errs) // 2] < max(2e-2, 1.25 * sorted(stock.values())[len(stock) // 2])
+    assert max(errs.values()) < max(2e-2, 1.5 * max(stock.values()))
+
+
 def test_decoder_lm_batch16_seq512_matches_cpu_fp32(ops):
     """Configuration 5's language model (16 layers, d_model 1024, 16 heads, FFN 4096, vocabulary 32000), batch 16, sequence
     512: forward pass with causal attention on the orion kernels against float32 CPU math on the same weights."""
