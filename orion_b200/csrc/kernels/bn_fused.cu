@@ -375,7 +375,7 @@ static ReduceShape reduce_shape(long long rows, int C, int num_ctas) {
 }
 
 static inline int apply_grid(long long items, int num_ctas, int per_sm, int c4) {
-    long long want = (items + BF_THREADS - 1) / BF_THREADS, cap = (long long)num_ctas * per_sm;
+    long long want = (items + BF_THREADS - 1) / BF_THREADS, cap = (long long)num_ctas * per_sm * grid_oversubscription();
     if (want < 1) want = 1;
     int g = (int)(want < cap ? want : cap);
     int need = 1;   // smallest grid multiple that makes grid * BF_THREADS divisible by c4

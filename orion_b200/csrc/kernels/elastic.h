@@ -8,6 +8,7 @@
 // nothing.
 #pragma once
 #include <dlfcn.h>
+#include <stdlib.h>
 
 namespace ob200 {
 
@@ -26,6 +27,19 @@ inline void annotate_launch(int op_class, double flop, double bytes) {
     using Fn = void (*)(int, double, double);
     static const Fn fn = reinterpret_cast<Fn>(dlsym(RTLD_DEFAULT, "orion_capture_annotate"));
     if (fn) fn(op_class, flop, bytes);
+}
+
+// Grid width of a grid-stride (elementwise, normalisation) kernel as a multiple of the resident CTAs: with 1 every CTA
+// stays for the whole launch; with k > 1 the work is cut into k times as many CTAs that retire one after the other, so that
+// the blocks of a kernel on a higher-priority stream find a free slot after 1/k of the launch's duration instead of at its
+// end.  ORION_ELT_OVERSUB overrides the default.  A launch that the scheduler cuts to its SM quota is persistent again.
+inline int grid_oversubscription() {
+    static const int v = [] {
+        const char* e = getenv("ORION_ELT_OVERSUB");
+        int k = e ? atoi(e) : 1;
+        return k < 1 ? 1 : (k > 16 ? 16 : k);
+    }();
+    return v;
 }
 
 // Arithmetic intensity (FLOP per byte of HBM traffic) above which a tensor-core kernel is compute-bound on

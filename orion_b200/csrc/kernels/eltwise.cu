@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(256) avgpool_nhwc_f32_v4_kernel(const float4* 
 
 static inline int elt_grid(long long work_items, int num_ctas) {
     long long want = (work_items + ELT_THREADS - 1) / ELT_THREADS;
-    long long cap = (long long)num_ctas * ELT_CTAS_PER_SM;
+    long long cap = (long long)num_ctas * ELT_CTAS_PER_SM * grid_oversubscription();
     if (want < 1) want = 1;
     return (int)(want < cap ? want : cap);
 }

@@ -334,7 +334,7 @@ static inline int grid_for_channels(long long items, int num_ctas, int per_sm, i
 
 static inline int grid_for(long long items, int num_ctas, int per_sm) {
     long long want = (items + TR_THREADS - 1) / TR_THREADS;
-    long long cap = (long long)num_ctas * per_sm;
+    long long cap = (long long)num_ctas * per_sm * grid_oversubscription();
     if (want < 1) want = 1;
     return (int)(want < cap ? want : cap);
 }
@@ -466,7 +466,7 @@ extern "C" int ob200_sgd_momentum_multi_f32(float* const* p, const float* const*
         }
         if (t.count == 0) continue;
         const int chunks = t.first_chunk[t.count];
-        const long long cap = (long long)num_ctas * 4;
+        const long long cap = (long long)num_ctas * 4 * grid_oversubscription();
         OB200_ELASTIC_HBM(sgd_momentum_multi_kernel, 4);
         sgd_momentum_multi_kernel<<<(unsigned)(chunks < cap ? chunks : cap), TR_THREADS, 0, (cudaStream_t)stream>>>(t, lr, mu, wd, nesterov,
                                                                                                               first_step);
