@@ -238,7 +238,9 @@ int ob200_adamw_f32(float* p, const float* g, float* m, float* v, long long n, f
                     float weight_decay, int step, int num_ctas, void* stream);
 
 /* Device status word of the current device (synchronises the device): 0, or the code of
- * the bounded wait a kernel gave up on.  Clears the word.  No counterpart in the reference. */
+ * the bounded wait a kernel gave up on.  Clears the word; after a non-zero status it also clears the split-K arrival
+ * counters of every stream of the device, which the kernel that gave up may have left above zero.  No counterpart in the
+ * reference. */
 int ob200_read_status(void);
 /* Tuning aid, no counterpart in the reference: `dev_buf` (8 long longs in device memory, or NULL to
  * switch off) receives from CTA 0 of every implicit-GEMM launch the cycles each warp role spent

@@ -556,7 +556,14 @@ extern "C" int ob200_read_status(void) {
     if (!p) return -1;
     int v = 0;
     if (cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (v) cudaMemset(p, 0, sizeof v);
+    if (v) {
+        cudaMemset(p, 0, sizeof v);
+        // A kernel that gave up a wait left early: the arrival counters of its stream's split-K scratch may not be back
+        // at zero, and a later split-K launch would count from there.  The copy above drained the device; clear them all.
+        std::lock_guard<std::mutex> lk(g_mu);
+        for (auto& kv : g_scratch)
+            if ((int)(kv.first >> 56) == dev && kv.second.counters) cudaMemset(kv.second.counters, 0, kMaxTilesSplit * sizeof(int));
+    }
     return v;
 }
 
