@@ -192,13 +192,13 @@ __global__ void __launch_bounds__(NT_THREADS) ln_backward_kernel(const T* __rest
     }
 }
 
-// out[which][col] = sum over parts of partial[part][which][col]; written as T.  A CTA of 256 threads owns 32 consecutive
-// (which, col) entries: thread (g, c) adds parts g, g + 8, ... of entry c (one coalesced 128-byte read per part and group),
-// then the eight group sums are added in group order, so the order of the additions is fixed.
+// out[which][col] = sum over parts of partial[part][which][col]; written as T.  A CTA of 1024 threads owns 32 consecutive
+// (which, col) entries: thread (g, c) adds parts g, g + 32, ... of entry c (one coalesced 128-byte read per part and group),
+// then the 32 group sums are added in group order, so the order of the additions is fixed.
 template <typename T>
-__global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int parts, int D, int n_which,
+__global__ void __launch_bounds__(1024) colsum_finish_kernel(const float* __restrict__ partial, int parts, int D, int n_which,
                                                             T* __restrict__ out0, T* __restrict__ out1) {
-    __shared__ float sh[8][33];
+    __shared__ float sh[32][33];
     const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int i = blockIdx.x * 32 + c;
     const int total = n_which * D;
@@ -208,14 +208,14 @@ __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restr
         const float* src = partial + (long long)which * D + col;
         const long long step = (long long)n_which * D;
 #pragma unroll 4
-        for (int p = g; p < parts; p += 8) s += src[p * step];
+        for (int p = g; p < parts; p += 32) s += src[p * step];
     }
     sh[g][c] = s;
     __syncthreads();
     if (g == 0 && i < total) {
         float t = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; k++) t += sh[k][c];
+        for (int k = 0; k < 32; k++) t += sh[k][c];
         const int which = i / D, col = i - which * D;
         T* out = which == 0 ? out0 : out1;
         if (out) out[col] = (T)t;
@@ -426,14 +426,35 @@ __global__ void __launch_bounds__(NT_THREADS) adamw_multi_kernel(const __grid_co
         const T* __restrict__ g = (const T*)t.g[lo];
         T* __restrict__ m = (T*)t.m[lo];
         T* __restrict__ v = (T*)t.v[lo];
-        for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float decay = 1.0f - lr * wd, step_size = lr / bc1, inv_bc2 = 1.0f / bc2_sqrt;
+        constexpr int N = Vec8<T>::N;
+        // 16-byte accesses where the four tensors are 16-byte aligned (chunks start at multiples of 16384 elements)
+        const bool vec = ((((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15) == 0);
+        const long long vec_end = vec ? begin + (end - begin) / N * N : begin;
+        for (long long i = begin + (long long)threadIdx.x * N; i < vec_end; i += (long long)blockDim.x * N) {
+            float gv[8], pv[8], mv[8], vv[8];
+            Vec8<T>::load(g + i, gv);
+            Vec8<T>::load(p + i, pv);
+            Vec8<T>::load(m + i, mv);
+            Vec8<T>::load(v + i, vv);
+#pragma unroll
+            for (int e = 0; e < N; e++) {
+                mv[e] = b1 * mv[e] + (1.0f - b1) * gv[e];
+                vv[e] = b2 * vv[e] + (1.0f - b2) * gv[e] * gv[e];
+                pv[e] = pv[e] * decay - step_size * mv[e] / (sqrtf(vv[e]) * inv_bc2 + eps);
+            }
+            Vec8<T>::store(m + i, mv);
+            Vec8<T>::store(v + i, vv);
+            Vec8<T>::store(p + i, pv);
+        }
+        for (long long i = vec_end + threadIdx.x; i < end; i += blockDim.x) {
             const float grad = to_f(g[i]);
-            float param = to_f(p[i]) * (1.0f - lr * wd);
+            float param = to_f(p[i]) * decay;
             const float mi = b1 * to_f(m[i]) + (1.0f - b1) * grad;
             const float vi = b2 * to_f(v[i]) + (1.0f - b2) * grad * grad;
             m[i] = from_f<T>(mi);
             v[i] = from_f<T>(vi);
-            param -= (lr / bc1) * mi / (sqrtf(vi) / bc2_sqrt + eps);
+            param -= step_size * mi / (sqrtf(vi) * inv_bc2 + eps);
             p[i] = from_f<T>(param);
         }
     }
@@ -516,7 +537,7 @@ extern "C" int ob200_layernorm_backward(const void* dy, const void* x, const voi
         ln_backward_kernel<T, CH><<<grid, NT_THREADS, smem, s>>>((const T*)dy, (const T*)x, (const T*)gamma, mean, rstd, (T*)dx, partial, \
                                                                  rows, D);                                                           \
         OB200_HBM_BOUND();                                                                                                           \
-        colsum_finish_kernel<T><<<(2 * D + 31) / 32, 256, 0, s>>>(partial, grid, D, 2, (T*)dgamma, (T*)dbeta);                      \
+        colsum_finish_kernel<T><<<(2 * D + 31) / 32, 1024, 0, s>>>(partial, grid, D, 2, (T*)dgamma, (T*)dbeta);                      \
     } while (0)
     if (dtype == 0) {
         if (chunks <= 2) OB200_LNB(float, 2); else OB200_LNB(float, 4);
@@ -574,8 +595,8 @@ extern "C" int ob200_bias_gelu_backward(const void* dy, const void* x, const voi
                                                                                (const __nv_bfloat16*)bias, (__nv_bfloat16*)dx, partial, rows, D);
     if (dbias) {
         OB200_HBM_BOUND();
-        if (dtype == 0) colsum_finish_kernel<float><<<(D + 31) / 32, 256, 0, s>>>(partial, grid, D, 1, (float*)dbias, (float*)nullptr);
-        else colsum_finish_kernel<__nv_bfloat16><<<(D + 31) / 32, 256, 0, s>>>(partial, grid, D, 1, (__nv_bfloat16*)dbias, (__nv_bfloat16*)nullptr);
+        if (dtype == 0) colsum_finish_kernel<float><<<(D + 31) / 32, 1024, 0, s>>>(partial, grid, D, 1, (float*)dbias, (float*)nullptr);
+        else colsum_finish_kernel<__nv_bfloat16><<<(D + 31) / 32, 1024, 0, s>>>(partial, grid, D, 1, (__nv_bfloat16*)dbias, (__nv_bfloat16*)nullptr);
     }
     return (int)cudaGetLastError();
 }

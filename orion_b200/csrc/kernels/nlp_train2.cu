@@ -98,24 +98,24 @@ __global__ void __launch_bounds__(N2_THREADS) colsum_rows_kernel(const T* __rest
     }
 }
 
-// out[col] = sum of the CTAs' partial sums.  Thread (g, c) of a 256-thread CTA adds parts g, g + 8, ... of column c (coalesced
-// 128-byte reads), then the eight group sums are added in group order: a fixed order of additions.
+// out[col] = sum of the CTAs' partial sums.  Thread (g, c) of a 1024-thread CTA adds parts g, g + 32, ... of column c (coalesced
+// 128-byte reads), then the 32 group sums are added in group order: a fixed order of additions.
 template <typename T>
-__global__ void __launch_bounds__(256) colsum_parts_kernel(const float* __restrict__ partial, int parts, int D, T* __restrict__ out) {
-    __shared__ float sh[8][33];
+__global__ void __launch_bounds__(1024) colsum_parts_kernel(const float* __restrict__ partial, int parts, int D, T* __restrict__ out) {
+    __shared__ float sh[32][33];
     const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + c;
     float s = 0.f;
     if (col < D) {
 #pragma unroll 4
-        for (int p = g; p < parts; p += 8) s += partial[(long long)p * D + col];
+        for (int p = g; p < parts; p += 32) s += partial[(long long)p * D + col];
     }
     sh[g][c] = s;
     __syncthreads();
     if (g == 0 && col < D) {
         float t = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; k++) t += sh[k][c];
+        for (int k = 0; k < 32; k++) t += sh[k][c];
         out[col] = (T)t;
     }
 }
@@ -250,7 +250,7 @@ extern "C" int ob200_colsum(const void* x, void* out, long long rows, int D, lon
     const int chunks = D / n;
     const int lanes_x = chunks < N2_THREADS ? chunks : N2_THREADS;
     const int rows_per_pass = N2_THREADS / lanes_x;
-    long long want = (rows + rows_per_pass - 1) / rows_per_pass, cap = (long long)num_ctas * 4;
+    long long want = (rows + rows_per_pass - 1) / rows_per_pass, cap = (long long)num_ctas * 2;
     if (cap > N2_MAX_PARTS) cap = N2_MAX_PARTS;
     const int grid = (int)(want < cap ? want : cap);
     const size_t smem = (size_t)rows_per_pass * D * sizeof(float);
@@ -258,8 +258,8 @@ extern "C" int ob200_colsum(const void* x, void* out, long long rows, int D, lon
     if (dtype == 0) colsum_rows_kernel<float><<<grid, N2_THREADS, smem, s>>>((const float*)x, partial, rows, D, ld);
     else colsum_rows_kernel<__nv_bfloat16><<<grid, N2_THREADS, smem, s>>>((const __nv_bfloat16*)x, partial, rows, D, ld);
     OB200_HBM_BOUND();
-    if (dtype == 0) colsum_parts_kernel<float><<<(D + 31) / 32, 256, 0, s>>>(partial, grid, D, (float*)out);
-    else colsum_parts_kernel<__nv_bfloat16><<<(D + 31) / 32, 256, 0, s>>>(partial, grid, D, (__nv_bfloat16*)out);
+    if (dtype == 0) colsum_parts_kernel<float><<<(D + 31) / 32, 1024, 0, s>>>(partial, grid, D, (float*)out);
+    else colsum_parts_kernel<__nv_bfloat16><<<(D + 31) / 32, 1024, 0, s>>>(partial, grid, D, (__nv_bfloat16*)out);
     return (int)cudaGetLastError();
 }
 
