@@ -460,8 +460,24 @@ static int gm_launch(const GemmParams& p, int grid, cudaStream_t stream) {
         attr_set[dev] = true;
     }
     OB200_ELASTIC(gemm_bf16_kernel<BN>, 1);
-    gemm_bf16_kernel<BN><<<grid, GM_THREADS, GemmCfg<BN>::SMEM, stream>>>(p);
-    return (int)cudaGetLastError();
+    // Programmatic dependent launch: the kernel's set-up (barriers, tensor memory, descriptor prefetch) may overlap the tail of
+    // the kernel before it in the stream; it reads and writes global memory only behind its griddepcontrol.wait.
+    static const bool pdl = [] {   // ORION_PDL=0: plain stream order between consecutive kernels
+        const char* e = getenv("ORION_PDL");
+        return !(e && e[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GM_THREADS);
+    cfg.dynamicSmemBytes = GemmCfg<BN>::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN>, p);
 }
 
 }  // namespace ob200

@@ -13,6 +13,7 @@
 #include <math.h>
 #include <stdint.h>
 #include "elastic.h"
+#include "pdl.cuh"
 #include "fast_gelu.cuh"
 
 namespace ob200 {
@@ -86,6 +87,7 @@ __global__ void __launch_bounds__(ROW_THREADS) layernorm_regs_kernel(const T* __
                                                                     const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                     float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                                     long long rows, int D, float eps) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = VecIO<T>::N;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
@@ -135,6 +137,7 @@ __global__ void __launch_bounds__(ROW_THREADS) layernorm_regs_kernel(const T* __
 template <typename T, int CH>
 __global__ void __launch_bounds__(ROW_THREADS) softmax_regs_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int D,
                                                                   float scale, int causal_period) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = VecIO<T>::N;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
@@ -187,6 +190,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) layernorm_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ gamma,
                                                                const float* __restrict__ beta, float* __restrict__ mean_out,
                                                                float* __restrict__ rstd_out, long long rows, int D, float eps) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = VecIO<T>::N;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
@@ -229,6 +233,7 @@ __global__ void __launch_bounds__(ROW_THREADS) layernorm_kernel(const T* __restr
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) softmax_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int D,
                                                              float scale, int causal_period) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = VecIO<T>::N;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
@@ -265,6 +270,7 @@ __global__ void __launch_bounds__(ROW_THREADS) softmax_kernel(const T* __restric
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) bias_gelu_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ bias,
                                                                long long n_vec, int D) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = VecIO<T>::N;
     const long long stride = (long long)gridDim.x * blockDim.x;
     long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;

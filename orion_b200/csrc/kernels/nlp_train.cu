@@ -19,6 +19,7 @@
 #include <unordered_map>
 
 #include "elastic.h"
+#include "pdl.cuh"
 #include "fast_gelu.cuh"
 
 namespace ob200 {
@@ -77,6 +78,7 @@ template <typename T, int CH>
 __global__ void __launch_bounds__(NT_THREADS) ln_train_forward_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restrict__ gamma,
                                                                      const T* __restrict__ beta, float* __restrict__ mean_out,
                                                                      float* __restrict__ rstd_out, long long rows, int D, float eps) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = Vec8<T>::N;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
@@ -126,6 +128,7 @@ template <typename T, int CH>
 __global__ void __launch_bounds__(NT_THREADS) ln_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                                                                 const float* __restrict__ mean, const float* __restrict__ rstd,
                                                                 T* __restrict__ dx, float* __restrict__ partial, long long rows, int D) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = Vec8<T>::N;
     extern __shared__ float sh[];   // [warps][2][D]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -198,6 +201,7 @@ __global__ void __launch_bounds__(NT_THREADS) ln_backward_kernel(const T* __rest
 template <typename T>
 __global__ void __launch_bounds__(1024) colsum_finish_kernel(const float* __restrict__ partial, int parts, int D, int n_which,
                                                             T* __restrict__ out0, T* __restrict__ out1) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     __shared__ float sh[32][33];
     const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int i = blockIdx.x * 32 + c;
@@ -226,6 +230,7 @@ __global__ void __launch_bounds__(1024) colsum_finish_kernel(const float* __rest
 template <typename T>
 __global__ void __launch_bounds__(NT_THREADS) bias_gelu_forward_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ y,
                                                                       long long n_vec, int D) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = Vec8<T>::N;
     const long long stride = (long long)gridDim.x * blockDim.x;
     long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -279,6 +284,7 @@ template <typename T>
 __global__ void __launch_bounds__(NT_THREADS) bias_gelu_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                                                        const T* __restrict__ bias, T* __restrict__ dx,
                                                                        float* __restrict__ partial, long long rows, int D) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = Vec8<T>::N;
     const int chunks = D / N;                       // 16-byte chunks per row
     const int lanes_x = chunks < NT_THREADS ? chunks : NT_THREADS;   // threads across a row

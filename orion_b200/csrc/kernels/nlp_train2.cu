@@ -12,6 +12,7 @@
 #include <unordered_map>
 
 #include "elastic.h"
+#include "pdl.cuh"
 
 namespace ob200 {
 
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(N2_THREADS) colsum_rows_kernel(const T* __rest
 // 128-byte reads), then the 32 group sums are added in group order: a fixed order of additions.
 template <typename T>
 __global__ void __launch_bounds__(1024) colsum_parts_kernel(const float* __restrict__ partial, int parts, int D, T* __restrict__ out) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     __shared__ float sh[32][33];
     const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + c;
@@ -124,6 +126,7 @@ __global__ void __launch_bounds__(1024) colsum_parts_kernel(const float* __restr
 template <typename T>
 __global__ void __launch_bounds__(N2_THREADS) softmax_backward_kernel(const T* __restrict__ prob, const T* __restrict__ dprob, T* __restrict__ ds,
                                                                      long long rows, int D, float scale, int causal_period) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = Ld8<T>::N;
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -172,6 +175,7 @@ struct EmbTables {
 
 template <typename T>
 __global__ void __launch_bounds__(N2_THREADS) embedding_sum_kernel(const EmbTables tb, T* __restrict__ out, long long tokens, int D) {
+    pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = Ld8<T>::N;
     const int chunks = D / N;
     const long long total = tokens * chunks;

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 namespace ob200 {
 
 // Status codes written to the kernel's status word (0 = ok).
@@ -129,13 +131,6 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
-
-// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
-// while the kernel before it in the stream is still running; pdl_wait() blocks the calling thread until that kernel
-// has completed and its writes are visible (a no-op for a normally launched kernel).  pdl_launch_dependents() tells the
-// device that, as far as this CTA is concerned, the next kernel of the stream may begin to start.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
