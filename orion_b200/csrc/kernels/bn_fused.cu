@@ -29,6 +29,7 @@
 #include <unordered_map>
 
 #include "elastic.h"
+#include "pdl.cuh"
 
 namespace ob200 {
 
@@ -206,6 +207,7 @@ __global__ void __launch_bounds__(BF_THREADS) bn_act_apply_kernel(const float4* 
                                                                  float4* __restrict__ y, const float* __restrict__ gamma,
                                                                  const float* __restrict__ beta, const float* __restrict__ mean,
                                                                  const float* __restrict__ invstd, long long n4, int c4, int act) {
+    pdl_launch_dependents();   // a convolution behind this kernel may set itself up meanwhile (pdl.cuh)
     const long long stride = (long long)gridDim.x * blockDim.x;
     long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     auto coef = [&](int c, float4& a, float4& b) {
@@ -260,6 +262,7 @@ __global__ void __launch_bounds__(BF_THREADS) bn_act_backward_apply_kernel(const
                                                                           const float* __restrict__ mean,
                                                                           const float* __restrict__ invstd, long long n4, int c4,
                                                                           int act) {
+    pdl_launch_dependents();   // a convolution behind this kernel may set itself up meanwhile (pdl.cuh)
     const int C = c4 * 4;
     const long long stride = (long long)gridDim.x * blockDim.x;
     long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;

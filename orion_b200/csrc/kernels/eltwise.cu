@@ -13,6 +13,7 @@
 #include <float.h>
 #include <stdint.h>
 #include "elastic.h"
+#include "pdl.cuh"
 
 namespace ob200 {
 
@@ -26,6 +27,7 @@ __global__ void __launch_bounds__(ELT_THREADS) bn_inference_f32_kernel(const flo
                                                                      const float* __restrict__ mean,
                                                                      const float* __restrict__ var, float eps,
                                                                      long long n4, int c4, int relu) {
+    pdl_launch_dependents();   // a convolution behind this kernel may set itself up meanwhile (pdl.cuh)
     // y = a * x + b per channel.  When the grid stride is a multiple of the channel-quad count a thread stays on one
     // channel quad: the coefficients (and their square roots) are computed once, the loop keeps four loads in flight.
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -82,6 +84,7 @@ __global__ void __launch_bounds__(ELT_THREADS) bn_inference_f32_scalar_kernel(co
 // mode 0: y = relu(a); 1: y = a + b; 2: y = relu(a + b)
 __global__ void __launch_bounds__(ELT_THREADS) binary_f32_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
                                                                float4* __restrict__ y, long long n4, int mode) {
+    pdl_launch_dependents();   // a convolution behind this kernel may set itself up meanwhile (pdl.cuh)
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         float4 v = __ldcs(a + i);
         if (mode != 0) {
@@ -108,6 +111,7 @@ __global__ void __launch_bounds__(ELT_THREADS) binary_f32_tail_kernel(const floa
 __global__ void __launch_bounds__(ELT_THREADS) maxpool_nhwc_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int Nb,
                                                                      int H, int W, int C, int P, int Q, int k, int stride,
                                                                      int pad) {
+    pdl_launch_dependents();   // a convolution behind this kernel may set itself up meanwhile (pdl.cuh)
     const int c4 = C >> 2;
     const long long total = (long long)Nb * P * Q * c4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -135,6 +139,7 @@ __global__ void __launch_bounds__(ELT_THREADS) maxpool_nhwc_f32_kernel(const flo
 // its channel quad, sharing the nine input columns they need (27 loads for four outputs instead of 36).
 __global__ void __launch_bounds__(ELT_THREADS) maxpool3x3s2_nhwc_f32_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                                           int Nb, int H, int W, int C, int P, int Q, int pad) {
+    pdl_launch_dependents();   // a convolution behind this kernel may set itself up meanwhile (pdl.cuh)
     const int c4 = C >> 2, qb_n = (Q + 3) / 4;
     const long long total = (long long)Nb * P * qb_n * c4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -179,6 +184,7 @@ __global__ void __launch_bounds__(ELT_THREADS) maxpool3x3s2_nhwc_f32_kernel(cons
 __global__ void __launch_bounds__(ELT_THREADS) maxpool_backward_nhwc_f32_kernel(const float* __restrict__ dy, const float* __restrict__ x,
                                                                               float* __restrict__ dx, int Nb, int H, int W, int C,
                                                                               int P, int Q, int k, int stride, int pad) {
+    pdl_launch_dependents();   // a convolution behind this kernel may set itself up meanwhile (pdl.cuh)
     const int c4 = C >> 2;
     const long long total = (long long)Nb * P * Q * c4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
