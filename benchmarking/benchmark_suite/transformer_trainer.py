@@ -35,6 +35,17 @@ BERT = dict(layers=12, hidden=768, heads=12, ffn=3072, vocab=30528, max_pos=512,
 LM = dict(layers=16, hidden=1024, heads=16, ffn=4096, vocab=32000, seq=512)
 
 
+def _f32(module, p):
+    """float32 copy of a parameter for the kernels that take their bias / scale in float32, made once per parameter version
+    (an inference model never changes it) instead of one cast kernel per use."""
+    cache = module.__dict__.setdefault("_f32_cache", {})
+    hit = cache.get(id(p))
+    if hit is None or hit[0] != p._version or hit[2] != p.data_ptr():
+        hit = (p._version, p.detach().float(), p.data_ptr())
+        cache[id(p)] = hit
+    return hit[1]
+
+
 class BertLayer(nn.Module):
     def __init__(self, h, heads, ffn):
         super().__init__()
@@ -74,7 +85,7 @@ class BertLayer(nn.Module):
         b, s, h = x.shape
         d = h // self.heads
         flat = x.reshape(b * s, h)
-        qkv = ops.linear(flat, self.qkv.weight, self.qkv.bias.float(), False)
+        qkv = ops.linear(flat, self.qkv.weight, _f32(self, self.qkv.bias), False)
         if d == 64 and s <= 384 and x.dtype == torch.bfloat16 and FUSED_ATTENTION:
             # scores, softmax and the context product in one kernel, read straight from the projection's output
             ctx = ops.attention(qkv.view(b, s, 3 * h), self.heads, 1.0 / math.sqrt(d), causal)
@@ -86,11 +97,11 @@ class BertLayer(nn.Module):
             probs = ops.softmax(ops.linear_batched(q, k), 1.0 / math.sqrt(d), s if causal else 0)
             ctx = ops.linear_batched(probs, vt).view(b, self.heads, s, d).permute(0, 2, 1, 3).reshape(b * s, h).contiguous()
         # the residual stream is added in the GEMM epilogue, in float32, before the sum is rounded to bfloat16
-        attn = ops.linear(ctx, self.out.weight, self.out.bias.float(), False, flat)
-        y = ops.layernorm(attn, self.ln1.weight.float(), self.ln1.bias.float(), self.ln1.eps)
-        hid = ops.bias_gelu(ops.linear(y, self.fc1.weight, None, False), self.fc1.bias.float())
-        out = ops.linear(hid, self.fc2.weight, self.fc2.bias.float(), False, y)
-        return ops.layernorm(out, self.ln2.weight.float(), self.ln2.bias.float(), self.ln2.eps).view(b, s, h)
+        attn = ops.linear(ctx, self.out.weight, _f32(self, self.out.bias), False, flat)
+        y = ops.layernorm(attn, _f32(self, self.ln1.weight), _f32(self, self.ln1.bias), self.ln1.eps)
+        hid = ops.bias_gelu(ops.linear(y, self.fc1.weight, None, False), _f32(self, self.fc1.bias))
+        out = ops.linear(hid, self.fc2.weight, _f32(self, self.fc2.bias), False, y)
+        return ops.layernorm(out, _f32(self, self.ln2.weight), _f32(self, self.ln2.bias), self.ln2.eps).view(b, s, h)
 
 
 class BertQA(nn.Module):
@@ -116,7 +127,13 @@ class BertQA(nn.Module):
         return self.ln(self.word(ids) + self.pos(pos)[None] + self.typ.weight[0])
 
     def forward(self, ids, orion=False):
-        x = self.embed(ids)
+        if orion and ids.is_cuda and self.word.weight.dtype == torch.bfloat16:
+            ops = torch.ops.orion   # the three lookups and their sum in one kernel, then the orion LayerNorm
+            b, s = ids.shape
+            emb = ops.embedding_train(ids.contiguous(), self.word.weight, self.pos.weight, self.typ.weight)
+            x = ops.layernorm(emb.view(b * s, -1), _f32(self, self.ln.weight), _f32(self, self.ln.bias), self.ln.eps).view(b, s, -1)
+        else:
+            x = self.embed(ids)
         for layer in self.layers:
             x = layer.forward_orion(x) if orion else layer(x)
         return self.qa(x)   # [B, S, 2]: start / end logits
@@ -150,8 +167,11 @@ class DecoderLM(nn.Module):
             for layer in self.layers:
                 x = layer(x, causal=True)
             return ops.linear_train(ops.layernorm_train(x, self.ln.weight, self.ln.bias, self.ln.eps), self.head.weight, None)
-        pos = torch.arange(ids.shape[1], device=ids.device)
-        x = self.word(ids) + self.pos(pos)[None]
+        if orion and ids.is_cuda and self.word.weight.dtype == torch.bfloat16:
+            x = torch.ops.orion.embedding_train(ids.contiguous(), self.word.weight, self.pos.weight)
+        else:
+            pos = torch.arange(ids.shape[1], device=ids.device)
+            x = self.word(ids) + self.pos(pos)[None]
         if not orion:
             for layer in self.layers:
                 x = layer(x, causal=True)
@@ -161,7 +181,7 @@ class DecoderLM(nn.Module):
         for layer in self.layers:
             x = layer.forward_orion(x, causal=True)
         b, s, h = x.shape
-        y = ops.layernorm(x.reshape(b * s, h), self.ln.weight.float(), self.ln.bias.float(), self.ln.eps)
+        y = ops.layernorm(x.reshape(b * s, h), _f32(self, self.ln.weight), _f32(self, self.ln.bias), self.ln.eps)
         return ops.linear(y, self.head.weight, None, False).view(b, s, -1)
 
 

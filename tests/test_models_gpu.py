@@ -97,5 +97,5 @@ def test_bert_layer_stack_on_orion_kernels_matches_cpu_fp32(ops):
         after = int(torch.ops.orion.own_launches())
     from orion_b200 import kernels
     assert kernels.read_status() == 0
-    assert after - before == 3 * 8                     # per layer: 4 GEMMs, fused attention, GELU, 2 LayerNorms
+    assert after - before == 3 * 8 + 2                 # per layer: 4 GEMMs, fused attention, GELU, 2 LayerNorms; + embedding sum and its LayerNorm
     assert _rel(got.float(), want) < 2e-2
