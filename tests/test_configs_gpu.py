@@ -320,7 +320,8 @@ def _colocate(tmp_path, hp_name, be_name, rps, requests):
     assert hp_solo["iterations"] == requests and hp_solo["p50_latency"] > 0
     depth = int(0.025 * hp_solo["p50_latency"] * 1e6)
     pair = [E.client_entry(be_name, be, 100000), E.client_entry(hp_name, hp, requests, rps=rps)]
-    co = E.run_launch_jobs(pair, os.path.join(out, "pair"), depth=depth, extra_env=env, timeout=300)
+    trace = os.path.join(out, "pair.obs")
+    co = E.run_launch_jobs(pair, os.path.join(out, "pair"), depth=depth, extra_env=dict(env, ORION_RECORD_OBS=trace), timeout=300)
     be_c, hp_c = co["clients"]
     st = co["scheduler"]["stats"]
     assert hp_c["iterations"] == requests
@@ -330,6 +331,16 @@ def _colocate(tmp_path, hp_name, be_name, rps, requests):
     print("%s + %s: HP p50 %.2f -> %.2f ms, p99 %.2f -> %.2f ms, BE %.0f samples/s" % (
         hp_name, be_name, hp_solo["p50_latency"], hp_c["p50_latency"], hp_solo["p99_latency"], hp_c["p99_latency"],
         be_c["samples_per_s"]))
+    # the decisions this run took, against the compiled reference scheduler fed the same observations (oracle/ref_driver.cpp)
+    import json
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.path.join(root, "oracle", "_ref", "ref_replay")
+    if os.path.exists(ref):
+        r = subprocess.run([ref, "--observations", trace, os.path.join(root, "oracle", "_ref")], capture_output=True, text=True, timeout=300)
+        rep = json.loads(r.stdout.strip().splitlines()[-1])
+        assert r.returncode == 0 and rep["matched"] is True, rep
+        assert rep["decisions"] > requests * 20
     return hp, be, co
 
 
