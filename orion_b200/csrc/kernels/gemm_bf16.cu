@@ -12,12 +12,16 @@
 //
 // One CTA = 128 x BN output tile per work unit, persistent over units.  Warp 0 issues TMA copies (4-D tensor maps:
 // inner, outer, batch_inner, batch_outer; out-of-range elements read as zero, so ragged M, N, K need no special path),
-// warp 1 issues tcgen05.mma kind::f16 into one of two tensor-memory accumulators, warps 2-5 drain the other one
-// (tcgen05.ld, one output row per thread) to global memory.  An MN-major operand is declared as such in the instruction
+// warp 1 issues tcgen05.mma kind::f16 into one of two tensor-memory accumulators, warps 2-5 drain the other one:
+// tcgen05.ld (one output row per thread), alpha / bias / residual in registers, 32 rows x 128 bytes staged in a swizzled
+// shared-memory slab per warp and written by a TMA store (two slabs per warp in flight; the tensor map clips ragged edges;
+// outputs whose rows are not 16-byte multiples take per-thread stores).  An MN-major operand is declared as such in the instruction
 // descriptor; its stage is filled by boxes of 64 reduction rows x 128 bytes, which is the canonical layout (atoms of
 // 8 rows x 128 bytes, 1024 bytes apart along the reduction, 8192 bytes apart along M / N).
 // Split-K (few output tiles, long reduction: the weight gradients) writes float32 partial matrices that a second
-// kernel sums in split order, so the result does not depend on timing or on the CTA count.
+// kernel sums in split order, so the result does not depend on timing or on the CTA count.  Causal attention: `tri` modes
+// skip the score tiles above the diagonal and cut the reductions over keys / queries at it.  The kernel is launched as a
+// programmatic dependent: its set-up overlaps the tail of the kernel before it in the stream.
 // Every wait is bounded; on expiry the kernel sets the status word, frees tensor memory and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
