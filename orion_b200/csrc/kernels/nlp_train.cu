@@ -124,22 +124,28 @@ __global__ void __launch_bounds__(NT_THREADS) ln_train_forward_kernel(const T* _
 }
 
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) with g = dy * gamma; column sums of dy * xhat and dy per CTA.
+// The column sums of a warp live in shared memory (each lane adds to its own columns, 16-byte accesses), not in registers:
+// with the row's dy and xhat that keeps a thread near 100 registers, so two CTAs share an SM and the whole grid is resident.
 template <typename T, int CH>
-__global__ void __launch_bounds__(NT_THREADS) ln_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
-                                                                const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                                T* __restrict__ dx, float* __restrict__ partial, long long rows, int D) {
+__global__ void __launch_bounds__(NT_THREADS, 2) ln_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                                                                   const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                   T* __restrict__ dx, float* __restrict__ partial, long long rows, int D) {
     pdl_launch_dependents();   // a GEMM behind this kernel may set itself up meanwhile (pdl.cuh)
     constexpr int N = Vec8<T>::N;
     extern __shared__ float sh[];   // [warps][2][D]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
-    float ag[CH][8], ab[CH][8];     // this lane's column sums over the rows its warp handles
-    float gm[CH][8];
+    float* acc_g = sh + (size_t)(wid * 2 + 0) * D;   // this warp's column sums of dy * xhat
+    float* acc_b = sh + (size_t)(wid * 2 + 1) * D;   // and of dy
 #pragma unroll
     for (int c = 0; c < CH; c++) {
         const int i = (c * 32 + lane) * N;
+        if (i < D) {
 #pragma unroll
-        for (int e = 0; e < 8; e++) ag[c][e] = ab[c][e] = gm[c][e] = 0.f;
-        if (i < D) Vec8<T>::load(gamma + i, gm[c]);
+            for (int e = 0; e < N; e += 4) {
+                *reinterpret_cast<float4*>(acc_g + i + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(acc_b + i + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
     }
     for (long long row = (long long)blockIdx.x * wpb + wid; row < rows; row += (long long)gridDim.x * wpb) {
         const float mu = mean[row], rs = rstd[row];
@@ -149,16 +155,26 @@ __global__ void __launch_bounds__(NT_THREADS) ln_backward_kernel(const T* __rest
         for (int c = 0; c < CH; c++) {
             const int i = (c * 32 + lane) * N;
             if (i < D) {
+                float gm[8];
                 Vec8<T>::load(dy + row * D + i, d[c]);
                 Vec8<T>::load(x + row * D + i, xh[c]);
+                Vec8<T>::load(gamma + i, gm);            // L1-resident after the first row
 #pragma unroll
-                for (int e = 0; e < N; e++) {
-                    xh[c][e] = (xh[c][e] - mu) * rs;
-                    ag[c][e] += d[c][e] * xh[c][e];
-                    ab[c][e] += d[c][e];
-                    d[c][e] *= gm[c][e];
-                    s1 += d[c][e];
-                    s2 += d[c][e] * xh[c][e];
+                for (int e = 0; e < N; e += 4) {
+                    float4 ag = *reinterpret_cast<float4*>(acc_g + i + e), ab = *reinterpret_cast<float4*>(acc_b + i + e);
+                    float* pg = &ag.x;
+                    float* pb = &ab.x;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        xh[c][e + k] = (xh[c][e + k] - mu) * rs;
+                        pg[k] += d[c][e + k] * xh[c][e + k];
+                        pb[k] += d[c][e + k];
+                        d[c][e + k] *= gm[e + k];
+                        s1 += d[c][e + k];
+                        s2 += d[c][e + k] * xh[c][e + k];
+                    }
+                    *reinterpret_cast<float4*>(acc_g + i + e) = ag;
+                    *reinterpret_cast<float4*>(acc_b + i + e) = ab;
                 }
             }
         }
@@ -175,17 +191,6 @@ __global__ void __launch_bounds__(NT_THREADS) ln_backward_kernel(const T* __rest
         }
     }
     // warps -> CTA (fixed order), CTA slice of the partial buffer
-#pragma unroll
-    for (int c = 0; c < CH; c++) {
-        const int i = (c * 32 + lane) * N;
-        if (i < D) {
-#pragma unroll
-            for (int e = 0; e < N; e++) {
-                sh[(wid * 2 + 0) * D + i + e] = ag[c][e];
-                sh[(wid * 2 + 1) * D + i + e] = ab[c][e];
-            }
-        }
-    }
     __syncthreads();
     for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
         const int which = i / D, col = i - which * D;
