@@ -82,7 +82,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_fwd_kernel(const __gr
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int* abort_flag = &ctl->abort_flag;
     const int items = p.B * p.H * p.q_tiles;
-    const int keys_padded = p.key_tiles * 128;
     uint32_t phase = 0;
 
     for (int item = blockIdx.x; item < items; item += gridDim.x, phase ^= 1u) {
@@ -231,7 +230,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_fwd_kernel(const __gr
         }
         __syncthreads();   // tensor memory and shared memory are free for the next item
         if (*abort_flag) break;
-        (void)keys_padded;
     }
     __syncthreads();
     if (warp == 4) {
