@@ -260,6 +260,18 @@ def cpu_baseline(sample_hp=12, sample_be=2, recorded_script=None, observations=N
                            live_decisions=live_decision_check(observations))}
 
 
+def aggregate_ranks(gathered):
+    """Whole-job figures from the per-rank records of independent replicas: throughputs add up, the timed region is the
+    longest rank's, and the latency ratio that is reported is the worst rank's.  Returns (worst, value, e2e_value,
+    step_time, solo_sum)."""
+    worst = max(gathered, key=lambda g: g["hp_p99"] / g["hp_solo_p99"])
+    value = sum(g["be_sps"] for g in gathered)
+    e2e_value = sum(g["be_sps_e2e"] for g in gathered)
+    step_time = max(g["timed_s"] for g in gathered)
+    solo_sum = sum(g["be_solo_sps"] for g in gathered)
+    return worst, value, e2e_value, step_time, solo_sum
+
+
 def paired_bootstrap_p99_ratio(coloc, solo, n_boot=1000, seed=7):
     """95 % interval of p99(co-located) / p99(alone).  Both runs see the same arrival sequence, so request i of one
     corresponds to request i of the other: indices are resampled, and both percentiles are taken over the same
@@ -459,11 +471,7 @@ def main():
     roof_hbm = hbm_roofline(peaks)
     roof_gemm = gemm_roofline(peaks)
     base = cpu_baseline(recorded_script=rep["script"], observations=rep.get("observations"))
-    worst = max(gathered, key=lambda g: g["hp_p99"] / g["hp_solo_p99"])
-    value = sum(g["be_sps"] for g in gathered)
-    e2e_value = sum(g["be_sps_e2e"] for g in gathered)
-    step_time = max(g["timed_s"] for g in gathered)
-    solo_sum = sum(g["be_solo_sps"] for g in gathered)
+    worst, value, e2e_value, step_time, solo_sum = aggregate_ranks(gathered)
     line = {
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": steps, "warmup": warm_steps,
         "ms_per_step": step_time * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
