@@ -485,6 +485,9 @@ static int run_observations(const std::string& trace, const std::string& ref_dir
         fprintf(stderr, "ref_replay: cannot open %s\n", trace.c_str());
         return 1;
     }
+    const size_t slash = trace.find_last_of('/');
+    const std::string trace_dir = slash == std::string::npos ? "." : trace.substr(0, slash);
+    auto rel = [&](const std::string& p) { return (!p.empty() && p[0] == '/') ? p : trace_dir + "/" + p; };   // as the product's loader
     int max_sms = 80, reef_streams = 0, n = 0;
     std::vector<int> num_kernels, num_iters, trains;
     std::vector<std::string> profiles;
@@ -510,6 +513,7 @@ static int run_observations(const std::string& trace, const std::string& ref_dir
             ls >> i;
             if (i < 0 || i >= n) return 1;
             ls >> k >> trains[i] >> k >> num_iters[i] >> k >> profiles[i] >> num_kernels[i];
+            profiles[i] = rel(profiles[i]);
         } else if (key == "phase") {
             ObsCommand c;
             c.kind = ObsCommand::PHASE;
@@ -528,6 +532,7 @@ static int run_observations(const std::string& trace, const std::string& ref_dir
             ObsCommand c;
             c.kind = ObsCommand::SETUP_CHANGE;
             ls >> c.client >> c.file >> c.num_kernels;
+            c.file = rel(c.file);
             cmds.push_back(c);
         } else if (key == "truncated") {
             truncated = true;

@@ -25,6 +25,11 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <stdlib.h>
+
+#include <fstream>
+#include <sstream>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -176,6 +181,187 @@ struct ObsEnv {
         sample_acks();
         in.poll_end(progressed);
     }
+};
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Reading a trace back, and an Env that replays it: the policy core gets the recorded answers and every call it makes
+// (release, lock, closed request, stop) is compared with the recorded one.  Used by `orion_replay --observations`.
+
+struct ObsTraceLine {
+    uint64_t rep = 1;
+    std::vector<ObsToken> toks;
+};
+struct ObsTraceCmd {
+    bool is_phase = true;            // else: setup_change
+    int args[7] = {0, 0, 0, 0, 0, 0, 0};   // phase: warmup, warmup_iters, reef, seq, depth, hp_limit, update_start
+    std::vector<ObsTraceLine> lines;
+    int client = 0, num_kernels = 0;
+    std::string file;
+};
+struct ObsTrace {
+    int max_sms = 80, reef = 0, n = 0;
+    std::vector<int> num_kernels, num_iters, train;
+    std::vector<std::string> profiles;
+    std::vector<ObsTraceCmd> cmds;
+    bool truncated = false;
+};
+
+// Throws std::runtime_error on a malformed file.  Profile paths that are not absolute are taken relative to the trace.
+inline ObsTrace load_obs_trace(const std::string& path) {
+    std::ifstream in(path);
+    if (!in.is_open()) throw std::runtime_error("orion: cannot open observation trace " + path);
+    const size_t slash = path.find_last_of('/');
+    const std::string dir = slash == std::string::npos ? "." : path.substr(0, slash);
+    auto rel = [&](const std::string& p) { return (!p.empty() && p[0] == '/') ? p : dir + "/" + p; };
+    ObsTrace t;
+    std::string line, key, k;
+    while (std::getline(in, line)) {
+        std::istringstream ls(line);
+        if (!(ls >> key)) continue;
+        if (key == "orion_observations" || key == "endphase" || key == "reset") continue;
+        if (key == "max_sms") {
+            ls >> t.max_sms >> k >> t.reef;
+        } else if (key == "nclients") {
+            ls >> t.n;
+            t.num_kernels.assign(t.n, 0);
+            t.num_iters.assign(t.n, 0);
+            t.train.assign(t.n, 0);
+            t.profiles.assign(t.n, "");
+        } else if (key == "client") {
+            int i = -1;
+            ls >> i;
+            if (i < 0 || i >= t.n) throw std::runtime_error("orion: observation trace names a client out of range");
+            ls >> k >> t.train[i] >> k >> t.num_iters[i] >> k >> t.profiles[i] >> t.num_kernels[i];
+            t.profiles[i] = rel(t.profiles[i]);
+        } else if (key == "phase") {
+            ObsTraceCmd c;
+            for (int a = 0; a < 7; a++) ls >> c.args[a];
+            t.cmds.push_back(c);
+        } else if (key == "setup_change") {
+            ObsTraceCmd c;
+            c.is_phase = false;
+            ls >> c.client >> c.file >> c.num_kernels;
+            c.file = rel(c.file);
+            t.cmds.push_back(c);
+        } else if (key == "truncated") {
+            t.truncated = true;
+        } else if (key == "p") {
+            if (t.cmds.empty() || !t.cmds.back().is_phase) throw std::runtime_error("orion: poll line outside a phase");
+            ObsTraceLine l;
+            ls >> l.rep;
+            std::string w;
+            while (ls >> w) {
+                ObsToken tk{w[0], 0, 0, 0, 0, 0, 0};
+                const char* p = w.c_str() + 1;
+                if (tk.kind == 'T') {
+                    tk.t = strtoll(p, nullptr, 10);
+                } else {
+                    int32_t* f[5] = {&tk.a, &tk.b, &tk.c, &tk.d, &tk.e};
+                    for (int q = 0; q < 5 && *p; q++) {
+                        char* end = nullptr;
+                        *f[q] = (int32_t)strtol(p, &end, 10);
+                        p = (*end == ':') ? end + 1 : end;
+                    }
+                }
+                if (!strchr("PQTKBSLDX", tk.kind)) throw std::runtime_error("orion: unknown token in observation trace");
+                l.toks.push_back(tk);
+            }
+            if (!l.toks.empty() && l.rep > 0) t.cmds.back().lines.push_back(l);
+        } else {
+            throw std::runtime_error("orion: unknown line in observation trace: " + key);
+        }
+    }
+    if (t.n < 1 || t.cmds.empty()) throw std::runtime_error("orion: observation trace holds no phase");
+    return t;
+}
+
+struct ObsMismatch {
+    bool exhausted;        // the trace ended (recording limit) before the policy did
+    std::string detail;
+};
+
+struct ObsReplayEnv {
+    const std::vector<ObsTraceLine>* lines = nullptr;
+    size_t line = 0, tok = 0;
+    uint64_t rep = 0;
+    uint32_t ack = 0;
+    int64_t last_t = 0;
+    uint64_t decisions = 0, closed = 0, polls = 0;
+
+    void begin(const std::vector<ObsTraceLine>* l) {
+        lines = l;
+        line = tok = 0;
+        rep = 0;
+    }
+    const ObsToken* cur() {
+        while (line < lines->size()) {
+            const ObsTraceLine& l = (*lines)[line];
+            if (tok < l.toks.size()) {
+                if (l.toks[tok].kind == 'K') {   // stop acknowledgements in force from this poll on
+                    ack = (uint32_t)l.toks[tok].a;
+                    tok++;
+                    continue;
+                }
+                return &l.toks[tok];
+            }
+            tok = 0;
+            polls++;
+            if (++rep >= l.rep) {
+                rep = 0;
+                line++;
+            }
+        }
+        return nullptr;
+    }
+    const ObsToken& expect(char kind, int a, const char* what) {
+        const ObsToken* t = cur();
+        if (!t) throw ObsMismatch{true, std::string("the trace ends before a ") + what};
+        if (t->kind != kind || t->a != a)
+            throw ObsMismatch{false, std::string(what) + ": the policy core asks for " + kind + std::to_string(a) + ", the trace holds " +
+                                         (char)t->kind + std::to_string(t->a)};
+        tok++;
+        return *t;
+    }
+    bool drained() { return cur() == nullptr; }
+
+    int peek(int i) { return expect('P', i, "queue head").b; }
+    int64_t now_us() {
+        const ObsToken* t = cur();
+        if (t && t->kind == 'T') {
+            last_t = t->t;
+            tok++;
+        }
+        return last_t;
+    }
+    void submit(int i, int type, int stream, int evl, int evs) {
+        const ObsToken& t = expect('S', i, "release");
+        if (t.b != orion_reference_type(type) || t.c != stream || t.d != evl || t.e != evs)
+            throw ObsMismatch{false, "release of client " + std::to_string(i) + " differs in type, stream or event"};
+        decisions++;
+    }
+    bool query(int evl, int evs) {
+        const ObsToken& t = expect('Q', evl, "event query");
+        if (t.b != evs) throw ObsMismatch{false, "event query of another slot"};
+        return t.c != 0;
+    }
+    void iter_lock(int i) { expect('L', i, "iteration lock"); }
+    void iter_done(int i, int iter) {
+        if (expect('D', i, "closed request").b != iter) throw ObsMismatch{false, "closed request of another index"};
+        closed++;
+    }
+    void stop(int k, bool locked) {
+        if (expect('X', k, "stop request").b != (locked ? 1 : 0)) throw ObsMismatch{false, "stop request with another lock state"};
+    }
+    bool stop_ack(int i) { return (ack >> i) & 1u; }
+    bool client_blocked(int i, int) {
+        const ObsToken* t = cur();
+        if (t && t->kind == 'B' && t->a == i) {
+            tok++;
+            return true;
+        }
+        return false;
+    }
+    void poll_end(bool) {}
 };
 
 }  // namespace orion

@@ -1,6 +1,11 @@
 // orion_replay: run an arrival script through the policy core in virtual time.
 //
 //   orion_replay <script> [--log <file>] [--repeat <n>]
+//   orion_replay --observations <trace>
+//
+// The second form feeds an observation trace of a live run (observation.hpp) to the policy core: the recorded queue heads,
+// event answers, clock reads and stop acknowledgements go in, and every release, lock, closed request and stop request the
+// core makes is compared with the recorded one.
 //
 // Prints one JSON line with the decision count, the FNV-1a hash of the decision
 // log and the wall time of the policy loop (decisions per second on one core).
@@ -15,6 +20,7 @@
 #include "../policy/arrival_script.hpp"
 #include "../policy/policy.hpp"
 #include "../policy/sim_env.hpp"
+#include "observation.hpp"
 
 using namespace orion;
 
@@ -64,9 +70,73 @@ static int run_once(const ArrivalScript& s, DecisionLog* out, PolicyStats* stats
     return 0;
 }
 
+static int run_observations(const char* path) {
+    ObsTrace t = load_obs_trace(path);
+    const int n = t.n;
+    PolicyCore core;
+    core.max_sms = t.max_sms;
+    core.op_info.resize(n);
+    for (int i = 0; i < n; i++) {
+        load_profile(t.profiles[i], core.op_info[i]);
+        core.max_sms_clients.push_back(max_sm_used(core.op_info[i]));
+        core.is_train.push_back(t.train[i] != 0);
+    }
+    core.init(n, t.num_kernels.data(), t.num_iters.data());
+    core.max_events = 30000;
+    ObsReplayEnv env;
+    bool matched = true, cut = false;
+    std::string detail = "every release, closed request and stop request of the live run is reproduced";
+    int phase = 0;
+    try {
+        for (ObsTraceCmd& c : t.cmds) {
+            if (!c.is_phase) {
+                core.op_info[c.client].clear();
+                load_profile(c.file, core.op_info[c.client]);
+                core.max_sms_clients[c.client] = max_sm_used(core.op_info[c.client]);
+                t.num_kernels[c.client] = c.num_kernels;
+                continue;
+            }
+            PhaseArgs a;
+            a.warmup = c.args[0] != 0;
+            a.warmup_iters = c.args[1];
+            a.reef = c.args[2] != 0;
+            a.seq = c.args[3] != 0;
+            a.depth = c.args[4];
+            a.hp_limit = c.args[5];
+            a.update_start = c.args[6];
+            env.begin(&c.lines);
+            core.run_phase(env, a);
+            if (core.error) throw ObsMismatch{false, "the policy core stopped on an unsupported record or an event overflow"};
+            if (!env.drained() && !t.truncated) throw ObsMismatch{false, "the policy core ended the phase, the live run went on"};
+            phase++;
+        }
+    } catch (const ObsMismatch& m) {
+        if (m.exhausted && t.truncated) {
+            cut = true;
+            detail = "the trace ends here (recording limit); every decision up to it is reproduced";
+        } else {
+            matched = false;
+            detail = m.detail;
+        }
+    }
+    printf("{\"impl\": \"orion_b200\", \"mode\": \"observations\", \"matched\": %s, \"truncated\": %s, \"decisions\": %llu, "
+           "\"requests_closed\": %llu, \"polls\": %llu, \"phase\": %d, \"detail\": \"%s\"}\n",
+           matched ? "true" : "false", (t.truncated || cut) ? "true" : "false", (unsigned long long)env.decisions,
+           (unsigned long long)env.closed, (unsigned long long)env.polls, phase, detail.c_str());
+    return matched ? 0 : 3;
+}
+
 int main(int argc, char** argv) {
+    if (argc >= 3 && !strcmp(argv[1], "--observations")) {
+        try {
+            return run_observations(argv[2]);
+        } catch (const std::exception& e) {
+            fprintf(stderr, "orion_replay: %s\n", e.what());
+            return 1;
+        }
+    }
     if (argc < 2) {
-        fprintf(stderr, "usage: orion_replay <script> [--log file] [--repeat n]\n");
+        fprintf(stderr, "usage: orion_replay <script> [--log file] [--repeat n]\n       orion_replay --observations <trace>\n");
         return 64;
     }
     std::string log_path;

@@ -91,3 +91,52 @@ def test_unsupported_record_type_aborts_the_policy(built, tmp_path):
                       "phases 1 0 0\n")
     out = subprocess.run([built["orion_replay"], str(script)], capture_output=True, text=True, timeout=60)
     assert out.returncode == 2
+
+
+# ---------------------------------------------------------------------------------------------- traces of live runs
+with open(os.path.join(GOLD, "live_index.json")) as _f:
+    LIVE = json.load(_f)
+
+
+@pytest.mark.parametrize("case", sorted(LIVE))
+def test_policy_core_reproduces_the_decisions_of_recorded_live_runs(case, built):
+    """tests/golden/live_*.obs: observation traces of live runs (queue heads, event answers, clock reads, stop acknowledgements in;
+    releases, closed requests, stop requests out).  The compiled reference scheduler, fed each trace, took exactly the recorded
+    decisions (counts in live_index.json, written by tests/golden/make_live_observations.py); the product's policy core fed the
+    same trace must take them too, to the last token."""
+    out = subprocess.run([built["orion_replay"], "--observations", os.path.join(GOLD, case + ".obs")], capture_output=True, text=True,
+                         timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    rep = json.loads(out.stdout.strip().splitlines()[-1])
+    want = LIVE[case]
+    assert rep["matched"] is True and not rep["truncated"]
+    assert (rep["decisions"], rep["requests_closed"], rep["polls"], rep["phase"]) == (want["decisions"], want["requests_closed"],
+                                                                                      want["polls"], want["phase"])
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "ref_replay")),
+                    reason="reference scheduler not compiled here (make -C oracle ref)")
+@pytest.mark.parametrize("case", sorted(LIVE))
+def test_reference_scheduler_still_agrees_with_the_recorded_live_runs(case):
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    out = subprocess.run([os.path.join(ref_dir, "ref_replay"), "--observations", os.path.join(GOLD, case + ".obs"), ref_dir],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    rep = json.loads(out.stdout.strip().splitlines()[-1])
+    assert rep["matched"] is True and {k: rep[k] for k in LIVE[case]} == LIVE[case]
+
+
+def test_policy_core_notices_a_decision_that_is_not_its_own(built, tmp_path):
+    """A release moved to the other stream in a recorded trace is a mismatch for the product's replay as well (exit 3)."""
+    import re
+    import shutil
+    for f in os.listdir(GOLD):
+        if f.startswith("live_pair."):
+            shutil.copy(os.path.join(GOLD, f), tmp_path / f)
+    text = (tmp_path / "live_pair.obs").read_text()
+    head, tail = text.split("\nphase 0 ", 1)
+    m = list(re.finditer(r" S0:0:0:0:(\d+)", tail))[3]
+    (tmp_path / "live_pair.obs").write_text(head + "\nphase 0 " + tail[:m.start()] + " S0:0:1:0:" + m.group(1) + tail[m.end():])
+    out = subprocess.run([built["orion_replay"], "--observations", str(tmp_path / "live_pair.obs")], capture_output=True, text=True,
+                         timeout=120)
+    assert out.returncode == 3 and json.loads(out.stdout.strip().splitlines()[-1])["matched"] is False
