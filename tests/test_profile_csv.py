@@ -1,6 +1,7 @@
 """Profile-file loader: same parsing rules as the reference's populate_kernel_info
 (reference src/scheduler/scheduler_eval.cpp:498-526)."""
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -61,3 +62,52 @@ def test_golden_profiles_load_identically_in_oracle_and_product(sched, golden_di
         assert n == len(rows)
         assert prof == [r[1] for r in rows] and sm == [r[3] for r in rows]
         assert dur == [float(r[4]) for r in rows]
+
+
+# ---------------------------------------------------------------------------------------------- ncu exports -> profile file
+import pytest
+
+PIPE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ncu_pipeline")
+
+
+@pytest.mark.parametrize("model_type", ["vision", "bert", "transformer"])
+def test_profile_from_ncu_exports_equals_the_reference_scripts(model_type, tmp_path):
+    """tests/golden/ncu_pipeline/: two synthetic ncu exports and what the reference's own four post-processing scripts made of
+    them (tests/golden/make_profile_pipeline_golden.py).  orion_b200/profile_from_ncu.py with the reference's device defaults
+    must write the same profile file, byte for byte: SM need, class (including unknown), grouping into Conv / BatchNorm rows,
+    dropped rows, names, durations."""
+    from orion_b200 import profile_from_ncu as P
+    out = tmp_path / "profile"
+    n = P.convert(PIPE, str(out), model_type=model_type, device="v100")
+    want = open(os.path.join(PIPE, "model_kernels_" + model_type)).read()
+    assert out.read_text() == want
+    assert n == want.count("\n") - 1
+
+
+def test_profile_from_ncu_intermediate_columns_match_the_reference():
+    """SM need and class of every kernel against the reference's intermediate file (before rows are grouped and dropped)."""
+    import csv
+    from orion_b200 import profile_from_ncu as P
+    kernels = P.process_ncu(os.path.join(PIPE, "output_ncu.csv"))
+    raw = list(csv.DictReader(open(os.path.join(PIPE, "raw_ncu.csv"), newline="")))
+    ref = list(csv.DictReader(open(os.path.join(PIPE, "output_ncu_sms_roofline.csv"), newline="")))
+    assert len(kernels) == len(raw) == len(ref) == 16
+    lim = P.DEVICES["v100"]
+    for k, r, want in zip(kernels, raw, ref):
+        assert k["name"] == want["Kernel_Name"]
+        assert P.sm_needed(k, lim["max_threads_sm"], lim["max_shmem_sm"]) == int(want["SM_needed"])
+        assert P.roofline_class(k, r, lim["ai_threshold"]) == int(want["Roofline_prof"])
+    classes = {int(w["Roofline_prof"]) for w in ref}
+    assert classes == {-1, 0, 1}                                    # the fixtures reach all three outcomes of the class rule
+
+
+def test_profile_from_ncu_b200_limits_and_scheduler_loader(tmp_path):
+    """With a B200's limits (228 KB of shared memory per SM) shared-memory-bound kernels need fewer SMs than on the V100 table,
+    and the file loads through the scheduler's own profile parser."""
+    from orion_b200 import profile_from_ncu as P
+    out = tmp_path / "b200"
+    n = P.convert(PIPE, str(out), model_type="vision", device="b200")
+    rows = [l.split(",") for l in out.read_text().strip().splitlines()[1:]]
+    ref = [l.split(",") for l in open(os.path.join(PIPE, "model_kernels_vision")).read().strip().splitlines()[1:]]
+    assert n == len(rows) == len(ref)
+    assert all(int(a[3]) <= int(b[3]) for a, b in zip(rows, ref)) and any(int(a[3]) < int(b[3]) for a, b in zip(rows, ref))
