@@ -111,3 +111,32 @@ def test_profile_from_ncu_b200_limits_and_scheduler_loader(tmp_path):
     ref = [l.split(",") for l in open(os.path.join(PIPE, "model_kernels_vision")).read().strip().splitlines()[1:]]
     assert n == len(rows) == len(ref)
     assert all(int(a[3]) <= int(b[3]) for a, b in zip(rows, ref)) and any(int(a[3]) < int(b[3]) for a, b in zip(rows, ref))
+
+
+# ---------------------------------------------------------------------------------------------- shipped client configurations
+def test_example_configurations_are_consistent_with_the_committed_profiles():
+    """benchmarking/configs/*.json: the client lists of configurations 2-5 and a three-client example, in the reference's schema
+    (benchmarking/multi_client_example.json).  Every profile they name exists beside them, `num_kernels` is its row count (the
+    scheduler refuses anything larger), the high-priority client is the last entry, and training clients carry the profile of
+    their first iteration and that of the steady state."""
+    import glob
+    import json
+    cfg_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarking", "configs")
+    files = sorted(glob.glob(os.path.join(cfg_dir, "*.json")))
+    assert len(files) >= 5
+    for path in files:
+        cfg = json.load(open(path))
+        assert len(cfg) >= 2
+        for i, c in enumerate(cfg):
+            assert set(c) >= {"arch", "kernel_file", "num_kernels", "num_iters", "args"}
+            assert set(c["args"]) >= {"model_name", "batchsize", "rps", "uniform", "dummy_data", "train"}
+            pairs = [(c["kernel_file"], c["num_kernels"])]
+            if c["args"]["train"]:
+                pairs.append((c["additional_kernel_file"], c["additional_num_kernels"]))
+            for rel, n in pairs:
+                prof = os.path.normpath(os.path.join(cfg_dir, rel))
+                with open(prof) as f:
+                    lines = f.read().strip().splitlines()
+                assert lines[0] == "Name,Profile,Memory_footprint,SM_usage,Duration"
+                assert len(lines) - 1 == n, (os.path.basename(path), rel)
+            assert c["args"]["train"] == (i < len(cfg) - 1)     # best-effort training clients first, the inference client last
