@@ -118,7 +118,7 @@ def test_example_configurations_are_consistent_with_the_committed_profiles():
     """benchmarking/configs/*.json: the client lists of configurations 2-5 and a three-client example, in the reference's schema
     (benchmarking/multi_client_example.json).  Every profile they name exists beside them, `num_kernels` is its row count (the
     scheduler refuses anything larger), the high-priority client is the last entry, and training clients carry the profile of
-    their first iteration and that of the steady state."""
+    their first iteration and that of the steady state, and so do the inference clients (their first request re-lays filters)."""
     import glob
     import json
     cfg_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarking", "configs")
@@ -130,9 +130,10 @@ def test_example_configurations_are_consistent_with_the_committed_profiles():
         for i, c in enumerate(cfg):
             assert set(c) >= {"arch", "kernel_file", "num_kernels", "num_iters", "args"}
             assert set(c["args"]) >= {"batchsize", "rps", "uniform", "dummy_data", "train"}    # vision clients add model_name
-            pairs = [(c["kernel_file"], c["num_kernels"])]
-            if c["args"]["train"]:
-                pairs.append((c["additional_kernel_file"], c["additional_num_kernels"]))
+            # every client's first request / iteration launches one-time work (lazy initialisation, filter re-layout), so each
+            # entry names the profile of the first iteration and the steady-state one that replaces it (setup_change)
+            pairs = [(c["kernel_file"], c["num_kernels"]), (c["additional_kernel_file"], c["additional_num_kernels"])]
+            assert c["num_kernels"] >= c["additional_num_kernels"]
             for rel, n in pairs:
                 prof = os.path.normpath(os.path.join(cfg_dir, rel))
                 with open(prof) as f:
