@@ -150,6 +150,10 @@ static inline bool is_default_stream(void* s) {
 // grant, so that records, grants and events stay paired.  Uncontended in the clients of the benchmark (forward and backward
 // of one client never overlap).
 static std::atomic<uint32_t> g_producer_lock[ORION_MAX_CLIENTS];
+// Set when a client gave up waiting for a grant while nobody was polling (a pause between two phases of the scheduler that
+// the client's op stream did not expect, e.g. a profile with fewer rows than the client launches ops): its further ops of the
+// same pause run unscheduled at once instead of waiting out the timeout one by one.  Cleared when polling is seen again.
+static std::atomic<uint32_t> g_gave_up_in_pause[ORION_MAX_CLIENTS];
 
 bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
     orion_shared& sh = g_shared;
@@ -196,10 +200,15 @@ bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
     bool self_granted = false;
     while (r.granted.load(std::memory_order_acquire) <= seq) {
         bool take = false;
+        const bool polling = sh.polling.load(std::memory_order_acquire) != 0;
+        if (polling && g_gave_up_in_pause[idx].load(std::memory_order_relaxed))   // read-only in the common case: no line bouncing
+            g_gave_up_in_pause[idx].store(0, std::memory_order_relaxed);
         if (!sh.active.load(std::memory_order_acquire)) {
             take = true;   // scheduler detached while we were queued: run the call unscheduled
-        } else if (memop && !sh.polling.load(std::memory_order_acquire)) {
+        } else if (memop && !polling) {
             take = true;   // nobody polls between two phases; memory operations need no decision
+        } else if (!polling && g_gave_up_in_pause[idx].load(std::memory_order_relaxed)) {
+            take = true;   // this pause already cost the client one full timeout
         } else if ((++spins & 0xfffff) == 0) {
             int64_t now = mono_ms();
             if (!t0) t0 = now;
@@ -208,6 +217,7 @@ bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
                                 "running the call unscheduled\n", idx, (long long)gate_timeout_ms(), type,
                         (unsigned long long)seq, sh.polling.load());
                 sh.wait_timeouts.fetch_add(1);
+                if (!sh.polling.load(std::memory_order_acquire)) g_gave_up_in_pause[idx].store(1, std::memory_order_relaxed);
                 take = true;
             }
         }
