@@ -152,7 +152,8 @@ static inline bool is_default_stream(void* s) {
 static std::atomic<uint32_t> g_producer_lock[ORION_MAX_CLIENTS];
 // Set when a client gave up waiting for a grant while nobody was polling (a pause between two phases of the scheduler that
 // the client's op stream did not expect, e.g. a profile with fewer rows than the client launches ops): its further ops of the
-// same pause run unscheduled at once instead of waiting out the timeout one by one.  Cleared when polling is seen again.
+// same pause run unscheduled at once instead of waiting out the timeout one by one.  Cleared when polling is seen again and
+// at the end of the client's request (block).
 static std::atomic<uint32_t> g_gave_up_in_pause[ORION_MAX_CLIENTS];
 
 bool gate_begin(Gate* g, int type, void* user_stream, uint64_t tag) {
@@ -266,6 +267,9 @@ void block(int it) {
     profile_mark_iteration(it);
     int idx = client_index_of_thread();
     if (idx < 0) return;
+    // the end of a request is where client and scheduler meet again: ops of the next request wait for their grants even if
+    // the scheduler needs a moment to start polling (see g_gave_up_in_pause)
+    g_gave_up_in_pause[idx].store(0, std::memory_order_relaxed);
     if (it < 0 || it >= sh.request_status_len[idx]) {
         fprintf(stderr, "orion: block(%d) outside the %d requests announced for client %d\n", it, sh.request_status_len[idx], idx);
         return;

@@ -28,7 +28,7 @@ DRIVER = textwrap.dedent('''
         barriers[0].wait()
         it = 0
         while it < c["iters"]:
-            for t in c["ops"]:
+            for t in (c.get("first_ops") if it == 0 and c.get("first_ops") else c["ops"]):
                 got = cap.orion_capture_op(t)
                 if got != i: wrong.append((i, got))
                 if t == 0: quotas[i].add(cap.orion_capture_last_quota())
@@ -111,6 +111,20 @@ def test_profile_shorter_than_the_op_stream_keeps_running(built, tmp_path):
     p = _profile(tmp_path, "p", [(1, 10, 1000)] * 3)
     r = _run({"clients": [{"profile": p, "num_kernels": 3, "iters": 13, "train": False, "ops": [0] * 5}]}, timeout=180)
     assert r["done"] == [13]
+
+
+def test_first_request_longer_than_its_profile_degrades_instead_of_stalling(built, tmp_path):
+    """An inference client whose first request launches one-time work (here 40 ops) under a profile that only describes the
+    steady state (5 rows): the scheduler closes eight "iterations" inside that first request and moves through its phases ahead
+    of the client.  The client must come through: it waits out one grant timeout per scheduler pause, runs the rest of the
+    pause unscheduled, and every request completes."""
+    import time
+    p = _profile(tmp_path, "p", [(1, 10, 1000)] * 5)
+    t0 = time.time()
+    r = _run({"clients": [{"profile": p, "num_kernels": 5, "iters": 16, "train": False, "ops": [0] * 5, "first_ops": [0] * 40}]},
+             env_extra={"ORION_GATE_TIMEOUT_S": "2"}, timeout=170)
+    assert r["done"] == [16]
+    assert time.time() - t0 < 120
 
 
 def test_recorded_run_replays_identically_through_policy_core_and_oracles(built, tmp_path):
